@@ -1,0 +1,182 @@
+/*
+ * libpk100 -- sm_100a (B200) kernels for the FastConformer / TDT hot path of
+ * l4-parakeet-rs behind a plain C ABI.
+ *
+ * Every entry point replaces one kernel (or host launch helper) of the
+ * reference's `kernels/sm89` translation units; the reference interface each
+ * one stands in for is cited as path:line inside the reference project.
+ *
+ * Conventions (the reference's, src/cuda.rs:698-778, src/cuda/cublas.rs:67-113):
+ *   - pointers are DEVICE pointers unless the name says host; the caller owns
+ *     every allocation, the library never allocates or frees device memory;
+ *   - activations are row-major [rows, width]; weights are row-major
+ *     [out (N), in (K)];
+ *   - `stream` is a CUstream / cudaStream_t passed as void*; every call is
+ *     asynchronous and stream-ordered, performs no synchronisation and no
+ *     allocation;
+ *   - return value: 0 success, negative = argument error found on the host
+ *     (nothing was launched), positive = CUDA error code of the launch.
+ *   - A batch of utterances is laid out as `segments` consecutive blocks of
+ *     `seg_stride` rows; the first valid rows of each block carry data
+ *     (`seg_valid[s]` when that device array is given, else `valid_rows`), the
+ *     remaining rows are zero -- the reference's rows / valid_rows /
+ *     padded_rows geometry (src/cuda/pipeline.rs:438-442) per utterance.
+ */
+#ifndef PK100_H_
+#define PK100_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    PK100_OK = 0,
+    PK100_ERR_NULL = -1,      /* a required pointer is null */
+    PK100_ERR_SHAPE = -2,     /* a dimension violates the documented constraint */
+    PK100_ERR_ALIGN = -3,     /* pointer / leading dimension not 16-byte aligned */
+    PK100_ERR_UNSUPPORTED = -4,
+    PK100_ERR_DRIVER = -5,    /* tensor-map encoding failed */
+    PK100_ERR_LIMIT = -6      /* size beyond a documented fixed capacity */
+};
+
+/* Operand kinds of pk100_gemm. */
+enum { PK100_KIND_F16 = 0, PK100_KIND_E4M3 = 1, PK100_KIND_S8 = 2 };
+/* Output encodings of pk100_gemm. */
+enum { PK100_OUT_F16 = 0, PK100_OUT_F32 = 1, PK100_OUT_E4M3 = 2, PK100_OUT_S8 = 3 };
+/* Activations (kernels/sm89/linear.cu:65-73). */
+enum { PK100_ACT_NONE = 0, PK100_ACT_SILU = 1, PK100_ACT_RELU = 2 };
+/* Epilogue families. */
+enum { PK100_EPI_LINEAR = 0, PK100_EPI_GLU = 1, PK100_EPI_SPARSE_OUT = 2 };
+/* LayerNorm output encodings. */
+enum {
+    PK100_LN_F16 = 0,        /* fp16 */
+    PK100_LN_E4M3_FIXED = 1, /* E4M3(y * inv_scale)                          */
+    PK100_LN_E4M3_ROW = 2,   /* E4M3(y / s), s = absmax/448 per row (0 -> 1) */
+    PK100_LN_S8_ROW = 3      /* clamp(rne(y / s)), s = absmax/127 per row    */
+};
+/* Weight packing formats of pk100_pack_weight_rows. */
+enum { PK100_PACK_E4M3 = 0, PK100_PACK_S8 = 1, PK100_PACK_S4_ROW = 2, PK100_PACK_S4_G128 = 3 };
+
+/*
+ * General tensor-core linear:  D[m,n] = epilogue(A[m,k] . B[n,k]^T).
+ * tcgen05.mma (kind::f16 / kind::f8f6f4 / kind::i8), TMA-staged operands, TMEM
+ * accumulators.  Replaces the GEMM family of the reference:
+ *   pk_sm89_fp16_linear_epilogue(_m64)   kernels/sm89/linear.cu:83-171, :243-320
+ *   pk_sm89_fp8_linear_epilogue          kernels/sm89/linear.cu:325-374
+ *   pk_sm89_int8_linear_epilogue         kernels/sm89/linear.cu:378-429
+ *   ffn_fp8_async<> and its 13 wrappers  kernels/sm89/encoder.cu:787-1127, :1313-1319, :2099-2107
+ *   pk_sm89_ffn_expand_async             kernels/sm89/encoder.cu:427-547
+ *   Cublas::linear (cublasGemmEx)        src/cuda/cublas.rs:67-113
+ * Epilogue algebra (kernels/sm89/encoder.cu:961-1005):
+ *   v = acc * row_scale(s)[m] * col_scales[n] + bias[n];  v = act(v);
+ *   v = residual ? fma(alpha, v, residual[m,n]) : alpha * v;   rows >= valid_rows -> 0
+ *   PK100_EPI_GLU: B rows [0,n/2) are values, [n/2,n) gates; out[m,c] =
+ *     f16(value) / (1 + exp(-f16(gate))), out has n/2 columns (encoder.cu:936-944).
+ *   PK100_EPI_SPARSE_OUT: v = SiLU(...); per [128-row x 64-col] tile t = max|v|;
+ *     keep_out[tile] = t >= tau; kept tiles are stored as INT8
+ *     clamp(rne(f16(v) * out_scale)), dropped tiles as zeros; stats_out[tile] = t.
+ *   keep_in: when given ([ceil(m/128), k/64] bytes) K tiles flagged 0 are skipped
+ *     (their A bytes must be zero).
+ * Constraints: k * elem_size, lda/ldb * elem_size multiples of 16 bytes;
+ *   n % 32 == 0; 16-byte aligned pointers; ld_out * out_elem_size % 16 == 0.
+ */
+typedef struct pk100_gemm_args {
+    int kind;                 /* PK100_KIND_* (A and B share it) */
+    int epilogue;             /* PK100_EPI_* */
+    int m, n, k;
+    const void* a;  int lda;  /* [m, k], leading dimension in elements */
+    const void* b;  int ldb;  /* [n, k] */
+    const float* row_scales;  /* [m] or NULL */
+    float row_scale;          /* used when row_scales == NULL */
+    const float* col_scales;  /* [n] or NULL */
+    const float* bias;        /* [n] or NULL */
+    int act;                  /* PK100_ACT_* */
+    const void* residual;     /* fp16 [m, ld_res] or NULL; may alias out */
+    int ld_res;
+    float alpha;
+    int valid_rows;           /* <= 0 means m */
+    void* out;      int ld_out;
+    int out_type;             /* PK100_OUT_* */
+    float out_scale;
+    float tau;
+    uint8_t* keep_out;
+    float* stats_out;
+    const uint8_t* keep_in;
+    int* status;              /* device int, set to 1 if a bounded wait expired; may be NULL */
+    int max_ctas;             /* <= 0: one CTA per SM */
+} pk100_gemm_args;
+
+int pk100_gemm(void* stream, const pk100_gemm_args* args);
+
+/* pk_sm89_layer_norm (kernels/sm89/encoder.cu:81-126) and
+ * pk_sm89_layer_norm_quantize_fp8_dynamic (:294-299); launcher launch_norm /
+ * launch_norm_quantize_fp8 (src/cuda/encoder.rs:1361-1468).  Width is 1024. */
+int pk100_layer_norm(void* stream, const void* input, const void* gamma, const void* beta,
+                     void* output, float* scales, int mode, float inv_scale, int total_rows,
+                     int seg_stride, int valid_rows, const int* seg_valid, float eps);
+
+/* pk_sm89_layer_norm_pair (kernels/sm89/encoder.cu:128-209; launch_norm_pair
+ * src/cuda/encoder.rs:1394-1433): fp16 first output, second LayerNorm of the
+ * rounded first output in `next_mode`. */
+int pk100_layer_norm_pair(void* stream, const void* input, const void* gamma, const void* beta,
+                          void* output, const void* next_gamma, const void* next_beta,
+                          void* next_output, float* next_scales, int next_mode,
+                          float next_inv_scale, int total_rows, int seg_stride, int valid_rows,
+                          const int* seg_valid, float eps);
+
+/* pk_sm89_quantize_fp8_fixed (kernels/sm89/encoder.cu:549-559). */
+int pk100_quantize_fp8_fixed(void* stream, const void* input, void* output, long long elements,
+                             float inverse_scale);
+
+/* pk_sm89_quantize_int8 (kernels/sm89/linear.cu:549-560); argument order as there. */
+int pk100_quantize_int8(void* stream, const void* input, void* output, float inverse_scale,
+                        long long elements);
+
+/* Load-time weight packing.  Replaces QuantizedFfnWeights::load_for
+ * (src/cuda/encoder.rs:361-422, CPU) and pk_sm89_quantize_rows1024 / _rows256 /
+ * _ffn_contract (kernels/sm89/encoder.cu:1129-1180, per request in the
+ * reference).  weight: fp16 [n, ldw]; packed: [n, k] bytes (E4M3, S8) or
+ * [n, k/2] (S4, low nibble = even k); scales fp32 [n]; group_scales fp16
+ * [k/128, n] (PK100_PACK_S4_G128 only). */
+int pk100_pack_weight_rows(void* stream, const void* weight, int n, int k, int ldw, int format,
+                           void* packed, float* scales, void* group_scales);
+
+/* INT4-g128 codes -> fp16 weights (the dequantisation the INT4 GEMM performs;
+ * idea of pk_sm89_q4_k_dequantize, kernels/sm89/linear.cu:458-472). */
+int pk100_dequant_w4g128(void* stream, const void* codes, const void* group_scales, int n, int k,
+                         void* weight_f16);
+
+/* pk_sm89_glu_masked (kernels/sm89/encoder.cu:308-330). input [rows, 2048]. */
+int pk100_glu_masked(void* stream, const void* input, void* output, int total_rows,
+                     int seg_stride, int valid_rows, const int* seg_valid);
+
+/* pk_sm89_depthwise_batchnorm_silu (kernels/sm89/encoder.cu:1182-1233) and, with
+ * quantize != 0, pk_sm89_depthwise_pack (:1235-1311): E4M3 bytes + per-row scales. */
+int pk100_depthwise_bn_silu(void* stream, const void* input, const void* dw_weight,
+                            const float* bn_gamma, const float* bn_beta, const float* bn_mean,
+                            const float* bn_var, void* output, float* row_scales, int quantize,
+                            int segments, int seg_stride, int valid_rows, const int* seg_valid,
+                            float eps);
+
+/* pk_sm89_local_relpos_attention (kernels/sm89/encoder.cu:1338-1461): the fp32
+ * CUDA-core statement of the operator, one warp per (query, head).  query /
+ * key / value are fp16 with row strides ldq / ldk / ldv (elements) so that the
+ * planes of a fused QKV projection can be passed directly; position is the
+ * head-major table [8, 272, 128]; bias_u / bias_v are [8, 128]. */
+int pk100_local_relpos_attention_simple(void* stream, const void* query, int ldq, const void* key,
+                                        int ldk, const void* value, int ldv, const void* position,
+                                        const void* bias_u, const void* bias_v, void* output,
+                                        int ldo, int segments, int seg_stride, int valid_rows,
+                                        const int* seg_valid);
+
+/* pk_sm89_pack_position_heads (kernels/sm89/encoder.cu:1321-1336):
+ * [272, 1024] -> head-major [8, 272, 128]. */
+int pk100_pack_position_heads(void* stream, const void* input, void* output);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* PK100_H_ */

@@ -1,0 +1,7 @@
+"""B200 (sm_100a) kernels for the FastConformer / TDT hot path of l4-parakeet-rs.
+
+`lib` is the ctypes view of the C ABI (include/pk100.h); `ops` wraps it for
+torch CUDA tensors (device memory and streams only -- no torch arithmetic).
+"""
+from . import lib  # noqa: F401  (raises if libpk100.so is not built)
+from . import ops  # noqa: F401

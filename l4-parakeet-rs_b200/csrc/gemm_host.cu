@@ -1,0 +1,190 @@
+// Host side of pk100_gemm: argument validation, TMA tensor-map encoding and the
+// dispatch table over (operand kind, tile width, swizzle, epilogue family).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "gemm_sm100.cuh"
+#include "pk100_internal.h"
+
+namespace pk100 {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+                cudaSuccess && qres == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        }
+    });
+    return fn;
+}
+
+// 2-D row-major matrix [rows, cols] with `ld` elements between rows; box =
+// [box_rows, swizzle_bytes / elem_bytes] elements, swizzle mode = box width.
+static int make_map(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows,
+                    uint64_t cols, uint64_t ld, int box_rows, int swizzle_bytes) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return PK100_ERR_DRIVER;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_bytes)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(swizzle_bytes / elem_bytes),
+                               static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUtensorMapDataType dtype =
+        elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const CUtensorMapSwizzle swz =
+        swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    const CUresult res = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box,
+                            elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return res == CUDA_SUCCESS ? PK100_OK : PK100_ERR_DRIVER;
+}
+
+static int sm_count() {
+    static int count = 0;
+    if (count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+        if (count <= 0) count = 148;
+    }
+    return count;
+}
+
+template <int Kind, int BlockN, int SwizzleBytes, int Epi>
+static int launch(const pk100_gemm_args& a, const GemmParams& p, cudaStream_t stream) {
+    using Smem = GemmSmem<BlockN, SwizzleBytes>;
+    auto kernel = gemm_kernel<Kind, BlockN, SwizzleBytes, Epi, BSRC_TMA>;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t err = cudaFuncSetAttribute(
+            kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
+        if (err != cudaSuccess) return static_cast<int>(err);
+        configured = true;
+    }
+    constexpr int elem = Kind == KIND_F16 ? 2 : 1;
+    CUtensorMap map_a, map_b;
+    int rc = make_map(&map_a, a.a, elem, a.m, a.k, a.lda, kBlockM, SwizzleBytes);
+    if (rc != PK100_OK) return rc;
+    rc = make_map(&map_b, a.b, elem, a.n, a.k, a.ldb, BlockN / 2, SwizzleBytes);
+    if (rc != PK100_OK) return rc;
+    const int m_tiles = (a.m + kBlockM - 1) / kBlockM;
+    const int n_tiles = (p.n + BlockN - 1) / BlockN;
+    int ctas = a.max_ctas > 0 ? a.max_ctas : sm_count();
+    if (ctas > m_tiles * n_tiles) ctas = m_tiles * n_tiles;
+    kernel<<<ctas, kGemmThreads, Smem::kTotal, stream>>>(map_a, map_b, p);
+    return pk100_launch_status();
+}
+
+static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
+
+}  // namespace pk100
+
+using namespace pk100;
+
+extern "C" int pk100_gemm(void* stream_v, const pk100_gemm_args* a) {
+    if (a == nullptr || a->a == nullptr || a->b == nullptr || a->out == nullptr) return PK100_ERR_NULL;
+    if (a->m < 0 || a->n <= 0 || a->k <= 0) return PK100_ERR_SHAPE;
+    if (a->m == 0) return PK100_OK;
+    if (a->kind < PK100_KIND_F16 || a->kind > PK100_KIND_S8) return PK100_ERR_UNSUPPORTED;
+    const int elem = a->kind == PK100_KIND_F16 ? 2 : 1;
+    if ((static_cast<long long>(a->k) * elem) % 16 != 0 ||
+        (static_cast<long long>(a->lda) * elem) % 16 != 0 ||
+        (static_cast<long long>(a->ldb) * elem) % 16 != 0 || a->lda < a->k || a->ldb < a->k)
+        return PK100_ERR_SHAPE;
+    if (a->n % 32 != 0) return PK100_ERR_SHAPE;
+    if (!aligned16(a->a) || !aligned16(a->b) || !aligned16(a->out)) return PK100_ERR_ALIGN;
+    if (a->out_type < PK100_OUT_F16 || a->out_type > PK100_OUT_S8) return PK100_ERR_UNSUPPORTED;
+    const int out_elem = a->out_type == PK100_OUT_F16 ? 2 : (a->out_type == PK100_OUT_F32 ? 4 : 1);
+    const int out_cols = a->epilogue == PK100_EPI_GLU ? a->n / 2 : a->n;
+    if (a->ld_out < out_cols || (static_cast<long long>(a->ld_out) * out_elem) % 16 != 0)
+        return PK100_ERR_SHAPE;
+    if (a->residual != nullptr) {
+        if (!aligned16(a->residual)) return PK100_ERR_ALIGN;
+        if (a->ld_res < out_cols || a->ld_res % 8 != 0) return PK100_ERR_SHAPE;
+        if (a->epilogue != PK100_EPI_LINEAR) return PK100_ERR_UNSUPPORTED;
+    }
+    if (a->keep_in != nullptr) {
+        if (elem != 1 || a->k % 64 != 0 || a->k > 4096) return PK100_ERR_SHAPE;
+    }
+    if (a->epilogue == PK100_EPI_GLU && (a->n % 128 != 0)) return PK100_ERR_SHAPE;
+    if (a->epilogue == PK100_EPI_SPARSE_OUT) {
+        if (a->keep_out == nullptr) return PK100_ERR_NULL;
+        if (a->n % 64 != 0 || a->out_type != PK100_OUT_S8) return PK100_ERR_SHAPE;
+    }
+
+    GemmParams p{};
+    p.m = a->m;
+    p.n = a->n;
+    p.k = a->k;
+    p.row_scales = a->row_scales;
+    p.row_scale = a->row_scale;
+    p.col_scales = a->col_scales;
+    p.bias = a->bias;
+    p.act = a->act;
+    p.residual = static_cast<const __half*>(a->residual);
+    p.ld_res = a->ld_res;
+    p.alpha = a->alpha;
+    p.valid_rows = a->valid_rows > 0 ? a->valid_rows : a->m;
+    p.out = a->out;
+    p.ld_out = a->ld_out;
+    p.out_type = a->out_type;
+    p.out_scale = a->out_scale;
+    p.tau = a->tau;
+    p.keep_out = a->keep_out;
+    p.stats_out = a->stats_out;
+    p.keep_in = a->keep_in;
+    p.w4_codes = nullptr;
+    p.w4_scales = nullptr;
+    p.status = a->status;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+    // Tile width: 256 columns unless that leaves too few tiles to fill the SMs.
+    const int m_tiles = (a->m + kBlockM - 1) / kBlockM;
+    const bool narrow = (a->n % 256 != 0) || (m_tiles * (a->n / 256) < sm_count());
+
+    switch (a->epilogue) {
+    case PK100_EPI_LINEAR:
+        if (a->kind == PK100_KIND_F16) {
+            return narrow ? launch<KIND_F16, 128, 128, EPI_LINEAR>(*a, p, stream)
+                          : launch<KIND_F16, 256, 128, EPI_LINEAR>(*a, p, stream);
+        }
+        if (a->kind == PK100_KIND_E4M3) {
+            return narrow ? launch<KIND_F8, 128, 128, EPI_LINEAR>(*a, p, stream)
+                          : launch<KIND_F8, 256, 128, EPI_LINEAR>(*a, p, stream);
+        }
+        if (a->keep_in != nullptr) {
+            // 64-byte K blocks: skip granularity equals the 64-wide sparsity tile
+            return narrow ? launch<KIND_I8, 128, 64, EPI_LINEAR>(*a, p, stream)
+                          : launch<KIND_I8, 256, 64, EPI_LINEAR>(*a, p, stream);
+        }
+        return narrow ? launch<KIND_I8, 128, 128, EPI_LINEAR>(*a, p, stream)
+                      : launch<KIND_I8, 256, 128, EPI_LINEAR>(*a, p, stream);
+    case PK100_EPI_GLU:
+        if (a->kind == PK100_KIND_E4M3) {
+            return (a->n % 256 != 0) ? launch<KIND_F8, 128, 128, EPI_GLU>(*a, p, stream)
+                                     : launch<KIND_F8, 256, 128, EPI_GLU>(*a, p, stream);
+        }
+        if (a->kind == PK100_KIND_F16) {
+            return (a->n % 256 != 0) ? launch<KIND_F16, 128, 128, EPI_GLU>(*a, p, stream)
+                                     : launch<KIND_F16, 256, 128, EPI_GLU>(*a, p, stream);
+        }
+        return PK100_ERR_UNSUPPORTED;
+    case PK100_EPI_SPARSE_OUT:
+        if (a->kind == PK100_KIND_E4M3) return launch<KIND_F8, 256, 128, EPI_SPARSE_OUT>(*a, p, stream);
+        if (a->kind == PK100_KIND_F16) return launch<KIND_F16, 256, 128, EPI_SPARSE_OUT>(*a, p, stream);
+        return PK100_ERR_UNSUPPORTED;
+    default:
+        return PK100_ERR_UNSUPPORTED;
+    }
+}

@@ -1,0 +1,550 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   D[M,N] = epilogue( A[M,K] . B[N,K]^T )      A, B row-major ("K-major")
+//
+// One CTA per SM loops over 128 x BLOCK_N output tiles.
+//   warp 0      TMA producer: global -> swizzled shared-memory stage ring
+//   warp 1      tcgen05.mma issuer (one elected lane); owns the TMEM allocation
+//   warps 2..9  epilogue: tcgen05.ld the fp32/s32 accumulator, apply scales /
+//               bias / activation / residual / quantisation, store to global
+// Accumulators are double-buffered in TMEM (2 x BLOCK_N columns) so the MMAs of
+// tile i+1 overlap the epilogue of tile i.  All waits are bounded (ptx_sm100.cuh).
+#pragma once
+
+#include <cuda_fp8.h>
+
+#include "ptx_sm100.cuh"
+
+namespace pk100 {
+
+enum : int { OUT_F16 = 0, OUT_F32 = 1, OUT_E4M3 = 2, OUT_S8 = 3 };
+enum : int { ACT_NONE = 0, ACT_SILU = 1, ACT_RELU = 2 };
+enum : int { EPI_LINEAR = 0, EPI_GLU = 1, EPI_SPARSE_OUT = 2 };
+// B operand sources: TMA from a K-major matrix, or INT4 group-quantised weights
+// dequantised to fp16 in shared memory by the producer warps.
+enum : int { BSRC_TMA = 0, BSRC_W4G128 = 1 };
+
+struct GemmParams {
+    int m, n, k;                 // n counts B rows (GLU: value rows + gate rows)
+    // epilogue inputs
+    const float* row_scales;     // [m] per-row activation scales, or nullptr
+    float row_scale;             // used when row_scales == nullptr
+    const float* col_scales;     // [n] per-output-channel weight scales, or nullptr
+    const float* bias;           // [n] or nullptr
+    int act;
+    const __half* residual;      // [m, ld_res] or nullptr; may alias `out`
+    int ld_res;
+    float alpha;                 // out = alpha * value (+ residual)
+    int valid_rows;              // rows >= valid_rows are stored as zero
+    // output
+    void* out;
+    int ld_out;                  // elements
+    int out_type;
+    float out_scale;             // multiplier applied before E4M3 / S8 encoding
+    // tile sparsity, producer side (EPI_SPARSE_OUT)
+    float tau;
+    uint8_t* keep_out;           // [ceil(m/128), n/64]
+    float* stats_out;            // [ceil(m/128), n/64] or nullptr
+    // tile sparsity, consumer side
+    const uint8_t* keep_in;      // [ceil(m/128), k/64] or nullptr
+    // INT4 group-128 weights (BSRC_W4G128)
+    const uint8_t* w4_codes;     // [n, k/2], low nibble = even k
+    const __half* w4_scales;     // [k/128, n]
+    int* status;                 // set non-zero when a bounded wait gave up
+};
+
+constexpr int kBlockM = 128;
+constexpr int kEpilogueWarps = 8;
+constexpr int kGemmThreads = 32 * (2 + kEpilogueWarps);
+
+template <int BlockN, int SwizzleBytes>
+struct GemmSmem {
+    static constexpr int kStageA = kBlockM * SwizzleBytes;
+    static constexpr int kStageB = BlockN * SwizzleBytes;
+    static constexpr int kStageBytes = kStageA + kStageB;
+    static constexpr int kBudget = 196 * 1024;
+    static constexpr int kStagesRaw = kBudget / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+    static constexpr int kTileBytes = kStages * kStageBytes;
+    // tail: barriers + tmem pointer + abort flag + epilogue staging
+    static constexpr int kTailBytes = 64 * 8 + 16 + 2 * BlockN * 4 + 64 * 4;
+    static constexpr int kTotal = kTileBytes + kTailBytes + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ float round_f16(float v) { return __half2float(__float2half_rn(v)); }
+
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+}
+
+__device__ __forceinline__ int quant_s8(float v) {
+    return max(-127, min(127, __float2int_rn(v)));
+}
+
+__device__ __forceinline__ uint32_t pack_s8x4(float a, float b, float c, float d) {
+    return (quant_s8(a) & 255) | ((quant_s8(b) & 255) << 8) | ((quant_s8(c) & 255) << 16) |
+           ((quant_s8(d) & 255) << 24);
+}
+
+template <int Kind>
+__device__ __forceinline__ float acc_to_float(uint32_t r) {
+    if constexpr (Kind == KIND_I8) {
+        return static_cast<float>(static_cast<int>(r));
+    } else {
+        return __uint_as_float(r);
+    }
+}
+
+// Named barrier over the epilogue warps only.
+__device__ __forceinline__ void epilogue_bar_sync() {
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+}
+
+// Store 32 consecutive output columns of one row.
+__device__ __forceinline__ void store_chunk(void* out_row, int out_type, float out_scale,
+                                            const float (&v)[32]) {
+    if (out_type == OUT_F16) {
+        uint4* dst = reinterpret_cast<uint4*>(out_row);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            dst[i] = make_uint4(pack_half2(v[8 * i + 0], v[8 * i + 1]),
+                                pack_half2(v[8 * i + 2], v[8 * i + 3]),
+                                pack_half2(v[8 * i + 4], v[8 * i + 5]),
+                                pack_half2(v[8 * i + 6], v[8 * i + 7]));
+        }
+    } else if (out_type == OUT_F32) {
+        float4* dst = reinterpret_cast<float4*>(out_row);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        }
+    } else if (out_type == OUT_E4M3) {
+        uint4* dst = reinterpret_cast<uint4*>(out_row);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int b = 16 * i + 4 * j;
+                w[j] = pack_e4m3x4(round_f16(v[b]) * out_scale, round_f16(v[b + 1]) * out_scale,
+                                   round_f16(v[b + 2]) * out_scale, round_f16(v[b + 3]) * out_scale);
+            }
+            dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else {
+        uint4* dst = reinterpret_cast<uint4*>(out_row);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int b = 16 * i + 4 * j;
+                w[j] = pack_s8x4(round_f16(v[b]) * out_scale, round_f16(v[b + 1]) * out_scale,
+                                 round_f16(v[b + 2]) * out_scale, round_f16(v[b + 3]) * out_scale);
+            }
+            dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+}
+
+__device__ __forceinline__ size_t out_elem_bytes(int out_type) {
+    return out_type == OUT_F16 ? 2 : (out_type == OUT_F32 ? 4 : 1);
+}
+
+// Bit i of the mask = "64-element K tile i of M tile `mt` holds a non-zero".
+// Without a bitmap every tile is live.  K <= 4096 (64 tiles) is checked on the host.
+__device__ __forceinline__ uint64_t load_live_mask(const uint8_t* keep_in, int mt, int k_tiles64) {
+    if (keep_in == nullptr) return ~0ull;
+    const uint8_t* row = keep_in + static_cast<size_t>(mt) * k_tiles64;
+    uint64_t mask = 0;
+    for (int i = 0; i < k_tiles64; ++i) mask |= static_cast<uint64_t>(row[i] != 0) << i;
+    return mask;
+}
+
+// Is K block `kb` (SwizzleBytes wide, 8-bit elements) live?
+template <int SwizzleBytes>
+__device__ __forceinline__ bool k_block_live(uint64_t mask, int kb) {
+    if constexpr (SwizzleBytes == 64) {
+        return (mask >> kb) & 1ull;
+    } else {
+        return ((mask >> (2 * kb)) & 3ull) != 0;
+    }
+}
+
+template <int Kind, int BlockN, int SwizzleBytes, int Epi, int BSrc>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const GemmParams p) {
+    using Smem = GemmSmem<BlockN, SwizzleBytes>;
+    constexpr int kStages = Smem::kStages;
+    constexpr int kElemBytes = Kind == KIND_F16 ? 2 : 1;
+    constexpr int kBlockK = SwizzleBytes / kElemBytes;       // elements per K block
+    constexpr int kMmasPerBlock = SwizzleBytes / 32;         // 32 bytes of K per MMA
+    constexpr uint32_t kTmemCols = 2 * BlockN;
+    constexpr int kBHalf = BlockN / 2;                       // rows per B load
+    static_assert(BlockN == 64 || BlockN == 128 || BlockN == 256, "BlockN");
+    static_assert(BSrc == BSRC_TMA || (Kind == KIND_F16 && SwizzleBytes == 128), "w4 needs f16");
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* tail = smem + Smem::kTileBytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);
+    uint64_t* empty_bar = full_bar + kStages;
+    uint64_t* tmem_full_bar = empty_bar + kStages;
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(tail + 64 * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 64 * 8 + 8);
+    float* s_col_scale = reinterpret_cast<float*>(tail + 64 * 8 + 16);
+    float* s_bias = s_col_scale + BlockN;
+    float* s_reduce = s_bias + BlockN;                       // [kEpilogueWarps][4]
+
+    const int warp = static_cast<int>(threadIdx.x) / 32;
+    const int lane = static_cast<int>(threadIdx.x) % 32;
+
+    const int m_tiles = (p.m + kBlockM - 1) / kBlockM;
+    const int n_tiles = (p.n + BlockN - 1) / BlockN;
+    const int num_tiles = m_tiles * n_tiles;
+    const int k_blocks = (p.k + kBlockK - 1) / kBlockK;
+    const int k_tiles64 = p.k / 64;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < kStages; ++s) {
+            // full: one arrive.expect_tx from the TMA lane (+ 4 producer warps for W4)
+            mbar_init(full_bar + s, BSrc == BSRC_W4G128 ? 1 + 4 : 1);
+            mbar_init(empty_bar + s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tmem_full_bar + b, 1);
+            mbar_init(tmem_empty_bar + b, kEpilogueWarps);
+        }
+        fence_barrier_init();
+        prefetch_tensormap(&map_a);
+        if constexpr (BSrc == BSRC_TMA) prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_ptr_smem, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int mt = tile % m_tiles;
+                const int nt = tile / m_tiles;
+                const int m0 = mt * kBlockM;
+                const uint64_t live_mask = load_live_mask(p.keep_in, mt, k_tiles64);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (p.keep_in != nullptr && !k_block_live<SwizzleBytes>(live_mask, kb)) continue;
+                    if (!mbar_wait_bounded(empty_bar + stage, phase ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem + stage * Smem::kStageBytes;
+                    uint8_t* sb = sa + Smem::kStageA;
+                    if constexpr (BSrc == BSRC_TMA) {
+                        mbar_arrive_expect_tx(full_bar + stage, Smem::kStageBytes);
+                        tma_load_2d(sa, &map_a, full_bar + stage, kb * kBlockK, m0);
+                        int n_first, n_second;
+                        if constexpr (Epi == EPI_GLU) {
+                            n_first = nt * kBHalf;
+                            n_second = p.n / 2 + nt * kBHalf;
+                        } else {
+                            n_first = nt * BlockN;
+                            n_second = n_first + kBHalf;
+                        }
+                        tma_load_2d(sb, &map_b, full_bar + stage, kb * kBlockK, n_first);
+                        tma_load_2d(sb + kBHalf * SwizzleBytes, &map_b, full_bar + stage,
+                                    kb * kBlockK, n_second);
+                    } else {
+                        mbar_arrive_expect_tx(full_bar + stage, Smem::kStageA);
+                        tma_load_2d(sa, &map_a, full_bar + stage, kb * kBlockK, m0);
+                    }
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_instr_desc<Kind>(kBlockM, BlockN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+                const int mt = tile % m_tiles;
+                const int buf = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                const uint64_t live_mask = load_live_mask(p.keep_in, mt, k_tiles64);
+                if (!mbar_wait_bounded(tmem_empty_bar + buf, acc_phase ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BlockN);
+                uint32_t accumulate = 0;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (p.keep_in != nullptr && !k_block_live<SwizzleBytes>(live_mask, kb)) continue;
+                    if (!mbar_wait_bounded(full_bar + stage, phase, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(smem + stage * Smem::kStageBytes);
+                    const uint32_t sb = sa + Smem::kStageA;
+                    const uint64_t desc_a = make_smem_desc<SwizzleBytes>(sa);
+                    const uint64_t desc_b = make_smem_desc<SwizzleBytes>(sb);
+#pragma unroll
+                    for (int j = 0; j < kMmasPerBlock; ++j) {
+                        // advance 32 bytes along K inside the swizzle atom: +2 in 16-byte units
+                        tc_mma<Kind>(tmem_d, desc_a + 2u * j, desc_b + 2u * j, idesc, accumulate);
+                        accumulate = 1;
+                    }
+                    tc_commit(empty_bar + stage);   // frees the stage once the MMAs retire
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                if (accumulate != 0) {
+                    tc_commit(tmem_full_bar + buf);
+                } else {
+                    mbar_arrive(tmem_full_bar + buf);  // no live K block: accumulator unused
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------- epilogue
+        const int ew = warp - 2;                 // 0..7
+        const int quad = warp % 4;               // TMEM lane quadrant this warp may read
+        const int half = ew / 4;                 // which half of the tile's columns
+        const int et = static_cast<int>(threadIdx.x) - 64;   // 0..255
+        int local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            const int mt = tile % m_tiles;
+            const int nt = tile / m_tiles;
+            const int buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            const int row = mt * kBlockM + quad * 32 + lane;
+            const int n0 = Epi == EPI_GLU ? nt * kBHalf : nt * BlockN;   // first output column
+            // stage per-column scale / bias for this tile
+            epilogue_bar_sync();
+            for (int c = et; c < BlockN; c += 32 * kEpilogueWarps) {
+                int src;
+                if constexpr (Epi == EPI_GLU) {
+                    src = c < kBHalf ? nt * kBHalf + c : p.n / 2 + nt * kBHalf + (c - kBHalf);
+                } else {
+                    src = nt * BlockN + c;
+                }
+                const bool in = src < p.n;
+                s_col_scale[c] = (p.col_scales != nullptr && in) ? p.col_scales[src] : 1.0f;
+                s_bias[c] = (p.bias != nullptr && in) ? p.bias[src] : 0.0f;
+            }
+            epilogue_bar_sync();
+
+            bool live = true;
+            if (p.keep_in != nullptr) {
+                const uint8_t* krow = p.keep_in + static_cast<size_t>(mt) * k_tiles64;
+                bool any = false;
+                for (int i = lane; i < k_tiles64; i += 32) any |= krow[i] != 0;
+                live = __any_sync(0xffffffffu, any);
+            }
+
+            const bool got = mbar_wait_bounded(tmem_full_bar + buf, acc_phase, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+
+            const float rs = p.row_scales != nullptr ? (row < p.m ? p.row_scales[row] : 0.0f)
+                                                     : p.row_scale;
+            const uint32_t taddr_base = tmem_base + static_cast<uint32_t>(buf * BlockN) +
+                                        (static_cast<uint32_t>(quad * 32) << 16);
+            const size_t obytes = out_elem_bytes(p.out_type);
+
+            if constexpr (Epi == EPI_LINEAR) {
+                constexpr int kChunks = BlockN / 2 / 32;
+#pragma unroll 1
+                for (int c = 0; c < kChunks; ++c) {
+                    const int col_local = half * (BlockN / 2) + c * 32;
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr_base + col_local, r);
+                    tmem_ld_wait();
+                    const int col = n0 + col_local;
+                    if (row < p.m && col < p.n) {
+                        float v[32];
+                        const bool zero_row = row >= p.valid_rows;
+                        uint4 res_raw[4];
+                        if (p.residual != nullptr) {
+                            const uint4* rp = reinterpret_cast<const uint4*>(
+                                p.residual + static_cast<size_t>(row) * p.ld_res + col);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) res_raw[i] = rp[i];
+                        }
+                        const __half* res_h = reinterpret_cast<const __half*>(res_raw);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            float x = live ? acc_to_float<Kind>(r[j]) : 0.0f;
+                            x = x * rs * s_col_scale[col_local + j] + s_bias[col_local + j];
+                            if (p.act == ACT_SILU) x = silu_f(x);
+                            else if (p.act == ACT_RELU) x = fmaxf(x, 0.0f);
+                            if (p.residual != nullptr) x = fmaf(p.alpha, x, __half2float(res_h[j]));
+                            else x *= p.alpha;
+                            v[j] = zero_row ? 0.0f : x;
+                        }
+                        uint8_t* out_row = reinterpret_cast<uint8_t*>(p.out) +
+                            (static_cast<size_t>(row) * p.ld_out + col) * obytes;
+                        store_chunk(out_row, p.out_type, p.out_scale, v);
+                    }
+                }
+            } else if constexpr (Epi == EPI_GLU) {
+                // columns [0, BlockN/2) hold values, [BlockN/2, BlockN) their gates
+                constexpr int kChunks = BlockN / 4 / 32;
+                static_assert(kChunks >= 1, "GLU needs BlockN >= 128");
+#pragma unroll 1
+                for (int c = 0; c < kChunks; ++c) {
+                    const int col_local = half * (BlockN / 4) + c * 32;
+                    uint32_t rv[32], rg[32];
+                    tmem_ld_32x32(taddr_base + col_local, rv);
+                    tmem_ld_32x32(taddr_base + kBHalf + col_local, rg);
+                    tmem_ld_wait();
+                    const int col = n0 + col_local;
+                    if (row < p.m && col < p.n / 2) {
+                        float v[32];
+                        const bool zero_row = row >= p.valid_rows;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float value = round_f16(acc_to_float<Kind>(rv[j]) * rs *
+                                                          s_col_scale[col_local + j]);
+                            const float gate = round_f16(acc_to_float<Kind>(rg[j]) * rs *
+                                                         s_col_scale[kBHalf + col_local + j]);
+                            v[j] = zero_row ? 0.0f : __fdividef(value, 1.0f + __expf(-gate));
+                        }
+                        uint8_t* out_row = reinterpret_cast<uint8_t*>(p.out) +
+                            (static_cast<size_t>(row) * p.ld_out + col) * obytes;
+                        store_chunk(out_row, p.out_type, p.out_scale, v);
+                    }
+                }
+            } else {
+                // EPI_SPARSE_OUT: SiLU, per-(128 x 64) tile max|a| against tau, INT8 store.
+                static_assert(Epi != EPI_SPARSE_OUT || BlockN == 256, "sparse-out uses BlockN 256");
+                constexpr int kChunks = BlockN / 2 / 32;     // 4 chunks = two 64-wide tiles
+                uint32_t h[kChunks][16];                      // f16x2-packed SiLU outputs
+                float tile_max[2] = {0.0f, 0.0f};
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c) {
+                    const int col_local = half * (BlockN / 2) + c * 32;
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr_base + col_local, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        float a = acc_to_float<Kind>(r[j]) * rs * s_col_scale[col_local + j];
+                        float b = acc_to_float<Kind>(r[j + 1]) * rs * s_col_scale[col_local + j + 1];
+                        a = silu_f(a);
+                        b = silu_f(b);
+                        if (row >= p.valid_rows || row >= p.m) { a = 0.0f; b = 0.0f; }
+                        tile_max[c / 2] = fmaxf(tile_max[c / 2], fmaxf(fabsf(a), fabsf(b)));
+                        h[c][j / 2] = pack_half2(a, b);
+                    }
+                }
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    float mx = tile_max[t];
+#pragma unroll
+                    for (int off = 16; off > 0; off /= 2)
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+                    tile_max[t] = mx;
+                }
+                if (lane == 0) {
+                    s_reduce[ew * 2 + 0] = tile_max[0];
+                    s_reduce[ew * 2 + 1] = tile_max[1];
+                }
+                epilogue_bar_sync();
+                bool keep[2];
+                const int n_tiles64 = p.n / 64;
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    float mx = 0.0f;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) mx = fmaxf(mx, s_reduce[(half * 4 + q) * 2 + t]);
+                    keep[t] = mx >= p.tau;
+                    const int tile64 = (n0 + half * (BlockN / 2)) / 64 + t;
+                    if (quad == 0 && lane == 0 && tile64 < n_tiles64) {
+                        p.keep_out[static_cast<size_t>(mt) * n_tiles64 + tile64] = keep[t] ? 1 : 0;
+                        if (p.stats_out != nullptr)
+                            p.stats_out[static_cast<size_t>(mt) * n_tiles64 + tile64] = mx;
+                    }
+                }
+                if (row < p.m) {
+#pragma unroll
+                    for (int c = 0; c < kChunks; ++c) {
+                        const int col = n0 + half * (BlockN / 2) + c * 32;
+                        if (col >= p.n) continue;
+                        uint4* dst = reinterpret_cast<uint4*>(
+                            reinterpret_cast<uint8_t*>(p.out) + static_cast<size_t>(row) * p.ld_out + col);
+                        uint32_t w[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const __half2 lo = *reinterpret_cast<const __half2*>(&h[c][2 * j]);
+                            const __half2 hi = *reinterpret_cast<const __half2*>(&h[c][2 * j + 1]);
+                            const float2 a = __half22float2(lo);
+                            const float2 b = __half22float2(hi);
+                            w[j] = keep[c / 2] ? pack_s8x4(a.x * p.out_scale, a.y * p.out_scale,
+                                                           b.x * p.out_scale, b.y * p.out_scale)
+                                               : 0u;
+                        }
+                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    }
+                }
+            }
+            // release the accumulator buffer
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty_bar + buf);
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    if (*abort_flag != 0) {
+        // give copies / MMAs still in flight time to land before shared memory
+        // and tensor memory are released
+        const uint64_t start = global_timer_ns();
+        while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
+        if (threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, 1);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace pk100

@@ -1,0 +1,16 @@
+// Shared between the translation units of libpk100: status codes, enums that are
+// also part of the C ABI (see include/pk100.h) and the launch-status helper.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "../../include/pk100.h"
+
+// Maps the sticky-free launch error of the last kernel launch to the ABI's
+// convention: 0 ok, positive = CUDA runtime error code.
+static inline int pk100_launch_status() {
+    const cudaError_t err = cudaPeekAtLastError();
+    if (err == cudaSuccess) return PK100_OK;
+    cudaGetLastError();   // clear the non-sticky launch error so later calls are not poisoned
+    return static_cast<int>(err);
+}

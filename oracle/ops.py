@@ -1,0 +1,328 @@
+"""CPU oracle -- encoder operators (TEST INFRASTRUCTURE, not product code).
+
+numpy restatement of the FastConformer hot path with the same quantisation
+points as the sm_100a kernels.  Accumulation is float64 (a strictly more
+accurate stand-in for the tensor core's fp32 accumulate); everything after the
+accumulator follows the reference's operation order in float32.
+
+Parity status.  Pinned by the reference's own known answers: E4M3 / INT8 / FP16
+codecs, layout sizes, generator (see codec.py).  Pinned against the reference's
+own kernels executed on a B200 (oracle/_ref cubins, tests/test_ref_kernels.py):
+LayerNorm, fixed FP8 quantiser, FP8 FF expand, GLU, depthwise+BN+SiLU, scalar
+local attention, TDT greedy decode.  The INT8 tile-sparse FF2, INT8 QKV and
+INT4-g128 operators have no reference implementation ("parity unpinned" beyond
+the integer codecs); they are defined here from the benchmark description.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import codec
+from .codec import F32, f16_round
+
+MODEL_WIDTH = 1024
+FF_WIDTH = 4096
+HEADS = 8
+HEAD_WIDTH = 128
+ATT_LEFT = 128
+ATT_RIGHT = 128
+POSITION_ROWS = 257
+POSITION_ROWS_PADDED = 272
+LN_EPS = F32(1e-5)
+FP8_INPUT_SCALE = F32(8.0 / 448.0)       # src/cuda/encoder.rs:28-29
+FP8_INPUT_INV = F32(56.0)
+SOFTMAX_SCALE = F32(0.08838834764831845)  # kernels/sm89/encoder.cu:1415
+INT8_HIDDEN_INV = F32(32.0)               # FF hidden INT8 fixed scale 1/32 (this build's choice)
+INT8_HIDDEN_SCALE = F32(1.0 / 32.0)
+SPARSE_TILE_ROWS = 128
+SPARSE_TILE_COLS = 64
+
+
+def silu(v):
+    """`v / (1 + expf(-v))` (kernels/sm89/encoder.cu:329, :337, :1000-1005)."""
+    v = np.asarray(v, dtype=F32)
+    return (v / (F32(1.0) + np.exp(-v, dtype=F32))).astype(F32)
+
+
+def sigmoid(v):
+    v = np.asarray(v, dtype=F32)
+    return (F32(1.0) / (F32(1.0) + np.exp(-v, dtype=F32))).astype(F32)
+
+
+# ----------------------------------------------------------------------------
+# LayerNorm (+ fused quantisers)
+# ----------------------------------------------------------------------------
+
+def layer_norm(x16, gamma16, beta16, rows=None, eps=LN_EPS):
+    """`pk_sm89_layer_norm` (kernels/sm89/encoder.cu:81-126): two-pass fp32
+    statistics, y = f16((x-mean)*rsqrt(var+eps)*gamma + beta); rows >= `rows`
+    are zero-filled."""
+    x = np.asarray(x16, dtype=F32)
+    m = x.shape[0]
+    rows = m if rows is None else rows
+    mean = (x.sum(axis=1, dtype=np.float64) / x.shape[1]).astype(F32)
+    d = x - mean[:, None]
+    var = ((d.astype(np.float64) ** 2).sum(axis=1) / x.shape[1]).astype(F32)
+    rstd = (F32(1.0) / np.sqrt(var + F32(eps), dtype=F32)).astype(F32)
+    y = (d * rstd[:, None]) * np.asarray(gamma16, dtype=F32) + np.asarray(beta16, dtype=F32)
+    y = f16_round(y)
+    y[rows:] = 0
+    return y
+
+
+def ln_quant_fp8_fixed(x16, gamma16, beta16, rows=None, inv=FP8_INPUT_INV):
+    """LN followed by `pk_sm89_quantize_fp8_fixed` on the f16-rounded result
+    (kernels/sm89/encoder.cu:549-559; second output of layer_norm_pair :200-205)."""
+    return codec.quantize_fp8_fixed(layer_norm(x16, gamma16, beta16, rows), inv)
+
+
+def quant_rows_fp8_dynamic(y16, rows=None):
+    """Per-row dynamic E4M3 (kernels/sm89/encoder.cu:271-289): scale = absmax/448
+    (0 -> 1), byte = E4M3(v / scale); pad rows -> byte 0, scale 1."""
+    y = np.asarray(y16, dtype=F32)
+    rows = y.shape[0] if rows is None else rows
+    absmax = np.max(np.abs(y), axis=1)
+    scale = np.where(absmax > 0, absmax / F32(448.0), F32(1.0)).astype(F32)
+    q = codec.e4m3_encode((y / scale[:, None]).astype(F32))
+    q[rows:] = 0
+    scale[rows:] = 1
+    return q, scale
+
+
+def quant_rows_int8_dynamic(y16, rows=None):
+    """Per-row dynamic INT8: scale = absmax/127 (0 -> 1), q = clamp(rne(v/scale))."""
+    y = np.asarray(y16, dtype=F32)
+    rows = y.shape[0] if rows is None else rows
+    absmax = np.max(np.abs(y), axis=1)
+    scale = np.where(absmax > 0, absmax / F32(127.0), F32(1.0)).astype(F32)
+    q = np.clip(codec.rne((y / scale[:, None]).astype(F32)), -127, 127).astype(np.int8)
+    q[rows:] = 0
+    scale[rows:] = 1
+    return q, scale
+
+
+# ----------------------------------------------------------------------------
+# GEMM with the reference's epilogue algebra
+# ----------------------------------------------------------------------------
+
+def accumulate(a, b):
+    """acc[m,n] = sum_k a[m,k]*b[n,k] in float64 (exact for INT8/INT4 codes)."""
+    return np.asarray(a, dtype=np.float64) @ np.asarray(b, dtype=np.float64).T
+
+
+def epilogue(acc, row_scale=1.0, col_scales=None, bias=None, act=0,
+             residual16=None, alpha=1.0):
+    """value = acc*row_scale*col_scale (kernels/sm89/encoder.cu:973-976), + bias
+    (:980-983), activation 0 none / 1 SiLU / 2 ReLU (kernels/sm89/linear.cu:65-73),
+    residual `fmaf(alpha, value, f32(out))` (:993-999).  Returns fp32 (unrounded)."""
+    v = np.asarray(acc, dtype=np.float64).astype(F32)
+    rs = np.asarray(row_scale, dtype=F32)
+    if rs.ndim == 1:
+        rs = rs[:, None]
+    v = v * rs
+    if col_scales is not None:
+        v = v * np.asarray(col_scales, dtype=F32)[None, :]
+    if bias is not None:
+        v = v + np.asarray(bias, dtype=F32)[None, :]
+    if act == 1:
+        v = silu(v)
+    elif act == 2:
+        v = np.maximum(v, F32(0.0))
+    if residual16 is not None:
+        v = (F32(alpha) * v + np.asarray(residual16, dtype=F32)).astype(F32)
+    elif alpha != 1.0:
+        v = (F32(alpha) * v).astype(F32)
+    return v.astype(F32)
+
+
+def linear_f16(x16, w16, bias=None, act=0, residual16=None, alpha=1.0):
+    """FP16 linear, fp32 accumulate (kernels/sm89/linear.cu:83-171;
+    cuBLAS call sites src/cuda/cublas.rs:87-112)."""
+    return f16_round(epilogue(accumulate(x16, w16), 1.0, None, bias, act, residual16, alpha))
+
+
+def linear_fp8(xq, wq, w_scales, row_scale, bias=None, act=0, residual16=None, alpha=1.0):
+    """E4M3 x E4M3 linear (kernels/sm89/encoder.cu:787-1061 epilogues 0/2/3/4/6;
+    kernels/sm89/linear.cu:325-374)."""
+    acc = accumulate(codec.e4m3_decode(xq), codec.e4m3_decode(wq))
+    return f16_round(epilogue(acc, row_scale, w_scales, bias, act, residual16, alpha))
+
+
+def linear_int8(xq, wq, w_scales, row_scale, bias=None, act=0, residual16=None, alpha=1.0):
+    """S8 x S8 -> S32 exact, `act(acc*s_in*ws[n] + b[n])`
+    (kernels/sm89/linear.cu:378-429)."""
+    acc = accumulate(xq, wq)
+    return f16_round(epilogue(acc, row_scale, w_scales, bias, act, residual16, alpha))
+
+
+def linear_w4g128(x16, packed, scales16, bias=None, act=0, residual16=None, alpha=1.0):
+    """fp16 activations x INT4-g128 weights dequantised to fp16, fp32 accumulate."""
+    w16 = codec.dequant_int4_g128(packed, scales16)
+    return f16_round(epilogue(accumulate(x16, w16), 1.0, None, bias, act, residual16, alpha))
+
+
+# ----------------------------------------------------------------------------
+# FF block (benchmark configuration 1)
+# ----------------------------------------------------------------------------
+
+def tile_stats(h32, rows):
+    """max |a| (fp32, before any rounding) over each [128-row x 64-col] tile of
+    the SiLU output; rows >= `rows` do not contribute."""
+    m, n = h32.shape
+    mt = (m + SPARSE_TILE_ROWS - 1) // SPARSE_TILE_ROWS
+    a = np.zeros((mt * SPARSE_TILE_ROWS, n), dtype=F32)
+    a[:min(m, rows)] = np.abs(h32[:min(m, rows)])
+    return a.reshape(mt, SPARSE_TILE_ROWS, n // SPARSE_TILE_COLS, SPARSE_TILE_COLS).max(axis=(1, 3))
+
+
+def calibrate_tau(stats, zero_fraction=0.7):
+    """tau such that `zero_fraction` of the tiles have stat < tau: the midpoint
+    between the two order statistics that straddle the cut (robust to 1-ulp
+    differences between implementations)."""
+    s = np.sort(np.asarray(stats, dtype=F32).ravel())
+    cut = int(round(zero_fraction * s.size))
+    if cut <= 0:
+        return F32(0.0)
+    if cut >= s.size:
+        return F32(np.inf)
+    return F32((np.float64(s[cut - 1]) + np.float64(s[cut])) * 0.5)
+
+
+def ff_expand(xq, w1q, w1_scales, rows, tau, row_scale=FP8_INPUT_SCALE):
+    """FP8 GEMM 1024->4096 + SiLU + tile threshold + fixed INT8 quantisation.
+
+    h32 = SiLU(acc * (8/448) * ws[n]) (kernels/sm89/encoder.cu:973-1005, epilogue 0);
+    a tile whose max|h32| < tau is zeroed entirely and flagged 0 in the bitmap;
+    kept tiles are stored as clamp(rne(f32(f16(h32)) * 32), +-127).
+    Returns (hq int8 [M,4096], keep uint8 [ceil(M/128), 64], stats fp32)."""
+    acc = accumulate(codec.e4m3_decode(xq), codec.e4m3_decode(w1q))
+    h32 = epilogue(acc, row_scale, w1_scales, None, 1)
+    h32[rows:] = 0
+    stats = tile_stats(h32, rows)
+    keep = (stats >= F32(tau)).astype(np.uint8)
+    hq = codec.quantize_int8(f16_round(h32), INT8_HIDDEN_INV)
+    m = hq.shape[0]
+    mask = np.repeat(np.repeat(keep, SPARSE_TILE_ROWS, axis=0)[:m], SPARSE_TILE_COLS, axis=1)
+    hq = np.where(mask.astype(bool), hq, np.int8(0)).astype(np.int8)
+    return hq, keep, stats
+
+
+def ff_contract(hq, w2q, w2_scales, x16, alpha=0.5, row_scale=INT8_HIDDEN_SCALE):
+    """INT8 GEMM 4096->1024 with `out = f16(fma(0.5, acc*s_in*ws[n], x))`."""
+    return linear_int8(hq, w2q, w2_scales, row_scale, None, 0, x16, alpha)
+
+
+def ff_block(x16, gamma16, beta16, w1q, w1_scales, w2q, w2_scales, rows, tau):
+    xq = ln_quant_fp8_fixed(x16, gamma16, beta16, rows)
+    hq, keep, stats = ff_expand(xq, w1q, w1_scales, rows, tau)
+    y = ff_contract(hq, w2q, w2_scales, x16)
+    return y, dict(xq=xq, hq=hq, keep=keep, stats=stats)
+
+
+# ----------------------------------------------------------------------------
+# Local relative-position attention
+# ----------------------------------------------------------------------------
+
+def relative_position_encoding():
+    """`relative_position_encoding` (src/cuda/encoder.rs:2038-2054): row j encodes
+    relative position 128-j (rows >= 257 -> 0); sin at even, cos at odd feature."""
+    factor = -(np.log(10000.0) / MODEL_WIDTH)
+    out = np.zeros((POSITION_ROWS_PADDED, MODEL_WIDTH), dtype=F32)
+    pair = np.arange(MODEL_WIDTH // 2, dtype=np.float64)
+    freq = np.exp(2.0 * pair * factor)
+    for j in range(POSITION_ROWS_PADDED):
+        pos = float(ATT_LEFT - j) if j < POSITION_ROWS else 0.0
+        arg = pos * freq
+        out[j, 0::2] = np.sin(arg).astype(F32)
+        out[j, 1::2] = np.cos(arg).astype(F32)
+    return f16_round(out)
+
+
+def position_table(wpos16):
+    """P = sinusoid[272,1024] . Wpos^T as an fp16 linear, repacked head-major
+    [8, 272, 128] (src/cuda/encoder.rs:441-482; kernels/sm89/encoder.cu:1321-1336)."""
+    p = linear_f16(relative_position_encoding(), wpos16)          # [272, 1024]
+    return np.ascontiguousarray(
+        p.reshape(POSITION_ROWS_PADDED, HEADS, HEAD_WIDTH).transpose(1, 0, 2))
+
+
+def local_attention(q16, k16, v16, pos16, bias_u16, bias_v16, rows, valid_rows,
+                    left=ATT_LEFT, right=ATT_RIGHT):
+    """`pk_sm89_local_relpos_attention` (kernels/sm89/encoder.cu:1338-1461), the
+    plain fp16-input fp32-math definition of the op:
+      score[q,k] = ((Q_q+u).K_k + (Q_q+v).P[128-q+k]) / sqrt(128),
+      keys clipped to [max(0,q-128), min(valid-1,q+128)], fp32 softmax with max
+      subtraction, ctx = sum p.V, rows >= min(rows, valid) -> 0."""
+    q = np.asarray(q16, dtype=F32)
+    k = np.asarray(k16, dtype=F32)
+    v = np.asarray(v16, dtype=F32)
+    m = q.shape[0]
+    out = np.zeros((m, MODEL_WIDTH), dtype=F32)
+    nq = min(rows, valid_rows)
+    band = left + right + 1
+    qi = np.arange(nq)[:, None]
+    ki = qi - left + np.arange(band)[None, :]                      # [nq, band]
+    ok = (ki >= 0) & (ki < valid_rows)
+    kc = np.clip(ki, 0, max(valid_rows - 1, 0))
+    for h in range(HEADS):
+        sl = slice(h * HEAD_WIDTH, (h + 1) * HEAD_WIDTH)
+        qu = (q[:nq, sl] + np.asarray(bias_u16, dtype=F32)[h]).astype(np.float64)
+        qv = (q[:nq, sl] + np.asarray(bias_v16, dtype=F32)[h]).astype(np.float64)
+        kh = k[:, sl].astype(np.float64)
+        content = np.einsum("qd,qjd->qj", qu, kh[kc])
+        posit = qv @ np.asarray(pos16[h], dtype=np.float64)[:band].T
+        s = ((content + posit).astype(F32) * SOFTMAX_SCALE).astype(F32)
+        s = np.where(ok, s, -np.inf)
+        mx = s.max(axis=1, keepdims=True)
+        e = np.where(ok, np.exp(s - mx, dtype=F32), F32(0.0))
+        p = e / e.sum(axis=1, keepdims=True, dtype=F32)
+        out[:nq, sl] = np.einsum("qj,qjd->qd", p.astype(np.float64),
+                                 v[:, sl].astype(np.float64)[kc]).astype(F32)
+    return f16_round(out)
+
+
+# ----------------------------------------------------------------------------
+# Convolution module
+# ----------------------------------------------------------------------------
+
+def glu_masked(e16, rows, valid_rows):
+    """`pk_sm89_glu_masked` (kernels/sm89/encoder.cu:308-330): a * sigmoid(b)
+    written as value / (1 + expf(-gate)); rows >= rows|valid -> 0."""
+    e = np.asarray(e16, dtype=F32)
+    val, gate = e[:, :MODEL_WIDTH], e[:, MODEL_WIDTH:]
+    out = f16_round(val / (F32(1.0) + np.exp(-gate, dtype=F32)))
+    out[min(rows, valid_rows):] = 0
+    return out
+
+
+def depthwise_bn_silu(g16, wdw16, bn_gamma, bn_beta, bn_mean, bn_var, rows, eps=LN_EPS):
+    """`pk_sm89_depthwise_batchnorm_silu` (kernels/sm89/encoder.cu:1182-1233):
+    depthwise conv k=9 pad 4 over time (taps outside [0, rows) skipped), eval
+    BatchNorm, SiLU; rows >= rows -> 0."""
+    g = np.asarray(g16, dtype=F32)
+    m = g.shape[0]
+    w = np.asarray(wdw16, dtype=F32).reshape(MODEL_WIDTH, 9)
+    gp = np.zeros((m + 8, MODEL_WIDTH), dtype=F32)
+    gp[4:4 + rows] = g[:rows]
+    acc = np.zeros((m, MODEL_WIDTH), dtype=F32)
+    for t in range(9):
+        acc += gp[t:t + m] * w[:, t][None, :]
+    rstd = (F32(1.0) / np.sqrt(np.asarray(bn_var, dtype=F32) + F32(eps), dtype=F32)).astype(F32)
+    y = (acc - np.asarray(bn_mean, dtype=F32)) * rstd * np.asarray(bn_gamma, dtype=F32) \
+        + np.asarray(bn_beta, dtype=F32)
+    out = f16_round(silu(y))
+    out[rows:] = 0
+    return out
+
+
+# ----------------------------------------------------------------------------
+# Reference micro-benchmark operands
+# ----------------------------------------------------------------------------
+
+def reference_bench_operands(m, n, k):
+    """Inputs of the reference's linear benches: salts 17/29/43, amplitudes
+    0.125/0.03125/0.0625 (src/cuda.rs:780-807)."""
+    x = f16_round(codec.pattern_array(m * k, 17, 0.125).reshape(m, k))
+    w = f16_round(codec.pattern_array(n * k, 29, 0.03125).reshape(n, k))
+    b = codec.pattern_array(n, 43, 0.0625)
+    return x, w, b
