@@ -1,0 +1,53 @@
+"""GPU parity: local relative-position attention vs the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import codec, ops as O
+from tests.util import dev16, host
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(seed, rows):
+    rng = np.random.default_rng(seed)
+    q = codec.f16_round(rng.standard_normal((rows, 1024)))
+    k = codec.f16_round(rng.standard_normal((rows, 1024)))
+    v = codec.f16_round(rng.standard_normal((rows, 1024)))
+    wpos = codec.f16_round(rng.standard_normal((1024, 1024)) * 0.02)
+    u = codec.f16_round(rng.standard_normal((8, 128)) * 0.02)
+    bv = codec.f16_round(rng.standard_normal((8, 128)) * 0.02)
+    pos = O.position_table(wpos)
+    return q, k, v, pos, u, bv
+
+
+@pytest.mark.parametrize("rows,valid", [(304, 300), (40, 33), (752, 750)])
+def test_simple_kernel_matches_oracle(pk, cuda, rows, valid):
+    q, k, v, pos, u, bv = _case(rows, rows)
+    want = O.local_attention(q, k, v, pos, u, bv, rows, valid)
+    got = host(pk.ops.local_attention_simple(dev16(q), dev16(k), dev16(v), dev16(pos), dev16(u),
+                                             dev16(bv), valid_rows=valid))
+    assert np.all(got[valid:] == 0)
+    assert np.max(np.abs(got - want)) <= 3e-3
+
+
+def test_fused_qkv_strides_and_segments(pk, cuda):
+    seg, valid = 272, [272, 150]
+    q, k, v, pos, u, bv = _case(5, 2 * seg)
+    qkv = np.concatenate([q, k, v], axis=1)
+    t = dev16(qkv)
+    sv = torch.tensor(valid, dtype=torch.int32, device=cuda)
+    got = host(pk.ops.local_attention_simple(t[:, :1024], t[:, 1024:2048], t[:, 2048:], dev16(pos),
+                                             dev16(u), dev16(bv), seg_stride=seg, seg_valid=sv))
+    for s, val in enumerate(valid):
+        blk = slice(s * seg, (s + 1) * seg)
+        want = O.local_attention(q[blk], k[blk], v[blk], pos, u, bv, seg, val)
+        assert np.max(np.abs(got[blk] - want)) <= 3e-3
+        assert np.all(got[blk][val:] == 0)
+
+
+def test_pack_position_heads(pk, cuda):
+    rng = np.random.default_rng(6)
+    p = codec.f16_round(rng.standard_normal((272, 1024)))
+    got = host(pk.ops.pack_position_heads(dev16(p)))
+    assert np.array_equal(got, p.reshape(272, 8, 128).transpose(1, 0, 2))

@@ -1,0 +1,214 @@
+"""GPU parity: tcgen05 GEMM family through pk100_gemm vs the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import codec, ops as O
+from tests.util import dev, dev16, host, nrmse
+
+pytestmark = pytest.mark.gpu
+
+
+def _status(cuda):
+    return torch.zeros(1, dtype=torch.int32, device=cuda)
+
+
+def _f16_case(seed, m, n, k):
+    rng = np.random.default_rng(seed)
+    x = codec.f16_round(rng.standard_normal((m, k)))
+    w = codec.f16_round(rng.standard_normal((n, k)) * 0.02)
+    return x, w
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 256, 128), (200, 384, 1024),
+                                   (752, 1024, 1024), (33, 640, 1024), (1, 256, 64)])
+def test_f16_linear(pk, cuda, m, n, k):
+    L = pk.lib
+    x, w = _f16_case(m + n, m, n, k)
+    st = _status(cuda)
+    out = torch.zeros((m, n), dtype=torch.float16, device=cuda)
+    pk.ops.gemm(dev16(x), dev16(w), kind=L.KIND_F16, out=out, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0, "a bounded wait expired inside the GEMM"
+    want = O.linear_f16(x, w)
+    got = host(out)
+    # reference gate for FP16 linears: abs <= 0.02 (src/cuda.rs:821-861); ours is tighter
+    assert np.max(np.abs(got - want)) <= 4e-3, (np.max(np.abs(got - want)), nrmse(got, want))
+
+
+def test_f16_linear_reference_bench_operands_bias_residual_relu(pk, cuda):
+    # operands of the reference's own linear micro-benchmark (src/cuda.rs:780-818)
+    L = pk.lib
+    m, n, k = 256, 1024, 1024
+    x, w, b = O.reference_bench_operands(m, n, k)
+    rng = np.random.default_rng(0)
+    res = codec.f16_round(rng.standard_normal((m, n)))
+    st = _status(cuda)
+    out = dev16(res).clone()
+    pk.ops.gemm(dev16(x), dev16(w), kind=L.KIND_F16, out=out, bias=dev(b), act=L.ACT_RELU,
+                residual=out, alpha=0.5, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    want = O.linear_f16(x, w, bias=b, act=2, residual16=res, alpha=0.5)
+    assert np.max(np.abs(host(out) - want)) <= 4e-3
+
+
+@pytest.mark.parametrize("m", [750, 128, 77])
+def test_fp8_ff_expand_silu(pk, cuda, m):
+    # pk_sm89_ffn_expand_fp8_async (kernels/sm89/encoder.cu:1063-1069): fixed 8/448
+    # activation scale, per-row weight scales, SiLU, fp16 out
+    L = pk.lib
+    rng = np.random.default_rng(11)
+    x = codec.f16_round(rng.standard_normal((m, 1024)))
+    w = codec.f16_round(rng.standard_normal((4096, 1024)) * 0.02)
+    xq = codec.quantize_fp8_fixed(x, 56.0)
+    wq, ws = codec.quantize_rows_fp8(w)
+    st = _status(cuda)
+    out = torch.zeros((m, 4096), dtype=torch.float16, device=cuda)
+    pk.ops.gemm(dev(xq), dev(wq), kind=L.KIND_E4M3, out=out, row_scale=8.0 / 448.0,
+                col_scales=dev(ws), act=L.ACT_SILU, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    want = O.linear_fp8(xq, wq, ws, O.FP8_INPUT_SCALE, act=1)
+    got = host(out)
+    assert np.max(np.abs(got - want)) <= 4e-3, np.max(np.abs(got - want))
+
+
+def test_int8_linear_exact_accumulate(pk, cuda):
+    # pk_sm89_int8_linear_epilogue contract (kernels/sm89/linear.cu:378-429): the S32
+    # accumulator is exact, so an fp32 output with unit scales must match bit for bit
+    L = pk.lib
+    rng = np.random.default_rng(12)
+    m, n, k = 300, 512, 4096
+    a = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    st = _status(cuda)
+    out = torch.zeros((m, n), dtype=torch.float32, device=cuda)
+    pk.ops.gemm(dev(a), dev(b), kind=L.KIND_S8, out=out, out_type=L.OUT_F32, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    acc = O.accumulate(a, b)
+    assert np.array_equal(host(out), acc.astype(np.float32))
+
+
+def test_int8_linear_scales_bias_rowscales(pk, cuda):
+    L = pk.lib
+    rng = np.random.default_rng(13)
+    m, n, k = 200, 3072, 1024
+    x = codec.f16_round(rng.standard_normal((m, k)))
+    w = codec.f16_round(rng.standard_normal((n, k)) * 0.02)
+    xq, xs = O.quant_rows_int8_dynamic(x)
+    wq, ws = codec.quantize_rows_int8(w)
+    bias = (0.1 * rng.standard_normal(n)).astype(np.float32)
+    st = _status(cuda)
+    out = torch.zeros((m, n), dtype=torch.float16, device=cuda)
+    pk.ops.gemm(dev(xq), dev(wq), kind=L.KIND_S8, out=out, row_scales=dev(xs), col_scales=dev(ws),
+                bias=dev(bias), status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    want = O.linear_int8(xq, wq, ws, xs, bias=bias)
+    assert np.max(np.abs(host(out) - want)) <= 2e-3
+
+
+def test_fp8_glu_epilogue(pk, cuda):
+    # pk_sm89_conv_glu_fp8 (kernels/sm89/encoder.cu:1121-1127): per-row activation
+    # scales, value/gate pairing, pad-row mask
+    L = pk.lib
+    rng = np.random.default_rng(14)
+    m, valid = 300, 290
+    x = codec.f16_round(rng.standard_normal((m, 1024)))
+    w = codec.f16_round(rng.standard_normal((2048, 1024)) * 0.03)
+    xq, xs = O.quant_rows_fp8_dynamic(x)
+    wq, ws = codec.quantize_rows_fp8(w)
+    st = _status(cuda)
+    out = torch.zeros((m, 1024), dtype=torch.float16, device=cuda)
+    pk.ops.gemm(dev(xq), dev(wq), kind=L.KIND_E4M3, epilogue=L.EPI_GLU, out=out, row_scales=dev(xs),
+                col_scales=dev(ws), valid_rows=valid, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    e = O.linear_fp8(xq, wq, ws, xs)
+    want = O.glu_masked(e, m, valid)
+    got = host(out)
+    assert np.all(got[valid:] == 0)
+    assert np.max(np.abs(got - want)) <= 4e-3
+
+
+def test_fp8_residual_in_place(pk, cuda):
+    # epilogue 6 (kernels/sm89/encoder.cu:993-999): out = f16(fma(1, v, out))
+    L = pk.lib
+    rng = np.random.default_rng(15)
+    m = 260
+    x = codec.f16_round(rng.standard_normal((m, 1024)))
+    w = codec.f16_round(rng.standard_normal((1024, 1024)) * 0.02)
+    res = codec.f16_round(rng.standard_normal((m, 1024)))
+    xq, xs = O.quant_rows_fp8_dynamic(x)
+    wq, ws = codec.quantize_rows_fp8(w)
+    st = _status(cuda)
+    out = dev16(res).clone()
+    pk.ops.gemm(dev(xq), dev(wq), kind=L.KIND_E4M3, out=out, row_scales=dev(xs), col_scales=dev(ws),
+                residual=out, alpha=1.0, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    want = O.linear_fp8(xq, wq, ws, xs, residual16=res, alpha=1.0)
+    assert np.max(np.abs(host(out) - want)) <= 4e-3
+
+
+@pytest.mark.parametrize("m", [750, 130])
+def test_ff_block_config1(pk, cuda, m):
+    """Benchmark configuration 1: LN -> FP8 GEMM -> SiLU -> 70 % of the 128x64 tiles
+    zeroed -> INT8 GEMM (skipping them) -> x + 0.5 * y."""
+    L = pk.lib
+    rng = np.random.default_rng(1)
+    x = codec.f16_round(rng.standard_normal((m, 1024)))
+    gamma, beta = np.ones(1024, np.float32), np.zeros(1024, np.float32)
+    w1 = codec.f16_round(rng.standard_normal((4096, 1024)) * 0.02)
+    w2 = codec.f16_round(rng.standard_normal((1024, 4096)) * 0.02)
+    w1q, w1s = codec.quantize_rows_fp8(w1)
+    w2q, w2s = codec.quantize_rows_int8(w2)
+    # oracle pass 1: statistics -> tau for 70 % zero tiles
+    xq_o = O.ln_quant_fp8_fixed(x, gamma, beta, m)
+    _, _, stats = O.ff_expand(xq_o, w1q, w1s, m, 0.0)
+    tau = O.calibrate_tau(stats, 0.7)
+    want, mid = O.ff_block(x, gamma, beta, w1q, w1s, w2q, w2s, m, tau)
+    assert abs(mid["keep"].mean() - 0.3) < 0.02
+
+    xd = dev16(x)
+    xq, _ = pk.ops.layer_norm(xd, dev16(gamma), dev16(beta), L.LN_E4M3_FIXED, inv_scale=56.0)
+    mt = (m + 127) // 128
+    hq = torch.zeros((m, 4096), dtype=torch.int8, device=cuda)
+    keep = torch.zeros((mt, 64), dtype=torch.uint8, device=cuda)
+    stats_d = torch.zeros((mt, 64), dtype=torch.float32, device=cuda)
+    st = _status(cuda)
+    pk.ops.gemm(xq, dev(w1q), kind=L.KIND_E4M3, epilogue=L.EPI_SPARSE_OUT, out=hq, out_type=L.OUT_S8,
+                out_scale=32.0, row_scale=8.0 / 448.0, col_scales=dev(w1s), tau=float(tau),
+                keep_out=keep, stats_out=stats_d, status=st)
+    y = xd.clone()
+    pk.ops.gemm(hq, dev(w2q), kind=L.KIND_S8, out=y, row_scale=1.0 / 32.0, col_scales=dev(w2s),
+                residual=y, alpha=0.5, keep_in=keep, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert np.allclose(host(stats_d), mid["stats"], rtol=1e-4, atol=1e-6)
+    assert np.array_equal(host(keep), mid["keep"])
+    # INT8 hidden codes: equal except values sitting on a rounding boundary
+    hq_h = host(hq)
+    diff = hq_h != mid["hq"]
+    assert diff.mean() < 2e-3 and np.max(np.abs(hq_h.astype(int) - mid["hq"].astype(int))) <= 1
+    # second GEMM fed with the GPU's own codes is exact up to the fp32 epilogue
+    want_gpu_codes = O.ff_contract(hq_h, w2q, w2s, x)
+    got = host(y)
+    assert np.max(np.abs(got - want_gpu_codes)) <= 2e-3
+    assert nrmse(got, want) <= 1e-2
+
+
+def test_gemm_rejects_bad_arguments(pk, cuda):
+    L = pk.lib
+    a = torch.zeros((8, 24), dtype=torch.float16, device=cuda)     # k*2 = 48 bytes: ok; n bad below
+    b = torch.zeros((40, 24), dtype=torch.float16, device=cuda)
+    out = torch.zeros((8, 40), dtype=torch.float16, device=cuda)
+    with pytest.raises(L.Pk100Error):
+        pk.ops.gemm(a, b, kind=L.KIND_F16, out=out)                 # n % 32 != 0
+    a = torch.zeros((8, 20), dtype=torch.float16, device=cuda)     # k*2 = 40 bytes: not /16
+    b = torch.zeros((64, 20), dtype=torch.float16, device=cuda)
+    out = torch.zeros((8, 64), dtype=torch.float16, device=cuda)
+    with pytest.raises(L.Pk100Error):
+        pk.ops.gemm(a, b, kind=L.KIND_F16, out=out)
