@@ -1,0 +1,166 @@
+"""Launches the reference's own kernels (oracle/_ref/*.cubin) on the GPU.
+
+TEST INFRASTRUCTURE.  Restates the launch geometry of the reference's Rust host
+(src/cuda/encoder.rs launch_* helpers, src/cuda/decoder.rs:274-353) through the
+CUDA driver API (cuda-python), the same way cudarc does there: cuModuleLoadData
++ cuModuleGetFunction("pk_sm89_*") + cuLaunchKernel with positional arguments.
+torch provides device memory only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+from cuda.bindings import driver as cu
+
+REF_DIR = Path(__file__).resolve().parent / "_ref"
+
+
+def available() -> bool:
+    return all((REF_DIR / f"{u}.cubin").exists() for u in ("linear", "encoder", "decoder"))
+
+
+def _ok(res):
+    err = res[0]
+    if err != cu.CUresult.CUDA_SUCCESS:
+        raise RuntimeError(f"CUDA driver error {err}")
+    return res[1] if len(res) == 2 else res[1:]
+
+
+class Module:
+    def __init__(self, unit: str):
+        torch.cuda.init()
+        torch.zeros(1, device="cuda")                      # make the primary context current
+        data = (REF_DIR / f"{unit}.cubin").read_bytes()
+        self.module = _ok(cu.cuModuleLoadData(data))
+        self.functions = {}
+
+    def fn(self, name: str):
+        if name not in self.functions:
+            self.functions[name] = _ok(cu.cuModuleGetFunction(self.module, name.encode()))
+        return self.functions[name]
+
+    def launch(self, name, grid, block, smem, args, cooperative=False):
+        """args: list of torch tensors (device pointer), None (null pointer), int or float."""
+        vals, types = [], []
+        for a in args:
+            if a is None:
+                vals.append(0); types.append(C.c_void_p)
+            elif isinstance(a, torch.Tensor):
+                vals.append(a.data_ptr()); types.append(C.c_void_p)
+            elif isinstance(a, float):
+                vals.append(a); types.append(C.c_float)
+            else:
+                vals.append(int(a)); types.append(C.c_int)
+        f = self.fn(name)
+        if smem > 48 * 1024:
+            _ok(cu.cuFuncSetAttribute(
+                f, cu.CUfunction_attribute.CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, smem))
+        stream = torch.cuda.current_stream().cuda_stream
+        g = tuple(grid) + (1,) * (3 - len(grid))
+        b = tuple(block) + (1,) * (3 - len(block))
+        launch = cu.cuLaunchCooperativeKernel if cooperative else cu.cuLaunchKernel
+        if cooperative:
+            _ok(launch(f, g[0], g[1], g[2], b[0], b[1], b[2], smem, stream, (tuple(vals), tuple(types))))
+        else:
+            _ok(launch(f, g[0], g[1], g[2], b[0], b[1], b[2], smem, stream, (tuple(vals), tuple(types)), 0))
+
+
+_modules = {}
+
+
+def module(unit: str) -> Module:
+    if unit not in _modules:
+        _modules[unit] = Module(unit)
+    return _modules[unit]
+
+
+def _cdiv(a, b):
+    return (a + b - 1) // b
+
+
+# ---- encoder.cu -----------------------------------------------------------
+
+def layer_norm(x, gamma, beta, rows, padded_rows, eps=1e-5):
+    """launch_norm (src/cuda/encoder.rs:1361-1391): grid padded_rows x 256."""
+    out = torch.empty_like(x)
+    module("encoder").launch("pk_sm89_layer_norm", (padded_rows,), (256,), 0,
+                             [x, gamma, beta, out, rows, padded_rows, float(eps)])
+    return out
+
+
+def quantize_fp8_fixed(x, inverse_scale):
+    """launch_quantize_fp8 (src/cuda/encoder.rs:1267-1291)."""
+    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    n = x.numel()
+    module("encoder").launch("pk_sm89_quantize_fp8_fixed", (_cdiv(n, 256),), (256,), 0,
+                             [x, out, n, float(inverse_scale)])
+    return out
+
+
+def ffn_expand_fp8(xq, wq, w_scales, rows):
+    """launch_ffn_expand_fp8 (src/cuda/encoder.rs:1322-1358): grid (32, ceil(rows/128)) x 256,
+    32768 B dynamic shared memory, input_scale 8/448, dynamic_scale 0."""
+    out = torch.zeros((rows, 4096), dtype=torch.float16, device=xq.device)
+    module("encoder").launch("pk_sm89_ffn_expand_fp8_async", (32, _cdiv(rows, 128)), (256,), 32768,
+                             [xq, wq, w_scales, w_scales, out, rows, 8.0 / 448.0, 0])
+    return out
+
+
+def glu_masked(e, rows, padded_rows, valid_rows):
+    """launch_glu_arena (src/cuda/encoder.rs:1965-1997)."""
+    out = torch.empty((padded_rows, 1024), dtype=torch.float16, device=e.device)
+    module("encoder").launch("pk_sm89_glu_masked", (_cdiv(padded_rows * 1024, 256),), (256,), 0,
+                             [e, out, rows, padded_rows, valid_rows])
+    return out
+
+
+def depthwise_bn_silu(g, wdw, bn_g, bn_b, bn_m, bn_v, rows, padded_rows, eps=1e-5):
+    """launch_depthwise_arena (src/cuda/encoder.rs:1999-2036): grid ceil(padded/8)*4 x 256."""
+    out = torch.empty((padded_rows, 1024), dtype=torch.float16, device=g.device)
+    module("encoder").launch("pk_sm89_depthwise_batchnorm_silu", (_cdiv(padded_rows, 8) * 4,), (256,), 0,
+                             [g, wdw, bn_g, bn_b, bn_m, bn_v, out, rows, padded_rows, float(eps)])
+    return out
+
+
+def local_attention_scalar(q, k, v, pos, u, bv, rows, padded_rows, valid_rows):
+    """pk_sm89_local_relpos_attention (src/cuda/encoder.rs:1925-1961 geometry
+    (padded_rows, 8) x 32)."""
+    out = torch.empty((padded_rows, 1024), dtype=torch.float16, device=q.device)
+    module("encoder").launch("pk_sm89_local_relpos_attention", (padded_rows, 8), (32,), 0,
+                             [q, k, v, pos, u, bv, out, rows, padded_rows, valid_rows, 128, 128])
+    return out
+
+
+# ---- linear.cu ------------------------------------------------------------
+
+def fp16_linear(x, w, bias, residual, m, n, k, output_scale=1.0, residual_scale=0.0, activation=0):
+    """launch_linear_view (src/cuda.rs:698-768): grid (n/32, ceil(m/32)) x 64."""
+    out = torch.zeros((m, n), dtype=torch.float16, device=x.device)
+    module("linear").launch("pk_sm89_fp16_linear_epilogue", (n // 32, _cdiv(m, 32)), (64,), 0,
+                            [x, w, bias, residual, out, m, n, k, float(output_scale),
+                             float(residual_scale), activation])
+    return out
+
+
+# ---- decoder.cu -----------------------------------------------------------
+
+def tdt_decode(enc_proj, w, frames, sms):
+    """launch_decode (src/cuda/decoder.rs:274-353), short-request kernel: cooperative
+    grid 3*SMs x 128 (the reference sizes it with L4_SMS = 58 -> 174 CTAs; any grid
+    that is co-resident works).  `w` holds the decoder tensors."""
+    dev = enc_proj.device
+    workspace = torch.zeros(9360 + 16 + 2088, dtype=torch.float32, device=dev)
+    control = torch.zeros(8, dtype=torch.int32, device=dev)
+    tokens = torch.zeros(frames * 10 + 16, dtype=torch.int32, device=dev)
+    count = torch.zeros(1, dtype=torch.int32, device=dev)
+    grid = min(3 * 58, 3 * sms)
+    module("decoder").launch(
+        "pk_sm89_tdt_persistent_v2", (grid,), (128,), 0,
+        [enc_proj, w["embedding"], w["w_ih0"], w["w_hh0"], w["b_ih0"], w["b_hh0"], w["w_ih1"],
+         w["w_hh1"], w["b_ih1"], w["b_hh1"], w["w_pred"], w["b_pred"], w["w_joint"], w["b_joint"],
+         None, workspace, control, tokens, count, frames], cooperative=True)
+    torch.cuda.synchronize()
+    n = int(count.item())
+    return tokens[:n].cpu().numpy()
