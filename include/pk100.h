@@ -175,6 +175,71 @@ int pk100_local_relpos_attention_simple(void* stream, const void* query, int ldq
  * [272, 1024] -> head-major [8, 272, 128]. */
 int pk100_pack_position_heads(void* stream, const void* input, void* output);
 
+/* ------------------------------------------------------------------------
+ * Encoder layer sequencer -- the host side of one FastConformer block.
+ * Replaces LayerWeights (src/cuda/encoder.rs:530-601), LayerBuffers (:432-439)
+ * and run_layer / run_layers (:484-528, :604-1126).
+ *
+ * Precision map of this build (one table for every layer and every size; the
+ * reference switches kernels by row count, src/cuda/encoder.rs:618-633):
+ *   FF modules   LN -> E4M3 (x56) | W1 E4M3 per-row scales, SiLU, 128x64 tile
+ *                threshold tau, INT8 (x32) | W2 INT8 per-row scales, tile skip,
+ *                x += 0.5 * y
+ *   attention    LN -> INT8 per-row | Wqkv INT8 per-row scales -> fp16 Q|K|V
+ *                [rows, 3072] | local rel-pos attention fp16 | Wo INT4 group-128
+ *                dequantised to fp16, x += y
+ *   conv module  LN -> E4M3 per-row | Wpw1 E4M3 + GLU + pad mask | depthwise k=9
+ *                + BatchNorm + SiLU -> E4M3 per-row | Wpw2 E4M3, x += y
+ *   output       LayerNorm (fused with the next block's first LayerNorm)
+ */
+typedef struct pk100_ff_weights {
+    const void* ln_gamma;  const void* ln_beta;      /* fp16 [1024] */
+    const void* w1;        const float* w1_scales;   /* E4M3 [4096,1024], fp32 [4096] */
+    const void* w2;        const float* w2_scales;   /* S8 [1024,4096], fp32 [1024] */
+    float tau;                                       /* tile threshold on max|SiLU| */
+} pk100_ff_weights;
+
+typedef struct pk100_layer_weights {
+    pk100_ff_weights ff1;
+    const void* ln_att_gamma;  const void* ln_att_beta;
+    const void* wqkv;          const float* wqkv_scales;   /* S8 [3072,1024] rows Q|K|V */
+    const void* position;                                   /* fp16 [8,272,128] */
+    const void* bias_u;        const void* bias_v;          /* fp16 [8,128] */
+    const void* wo_f16;                                     /* fp16 [1024,1024] (dequantised INT4-g128) */
+    const void* ln_conv_gamma; const void* ln_conv_beta;
+    const void* wpw1;          const float* wpw1_scales;   /* E4M3 [2048,1024] */
+    const void* dw_weight;                                  /* fp16 [1024,9] */
+    const float* bn_gamma; const float* bn_beta; const float* bn_mean; const float* bn_var;
+    const void* wpw2;          const float* wpw2_scales;   /* E4M3 [1024,1024] */
+    pk100_ff_weights ff2;
+    const void* ln_out_gamma;  const void* ln_out_beta;
+} pk100_layer_weights;
+
+/* Caller-owned scratch for `rows` = segments * seg_stride rows.  Sizes in bytes:
+ * q8 rows*1024, row_scales rows*4, hidden8 rows*4096, keep ceil(rows/128)*64,
+ * qkv rows*3072*2, att rows*1024*2, glu rows*1024*2, dw8 rows*1024,
+ * dw_scales rows*4, status 4.  All 256-byte aligned. */
+typedef struct pk100_encoder_workspace {
+    void* q8; float* row_scales; void* hidden8; uint8_t* keep; void* qkv; void* att;
+    void* glu; void* dw8; float* dw_scales; int* status;
+} pk100_encoder_workspace;
+
+/* Bytes needed for one arena holding every field above. */
+long long pk100_encoder_workspace_bytes(int rows);
+/* Carves `base` (256-byte aligned, >= pk100_encoder_workspace_bytes(rows)). */
+int pk100_encoder_workspace_carve(void* base, int rows, pk100_encoder_workspace* out);
+
+/* Runs layers [0, n_layers).  state_a holds the input rows [rows,1024] fp16 and is
+ * updated in place (residual stream); layer i writes its output norm to state_b
+ * (i even) or state_a (i odd) and the next layer continues from there;
+ * *output receives the buffer that holds the final result.  tile_stats, when not
+ * NULL, receives max|SiLU| per 128x64 tile: [n_layers][2][ceil(rows/128)*64].
+ * attention_impl: 0 = tensor-core kernel, 1 = fp32 CUDA-core kernel. */
+int pk100_run_layers(void* stream, const pk100_layer_weights* layers, int n_layers, void* state_a,
+                     void* state_b, const pk100_encoder_workspace* ws, int segments,
+                     int seg_stride, int valid_rows, const int* seg_valid, float* tile_stats,
+                     int attention_impl, void** output);
+
 #ifdef __cplusplus
 }
 #endif

@@ -5,3 +5,5 @@ torch CUDA tensors (device memory and streams only -- no torch arithmetic).
 """
 from . import lib  # noqa: F401  (raises if libpk100.so is not built)
 from . import ops  # noqa: F401
+from . import encoder  # noqa: F401
+from . import synth  # noqa: F401

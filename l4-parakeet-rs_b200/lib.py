@@ -48,11 +48,16 @@ SIGNATURES = {
     "pk100_local_relpos_attention_simple": [vp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, i32,
                                             i32, i32, i32, vp],
     "pk100_pack_position_heads": [vp, vp, vp],
+    # struct-taking entry points: argtypes are completed in encoder.py / decoder.py
+    "pk100_encoder_workspace_bytes": None,
+    "pk100_encoder_workspace_carve": None,
+    "pk100_run_layers": None,
 }
 
 for _name, _argtypes in SIGNATURES.items():
     _fn = getattr(lib, _name)          # AttributeError here = header / library mismatch
-    _fn.argtypes = _argtypes
+    if _argtypes is not None:
+        _fn.argtypes = _argtypes
     _fn.restype = i32
 
 # enums (include/pk100.h)

@@ -175,17 +175,21 @@ def tile_stats(h32, rows):
     return a.reshape(mt, SPARSE_TILE_ROWS, n // SPARSE_TILE_COLS, SPARSE_TILE_COLS).max(axis=(1, 3))
 
 
-def calibrate_tau(stats, zero_fraction=0.7):
-    """tau such that `zero_fraction` of the tiles have stat < tau: the midpoint
-    between the two order statistics that straddle the cut (robust to 1-ulp
-    differences between implementations)."""
+def calibrate_tau(stats, zero_fraction=0.7, window=0.03):
+    """tau such that about `zero_fraction` of the tiles have stat < tau.  Among the
+    cuts within +-`window` of the target fraction the one with the widest relative gap
+    between neighbouring order statistics is taken and tau is the midpoint of that gap,
+    so the tile decisions do not depend on last-bit differences between implementations."""
     s = np.sort(np.asarray(stats, dtype=F32).ravel())
-    cut = int(round(zero_fraction * s.size))
-    if cut <= 0:
-        return F32(0.0)
-    if cut >= s.size:
-        return F32(np.inf)
-    return F32((np.float64(s[cut - 1]) + np.float64(s[cut])) * 0.5)
+    lo = max(1, int(round((zero_fraction - window) * s.size)))
+    hi = min(s.size - 1, int(round((zero_fraction + window) * s.size)))
+    if hi < lo:
+        return F32(0.0) if zero_fraction <= 0 else F32(np.inf)
+    cuts = np.arange(lo, hi + 1)
+    a, b = s[cuts - 1].astype(np.float64), s[cuts].astype(np.float64)
+    gap = (b - a) / np.maximum(b, 1e-30)
+    best = int(cuts[int(np.argmax(gap))])
+    return F32((np.float64(s[best - 1]) + np.float64(s[best])) * 0.5)
 
 
 def ff_expand(xq, w1q, w1_scales, rows, tau, row_scale=FP8_INPUT_SCALE):
@@ -326,3 +330,58 @@ def reference_bench_operands(m, n, k):
     w = f16_round(codec.pattern_array(n * k, 29, 0.03125).reshape(n, k))
     b = codec.pattern_array(n, 43, 0.0625)
     return x, w, b
+
+
+# ----------------------------------------------------------------------------
+# Whole encoder block with this build's precision map (one utterance)
+# ----------------------------------------------------------------------------
+
+def prepare_layer(w):
+    """fp16 layer tensors -> packed operands, the CPU twin of the load-time packing
+    (per-row rules: src/cuda/encoder.rs:385-411, src/cuda/quant_benchmark.rs:779-825)."""
+    p = dict(w)
+    for ff in ("ff1", "ff2"):
+        p[f"{ff}_w1q"], p[f"{ff}_w1s"] = codec.quantize_rows_fp8(w[f"{ff}_w1"])
+        p[f"{ff}_w2q"], p[f"{ff}_w2s"] = codec.quantize_rows_int8(w[f"{ff}_w2"])
+    wqkv = np.concatenate([w["wq"], w["wk"], w["wv"]], axis=0)
+    p["wqkv_q"], p["wqkv_s"] = codec.quantize_rows_int8(wqkv)
+    codes, gs = codec.quantize_int4_g128(w["wo"])
+    p["wo_codes"], p["wo_gs"] = codes, gs
+    p["wo16"] = codec.dequant_int4_g128(codes, gs)
+    p["pos"] = position_table(w["wpos"])
+    p["wpw1_q"], p["wpw1_s"] = codec.quantize_rows_fp8(w["wpw1"])
+    p["wpw2_q"], p["wpw2_s"] = codec.quantize_rows_fp8(w["wpw2"])
+    return p
+
+
+def ff_module(x16, p, ff, valid, tau, xq=None):
+    if xq is None:
+        xq = ln_quant_fp8_fixed(x16, p[f"ln_{ff}_g"], p[f"ln_{ff}_b"], valid)
+    hq, keep, stats = ff_expand(xq, p[f"{ff}_w1q"], p[f"{ff}_w1s"], valid, tau)
+    return ff_contract(hq, p[f"{ff}_w2q"], p[f"{ff}_w2s"], x16), stats, keep
+
+
+def encoder_layer(x16, p, valid, tau1, tau2, next_ln=None, collect=None):
+    """One FastConformer block on one utterance ([rows,1024], first `valid` rows live).
+    Returns (output norm, fp16) and, when `next_ln` = (gamma, beta) is given, also the
+    E4M3 bytes of the next block's first LayerNorm (the fused pair form)."""
+    x = np.asarray(x16, dtype=F32)
+    x, st1, _ = ff_module(x, p, "ff1", valid, tau1)
+    n2 = layer_norm(x, p["ln_att_g"], p["ln_att_b"], valid)
+    q8, qs = quant_rows_int8_dynamic(n2, valid)
+    qkv = linear_int8(q8, p["wqkv_q"], p["wqkv_s"], qs)
+    att = local_attention(qkv[:, :1024], qkv[:, 1024:2048], qkv[:, 2048:], p["pos"], p["bias_u"],
+                          p["bias_v"], valid, valid)
+    x = linear_f16(att, p["wo16"], residual16=x, alpha=1.0)
+    n3 = layer_norm(x, p["ln_conv_g"], p["ln_conv_b"], valid)
+    c8, cs = quant_rows_fp8_dynamic(n3, valid)
+    e = linear_fp8(c8, p["wpw1_q"], p["wpw1_s"], cs)
+    g = glu_masked(e, valid, valid)
+    d = depthwise_bn_silu(g, p["dw"], p["bn_g"], p["bn_b"], p["bn_m"], p["bn_v"], valid)
+    d8, ds = quant_rows_fp8_dynamic(d, valid)
+    x = linear_fp8(d8, p["wpw2_q"], p["wpw2_s"], ds, residual16=x, alpha=1.0)
+    x, st2, _ = ff_module(x, p, "ff2", valid, tau2)
+    out = layer_norm(x, p["ln_out_g"], p["ln_out_b"], valid)
+    if collect is not None:
+        collect.update(stats1=st1, stats2=st2, qkv=qkv, att=att, glu=g, dw=d, pre_norm=x)
+    return out

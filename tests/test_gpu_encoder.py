@@ -1,0 +1,163 @@
+"""GPU parity: whole FastConformer blocks through `pk100_run_layers` vs the CPU oracle.
+
+Tolerance (stated): normalised RMSE <= 1e-2 on every block output against the oracle that
+applies the same quantisation points; the reference's own gate for a layer stack is
+nRMSE <= 0.03 (src/cuda/encoder.rs:204-239)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import codec, ops as O
+from tests.util import dev16, host, nrmse
+
+pytestmark = pytest.mark.gpu
+
+
+def _input(seed, rows, valid):
+    rng = np.random.default_rng(seed)
+    x = codec.f16_round(rng.standard_normal((rows, 1024)))
+    x[valid:] = 0
+    return x
+
+
+def _oracle_layer_with_calibration(x, p, valid):
+    info = {}
+    O.encoder_layer(x, p, valid, 0.0, 0.0, collect=info)
+    tau1 = O.calibrate_tau(info["stats1"][: (valid + 127) // 128], 0.7)
+    O.encoder_layer(x, p, valid, tau1, 0.0, collect=info)
+    tau2 = O.calibrate_tau(info["stats2"][: (valid + 127) // 128], 0.7)
+    out = O.encoder_layer(x, p, valid, tau1, tau2, collect=info)
+    return out, tau1, tau2, info
+
+
+@pytest.mark.parametrize("rows,valid", [(304, 300), (128, 128)])
+def test_single_layer_single_utterance(pk, cuda, rows, valid):
+    w = pk.synth.layer_weights(3, 0, randomize_norms=True)
+    p = O.prepare_layer(w)
+    x = _input(1, rows, valid)
+    want, tau1, tau2, info = _oracle_layer_with_calibration(x, p, valid)
+
+    enc = pk.encoder.EncoderLayers(cuda)
+    enc.add_layer(w, tau1, tau2)
+    arena, ws = enc.make_workspace(rows)
+    a, b = dev16(x), torch.zeros((rows, 1024), dtype=torch.float16, device=cuda)
+    stats = torch.zeros((2, (rows + 127) // 128 * 64), dtype=torch.float32, device=cuda)
+    out = enc.run(a, b, ws, 1, rows, valid, tile_stats=stats)
+    torch.cuda.synchronize()
+    assert enc.status(arena, ws) == 0
+    got = host(out)
+    assert np.all(got[valid:] == 0)
+    st = host(stats).reshape(2, -1, 64)
+    assert np.allclose(st[0], info["stats1"], rtol=2e-3, atol=1e-5)
+    err = nrmse(got[:valid], want[:valid])
+    assert err <= 1e-2, err
+    assert np.max(np.abs(got - want)) <= 0.1
+
+
+def test_packed_weights_match_oracle(pk, cuda):
+    """Load-time packing on the GPU is bit-identical to the CPU twin, including the
+    position table (fp16 GEMM of the sinusoid) up to fp16 rounding."""
+    w = pk.synth.layer_weights(4, 1)
+    p = O.prepare_layer(w)
+    assert np.array_equal(pk.encoder.relative_position_encoding().astype(np.float32),
+                          O.relative_position_encoding())
+    enc = pk.encoder.EncoderLayers(cuda)
+    enc.add_layer(w)
+    by_ptr = {t.data_ptr(): t for t in enc.tensors}
+    lw = enc.layers[0]
+    assert np.array_equal(host(by_ptr[lw.ff1.w1]), p["ff1_w1q"])
+    assert np.array_equal(host(by_ptr[lw.ff1.w2_scales]), p["ff1_w2s"])
+    assert np.array_equal(host(by_ptr[lw.wqkv]), p["wqkv_q"])
+    assert np.array_equal(host(by_ptr[lw.wo_f16]), p["wo16"])
+    assert np.array_equal(host(by_ptr[lw.wpw1]), p["wpw1_q"])
+    pos = host(by_ptr[lw.position])
+    assert np.max(np.abs(pos - p["pos"])) <= 2e-3
+
+
+def _calibrate_over_utterances(xs, p, valids):
+    """One tau per FF module for a batch: oracle statistics of every utterance pooled."""
+    infos = [dict() for _ in xs]
+    for x, v, info in zip(xs, valids, infos):
+        O.encoder_layer(x, p, v, 0.0, 0.0, collect=info)
+    tau1 = O.calibrate_tau(np.concatenate([i["stats1"][: (v + 127) // 128] for i, v in zip(infos, valids)]), 0.7)
+    for x, v, info in zip(xs, valids, infos):
+        O.encoder_layer(x, p, v, tau1, 0.0, collect=info)
+    tau2 = O.calibrate_tau(np.concatenate([i["stats2"][: (v + 127) // 128] for i, v in zip(infos, valids)]), 0.7)
+    return float(tau1), float(tau2)
+
+
+def test_batched_ragged_utterances_match_per_utterance_oracle(pk, cuda):
+    seg_stride, valids = 256, [256, 170, 129]
+    w = pk.synth.layer_weights(5, 0, randomize_norms=True)
+    p = O.prepare_layer(w)
+    xs = [_input(10 + i, seg_stride, v) for i, v in enumerate(valids)]
+    tau1, tau2 = _calibrate_over_utterances(xs, p, valids)
+    enc = pk.encoder.EncoderLayers(cuda)
+    enc.add_layer(w, tau1, tau2)
+    rows = seg_stride * len(valids)
+    arena, ws = enc.make_workspace(rows)
+    a = dev16(np.concatenate(xs, axis=0))
+    b = torch.zeros_like(a)
+    sv = torch.tensor(valids, dtype=torch.int32, device=cuda)
+    out = host(enc.run(a, b, ws, len(valids), seg_stride, seg_stride, seg_valid=sv))
+    torch.cuda.synchronize()
+    assert enc.status(arena, ws) == 0
+    for i, v in enumerate(valids):
+        blk = out[i * seg_stride:(i + 1) * seg_stride]
+        want = O.encoder_layer(xs[i], p, v, tau1, tau2)
+        assert np.all(blk[v:] == 0)
+        assert nrmse(blk[:v], want[:v]) <= 1e-2
+
+
+def test_three_layer_stack_and_product_calibration(pk, cuda):
+    """Thresholds calibrated by the product; every layer's output is then held to 1e-2
+    against the oracle run on the SAME layer input (per-layer parity), and the free-running
+    stack to the reference's own layer-stack gate."""
+    rows, valid = 256, 250
+    ws_list = [pk.synth.layer_weights(6, l) for l in range(3)]
+    ps = [O.prepare_layer(w) for w in ws_list]
+    x = _input(20, rows, valid)
+    enc = pk.encoder.EncoderLayers(cuda)
+    for w in ws_list:
+        enc.add_layer(w)
+    arena, ws = enc.make_workspace(rows)
+    got = host(pk.encoder.calibrate_tile_thresholds(enc, dev16(x), ws, 1, rows, valid))
+    assert enc.status(arena, ws) == 0
+    # the calibrated thresholds drop ~70 % of the live tiles
+    info = {}
+    O.encoder_layer(x, ps[0], valid, enc.layers[0].ff1.tau, enc.layers[0].ff2.tau, collect=info)
+    assert abs((info["stats1"] < enc.layers[0].ff1.tau).mean() - 0.7) < 0.05
+    # per-layer parity on identical inputs
+    cur = x
+    for l, p in enumerate(ps):
+        a, b = dev16(cur), torch.zeros((rows, 1024), dtype=torch.float16, device=cuda)
+        layer_out = host(enc.run(a, b, ws, 1, rows, valid, first=l, count=1))
+        want = O.encoder_layer(cur, p, valid, enc.layers[l].ff1.tau, enc.layers[l].ff2.tau)
+        assert nrmse(layer_out[:valid], want[:valid]) <= 1e-2, l
+        cur = layer_out
+    # one call over all layers equals the layer-by-layer runs bit for bit
+    a, b = dev16(x), torch.zeros((rows, 1024), dtype=torch.float16, device=cuda)
+    again = host(enc.run(a, b, ws, 1, rows, valid))
+    assert np.array_equal(again, cur)
+    assert np.array_equal(again, got)
+
+
+def test_three_layer_stack_dense_hidden(pk, cuda):
+    """Free-running stack with the tile threshold off (tau = 0, a continuous operator):
+    rounding noise is re-amplified at every E4M3 / INT8 quantisation point (a 1-ulp fp16
+    difference that crosses a code boundary becomes a 6 % step), so stacks are held to the
+    reference's own layer-stack gate, nRMSE <= 0.03 (src/cuda/encoder.rs:204-239)."""
+    rows, valid = 256, 250
+    ws_list = [pk.synth.layer_weights(7, l, randomize_norms=True) for l in range(3)]
+    x = _input(21, rows, valid)
+    enc = pk.encoder.EncoderLayers(cuda)
+    for w in ws_list:
+        enc.add_layer(w, 0.0, 0.0)
+    arena, ws = enc.make_workspace(rows)
+    a, b = dev16(x), torch.zeros((rows, 1024), dtype=torch.float16, device=cuda)
+    got = host(enc.run(a, b, ws, 1, rows, valid))
+    assert enc.status(arena, ws) == 0
+    cur = x
+    for w in ws_list:
+        cur = O.encoder_layer(cur, O.prepare_layer(w), valid, 0.0, 0.0)
+    assert nrmse(got[:valid], cur[:valid]) <= 3e-2

@@ -170,7 +170,7 @@ def test_ff_block_config1(pk, cuda, m):
     _, _, stats = O.ff_expand(xq_o, w1q, w1s, m, 0.0)
     tau = O.calibrate_tau(stats, 0.7)
     want, mid = O.ff_block(x, gamma, beta, w1q, w1s, w2q, w2s, m, tau)
-    assert abs(mid["keep"].mean() - 0.3) < 0.02
+    assert abs(mid["keep"].mean() - 0.3) < 0.04
 
     xd = dev16(x)
     xq, _ = pk.ops.layer_norm(xd, dev16(gamma), dev16(beta), L.LN_E4M3_FIXED, inv_scale=56.0)
