@@ -240,6 +240,41 @@ int pk100_run_layers(void* stream, const pk100_layer_weights* layers, int n_laye
                      int seg_stride, int valid_rows, const int* seg_valid, float* tile_stats,
                      int attention_impl, void** output);
 
+/* ------------------------------------------------------------------------
+ * TDT greedy decoder.  Replaces DecoderWeights (src/cuda/decoder.rs:227-271),
+ * launch_decode (:274-353) and the persistent kernels pk_sm89_tdt_persistent_v2
+ * / _fp8_ih (kernels/sm89/decoder.cu:165-447, :452-784) for a BATCH of
+ * utterances.  `layers` is 1 or 2 LSTM layers (the reference model has 2).
+ * The encoder projection (enc_proj = state . W_enc^T + b, fp16 [rows, 640]) is
+ * an ordinary pk100_gemm call made by the caller, as in decoder.rs:298-313.
+ */
+#define PK100_DECODER_MAX_UTTERANCES 8
+
+typedef struct pk100_decoder_weights {
+    int layers;
+    const void* embedding;                 /* fp16 [1025, 640] */
+    const void* w_ih[2]; const void* w_hh[2];   /* fp16 [2560, 640], gate order i f g o */
+    const float* b_ih[2]; const float* b_hh[2]; /* fp32 [2560] */
+    const void* w_pred; const float* b_pred;    /* fp16 [640, 640], fp32 [640] */
+    const void* w_joint; const float* b_joint;  /* fp16 [1030, 640], fp32 [1030]: 1025 tokens + 5 durations */
+} pk100_decoder_weights;
+
+/* Scratch bytes for `utterances` (<= PK100_DECODER_MAX_UTTERANCES); 0 if out of range. */
+long long pk100_tdt_workspace_bytes(int utterances);
+
+/* Decodes `utterances` sequences in lockstep.  enc_proj rows of utterance u start at
+ * u * seg_stride; frames[u] (device int array) frames are consumed.  tokens /
+ * durations: [utterances, max_tokens] int32 (durations may be NULL), counts:
+ * [utterances].  workspace: >= pk100_tdt_workspace_bytes(utterances), 256-byte
+ * aligned; it is cleared by the call.  *status (device int, may be NULL) becomes 2 if
+ * a bounded grid barrier expired.  Token rule: highest joint score, ties to the lower
+ * id; duration: first strict maximum of 5 logits; at most 10 symbols per frame; blank
+ * (1024) never updates the prediction network (kernels/sm89/decoder.cu:35-46, :416-445). */
+int pk100_tdt_decode(void* stream, const pk100_decoder_weights* weights, const void* enc_proj,
+                     int utterances, int seg_stride, const int* frames, void* workspace,
+                     int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                     int* status);
+
 #ifdef __cplusplus
 }
 #endif

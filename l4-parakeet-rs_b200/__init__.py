@@ -7,3 +7,4 @@ from . import lib  # noqa: F401  (raises if libpk100.so is not built)
 from . import ops  # noqa: F401
 from . import encoder  # noqa: F401
 from . import synth  # noqa: F401
+from . import decoder  # noqa: F401

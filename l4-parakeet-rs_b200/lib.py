@@ -52,6 +52,8 @@ SIGNATURES = {
     "pk100_encoder_workspace_bytes": None,
     "pk100_encoder_workspace_carve": None,
     "pk100_run_layers": None,
+    "pk100_tdt_workspace_bytes": None,
+    "pk100_tdt_decode": None,
 }
 
 for _name, _argtypes in SIGNATURES.items():
