@@ -275,6 +275,31 @@ int pk100_tdt_decode(void* stream, const pk100_decoder_weights* weights, const v
                      int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
                      int* status);
 
+/* ------------------------------------------------------------------------
+ * 8x convolution subsampling for a batch of utterances: mel fp32
+ * [utterances, frames, 128] -> fp16 rows [utterances * seg_stride, 1024].
+ * Replaces run_subsampling (src/cuda/subsampling.rs:436-804) and
+ * pk_sm89_subsample_first / _depthwise / _flatten
+ * (kernels/sm89/subsampling.cu:11-226); the pointwise layers and the projection
+ * are pk100_gemm calls (fp16, bias, ReLU) like launch_linear_view there.
+ * mel_frames (device int [utterances], may be NULL = `frames` for all) gives each
+ * utterance's true frame count; utterance u yields ceil(ceil(ceil(f/2)/2)/2) rows,
+ * the remaining rows of its block are "don't care" (every consumer masks them). */
+typedef struct pk100_subsampling_weights {
+    const void* conv0_w; const void* conv0_b;   /* fp16 [256,9] (3x3), fp16 [256] */
+    const void* dw1_w;   const void* dw1_b;     /* fp16 [256,9], fp16 [256] */
+    const void* pw1_w;   const float* pw1_b;    /* fp16 [256,256], fp32 [256] */
+    const void* dw2_w;   const void* dw2_b;
+    const void* pw2_w;   const float* pw2_b;
+    const void* proj_w;  const float* proj_b;   /* fp16 [1024,4096], fp32 [1024] */
+} pk100_subsampling_weights;
+
+long long pk100_subsampling_workspace_bytes(int utterances, int frames, int seg_stride);
+
+int pk100_run_subsampling(void* stream, const pk100_subsampling_weights* weights, const float* mel,
+                          int utterances, int frames, const int* mel_frames, void* workspace,
+                          void* output, int seg_stride, int* status);
+
 #ifdef __cplusplus
 }
 #endif

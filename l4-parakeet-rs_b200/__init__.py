@@ -8,3 +8,4 @@ from . import ops  # noqa: F401
 from . import encoder  # noqa: F401
 from . import synth  # noqa: F401
 from . import decoder  # noqa: F401
+from . import subsampling  # noqa: F401

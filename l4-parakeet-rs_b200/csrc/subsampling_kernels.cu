@@ -1,0 +1,214 @@
+// 8x depthwise-striding convolution subsampling (mel [frames,128] -> [frames/8, 1024])
+// for a batch of utterances.  The convolutions are simple channel-parallel kernels
+// (thread = channel, coalesced over the 256 channels); the two pointwise layers and
+// the 4096 -> 1024 projection are tcgen05 GEMMs (pk100_gemm).  Semantics follow
+// kernels/sm89/subsampling.cu:11-226 and the host tiling of
+// src/cuda/subsampling.rs:436-804 (without its 256-frame tiles: the whole batch is
+// processed at once).
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "pk100_internal.h"
+
+namespace pk100 {
+
+constexpr int kChannels = 256;
+constexpr int kMelBins = 128;
+constexpr int kGroup = 8;
+
+__device__ __forceinline__ int frames_of(const int* per_utt, int utt, int uniform) {
+    return per_utt != nullptr ? per_utt[utt] : uniform;
+}
+
+// conv 3x3, stride 2, pad 1, 1 -> 256 channels, + bias, ReLU.
+// in  [utt][in_stride frames][128] fp32;  out [utt][out_frames_cap][64][256] fp16
+__global__ void __launch_bounds__(256)
+subsample_first_kernel(const float* __restrict__ in, const __half* __restrict__ w,
+                       const __half* __restrict__ b, __half* __restrict__ out, int in_stride,
+                       int in_frames_uniform, const int* __restrict__ in_frames_per_utt,
+                       int out_frames_cap) {
+    const int ch = threadIdx.x;
+    const int feat0 = blockIdx.x * kGroup;
+    const int of = blockIdx.y;
+    const int utt = blockIdx.z;
+    const int in_frames = frames_of(in_frames_per_utt, utt, in_frames_uniform);
+    const int out_frames = (in_frames + 1) / 2;
+    if (of >= out_frames) return;
+    const float* src = in + static_cast<size_t>(utt) * in_stride * kMelBins;
+    float wk[9];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) wk[i] = __half2float(w[ch * 9 + i]);
+    const float bias = __half2float(b[ch]);
+    float sums[kGroup];
+#pragma unroll
+    for (int g = 0; g < kGroup; ++g) sums[g] = bias;
+#pragma unroll
+    for (int kf = 0; kf < 3; ++kf) {
+        const int f = of * 2 + kf - 1;
+        if (f < 0 || f >= in_frames) continue;
+#pragma unroll
+        for (int kt = 0; kt < 3; ++kt) {
+#pragma unroll
+            for (int g = 0; g < kGroup; ++g) {
+                const int t = (feat0 + g) * 2 + kt - 1;
+                if (t >= 0 && t < kMelBins)
+                    sums[g] = fmaf(src[static_cast<size_t>(f) * kMelBins + t], wk[kf * 3 + kt], sums[g]);
+            }
+        }
+    }
+    __half* dst = out + ((static_cast<size_t>(utt) * out_frames_cap + of) * 64 + feat0) * kChannels + ch;
+#pragma unroll
+    for (int g = 0; g < kGroup; ++g) dst[g * kChannels] = __float2half_rn(fmaxf(sums[g], 0.0f));
+}
+
+// depthwise conv 3x3, stride 2, pad 1, + bias (no activation).
+// in [utt][in_cap][in_feats][256] -> out [utt][out_cap][in_feats/2][256]
+__global__ void __launch_bounds__(256)
+subsample_depthwise_kernel(const __half* __restrict__ in, const __half* __restrict__ w,
+                           const __half* __restrict__ b, __half* __restrict__ out, int in_cap,
+                           int in_feats, int out_cap, int mel_frames_uniform,
+                           const int* __restrict__ mel_frames_per_utt, int in_level) {
+    const int ch = threadIdx.x;
+    const int out_feats = in_feats / 2;
+    const int feat0 = blockIdx.x * kGroup;
+    const int of = blockIdx.y;
+    const int utt = blockIdx.z;
+    int in_frames = frames_of(mel_frames_per_utt, utt, mel_frames_uniform);
+    for (int l = 0; l < in_level; ++l) in_frames = (in_frames + 1) / 2;
+    const int out_frames = (in_frames + 1) / 2;
+    if (of >= out_frames || feat0 >= out_feats) return;
+    float wk[9];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) wk[i] = __half2float(w[ch * 9 + i]);
+    const float bias = __half2float(b[ch]);
+    float sums[kGroup];
+#pragma unroll
+    for (int g = 0; g < kGroup; ++g) sums[g] = bias;
+    const __half* src = in + static_cast<size_t>(utt) * in_cap * in_feats * kChannels + ch;
+#pragma unroll
+    for (int kf = 0; kf < 3; ++kf) {
+        const int f = of * 2 + kf - 1;
+        if (f < 0 || f >= in_frames) continue;
+#pragma unroll
+        for (int kt = 0; kt < 3; ++kt) {
+#pragma unroll
+            for (int g = 0; g < kGroup; ++g) {
+                const int t = (feat0 + g) * 2 + kt - 1;
+                if (feat0 + g < out_feats && t >= 0 && t < in_feats)
+                    sums[g] = fmaf(__half2float(src[(static_cast<size_t>(f) * in_feats + t) * kChannels]),
+                                   wk[kf * 3 + kt], sums[g]);
+            }
+        }
+    }
+    __half* dst = out + ((static_cast<size_t>(utt) * out_cap + of) * out_feats + feat0) * kChannels + ch;
+#pragma unroll
+    for (int g = 0; g < kGroup; ++g)
+        if (feat0 + g < out_feats) dst[g * kChannels] = __float2half_rn(sums[g]);
+}
+
+// [utt][cap][16][256] -> rows [utt*seg_stride + frame][channel*16 + feature]; rows at or
+// beyond the utterance's output length are zero (kernels/sm89/subsampling.cu:202-226).
+__global__ void __launch_bounds__(256)
+subsample_flatten_kernel(const __half* __restrict__ in, __half* __restrict__ out, int in_cap,
+                         int seg_stride, int mel_frames_uniform,
+                         const int* __restrict__ mel_frames_per_utt) {
+    __shared__ __half tile[16][kChannels + 2];
+    const int frame = blockIdx.x, utt = blockIdx.y, tid = threadIdx.x;
+    int valid = frames_of(mel_frames_per_utt, utt, mel_frames_uniform);
+    for (int l = 0; l < 3; ++l) valid = (valid + 1) / 2;
+    __half* dst = out + (static_cast<size_t>(utt) * seg_stride + frame) * 4096;
+    if (frame >= valid) {
+        for (int i = tid; i < 4096 / 8; i += 256) reinterpret_cast<uint4*>(dst)[i] = make_uint4(0, 0, 0, 0);
+        return;
+    }
+    const __half* src = in + (static_cast<size_t>(utt) * in_cap + frame) * 16 * kChannels;
+#pragma unroll
+    for (int f = 0; f < 16; ++f) tile[f][tid] = src[f * kChannels + tid];
+    __syncthreads();
+    for (int i = tid; i < 4096; i += 256) dst[i] = tile[i % 16][i / 16];
+}
+
+}  // namespace pk100
+
+using namespace pk100;
+
+namespace {
+long long up256(long long v) { return (v + 255) / 256 * 256; }
+struct Caps { int f1, f2, f3; };
+Caps caps(int frames) {
+    Caps c;
+    c.f1 = (frames + 1) / 2;
+    c.f2 = (c.f1 + 1) / 2;
+    c.f3 = (c.f2 + 1) / 2;
+    return c;
+}
+}  // namespace
+
+extern "C" long long pk100_subsampling_workspace_bytes(int utterances, int frames, int seg_stride) {
+    if (utterances <= 0 || frames <= 0 || seg_stride <= 0) return 0;
+    const Caps c = caps(frames);
+    const long long u = utterances;
+    return up256(u * c.f1 * 64 * 256 * 2) + 2 * up256(u * c.f2 * 32 * 256 * 2) +
+           2 * up256(u * c.f3 * 16 * 256 * 2) + up256(u * seg_stride * 4096LL * 2) + 256;
+}
+
+extern "C" int pk100_run_subsampling(void* stream_v, const pk100_subsampling_weights* w,
+                                     const float* mel, int utterances, int frames,
+                                     const int* mel_frames, void* workspace, void* output,
+                                     int seg_stride, int* status) {
+    if (!w || !mel || !workspace || !output) return PK100_ERR_NULL;
+    if (!w->conv0_w || !w->conv0_b || !w->dw1_w || !w->dw1_b || !w->pw1_w || !w->pw1_b || !w->dw2_w ||
+        !w->dw2_b || !w->pw2_w || !w->pw2_b || !w->proj_w || !w->proj_b)
+        return PK100_ERR_NULL;
+    if (utterances == 0) return PK100_OK;
+    if (utterances < 0 || frames <= 0) return PK100_ERR_SHAPE;
+    const Caps c = caps(frames);
+    if (seg_stride < c.f3) return PK100_ERR_SHAPE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return PK100_ERR_ALIGN;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const long long u = utterances;
+    char* p = static_cast<char*>(workspace);
+    auto take = [&p](long long bytes) { char* cur = p; p += up256(bytes); return cur; };
+    __half* s1 = reinterpret_cast<__half*>(take(u * c.f1 * 64 * 256 * 2));
+    __half* s2 = reinterpret_cast<__half*>(take(u * c.f2 * 32 * 256 * 2));
+    __half* s3 = reinterpret_cast<__half*>(take(u * c.f2 * 32 * 256 * 2));
+    __half* s4 = reinterpret_cast<__half*>(take(u * c.f3 * 16 * 256 * 2));
+    __half* s5 = reinterpret_cast<__half*>(take(u * c.f3 * 16 * 256 * 2));
+    __half* flat = reinterpret_cast<__half*>(take(u * seg_stride * 4096LL * 2));
+
+    subsample_first_kernel<<<dim3(64 / kGroup, c.f1, utterances), 256, 0, stream>>>(
+        mel, static_cast<const __half*>(w->conv0_w), static_cast<const __half*>(w->conv0_b), s1, frames,
+        frames, mel_frames, c.f1);
+    int rc = pk100_launch_status();
+    if (rc != PK100_OK) return rc;
+    subsample_depthwise_kernel<<<dim3(32 / kGroup, c.f2, utterances), 256, 0, stream>>>(
+        s1, static_cast<const __half*>(w->dw1_w), static_cast<const __half*>(w->dw1_b), s2, c.f1, 64,
+        c.f2, frames, mel_frames, 1);
+    if ((rc = pk100_launch_status()) != PK100_OK) return rc;
+
+    pk100_gemm_args a{};
+    a.kind = PK100_KIND_F16; a.epilogue = PK100_EPI_LINEAR;
+    a.m = static_cast<int>(u * c.f2 * 32); a.n = 256; a.k = 256;
+    a.a = s2; a.lda = 256; a.b = w->pw1_w; a.ldb = 256;
+    a.row_scale = 1.0f; a.alpha = 1.0f; a.bias = w->pw1_b; a.act = PK100_ACT_RELU;
+    a.out = s3; a.ld_out = 256; a.out_type = PK100_OUT_F16; a.out_scale = 1.0f; a.status = status;
+    if ((rc = pk100_gemm(stream, &a)) != PK100_OK) return rc;
+
+    subsample_depthwise_kernel<<<dim3(16 / kGroup, c.f3, utterances), 256, 0, stream>>>(
+        s3, static_cast<const __half*>(w->dw2_w), static_cast<const __half*>(w->dw2_b), s4, c.f2, 32,
+        c.f3, frames, mel_frames, 2);
+    if ((rc = pk100_launch_status()) != PK100_OK) return rc;
+
+    a.m = static_cast<int>(u * c.f3 * 16);
+    a.a = s4; a.b = w->pw2_w; a.bias = w->pw2_b; a.out = s5;
+    if ((rc = pk100_gemm(stream, &a)) != PK100_OK) return rc;
+
+    subsample_flatten_kernel<<<dim3(seg_stride, utterances), 256, 0, stream>>>(
+        s5, flat, c.f3, seg_stride, frames, mel_frames);
+    if ((rc = pk100_launch_status()) != PK100_OK) return rc;
+
+    a.m = static_cast<int>(u * seg_stride); a.n = 1024; a.k = 4096;
+    a.a = flat; a.lda = 4096; a.b = w->proj_w; a.ldb = 4096; a.bias = w->proj_b; a.act = PK100_ACT_NONE;
+    a.out = output; a.ld_out = 1024;
+    return pk100_gemm(stream, &a);
+}

@@ -54,6 +54,8 @@ SIGNATURES = {
     "pk100_run_layers": None,
     "pk100_tdt_workspace_bytes": None,
     "pk100_tdt_decode": None,
+    "pk100_subsampling_workspace_bytes": None,
+    "pk100_run_subsampling": None,
 }
 
 for _name, _argtypes in SIGNATURES.items():

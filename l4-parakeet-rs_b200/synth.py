@@ -58,3 +58,33 @@ def layer_weights(seed: int, layer: int, randomize_norms: bool = False, std: flo
 def mel_input(seed: int, frames: int = 6000, bins: int = 128):
     """Seeded Gaussian log-mel stand-in [frames, 128] fp32."""
     return torch.randn((frames, bins), generator=_gen(seed)).numpy().astype(np.float32)
+
+
+def subsampling_weights(seed: int, std: float = 0.02):
+    """Shapes of `pre_encode` in the manifest (src/weights.rs:552-568).  The 3x3 taps are
+    drawn wider than the linears so that activations keep a usable dynamic range."""
+    g = _gen(seed * 1000 + 900)
+    w = {"conv0_w": _normal(g, (256, 9), 0.3), "conv0_b": _normal(g, (256,), 0.1)}
+    for stage in (1, 2):
+        w[f"dw{stage}_w"] = _normal(g, (256, 9), 0.3)
+        w[f"dw{stage}_b"] = _normal(g, (256,), 0.1)
+        w[f"pw{stage}_w"] = _normal(g, (256, 256), 0.06)
+        w[f"pw{stage}_b"] = (torch.randn(256, generator=g) * 0.05).numpy().astype(np.float32)
+    w["proj_w"] = _normal(g, (1024, 4096), std)
+    w["proj_b"] = (torch.randn(1024, generator=g) * 0.05).numpy().astype(np.float32)
+    return w
+
+
+def decoder_weights(seed: int, layers: int = 2, std: float = 0.05):
+    """Decoder / joint tensors (src/weights.rs:526-550, :633-644)."""
+    g = _gen(seed * 1000 + 950)
+    w = {"layers": layers, "embedding": _normal(g, (1025, 640), 0.2),
+         "w_pred": _normal(g, (640, 640), std), "b_pred": (torch.randn(640, generator=g) * std).numpy(),
+         "w_joint": _normal(g, (1030, 640), std), "b_joint": (torch.randn(1030, generator=g) * std).numpy(),
+         "w_enc": _normal(g, (640, 1024), std), "b_enc": (torch.randn(640, generator=g) * std).numpy()}
+    for l in range(layers):
+        w[f"w_ih{l}"] = _normal(g, (2560, 640), std)
+        w[f"w_hh{l}"] = _normal(g, (2560, 640), std)
+        w[f"b_ih{l}"] = (torch.randn(2560, generator=g) * std).numpy()
+        w[f"b_hh{l}"] = (torch.randn(2560, generator=g) * std).numpy()
+    return {k: (v.astype(np.float32) if isinstance(v, np.ndarray) else v) for k, v in w.items()}

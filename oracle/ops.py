@@ -385,3 +385,37 @@ def encoder_layer(x16, p, valid, tau1, tau2, next_ln=None, collect=None):
     if collect is not None:
         collect.update(stats1=st1, stats2=st2, qkv=qkv, att=att, glu=g, dw=d, pre_norm=x)
     return out
+
+
+# ----------------------------------------------------------------------------
+# 8x convolution subsampling (one utterance)
+# ----------------------------------------------------------------------------
+
+def _conv_s2(x, w, b):
+    """3x3 stride-2 pad-1 convolution over (frame, feature) with per-channel taps:
+    x [F, T, C] (C = 1 broadcasts), w [256, 3, 3], b [256]; fp32 accumulate in the
+    reference's tap order (kernels/sm89/subsampling.cu:37-58, :100-124)."""
+    f_in, t_in, _ = x.shape
+    f_out, t_out = (f_in + 1) // 2, (t_in + 1) // 2
+    xp = np.zeros((2 * f_out + 2, 2 * t_out + 2, x.shape[2]), dtype=F32)
+    xp[1:1 + f_in, 1:1 + t_in] = x
+    acc = np.broadcast_to(np.asarray(b, dtype=F32), (f_out, t_out, 256)).copy()
+    for kf in range(3):
+        for kt in range(3):
+            acc += xp[kf:kf + 2 * f_out:2, kt:kt + 2 * t_out:2] * np.asarray(w, dtype=F32)[:, kf, kt]
+    return acc
+
+
+def subsampling(mel, w):
+    """mel fp32 [frames, 128] -> fp16 [ceil(frames/8), 1024]
+    (src/cuda/subsampling.rs:436-804 without the 256-frame tiling, which only bounds
+    memory; kernels/sm89/subsampling.cu)."""
+    x = f16_round(np.maximum(_conv_s2(np.asarray(mel, dtype=F32)[:, :, None], w["conv0_w"].reshape(256, 3, 3),
+                                      w["conv0_b"]), 0))
+    for stage in (1, 2):
+        x = f16_round(_conv_s2(x, w[f"dw{stage}_w"].reshape(256, 3, 3), w[f"dw{stage}_b"]))
+        f, t, c = x.shape
+        x = linear_f16(x.reshape(f * t, c), w[f"pw{stage}_w"], bias=w[f"pw{stage}_b"], act=2).reshape(f, t, c)
+    f, t, c = x.shape                                   # [F3, 16, 256]
+    flat = np.ascontiguousarray(x.transpose(0, 2, 1)).reshape(f, c * t)   # channel*16 + feature
+    return linear_f16(flat, w["proj_w"], bias=w["proj_b"])

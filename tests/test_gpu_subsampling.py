@@ -1,0 +1,33 @@
+"""GPU parity: batched convolution subsampling vs the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ops as O
+from tests.util import dev, host, nrmse
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("frames_list", [[400, 400], [203, 77, 8, 1]])
+def test_subsampling_matches_oracle(pk, cuda, frames_list):
+    w = pk.synth.subsampling_weights(2)
+    sub = pk.subsampling.Subsampling(w, cuda)
+    cap = max(frames_list)
+    mels = [pk.synth.mel_input(30 + i, f) for i, f in enumerate(frames_list)]
+    batch = np.zeros((len(mels), cap, 128), np.float32)
+    for i, m in enumerate(mels):
+        batch[i, :m.shape[0]] = m
+    seg_stride = (pk.subsampling.output_frames(cap) + 127) // 128 * 128
+    mf = torch.tensor(frames_list, dtype=torch.int32, device=cuda)
+    out = host(sub.run(dev(batch), seg_stride, mel_frames=mf))
+    torch.cuda.synchronize()
+    assert int(sub.status.item()) == 0
+    for i, m in enumerate(mels):
+        want = O.subsampling(m, w)
+        got = out[i * seg_stride:i * seg_stride + want.shape[0]]
+        assert want.shape[0] == pk.subsampling.output_frames(frames_list[i])
+        # reference gate for this stage: max abs <= 2.0 and nRMSE <= 0.002
+        # (src/cuda/subsampling.rs:375); ours is far inside it
+        assert np.max(np.abs(got - want)) <= 2e-2
+        assert nrmse(got, want) <= 2e-3
