@@ -110,6 +110,9 @@ typedef struct pk100_gemm_args {
 
 int pk100_gemm(void* stream, const pk100_gemm_args* args);
 
+/* Number of kernels this library has launched in the calling process (monotonic). */
+long long pk100_launch_count(void);
+
 /* pk_sm89_layer_norm (kernels/sm89/encoder.cu:81-126) and
  * pk_sm89_layer_norm_quantize_fp8_dynamic (:294-299); launcher launch_norm /
  * launch_norm_quantize_fp8 (src/cuda/encoder.rs:1361-1468).  Width is 1024. */
@@ -222,6 +225,10 @@ typedef struct pk100_layer_weights {
 typedef struct pk100_encoder_workspace {
     void* q8; float* row_scales; void* hidden8; uint8_t* keep; void* qkv; void* att;
     void* glu; void* dw8; float* dw_scales; int* status;
+    /* Optional timing hook (HOST array of cudaEvent_t, may be NULL): the FF-expand GEMM of
+     * layer l, module m (0/1) is bracketed by events[2*(2*l+m)] and [2*(2*l+m)+1] when
+     * 2*(2*l+m)+1 < profile_events_len.  Recording an event does not synchronise. */
+    void** profile_events; int profile_events_len;
 } pk100_encoder_workspace;
 
 /* Bytes needed for one arena holding every field above. */

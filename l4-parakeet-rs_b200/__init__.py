@@ -9,3 +9,5 @@ from . import encoder  # noqa: F401
 from . import synth  # noqa: F401
 from . import decoder  # noqa: F401
 from . import subsampling  # noqa: F401
+from . import pipeline  # noqa: F401
+from . import parallel  # noqa: F401

@@ -453,5 +453,6 @@ extern "C" int pk100_tdt_decode(void* stream_v, const pk100_decoder_weights* w, 
         cudaGetLastError();
         return static_cast<int>(err);
     }
+    pk100_count_launch();
     return PK100_OK;
 }

@@ -44,8 +44,11 @@ int gemm_base(pk100_gemm_args& a, int kind, int m, int n, int k, const void* x, 
 
 // LN (already applied) -> FP8 expand + SiLU + tile threshold -> INT8 contract, x += 0.5*y
 int ff_module(void* stream, const pk100_ff_weights& w, void* x, const pk100_encoder_workspace& ws,
-              const Geometry& g, float* stats) {
+              const Geometry& g, float* stats, int profile_slot) {
     pk100_gemm_args a;
+    const bool timed = ws.profile_events != nullptr && 2 * profile_slot + 1 < ws.profile_events_len;
+    if (timed) cudaEventRecord(static_cast<cudaEvent_t>(ws.profile_events[2 * profile_slot]),
+                               static_cast<cudaStream_t>(stream));
     gemm_base(a, PK100_KIND_E4M3, g.rows, kFf, kWidth, ws.q8, w.w1);
     a.epilogue = PK100_EPI_SPARSE_OUT;
     a.row_scale = kFp8InputScale;
@@ -53,6 +56,8 @@ int ff_module(void* stream, const pk100_ff_weights& w, void* x, const pk100_enco
     a.out = ws.hidden8; a.ld_out = kFf; a.out_type = PK100_OUT_S8; a.out_scale = kHiddenInv;
     a.tau = w.tau; a.keep_out = ws.keep; a.stats_out = stats; a.status = ws.status;
     PK_TRY(pk100_gemm(stream, &a));
+    if (timed) cudaEventRecord(static_cast<cudaEvent_t>(ws.profile_events[2 * profile_slot + 1]),
+                               static_cast<cudaStream_t>(stream));
 
     gemm_base(a, PK100_KIND_S8, g.rows, kWidth, kFf, ws.hidden8, w.w2);
     a.row_scale = kHiddenScale;
@@ -92,6 +97,8 @@ extern "C" int pk100_encoder_workspace_carve(void* base, int rows, pk100_encoder
     out->dw8 = take(r * 1024);
     out->dw_scales = reinterpret_cast<float*>(take(r * 4));
     out->status = reinterpret_cast<int*>(take(4));
+    out->profile_events = nullptr;
+    out->profile_events_len = 0;
     return PK100_OK;
 }
 
@@ -124,7 +131,7 @@ extern "C" int pk100_run_layers(void* stream, const pk100_layer_weights* layers,
                                     PK100_LN_E4M3_FIXED, kFp8InputInv, g.rows, seg_stride,
                                     valid_rows, seg_valid, kEps));
         }
-        PK_TRY(ff_module(stream, w.ff1, x, ws, g, stats1));
+        PK_TRY(ff_module(stream, w.ff1, x, ws, g, stats1, 2 * i));
 
         // ---- self-attention
         PK_TRY(pk100_layer_norm(stream, x, w.ln_att_gamma, w.ln_att_beta, ws.q8, ws.row_scales,
@@ -172,7 +179,7 @@ extern "C" int pk100_run_layers(void* stream, const pk100_layer_weights* layers,
         PK_TRY(pk100_layer_norm(stream, x, w.ff2.ln_gamma, w.ff2.ln_beta, ws.q8, nullptr,
                                 PK100_LN_E4M3_FIXED, kFp8InputInv, g.rows, seg_stride, valid_rows,
                                 seg_valid, kEps));
-        PK_TRY(ff_module(stream, w.ff2, x, ws, g, stats2));
+        PK_TRY(ff_module(stream, w.ff2, x, ws, g, stats2, 2 * i + 1));
 
         // ---- output norm, fused with the next block's first norm
         if (i + 1 < n_layers) {

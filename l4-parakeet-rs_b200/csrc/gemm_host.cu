@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "gemm_sm100.cuh"
@@ -91,6 +92,10 @@ static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr
 }  // namespace pk100
 
 using namespace pk100;
+
+static std::atomic<long long> g_launches{0};
+void pk100_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+extern "C" long long pk100_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int pk100_gemm(void* stream_v, const pk100_gemm_args* a) {
     if (a == nullptr || a->a == nullptr || a->b == nullptr || a->out == nullptr) return PK100_ERR_NULL;

@@ -8,9 +8,16 @@
 
 // Maps the sticky-free launch error of the last kernel launch to the ABI's
 // convention: 0 ok, positive = CUDA runtime error code.
+// Number of kernels launched through this library by the calling process (monotonic).
+extern "C" long long pk100_launch_count(void);
+void pk100_count_launch();
+
 static inline int pk100_launch_status() {
     const cudaError_t err = cudaPeekAtLastError();
-    if (err == cudaSuccess) return PK100_OK;
+    if (err == cudaSuccess) {
+        pk100_count_launch();
+        return PK100_OK;
+    }
     cudaGetLastError();   // clear the non-sticky launch error so later calls are not poisoned
     return static_cast<int>(err);
 }

@@ -56,6 +56,7 @@ SIGNATURES = {
     "pk100_tdt_decode": None,
     "pk100_subsampling_workspace_bytes": None,
     "pk100_run_subsampling": None,
+    "pk100_launch_count": None,
 }
 
 for _name, _argtypes in SIGNATURES.items():
@@ -63,6 +64,8 @@ for _name, _argtypes in SIGNATURES.items():
     if _argtypes is not None:
         _fn.argtypes = _argtypes
     _fn.restype = i32
+lib.pk100_launch_count.restype = i64
+lib.pk100_launch_count.argtypes = []
 
 # enums (include/pk100.h)
 OK, ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_UNSUPPORTED, ERR_DRIVER, ERR_LIMIT = 0, -1, -2, -3, -4, -5, -6

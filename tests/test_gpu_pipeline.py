@@ -1,0 +1,74 @@
+"""GPU parity: the whole path (subsampling -> blocks -> projection -> TDT decode) through the
+public pipeline API vs the CPU oracle, on a reduced model (2 blocks, short utterances)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import decoder as D, ops as O, pipeline as P
+from tests.util import nrmse
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def engine(pk, cuda):
+    eng = pk.pipeline.PipelineEngine(cuda, layers=2, decoder_layers=2, seed=9, max_utterances=3,
+                                     mel_frames=1000, randomize_norms=True)
+    return eng
+
+
+def _weights(pk, eng):
+    sub_w = pk.synth.subsampling_weights(9)
+    layers = [O.prepare_layer(pk.synth.layer_weights(9, l, randomize_norms=True)) for l in range(2)]
+    dec_w = pk.synth.decoder_weights(9, 2)
+    return sub_w, layers, dec_w
+
+
+def test_transcribe_batch_matches_oracle(pk, cuda, engine):
+    eng = engine
+    frames = [1000, 1000, 1000]
+    mels = np.stack([pk.synth.mel_input(100 + u, 1000) for u in range(3)])
+    mel_host = torch.from_numpy(mels).pin_memory()
+    eng.set_lengths(frames)
+    # tile thresholds stay 0 here: the free-running stack is compared as a continuous
+    # operator (per-block parity WITH thresholds is covered in test_gpu_encoder.py)
+    tokens = eng.transcribe_batch(mel_host)
+    assert eng.status() == 0
+    sub_w, layers, dec_w = _weights(pk, eng)
+    taus = [(eng.enc.layers[l].ff1.tau, eng.enc.layers[l].ff2.tau) for l in range(2)]
+    for u in range(3):
+        want_tokens, want_enc, amb = P.transcribe(mels[u], sub_w, layers, taus, dec_w)
+        # encoder output of the free-running 2-block stack: reference's stack gate
+        blk = slice(u * eng.seg_stride, u * eng.seg_stride + eng.frames_out)
+        got_proj = eng.enc_proj[blk].float().cpu().numpy()
+        want_proj = P.project(want_enc, dec_w)
+        assert nrmse(got_proj, want_proj) <= 3e-2
+        # token ids: exact on the SAME encoder projection (the GPU's), up to the first
+        # decision inside fp32 summation noise
+        same_tokens, _, amb2 = D.tdt_greedy(got_proj, dec_w, eng.frames_out)
+        n = len(same_tokens) if amb2 is None else amb2
+        assert n > 10
+        assert np.array_equal(tokens[u][:n], same_tokens[:n])
+        if amb2 is None:
+            assert len(tokens[u]) == len(same_tokens)
+
+
+def test_resident_path_is_deterministic_and_ragged_lengths(pk, cuda, engine):
+    eng = engine
+    frames = [1000, 617, 40]
+    mels = np.zeros((3, 1000, 128), np.float32)
+    for u, f in enumerate(frames):
+        mels[u, :f] = pk.synth.mel_input(200 + u, f)
+    mel_host = torch.from_numpy(mels).pin_memory()
+    eng.set_lengths(frames)
+    eng.mel_dev.copy_(mel_host)
+    eng.calibrate(3)                       # 70 % zero tiles from here on
+    assert all(l.ff1.tau > 0 and l.ff2.tau > 0 for l in eng.enc.layers)
+    a = eng.transcribe_batch(mel_host)
+    b = eng.transcribe_batch(mel_host)
+    assert all(np.array_equal(x, y) for x, y in zip(a, b))
+    # a shorter utterance in a batch decodes like the same utterance alone
+    eng.set_lengths([617, 617, 617])
+    solo = eng.transcribe_batch(torch.from_numpy(np.stack([mels[1]] * 3)).pin_memory())
+    assert np.array_equal(solo[0], a[1])
+    eng.set_lengths([1000, 1000, 1000])
