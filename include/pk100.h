@@ -174,6 +174,15 @@ int pk100_local_relpos_attention_simple(void* stream, const void* query, int ldq
                                         int ldo, int segments, int seg_stride, int valid_rows,
                                         const int* seg_valid);
 
+/* pk_sm89_local_relpos_attention_tc_scores / _packed (kernels/sm89/encoder.cu:1500-2052;
+ * launch_attention_arena src/cuda/encoder.rs:1839-1963): the tensor-core kernel of the
+ * hot path.  Same arguments and semantics as the _simple entry point; Q.K^T, Q.P^T and
+ * P.V run as fp16 MMAs with fp32 accumulation and an fp32 online softmax. */
+int pk100_local_relpos_attention(void* stream, const void* query, int ldq, const void* key, int ldk,
+                                 const void* value, int ldv, const void* position,
+                                 const void* bias_u, const void* bias_v, void* output, int ldo,
+                                 int segments, int seg_stride, int valid_rows, const int* seg_valid);
+
 /* pk_sm89_pack_position_heads (kernels/sm89/encoder.cu:1321-1336):
  * [272, 1024] -> head-major [8, 272, 128]. */
 int pk100_pack_position_heads(void* stream, const void* input, void* output);

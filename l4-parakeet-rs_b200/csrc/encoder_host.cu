@@ -144,11 +144,17 @@ extern "C" int pk100_run_layers(void* stream, const pk100_layer_weights* layers,
         PK_TRY(pk100_gemm(stream, &a));
         {
             const __half* qkv = static_cast<const __half*>(ws.qkv);
-            (void)attention_impl;
-            PK_TRY(pk100_local_relpos_attention_simple(
-                stream, qkv, 3 * kWidth, qkv + kWidth, 3 * kWidth, qkv + 2 * kWidth, 3 * kWidth,
-                w.position, w.bias_u, w.bias_v, ws.att, kWidth, segments, seg_stride, valid_rows,
-                seg_valid));
+            if (attention_impl == 1) {
+                PK_TRY(pk100_local_relpos_attention_simple(
+                    stream, qkv, 3 * kWidth, qkv + kWidth, 3 * kWidth, qkv + 2 * kWidth, 3 * kWidth,
+                    w.position, w.bias_u, w.bias_v, ws.att, kWidth, segments, seg_stride, valid_rows,
+                    seg_valid));
+            } else {
+                PK_TRY(pk100_local_relpos_attention(
+                    stream, qkv, 3 * kWidth, qkv + kWidth, 3 * kWidth, qkv + 2 * kWidth, 3 * kWidth,
+                    w.position, w.bias_u, w.bias_v, ws.att, kWidth, segments, seg_stride, valid_rows,
+                    seg_valid));
+            }
         }
         gemm_base(a, PK100_KIND_F16, g.rows, kWidth, kWidth, ws.att, w.wo_f16);
         a.residual = x; a.ld_res = kWidth; a.out = x; a.ld_out = kWidth; a.status = ws.status;

@@ -47,6 +47,8 @@ SIGNATURES = {
     "pk100_depthwise_bn_silu": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, f32],
     "pk100_local_relpos_attention_simple": [vp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, i32,
                                             i32, i32, i32, vp],
+    "pk100_local_relpos_attention": [vp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, i32,
+                                     i32, i32, i32, vp],
     "pk100_pack_position_heads": [vp, vp, vp],
     # struct-taking entry points: argtypes are completed in encoder.py / decoder.py
     "pk100_encoder_workspace_bytes": None,

@@ -162,6 +162,21 @@ def depthwise_bn_silu(g, wdw, bn_gamma, bn_beta, bn_mean, bn_var, quantize=False
     return out, scales
 
 
+def local_attention(q, k, v, pos, bias_u, bias_v, seg_stride=None, valid_rows=None,
+                    seg_valid=None, out=None):
+    """Tensor-core local relative-position attention (the hot-path kernel)."""
+    rows = q.shape[0]
+    seg_stride = rows if seg_stride is None else seg_stride
+    valid_rows = seg_stride if valid_rows is None else valid_rows
+    if out is None:
+        out = torch.empty((rows, 1024), device=q.device, dtype=torch.float16)
+    L.check(L.lib.pk100_local_relpos_attention(
+        _stream(), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(pos),
+        _ptr(bias_u), _ptr(bias_v), _ptr(out), out.stride(0), rows // seg_stride, seg_stride,
+        valid_rows, _ptr(seg_valid)), "pk100_local_relpos_attention")
+    return out
+
+
 def local_attention_simple(q, k, v, pos, bias_u, bias_v, seg_stride=None, valid_rows=None,
                            seg_valid=None, out=None):
     rows = q.shape[0]

@@ -21,14 +21,26 @@ def _case(seed, rows):
     return q, k, v, pos, u, bv
 
 
-@pytest.mark.parametrize("rows,valid", [(304, 300), (40, 33), (752, 750)])
-def test_simple_kernel_matches_oracle(pk, cuda, rows, valid):
+@pytest.mark.parametrize("impl", ["mma", "simple"])
+@pytest.mark.parametrize("rows,valid", [(304, 300), (40, 33), (752, 750), (768, 750), (1, 1), (130, 129)])
+def test_kernels_match_oracle(pk, cuda, rows, valid, impl):
     q, k, v, pos, u, bv = _case(rows, rows)
     want = O.local_attention(q, k, v, pos, u, bv, rows, valid)
-    got = host(pk.ops.local_attention_simple(dev16(q), dev16(k), dev16(v), dev16(pos), dev16(u),
-                                             dev16(bv), valid_rows=valid))
+    fn = pk.ops.local_attention if impl == "mma" else pk.ops.local_attention_simple
+    got = host(fn(dev16(q), dev16(k), dev16(v), dev16(pos), dev16(u), dev16(bv), valid_rows=valid))
     assert np.all(got[valid:] == 0)
-    assert np.max(np.abs(got - want)) <= 3e-3
+    # tolerance: fp16 output ulp + fp16-rounded probabilities / position scores (mma kernel)
+    assert np.max(np.abs(got - want)) <= 3e-3, np.max(np.abs(got - want))
+
+
+def test_large_scores_do_not_overflow(pk, cuda):
+    # queries/keys 4x larger: scores of a few hundred before scaling, softmax nearly one-hot
+    q, k, v, pos, u, bv = _case(77, 200)
+    q, k = q * 4, k * 4
+    want = O.local_attention(q, k, v, pos, u, bv, 200, 200)
+    got = host(pk.ops.local_attention(dev16(q), dev16(k), dev16(v), dev16(pos), dev16(u), dev16(bv)))
+    assert np.all(np.isfinite(got))
+    assert np.max(np.abs(got - want)) <= 2e-2
 
 
 def test_fused_qkv_strides_and_segments(pk, cuda):
@@ -37,8 +49,13 @@ def test_fused_qkv_strides_and_segments(pk, cuda):
     qkv = np.concatenate([q, k, v], axis=1)
     t = dev16(qkv)
     sv = torch.tensor(valid, dtype=torch.int32, device=cuda)
-    got = host(pk.ops.local_attention_simple(t[:, :1024], t[:, 1024:2048], t[:, 2048:], dev16(pos),
-                                             dev16(u), dev16(bv), seg_stride=seg, seg_valid=sv))
+    for fn in (pk.ops.local_attention, pk.ops.local_attention_simple):
+        got = host(fn(t[:, :1024], t[:, 1024:2048], t[:, 2048:], dev16(pos), dev16(u), dev16(bv),
+                      seg_stride=seg, seg_valid=sv))
+        _check_segments(got, q, k, v, pos, u, bv, seg, valid)
+
+
+def _check_segments(got, q, k, v, pos, u, bv, seg, valid):
     for s, val in enumerate(valid):
         blk = slice(s * seg, (s + 1) * seg)
         want = O.local_attention(q[blk], k[blk], v[blk], pos, u, bv, seg, val)
