@@ -291,6 +291,15 @@ int pk100_tdt_decode(void* stream, const pk100_decoder_weights* weights, const v
                      int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
                      int* status);
 
+/* Same contract, earlier design kept as a cross-check: weights in shared memory and a
+ * bounded grid barrier between the phases (the structure of the reference kernel,
+ * kernels/sm89/decoder.cu:227-414).  pk100_tdt_decode falls back to it on devices whose SM
+ * count does not fit the register-resident slicing. */
+int pk100_tdt_decode_barrier(void* stream, const pk100_decoder_weights* weights, const void* enc_proj,
+                             int utterances, int seg_stride, const int* frames, void* workspace,
+                             int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                             int* status);
+
 /* ------------------------------------------------------------------------
  * 8x convolution subsampling for a batch of utterances: mel fp32
  * [utterances, frames, 128] -> fp16 rows [utterances * seg_stride, 1024].

@@ -368,6 +368,440 @@ __global__ void __launch_bounds__(kDecThreads, 1) tdt_greedy_kernel(const DecPar
 
 }  // namespace pk100
 
+namespace pk100 {
+
+// ===========================================================================
+// Exchange-based decoder (the hot-path kernel).
+//
+// Same slicing of the work across one CTA per SM, but (a) every weight slice lives in
+// REGISTERS (each of the 20 warps owns one gate row of one hidden unit, one prediction
+// row and one joint row; a lane keeps its 20-element slices as half2), and (b) there
+// is no grid barrier: producers publish every value together with a tag
+// ({fp32 value, u32 tag} in one 64-bit store) and consumers poll the data itself until
+// the tag matches the version they need.  Tags are the per-utterance LSTM version for
+// hidden states / prediction vectors and the round number for the joint decisions, so
+// a slot can never be confused with its previous content, and nobody can run two
+// versions ahead of anybody else because every decision needs a key from every CTA.
+// Every poll is bounded; when one expires the kernel raises a global abort flag,
+// records status 2 and all CTAs leave.
+constexpr int kXThreads = 640;
+constexpr int kXWarps = kXThreads / 32;
+constexpr int kXMaxGrid = 256;
+constexpr unsigned kEpochMask = 0x1FFFFFu;
+
+struct XchLayout { size_t xh, xp, xk, xd, abort, total; };
+__host__ __device__ inline XchLayout xch_layout(int utts) {
+    XchLayout l;
+    size_t off = 0;
+    l.xh = off; off += static_cast<size_t>(2) * 2 * utts * kHidden * 8;
+    l.xp = off; off += static_cast<size_t>(2) * utts * kHidden * 8;
+    l.xk = off; off += static_cast<size_t>(2) * utts * kXMaxGrid * 8;
+    l.xd = off; off += static_cast<size_t>(2) * utts * 8 * 8;
+    l.abort = off; off += 256;
+    l.total = off;
+    return l;
+}
+
+__device__ __forceinline__ void xch_store(unsigned long long* slot, float value, unsigned tag) {
+    const unsigned long long packed = (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(value);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(slot), "l"(packed) : "memory");
+}
+__device__ __forceinline__ unsigned long long xch_load(const unsigned long long* slot) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(slot) : "memory");
+    return v;
+}
+
+// Poll one tagged slot until its tag equals `tag`.  Returns false (and raises the global
+// abort flag) when the budget runs out or another thread already gave up.
+__device__ __forceinline__ bool xch_wait(const unsigned long long* slot, unsigned tag, float* value,
+                                         volatile int* abort_flag) {
+    unsigned long long v = xch_load(slot);
+    if (static_cast<unsigned>(v >> 32) != tag) {
+        const long long start = clock64();
+        unsigned polls = 0;
+        do {
+            v = xch_load(slot);
+            if ((++polls & 127u) == 0u) {
+                if (*abort_flag != 0 || clock64() - start > 2000000000ll) {   // ~1 s
+                    *abort_flag = 1;
+                    return false;
+                }
+            }
+        } while (static_cast<unsigned>(v >> 32) != tag);
+    }
+    *value = __uint_as_float(static_cast<unsigned>(v));
+    return true;
+}
+
+// Sum 8 per-lane partials across the warp with 9 shuffles.  On return every lane holds
+// the total of utterance  u = 4*bit4(lane) + 2*bit3(lane) + bit2(lane).
+__device__ __forceinline__ float reduce8(const float (&v)[8], int lane) {
+    float a[4], b[2], c;
+    const bool hi16 = lane & 16, hi8 = lane & 8, hi4 = lane & 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float send = hi16 ? v[j] : v[j + 4];
+        const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
+        a[j] = (hi16 ? v[j + 4] : v[j]) + recv;
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const float send = hi8 ? a[j] : a[j + 2];
+        const float recv = __shfl_xor_sync(0xffffffffu, send, 8);
+        b[j] = (hi8 ? a[j + 2] : a[j]) + recv;
+    }
+    {
+        const float send = hi4 ? b[0] : b[1];
+        const float recv = __shfl_xor_sync(0xffffffffu, send, 4);
+        c = (hi4 ? b[1] : b[0]) + recv;
+    }
+    c += __shfl_xor_sync(0xffffffffu, c, 2);
+    c += __shfl_xor_sync(0xffffffffu, c, 1);
+    return c;
+}
+
+__device__ __forceinline__ void load_row_slices(const __half* row, int lane, __half2 (&w)[10]) {
+#pragma unroll
+    for (int m = 0; m < 10; ++m) w[m] = *reinterpret_cast<const __half2*>(row + 2 * lane + 64 * m);
+}
+
+// partial dot of this lane's 20 weights with x[u][...] for 8 utterances
+__device__ __forceinline__ void dot8(const __half2 (&w)[10], const float* x, int lane, float (&acc)[8]) {
+#pragma unroll
+    for (int m = 0; m < 10; ++m) {
+        const float2 wf = __half22float2(w[m]);
+        const int idx = 2 * lane + 64 * m;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float2 xv = *reinterpret_cast<const float2*>(x + u * kHidden + idx);
+            acc[u] = fmaf(wf.x, xv.x, acc[u]);
+            acc[u] = fmaf(wf.y, xv.y, acc[u]);
+        }
+    }
+}
+
+struct XSmem {
+    float hcur[2][kMaxUtt][kHidden];     // committed hidden state per layer (all units)
+    float x[kMaxUtt][kHidden];           // LSTM input / joint input staging
+    float pred[kMaxUtt][kHidden];        // cached prediction vectors
+    float gate[kMaxUtt][8][4];           // [utt][unit slot][gate]
+    float cstate[2][2][8][kMaxUtt];      // [layer][version parity][unit slot][utt]
+    __half w_pred[8][kHidden];           // this CTA's prediction-projection rows
+    __half w_joint[8][kHidden];          // this CTA's joint rows
+    float bias[2][8][4];                 // b_ih + b_hh per owned unit and gate
+    float pred_bias[8];
+    float joint_bias[8];
+    unsigned long long best[kMaxUtt];
+    int frame[kMaxUtt], symbols[kMaxUtt], last[kMaxUtt], count[kMaxUtt], ver[kMaxUtt], pred_ver[kMaxUtt];
+    unsigned char emitted[kMaxUtt], valid[kMaxUtt], done[kMaxUtt], need[kMaxUtt];
+    int ok;
+};
+
+__global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecParams p) {
+    extern __shared__ __align__(16) uint8_t xs_raw[];
+    XSmem& sm = *reinterpret_cast<XSmem*>(xs_raw);
+    const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
+    const int G = gridDim.x, cta = blockIdx.x;
+    const int units = (kHidden + G - 1) / G;            // <= 5 (checked on the host)
+    const int jrows = (kJointRows + G - 1) / G;         // <= 8
+    const XchLayout lay = xch_layout(p.utts);
+    unsigned long long* xh = reinterpret_cast<unsigned long long*>(p.workspace + lay.xh);
+    unsigned long long* xp = reinterpret_cast<unsigned long long*>(p.workspace + lay.xp);
+    unsigned long long* xk = reinterpret_cast<unsigned long long*>(p.workspace + lay.xk);
+    unsigned long long* xd = reinterpret_cast<unsigned long long*>(p.workspace + lay.xd);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(p.workspace + lay.abort);
+    const int U = p.utts;
+
+    // ---- register-resident weight slices
+    const int my_unit_slot = warp / 4, my_gate = warp % 4;
+    const int my_unit = cta + G * my_unit_slot;
+    const bool lstm_warp = my_unit_slot < units && my_unit < kHidden;
+    __half2 w_ih[2][10], w_hh[2][10];
+#pragma unroll
+    for (int l = 0; l < 2; ++l) {
+#pragma unroll
+        for (int m = 0; m < 10; ++m) { w_ih[l][m] = __float2half2_rn(0.0f); w_hh[l][m] = w_ih[l][m]; }
+        if (l < p.layers && lstm_warp) {
+            load_row_slices(p.w_ih[l] + (static_cast<size_t>(my_gate) * kHidden + my_unit) * kHidden, lane, w_ih[l]);
+            load_row_slices(p.w_hh[l] + (static_cast<size_t>(my_gate) * kHidden + my_unit) * kHidden, lane, w_hh[l]);
+        }
+    }
+    const int pred_row = cta + G * warp;
+    const bool pred_warp = warp < units && pred_row < kHidden;
+    const int joint_row = cta + G * warp;
+    const bool joint_warp = warp < jrows && joint_row < kJointRows;
+    for (int i = tid; i < 8 * kHidden; i += kXThreads) {
+        const int slot = i / kHidden, c = i % kHidden;
+        const int row = cta + G * slot;
+        sm.w_pred[slot][c] = (slot < units && row < kHidden) ? p.w_pred[static_cast<size_t>(row) * kHidden + c]
+                                                             : __float2half(0.0f);
+        sm.w_joint[slot][c] = (slot < jrows && row < kJointRows)
+            ? p.w_joint[static_cast<size_t>(row) * kHidden + c] : __float2half(0.0f);
+    }
+
+    // ---- shared state
+    for (int i = tid; i < 2 * kMaxUtt * kHidden; i += kXThreads) (&sm.hcur[0][0][0])[i] = 0.0f;
+    for (int i = tid; i < kMaxUtt * kHidden; i += kXThreads) { (&sm.x[0][0])[i] = 0.0f; (&sm.pred[0][0])[i] = 0.0f; }
+    for (int i = tid; i < 2 * 2 * 8 * kMaxUtt; i += kXThreads) (&sm.cstate[0][0][0][0])[i] = 0.0f;
+    if (tid < 2 * 8 * 4) {
+        const int l = tid / 32, slot = (tid / 4) % 8, gt = tid % 4;
+        const int unit = cta + G * slot;
+        sm.bias[l][slot][gt] = (l < p.layers && slot < units && unit < kHidden)
+            ? p.b_ih[l][gt * kHidden + unit] + p.b_hh[l][gt * kHidden + unit] : 0.0f;
+    }
+    if (tid < 8) {
+        const int row = cta + G * tid;
+        sm.pred_bias[tid] = (tid < units && row < kHidden) ? p.b_pred[row] : 0.0f;
+        sm.joint_bias[tid] = (tid < jrows && row < kJointRows) ? p.b_joint[row] : 0.0f;
+    }
+    if (tid < kMaxUtt) {
+        sm.frame[tid] = 0; sm.symbols[tid] = 0; sm.last[tid] = kBlank; sm.count[tid] = 0;
+        sm.ver[tid] = 0; sm.pred_ver[tid] = 0; sm.emitted[tid] = 0; sm.valid[tid] = 0;
+        sm.done[tid] = tid >= U || p.frames[tid] <= 0;
+        sm.need[tid] = 0;
+    }
+    if (tid == 0) sm.ok = 1;
+    __syncthreads();
+
+    unsigned round = 0;
+    while (true) {
+        // ---- who runs, who needs a new prediction
+        bool any_running = false, any_need = false;
+        for (int u = 0; u < U; ++u) {
+            any_running |= !sm.done[u];
+            any_need |= !sm.done[u] && !sm.valid[u];
+        }
+        if (!any_running || sm.ok == 0) break;
+        if (tid < kMaxUtt) sm.need[tid] = tid < U && !sm.done[tid] && !sm.valid[tid];
+        __syncthreads();
+
+        if (any_need) {
+#pragma unroll
+            for (int l = 0; l < 2; ++l) {       // unrolled so the weight registers are indexed statically
+                if (l >= p.layers || sm.ok == 0) break;
+                // input of layer l: embedding of the last token (layer 0) or the lower layer's
+                // fresh hidden state, which arrives through the exchange buffer
+                if (l == 0) {
+                    for (int i = tid; i < U * kHidden; i += kXThreads) {
+                        const int u = i / kHidden, c = i % kHidden;
+                        if (!sm.need[u]) continue;
+                        sm.x[u][c] = sm.emitted[u]
+                            ? __half2float(p.embedding[static_cast<size_t>(sm.last[u]) * kHidden + c]) : 0.0f;
+                    }
+                } else {
+                    bool good = true;
+                    for (int i = tid; i < U * kHidden; i += kXThreads) {
+                        const int u = i / kHidden, c = i % kHidden;
+                        if (!sm.need[u]) continue;
+                        const unsigned tag = static_cast<unsigned>(sm.ver[u] + 1);
+                        float v;
+                        good &= xch_wait(xh + ((static_cast<size_t>(l - 1) * 2 + (tag & 1)) * U + u) * kHidden + c,
+                                         tag, &v, abort_flag);
+                        sm.x[u][c] = v;
+                    }
+                    if (!good) sm.ok = 0;
+                }
+                __syncthreads();
+                if (sm.ok == 0) break;
+                if (lstm_warp) {
+                    float acc[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
+                    dot8(w_ih[l], &sm.x[0][0], lane, acc);
+                    dot8(w_hh[l], &sm.hcur[l][0][0], lane, acc);
+                    const float total = reduce8(acc, lane);
+                    const int u = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                    if ((lane & 3) == 0) sm.gate[u][my_unit_slot][my_gate] = total + sm.bias[l][my_unit_slot][my_gate];
+                }
+                __syncthreads();
+                // the lower layer's new state becomes that layer's committed state for the next version
+                if (l > 0) {
+                    for (int i = tid; i < U * kHidden; i += kXThreads) {
+                        const int u = i / kHidden, c = i % kHidden;
+                        if (sm.need[u]) sm.hcur[l - 1][u][c] = sm.x[u][c];
+                    }
+                }
+                if (tid < units * U) {
+                    const int slot = tid / U, u = tid % U;
+                    const int unit = cta + G * slot;
+                    if (unit < kHidden && sm.need[u]) {
+                        const unsigned tag = static_cast<unsigned>(sm.ver[u] + 1);
+                        const float ig = 1.0f / (1.0f + expf(-sm.gate[u][slot][0]));
+                        const float fg = 1.0f / (1.0f + expf(-sm.gate[u][slot][1]));
+                        const float gg = tanhf(sm.gate[u][slot][2]);
+                        const float og = 1.0f / (1.0f + expf(-sm.gate[u][slot][3]));
+                        const float cell = fg * sm.cstate[l][(tag & 1) ^ 1][slot][u] + ig * gg;
+                        sm.cstate[l][tag & 1][slot][u] = cell;
+                        xch_store(xh + ((static_cast<size_t>(l) * 2 + (tag & 1)) * U + u) * kHidden + unit,
+                                  og * tanhf(cell), tag);
+                    }
+                }
+                __syncthreads();
+            }
+            if (sm.ok == 0) break;
+            // ---- top layer's fresh hidden state -> committed copy + prediction projection
+            {
+                const int top = p.layers - 1;
+                bool good = true;
+                for (int i = tid; i < U * kHidden; i += kXThreads) {
+                    const int u = i / kHidden, c = i % kHidden;
+                    if (!sm.need[u]) continue;
+                    const unsigned tag = static_cast<unsigned>(sm.ver[u] + 1);
+                    float v;
+                    good &= xch_wait(xh + ((static_cast<size_t>(top) * 2 + (tag & 1)) * U + u) * kHidden + c,
+                                     tag, &v, abort_flag);
+                    sm.hcur[top][u][c] = v;
+                }
+                if (!good) sm.ok = 0;
+            }
+            __syncthreads();
+            if (sm.ok == 0) break;
+            if (pred_warp) {
+                float acc[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
+                __half2 wp[10];
+                load_row_slices(sm.w_pred[warp], lane, wp);
+                dot8(wp, &sm.hcur[p.layers - 1][0][0], lane, acc);
+                const float total = reduce8(acc, lane);
+                const int u = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                if ((lane & 3) == 0 && u < U && sm.need[u]) {
+                    const unsigned tag = static_cast<unsigned>(sm.ver[u] + 1);
+                    xch_store(xp + (static_cast<size_t>(tag & 1) * U + u) * kHidden + pred_row,
+                              total + sm.pred_bias[warp], tag);
+                }
+            }
+            __syncthreads();
+            if (tid < U && sm.need[tid]) { sm.ver[tid] += 1; sm.valid[tid] = 1; }
+            __syncthreads();
+        }
+
+        // ---- joint: refresh cached prediction vectors whose version changed, build relu(enc + pred)
+        {
+            bool good = true;
+            for (int i = tid; i < U * kHidden; i += kXThreads) {
+                const int u = i / kHidden, c = i % kHidden;
+                if (sm.done[u]) continue;
+                if (sm.pred_ver[u] != sm.ver[u]) {
+                    const unsigned tag = static_cast<unsigned>(sm.ver[u]);
+                    float v;
+                    good &= xch_wait(xp + (static_cast<size_t>(tag & 1) * U + u) * kHidden + c, tag, &v, abort_flag);
+                    sm.pred[u][c] = v;
+                }
+                const float e = __half2float(
+                    p.enc_proj[(static_cast<size_t>(u) * p.seg_stride + sm.frame[u]) * kHidden + c]);
+                sm.x[u][c] = fmaxf(e + sm.pred[u][c], 0.0f);
+            }
+            if (!good) sm.ok = 0;
+            if (tid < kMaxUtt) sm.best[tid] = 0ull;
+        }
+        __syncthreads();
+        if (sm.ok == 0) break;
+        if (tid < U) sm.pred_ver[tid] = sm.ver[tid];
+        const unsigned epoch = (round + 1) & kEpochMask;
+        if (joint_warp) {
+            float acc[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
+            __half2 wj[10];
+            load_row_slices(sm.w_joint[warp], lane, wj);
+            dot8(wj, &sm.x[0][0], lane, acc);
+            const float total = reduce8(acc, lane) + sm.joint_bias[warp];
+            const int u = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+            if ((lane & 3) == 0 && u < U && !sm.done[u]) {
+                if (joint_row >= kTokenOutputs) {
+                    xch_store(xd + (static_cast<size_t>(round & 1) * U + u) * 8 + (joint_row - kTokenOutputs),
+                              total, round + 1);
+                } else if (total == total) {          // NaN never wins
+                    float sc = total;
+                    if (sc == 0.0f) sc = 0.0f;
+                    const unsigned bits = __float_as_uint(sc);
+                    const unsigned ordered = (bits & 0x80000000u) ? ~bits : (bits ^ 0x80000000u);
+                    const unsigned long long key = (static_cast<unsigned long long>(ordered) << 32) |
+                        (static_cast<unsigned long long>(2047 - joint_row) << 21) | epoch;
+                    atomicMax(&sm.best[u], key);
+                }
+            }
+        }
+        __syncthreads();
+        if (tid < U && !sm.done[tid]) {
+            // a CTA whose rows all produced NaN still publishes a (losing) key for this round
+            const unsigned long long key = sm.best[tid] != 0ull ? sm.best[tid]
+                : ((static_cast<unsigned long long>(2047 - kTokenOutputs) << 21) | epoch);
+            asm volatile("st.relaxed.gpu.global.u64 [%0], %1;"
+                         ::"l"(xk + (static_cast<size_t>(round & 1) * U + tid) * kXMaxGrid + cta), "l"(key) : "memory");
+            sm.best[tid] = 0ull;
+        }
+        __syncthreads();
+
+        // ---- decision: the best key over all CTAs, first strict maximum of the durations
+        {
+            bool good = true;
+            for (int i = tid; i < U * G; i += kXThreads) {
+                const int u = i / G, c = i % G;
+                if (sm.done[u]) continue;
+                const unsigned long long* slot = xk + (static_cast<size_t>(round & 1) * U + u) * kXMaxGrid + c;
+                unsigned long long v = xch_load(slot);
+                if ((static_cast<unsigned>(v) & kEpochMask) != epoch) {
+                    const long long start = clock64();
+                    unsigned polls = 0;
+                    do {
+                        v = xch_load(slot);
+                        if ((++polls & 127u) == 0u &&
+                            (*abort_flag != 0 || clock64() - start > 2000000000ll)) {
+                            *abort_flag = 1;
+                            good = false;
+                            break;
+                        }
+                    } while ((static_cast<unsigned>(v) & kEpochMask) != epoch);
+                }
+                if (good) atomicMax(&sm.best[u], v);
+            }
+            if (!good) sm.ok = 0;
+        }
+        __syncthreads();
+        if (sm.ok == 0) break;
+        if (tid < U && !sm.done[tid]) {
+            const int u = tid;
+            const int token = 2047 - static_cast<int>((sm.best[u] >> 21) & 0x7FFull);
+            float dl[kDurations];
+            bool good = true;
+            for (int i = 0; i < kDurations; ++i)
+                good &= xch_wait(xd + (static_cast<size_t>(round & 1) * U + u) * 8 + i, round + 1, &dl[i], abort_flag);
+            if (!good) sm.ok = 0;
+            int duration = 0;
+            for (int i = 1; i < kDurations; ++i)
+                if (dl[i] > dl[duration]) duration = i;
+            if (token != kBlank) {
+                if (cta == 0 && sm.count[u] < p.max_tokens) {
+                    p.tokens[static_cast<size_t>(u) * p.max_tokens + sm.count[u]] = token;
+                    if (p.durations_out != nullptr)
+                        p.durations_out[static_cast<size_t>(u) * p.max_tokens + sm.count[u]] = duration;
+                }
+                sm.count[u] += 1;
+                sm.last[u] = token;
+                sm.emitted[u] = 1;
+                sm.valid[u] = 0;
+            }
+            sm.symbols[u] += 1;
+            sm.frame[u] += duration;
+            if (duration != 0 || sm.symbols[u] == kMaxSymbols) {
+                if (duration == 0) sm.frame[u] += 1;
+                sm.symbols[u] = 0;
+            }
+            if (sm.frame[u] >= p.frames[u]) sm.done[u] = 1;
+        }
+        __syncthreads();
+        round += 1;
+    }
+    __syncthreads();
+    if (cta == 0 && tid < U) p.counts[tid] = min(sm.count[tid], p.max_tokens);
+    if (sm.ok == 0 && tid == 0 && p.status != nullptr) atomicExch(p.status, 2);
+}
+
+}  // namespace pk100
+
 using namespace pk100;
 
 namespace {
@@ -391,10 +825,11 @@ int check_weights(const pk100_decoder_weights* w) {
 
 extern "C" long long pk100_tdt_workspace_bytes(int utterances) {
     if (utterances <= 0 || utterances > kMaxUtt) return 0;
-    return static_cast<long long>(dec_layout(utterances).total);
+    const size_t a = dec_layout(utterances).total, b = pk100::xch_layout(utterances).total;
+    return static_cast<long long>(a > b ? a : b);
 }
 
-extern "C" int pk100_tdt_decode(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+extern "C" int pk100_tdt_decode_barrier(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
                                 int utterances, int seg_stride, const int* frames, void* workspace,
                                 int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
                                 int* status) {
@@ -449,6 +884,67 @@ extern "C" int pk100_tdt_decode(void* stream_v, const pk100_decoder_weights* w, 
     // which the grid barrier needs
     err = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(tdt_greedy_kernel), dim3(grid),
                                       dim3(kDecThreads), args, smem, stream);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return static_cast<int>(err);
+    }
+    pk100_count_launch();
+    return PK100_OK;
+}
+
+extern "C" int pk100_tdt_decode(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+                                int utterances, int seg_stride, const int* frames, void* workspace,
+                                int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                                int* status) {
+    const int rc = check_weights(w);
+    if (rc != PK100_OK) return rc;
+    if (!enc_proj || !frames || !workspace || !tokens || !counts) return PK100_ERR_NULL;
+    if (utterances == 0) return PK100_OK;
+    if (utterances < 0 || seg_stride <= 0 || max_tokens <= 0) return PK100_ERR_SHAPE;
+    if (utterances > kMaxUtt) return PK100_ERR_LIMIT;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // 20 warps per CTA own (5 hidden units x 4 gates): the grid must cover 640 units with
+    // at most 5 per CTA and 1030 joint rows with at most 8 per CTA
+    if (sms < 129 || sms > kXMaxGrid) return pk100_tdt_decode_barrier(stream_v, w, enc_proj, utterances,
+                                                                      seg_stride, frames, workspace, tokens,
+                                                                      durations, counts, max_tokens, status);
+    const int grid = sms;
+    cudaError_t err = cudaFuncSetAttribute(tdt_exchange_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(sizeof(XSmem)));
+    if (err != cudaSuccess) return static_cast<int>(err);
+    DecParams p{};
+    p.enc_proj = static_cast<const __half*>(enc_proj);
+    p.seg_stride = seg_stride;
+    p.frames = frames;
+    p.utts = utterances;
+    p.layers = w->layers;
+    p.embedding = static_cast<const __half*>(w->embedding);
+    for (int l = 0; l < w->layers; ++l) {
+        p.w_ih[l] = static_cast<const __half*>(w->w_ih[l]);
+        p.w_hh[l] = static_cast<const __half*>(w->w_hh[l]);
+        p.b_ih[l] = w->b_ih[l];
+        p.b_hh[l] = w->b_hh[l];
+    }
+    p.w_pred = static_cast<const __half*>(w->w_pred);
+    p.b_pred = w->b_pred;
+    p.w_joint = static_cast<const __half*>(w->w_joint);
+    p.b_joint = w->b_joint;
+    p.workspace = static_cast<uint8_t*>(workspace);
+    p.tokens = tokens;
+    p.durations_out = durations;
+    p.counts = counts;
+    p.max_tokens = max_tokens;
+    p.status = status;
+    // tags start at 1, so a cleared workspace holds no valid entry
+    err = cudaMemsetAsync(workspace, 0, xch_layout(utterances).total, stream);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    void* args[] = {&p};
+    // cooperative launch = the runtime guarantees all CTAs are co-resident (they poll each other)
+    err = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(tdt_exchange_kernel), dim3(grid),
+                                      dim3(kXThreads), args, sizeof(XSmem), stream);
     if (err != cudaSuccess) {
         cudaGetLastError();
         return static_cast<int>(err);

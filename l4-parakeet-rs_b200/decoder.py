@@ -27,6 +27,8 @@ L.lib.pk100_tdt_workspace_bytes.restype = C.c_longlong
 L.lib.pk100_tdt_decode.argtypes = [vp, C.POINTER(DecoderWeightsC), vp, C.c_int, C.c_int, vp, vp, vp, vp,
                                    vp, C.c_int, vp]
 L.lib.pk100_tdt_decode.restype = C.c_int
+L.lib.pk100_tdt_decode_barrier.argtypes = L.lib.pk100_tdt_decode.argtypes
+L.lib.pk100_tdt_decode_barrier.restype = C.c_int
 
 
 class TdtDecoder:
@@ -69,7 +71,7 @@ class TdtDecoder:
         return ops.gemm(encoded, self.t["w_enc"], kind=L.KIND_F16, out=out, bias=self.t["b_enc"])
 
     def decode(self, enc_proj, utterances, seg_stride, frames, max_tokens, tokens=None, durations=None,
-               counts=None):
+               counts=None, barrier_kernel=False):
         """frames: int32 CUDA tensor [utterances].  Returns (tokens, durations, counts) CUDA tensors."""
         if tokens is None:
             tokens = torch.zeros((utterances, max_tokens), dtype=torch.int32, device=self.device)
@@ -77,7 +79,8 @@ class TdtDecoder:
             durations = torch.zeros((utterances, max_tokens), dtype=torch.int32, device=self.device)
         if counts is None:
             counts = torch.zeros(utterances, dtype=torch.int32, device=self.device)
-        rc = L.lib.pk100_tdt_decode(torch.cuda.current_stream().cuda_stream, C.byref(self.c),
+        fn = L.lib.pk100_tdt_decode_barrier if barrier_kernel else L.lib.pk100_tdt_decode
+        rc = fn(torch.cuda.current_stream().cuda_stream, C.byref(self.c),
                                     enc_proj.data_ptr(), utterances, seg_stride, frames.data_ptr(),
                                     self.workspace.data_ptr(), tokens.data_ptr(), durations.data_ptr(),
                                     counts.data_ptr(), max_tokens, self.status.data_ptr())
