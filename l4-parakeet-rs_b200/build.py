@@ -16,7 +16,7 @@ NVCC_FLAGS = [
     "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-O3",
     "--expt-relaxed-constexpr",
-]
+] + os.environ.get("PK100_EXTRA_NVCC_FLAGS", "").split()
 
 
 def _nvcc() -> str:

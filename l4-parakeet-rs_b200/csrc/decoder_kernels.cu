@@ -373,10 +373,9 @@ namespace pk100 {
 // ===========================================================================
 // Exchange-based decoder (the hot-path kernel).
 //
-// Same slicing of the work across one CTA per SM, but (a) every weight slice lives in
-// REGISTERS (each of the 20 warps owns one gate row of one hidden unit, one prediction
-// row and one joint row; a lane keeps its 20-element slices as half2), and (b) there
-// is no grid barrier: producers publish every value together with a tag
+// Same slicing of the work across one CTA per SM (every weight slice resident in shared
+// memory; each of the 20 warps owns one gate row of one hidden unit and computes it for
+// all utterances at once), but there is no grid barrier: producers publish every value together with a tag
 // ({fp32 value, u32 tag} in one 64-bit store) and consumers poll the data itself until
 // the tag matches the version they need.  Tags are the per-utterance LSTM version for
 // hidden states / prediction vectors and the round number for the joint decisions, so
@@ -434,6 +433,37 @@ __device__ __forceinline__ bool xch_wait(const unsigned long long* slot, unsigne
     return true;
 }
 
+
+// Column `c` of up to 8 utterances at once: all loads are issued before any tag is
+// checked, so a phase costs one memory round trip when the data is already there.
+// slot(u) = base + u * stride; want[u] == 0 means "skip utterance u".
+__device__ __forceinline__ bool xch_wait8(const unsigned long long* base, size_t stride, const unsigned (&want)[8],
+                                          const size_t (&offset)[8], float (&value)[8], volatile int* abort_flag) {
+    unsigned long long v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+        if (want[u] != 0u) v[u] = xch_load(base + u * stride + offset[u]);
+    bool good = true;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        if (want[u] == 0u) continue;
+        if (static_cast<unsigned>(v[u] >> 32) != want[u]) {
+            const long long start = clock64();
+            unsigned polls = 0;
+            do {
+                v[u] = xch_load(base + u * stride + offset[u]);
+                if ((++polls & 127u) == 0u && (*abort_flag != 0 || clock64() - start > 2000000000ll)) {
+                    *abort_flag = 1;
+                    good = false;
+                    break;
+                }
+            } while (static_cast<unsigned>(v[u] >> 32) != want[u]);
+        }
+        value[u] = __uint_as_float(static_cast<unsigned>(v[u]));
+    }
+    return good;
+}
+
 // Sum 8 per-lane partials across the warp with 9 shuffles.  On return every lane holds
 // the total of utterance  u = 4*bit4(lane) + 2*bit3(lane) + bit2(lane).
 __device__ __forceinline__ float reduce8(const float (&v)[8], int lane) {
@@ -487,18 +517,31 @@ struct XSmem {
     float pred[kMaxUtt][kHidden];        // cached prediction vectors
     float gate[kMaxUtt][8][4];           // [utt][unit slot][gate]
     float cstate[2][2][8][kMaxUtt];      // [layer][version parity][unit slot][utt]
+    __half w_lstm[2][5][8][kHidden];     // [layer][unit slot][ih gates 0-3 | hh gates 0-3]
     __half w_pred[8][kHidden];           // this CTA's prediction-projection rows
     __half w_joint[8][kHidden];          // this CTA's joint rows
     float bias[2][8][4];                 // b_ih + b_hh per owned unit and gate
     float pred_bias[8];
     float joint_bias[8];
     unsigned long long best[kMaxUtt];
+    unsigned long long rowkey[kMaxUtt][8];   // this CTA's joint rows: one key per (utterance, row slot)
+    float dur[kMaxUtt][8];
     int frame[kMaxUtt], symbols[kMaxUtt], last[kMaxUtt], count[kMaxUtt], ver[kMaxUtt], pred_ver[kMaxUtt];
     unsigned char emitted[kMaxUtt], valid[kMaxUtt], done[kMaxUtt], need[kMaxUtt];
     int ok;
 };
 
+#ifdef PK100_DEC_PROFILE
+#define PK_STAMP(i) do { if (tid == 0) { const long long now__ = clock64(); prof[i] += now__ - last_stamp; last_stamp = now__; } } while (0)
+#else
+#define PK_STAMP(i) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecParams p) {
+#ifdef PK100_DEC_PROFILE
+    long long prof[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+    long long last_stamp = clock64();
+#endif
     extern __shared__ __align__(16) uint8_t xs_raw[];
     XSmem& sm = *reinterpret_cast<XSmem*>(xs_raw);
     const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
@@ -517,15 +560,13 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
     const int my_unit_slot = warp / 4, my_gate = warp % 4;
     const int my_unit = cta + G * my_unit_slot;
     const bool lstm_warp = my_unit_slot < units && my_unit < kHidden;
-    __half2 w_ih[2][10], w_hh[2][10];
-#pragma unroll
-    for (int l = 0; l < 2; ++l) {
-#pragma unroll
-        for (int m = 0; m < 10; ++m) { w_ih[l][m] = __float2half2_rn(0.0f); w_hh[l][m] = w_ih[l][m]; }
-        if (l < p.layers && lstm_warp) {
-            load_row_slices(p.w_ih[l] + (static_cast<size_t>(my_gate) * kHidden + my_unit) * kHidden, lane, w_ih[l]);
-            load_row_slices(p.w_hh[l] + (static_cast<size_t>(my_gate) * kHidden + my_unit) * kHidden, lane, w_hh[l]);
-        }
+    for (int i = tid; i < 2 * 5 * 8 * kHidden; i += kXThreads) {
+        const int c = i % kHidden, r = (i / kHidden) % 8, slot = (i / (8 * kHidden)) % 5, l = i / (5 * 8 * kHidden);
+        const int unit = cta + G * slot;
+        __half v = __float2half(0.0f);
+        if (l < p.layers && slot < units && unit < kHidden)
+            v = (r < 4 ? p.w_ih[l] : p.w_hh[l])[(static_cast<size_t>(r & 3) * kHidden + unit) * kHidden + c];
+        sm.w_lstm[l][slot][r][c] = v;
     }
     const int pred_row = cta + G * warp;
     const bool pred_warp = warp < units && pred_row < kHidden;
@@ -575,41 +616,49 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
         if (!any_running || sm.ok == 0) break;
         if (tid < kMaxUtt) sm.need[tid] = tid < U && !sm.done[tid] && !sm.valid[tid];
         __syncthreads();
+        PK_STAMP(0);
 
         if (any_need) {
-#pragma unroll
-            for (int l = 0; l < 2; ++l) {       // unrolled so the weight registers are indexed statically
-                if (l >= p.layers || sm.ok == 0) break;
+            for (int l = 0; l < p.layers; ++l) {
+                if (sm.ok == 0) break;
                 // input of layer l: embedding of the last token (layer 0) or the lower layer's
                 // fresh hidden state, which arrives through the exchange buffer
+                // (one thread per column: kXThreads == kHidden)
                 if (l == 0) {
-                    for (int i = tid; i < U * kHidden; i += kXThreads) {
-                        const int u = i / kHidden, c = i % kHidden;
-                        if (!sm.need[u]) continue;
-                        sm.x[u][c] = sm.emitted[u]
-                            ? __half2float(p.embedding[static_cast<size_t>(sm.last[u]) * kHidden + c]) : 0.0f;
-                    }
+                    __half e[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (u < U && sm.need[u] && sm.emitted[u])
+                            e[u] = __ldg(p.embedding + static_cast<size_t>(sm.last[u]) * kHidden + tid);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (u < U && sm.need[u]) sm.x[u][tid] = sm.emitted[u] ? __half2float(e[u]) : 0.0f;
                 } else {
-                    bool good = true;
-                    for (int i = tid; i < U * kHidden; i += kXThreads) {
-                        const int u = i / kHidden, c = i % kHidden;
-                        if (!sm.need[u]) continue;
-                        const unsigned tag = static_cast<unsigned>(sm.ver[u] + 1);
-                        float v;
-                        good &= xch_wait(xh + ((static_cast<size_t>(l - 1) * 2 + (tag & 1)) * U + u) * kHidden + c,
-                                         tag, &v, abort_flag);
-                        sm.x[u][c] = v;
+                    unsigned want[8];
+                    size_t off[8];
+                    float val[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        want[u] = (u < U && sm.need[u]) ? static_cast<unsigned>(sm.ver[u] + 1) : 0u;
+                        off[u] = (static_cast<size_t>(l - 1) * 2 + (want[u] & 1)) * U * kHidden + tid;
                     }
-                    if (!good) sm.ok = 0;
+                    if (!xch_wait8(xh, kHidden, want, off, val, abort_flag)) sm.ok = 0;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (want[u] != 0u) sm.x[u][tid] = val[u];
                 }
                 __syncthreads();
+                PK_STAMP(1);
                 if (sm.ok == 0) break;
                 if (lstm_warp) {
                     float acc[8];
 #pragma unroll
                     for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
-                    dot8(w_ih[l], &sm.x[0][0], lane, acc);
-                    dot8(w_hh[l], &sm.hcur[l][0][0], lane, acc);
+                    __half2 wv[10];
+                    load_row_slices(sm.w_lstm[l][my_unit_slot][my_gate], lane, wv);
+                    dot8(wv, &sm.x[0][0], lane, acc);
+                    load_row_slices(sm.w_lstm[l][my_unit_slot][4 + my_gate], lane, wv);
+                    dot8(wv, &sm.hcur[l][0][0], lane, acc);
                     const float total = reduce8(acc, lane);
                     const int u = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
                     if ((lane & 3) == 0) sm.gate[u][my_unit_slot][my_gate] = total + sm.bias[l][my_unit_slot][my_gate];
@@ -638,24 +687,27 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
                     }
                 }
                 __syncthreads();
+                PK_STAMP(2);
             }
             if (sm.ok == 0) break;
             // ---- top layer's fresh hidden state -> committed copy + prediction projection
             {
                 const int top = p.layers - 1;
-                bool good = true;
-                for (int i = tid; i < U * kHidden; i += kXThreads) {
-                    const int u = i / kHidden, c = i % kHidden;
-                    if (!sm.need[u]) continue;
-                    const unsigned tag = static_cast<unsigned>(sm.ver[u] + 1);
-                    float v;
-                    good &= xch_wait(xh + ((static_cast<size_t>(top) * 2 + (tag & 1)) * U + u) * kHidden + c,
-                                     tag, &v, abort_flag);
-                    sm.hcur[top][u][c] = v;
+                unsigned want[8];
+                size_t off[8];
+                float val[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    want[u] = (u < U && sm.need[u]) ? static_cast<unsigned>(sm.ver[u] + 1) : 0u;
+                    off[u] = (static_cast<size_t>(top) * 2 + (want[u] & 1)) * U * kHidden + tid;
                 }
-                if (!good) sm.ok = 0;
+                if (!xch_wait8(xh, kHidden, want, off, val, abort_flag)) sm.ok = 0;
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (want[u] != 0u) sm.hcur[top][u][tid] = val[u];
             }
             __syncthreads();
+            PK_STAMP(3);
             if (sm.ok == 0) break;
             if (pred_warp) {
                 float acc[8];
@@ -675,28 +727,33 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
             __syncthreads();
             if (tid < U && sm.need[tid]) { sm.ver[tid] += 1; sm.valid[tid] = 1; }
             __syncthreads();
+            PK_STAMP(4);
         }
 
         // ---- joint: refresh cached prediction vectors whose version changed, build relu(enc + pred)
         {
-            bool good = true;
-            for (int i = tid; i < U * kHidden; i += kXThreads) {
-                const int u = i / kHidden, c = i % kHidden;
-                if (sm.done[u]) continue;
-                if (sm.pred_ver[u] != sm.ver[u]) {
-                    const unsigned tag = static_cast<unsigned>(sm.ver[u]);
-                    float v;
-                    good &= xch_wait(xp + (static_cast<size_t>(tag & 1) * U + u) * kHidden + c, tag, &v, abort_flag);
-                    sm.pred[u][c] = v;
-                }
-                const float e = __half2float(
-                    p.enc_proj[(static_cast<size_t>(u) * p.seg_stride + sm.frame[u]) * kHidden + c]);
-                sm.x[u][c] = fmaxf(e + sm.pred[u][c], 0.0f);
+            unsigned want[8];
+            size_t off[8];
+            float val[8];
+            __half e[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool live = u < U && !sm.done[u];
+                want[u] = (live && sm.pred_ver[u] != sm.ver[u]) ? static_cast<unsigned>(sm.ver[u]) : 0u;
+                off[u] = static_cast<size_t>(want[u] & 1) * U * kHidden + tid;
+                if (live)
+                    e[u] = __ldg(p.enc_proj + (static_cast<size_t>(u) * p.seg_stride + sm.frame[u]) * kHidden + tid);
             }
-            if (!good) sm.ok = 0;
-            if (tid < kMaxUtt) sm.best[tid] = 0ull;
+            if (!xch_wait8(xp, kHidden, want, off, val, abort_flag)) sm.ok = 0;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (u >= U || sm.done[u]) continue;
+                if (want[u] != 0u) sm.pred[u][tid] = val[u];
+                sm.x[u][tid] = fmaxf(__half2float(e[u]) + sm.pred[u][tid], 0.0f);
+            }
         }
         __syncthreads();
+        PK_STAMP(5);
         if (sm.ok == 0) break;
         if (tid < U) sm.pred_ver[tid] = sm.ver[tid];
         const unsigned epoch = (round + 1) & kEpochMask;
@@ -710,6 +767,7 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
             const float total = reduce8(acc, lane) + sm.joint_bias[warp];
             const int u = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
             if ((lane & 3) == 0 && u < U && !sm.done[u]) {
+                unsigned long long key = 0ull;
                 if (joint_row >= kTokenOutputs) {
                     xch_store(xd + (static_cast<size_t>(round & 1) * U + u) * 8 + (joint_row - kTokenOutputs),
                               total, round + 1);
@@ -718,58 +776,89 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
                     if (sc == 0.0f) sc = 0.0f;
                     const unsigned bits = __float_as_uint(sc);
                     const unsigned ordered = (bits & 0x80000000u) ? ~bits : (bits ^ 0x80000000u);
-                    const unsigned long long key = (static_cast<unsigned long long>(ordered) << 32) |
-                        (static_cast<unsigned long long>(2047 - joint_row) << 21) | epoch;
-                    atomicMax(&sm.best[u], key);
+                    key = (static_cast<unsigned long long>(ordered) << 32) |
+                          (static_cast<unsigned long long>(2047 - joint_row) << 21) | epoch;
                 }
+                sm.rowkey[u][warp] = key;
             }
+        } else if (warp < 8 && (lane & 3) == 0) {
+            const int u = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+            sm.rowkey[u][warp] = 0ull;
         }
         __syncthreads();
+        PK_STAMP(6);
         if (tid < U && !sm.done[tid]) {
+            unsigned long long best = 0ull;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) best = sm.rowkey[tid][w] > best ? sm.rowkey[tid][w] : best;
             // a CTA whose rows all produced NaN still publishes a (losing) key for this round
-            const unsigned long long key = sm.best[tid] != 0ull ? sm.best[tid]
-                : ((static_cast<unsigned long long>(2047 - kTokenOutputs) << 21) | epoch);
+            if (best == 0ull) best = (static_cast<unsigned long long>(2047 - kTokenOutputs) << 21) | epoch;
             asm volatile("st.relaxed.gpu.global.u64 [%0], %1;"
-                         ::"l"(xk + (static_cast<size_t>(round & 1) * U + tid) * kXMaxGrid + cta), "l"(key) : "memory");
-            sm.best[tid] = 0ull;
+                         ::"l"(xk + (static_cast<size_t>(round & 1) * U + tid) * kXMaxGrid + cta), "l"(best) : "memory");
         }
-        __syncthreads();
 
-        // ---- decision: the best key over all CTAs, first strict maximum of the durations
-        {
+        // ---- decision: warp u reduces the keys of all CTAs for utterance u (loads in flight
+        // together, shuffle reduction) and fetches the five duration logits
+        if (warp < U && !sm.done[warp]) {
+            const int u = warp;
+            const unsigned long long* row = xk + (static_cast<size_t>(round & 1) * U + u) * kXMaxGrid;
+            unsigned long long v[8];
             bool good = true;
-            for (int i = tid; i < U * G; i += kXThreads) {
-                const int u = i / G, c = i % G;
-                if (sm.done[u]) continue;
-                const unsigned long long* slot = xk + (static_cast<size_t>(round & 1) * U + u) * kXMaxGrid + c;
-                unsigned long long v = xch_load(slot);
-                if ((static_cast<unsigned>(v) & kEpochMask) != epoch) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int c = lane + 32 * j;
+                v[j] = c < G ? xch_load(row + c) : 0ull;
+            }
+            unsigned long long dv = 0ull;
+            const unsigned long long* dslot = xd + (static_cast<size_t>(round & 1) * U + u) * 8 + lane;
+            if (lane < kDurations) dv = xch_load(dslot);
+            unsigned long long best = 0ull;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int c = lane + 32 * j;
+                if (c >= G) continue;
+                if ((static_cast<unsigned>(v[j]) & kEpochMask) != epoch) {
                     const long long start = clock64();
                     unsigned polls = 0;
                     do {
-                        v = xch_load(slot);
-                        if ((++polls & 127u) == 0u &&
-                            (*abort_flag != 0 || clock64() - start > 2000000000ll)) {
+                        v[j] = xch_load(row + c);
+                        if ((++polls & 127u) == 0u && (*abort_flag != 0 || clock64() - start > 2000000000ll)) {
                             *abort_flag = 1;
                             good = false;
                             break;
                         }
-                    } while ((static_cast<unsigned>(v) & kEpochMask) != epoch);
+                    } while ((static_cast<unsigned>(v[j]) & kEpochMask) != epoch);
                 }
-                if (good) atomicMax(&sm.best[u], v);
+                best = v[j] > best ? v[j] : best;
             }
-            if (!good) sm.ok = 0;
+            if (lane < kDurations && static_cast<unsigned>(dv >> 32) != round + 1) {
+                const long long start = clock64();
+                unsigned polls = 0;
+                do {
+                    dv = xch_load(dslot);
+                    if ((++polls & 127u) == 0u && (*abort_flag != 0 || clock64() - start > 2000000000ll)) {
+                        *abort_flag = 1;
+                        good = false;
+                        break;
+                    }
+                } while (static_cast<unsigned>(dv >> 32) != round + 1);
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off /= 2) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, off);
+                best = other > best ? other : best;
+            }
+            if (lane == 0) sm.best[u] = best;
+            if (lane < kDurations) sm.dur[u][lane] = __uint_as_float(static_cast<unsigned>(dv));
+            if (!__all_sync(0xffffffffu, good)) sm.ok = 0;
         }
         __syncthreads();
+        PK_STAMP(7);
         if (sm.ok == 0) break;
         if (tid < U && !sm.done[tid]) {
             const int u = tid;
             const int token = 2047 - static_cast<int>((sm.best[u] >> 21) & 0x7FFull);
-            float dl[kDurations];
-            bool good = true;
-            for (int i = 0; i < kDurations; ++i)
-                good &= xch_wait(xd + (static_cast<size_t>(round & 1) * U + u) * 8 + i, round + 1, &dl[i], abort_flag);
-            if (!good) sm.ok = 0;
+            const float* dl = sm.dur[u];
             int duration = 0;
             for (int i = 1; i < kDurations; ++i)
                 if (dl[i] > dl[duration]) duration = i;
@@ -793,10 +882,17 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
             if (sm.frame[u] >= p.frames[u]) sm.done[u] = 1;
         }
         __syncthreads();
+        PK_STAMP(8);
         round += 1;
     }
     __syncthreads();
+#ifdef PK100_DEC_PROFILE
+    if (cta == 0 && tid == 0)
+        for (int i = 0; i < 10; ++i) reinterpret_cast<volatile long long*>(p.workspace + lay.abort)[2 + i] = prof[i];
+#endif
     if (cta == 0 && tid < U) p.counts[tid] = min(sm.count[tid], p.max_tokens);
+    // number of lockstep rounds of this decode, for diagnostics (second word of the flag area)
+    if (cta == 0 && tid == 0) reinterpret_cast<volatile int*>(p.workspace + lay.abort)[2] = static_cast<int>(round);
     if (sm.ok == 0 && tid == 0 && p.status != nullptr) atomicExch(p.status, 2);
 }
 

@@ -192,7 +192,7 @@ def calibrate_tau(stats, zero_fraction=0.7, window=0.03):
     return F32((np.float64(s[best - 1]) + np.float64(s[best])) * 0.5)
 
 
-def ff_expand(xq, w1q, w1_scales, rows, tau, row_scale=FP8_INPUT_SCALE):
+def ff_expand(xq, w1q, w1_scales, rows, tau, row_scale=FP8_INPUT_SCALE, keep_override=None):
     """FP8 GEMM 1024->4096 + SiLU + tile threshold + fixed INT8 quantisation.
 
     h32 = SiLU(acc * (8/448) * ws[n]) (kernels/sm89/encoder.cu:973-1005, epilogue 0);
@@ -204,6 +204,8 @@ def ff_expand(xq, w1q, w1_scales, rows, tau, row_scale=FP8_INPUT_SCALE):
     h32[rows:] = 0
     stats = tile_stats(h32, rows)
     keep = (stats >= F32(tau)).astype(np.uint8)
+    if keep_override is not None:      # decisions imposed by the caller (ambiguous tiles)
+        keep = np.asarray(keep_override, dtype=np.uint8).reshape(keep.shape)
     hq = codec.quantize_int8(f16_round(h32), INT8_HIDDEN_INV)
     m = hq.shape[0]
     mask = np.repeat(np.repeat(keep, SPARSE_TILE_ROWS, axis=0)[:m], SPARSE_TILE_COLS, axis=1)
@@ -354,19 +356,19 @@ def prepare_layer(w):
     return p
 
 
-def ff_module(x16, p, ff, valid, tau, xq=None):
+def ff_module(x16, p, ff, valid, tau, xq=None, keep=None):
     if xq is None:
         xq = ln_quant_fp8_fixed(x16, p[f"ln_{ff}_g"], p[f"ln_{ff}_b"], valid)
-    hq, keep, stats = ff_expand(xq, p[f"{ff}_w1q"], p[f"{ff}_w1s"], valid, tau)
+    hq, keep, stats = ff_expand(xq, p[f"{ff}_w1q"], p[f"{ff}_w1s"], valid, tau, keep_override=keep)
     return ff_contract(hq, p[f"{ff}_w2q"], p[f"{ff}_w2s"], x16), stats, keep
 
 
-def encoder_layer(x16, p, valid, tau1, tau2, next_ln=None, collect=None):
+def encoder_layer(x16, p, valid, tau1, tau2, next_ln=None, collect=None, keep1=None, keep2=None):
     """One FastConformer block on one utterance ([rows,1024], first `valid` rows live).
     Returns (output norm, fp16) and, when `next_ln` = (gamma, beta) is given, also the
     E4M3 bytes of the next block's first LayerNorm (the fused pair form)."""
     x = np.asarray(x16, dtype=F32)
-    x, st1, _ = ff_module(x, p, "ff1", valid, tau1)
+    x, st1, _ = ff_module(x, p, "ff1", valid, tau1, keep=keep1)
     n2 = layer_norm(x, p["ln_att_g"], p["ln_att_b"], valid)
     q8, qs = quant_rows_int8_dynamic(n2, valid)
     qkv = linear_int8(q8, p["wqkv_q"], p["wqkv_s"], qs)
@@ -380,7 +382,7 @@ def encoder_layer(x16, p, valid, tau1, tau2, next_ln=None, collect=None):
     d = depthwise_bn_silu(g, p["dw"], p["bn_g"], p["bn_b"], p["bn_m"], p["bn_v"], valid)
     d8, ds = quant_rows_fp8_dynamic(d, valid)
     x = linear_fp8(d8, p["wpw2_q"], p["wpw2_s"], ds, residual16=x, alpha=1.0)
-    x, st2, _ = ff_module(x, p, "ff2", valid, tau2)
+    x, st2, _ = ff_module(x, p, "ff2", valid, tau2, keep=keep2)
     out = layer_norm(x, p["ln_out_g"], p["ln_out_b"], valid)
     if collect is not None:
         collect.update(stats1=st1, stats2=st2, qkv=qkv, att=att, glu=g, dw=d, pre_norm=x)

@@ -20,6 +20,27 @@ def _input(seed, rows, valid):
     return x
 
 
+AMBIGUOUS = 0.02     # a tile whose statistic is within 2 % of tau may legitimately fall on either side
+
+
+def _oracle_layer_same_decisions(x, p, valid, tau1, tau2, gpu_stats):
+    """Oracle block whose tile decisions follow the GPU's wherever the oracle's own statistic
+    is within AMBIGUOUS of the threshold (a discontinuous operator: like an argmax tie, such a
+    tile has no single right answer); every other decision must agree exactly."""
+    mt = gpu_stats.shape[1]
+    info = {}
+    keeps = [None, None]
+    for which, tau in ((0, tau1), (1, tau2)):
+        O.encoder_layer(x, p, valid, tau1, tau2, collect=info, keep1=keeps[0], keep2=keeps[1])
+        own = info[f"stats{which + 1}"][:mt]
+        gpu_keep, own_keep = gpu_stats[which] >= tau, own >= tau
+        diff = gpu_keep != own_keep
+        if tau > 0:
+            assert np.all(np.abs(own[diff] / tau - 1.0) <= AMBIGUOUS), "an unambiguous tile decision differs"
+        keeps[which] = gpu_keep.astype(np.uint8)
+    return O.encoder_layer(x, p, valid, tau1, tau2, collect=info, keep1=keeps[0], keep2=keeps[1]), info
+
+
 def _oracle_layer_with_calibration(x, p, valid):
     info = {}
     O.encoder_layer(x, p, valid, 0.0, 0.0, collect=info)
@@ -49,6 +70,7 @@ def test_single_layer_single_utterance(pk, cuda, rows, valid):
     assert np.all(got[valid:] == 0)
     st = host(stats).reshape(2, -1, 64)
     assert np.allclose(st[0], info["stats1"], rtol=2e-3, atol=1e-5)
+    want, _ = _oracle_layer_same_decisions(x, p, valid, tau1, tau2, st)
     err = nrmse(got[:valid], want[:valid])
     assert err <= 1e-2, err
     assert np.max(np.abs(got - want)) <= 0.1
@@ -99,12 +121,15 @@ def test_batched_ragged_utterances_match_per_utterance_oracle(pk, cuda):
     a = dev16(np.concatenate(xs, axis=0))
     b = torch.zeros_like(a)
     sv = torch.tensor(valids, dtype=torch.int32, device=cuda)
-    out = host(enc.run(a, b, ws, len(valids), seg_stride, seg_stride, seg_valid=sv))
+    stats = torch.zeros((2, rows // 128 * 64), dtype=torch.float32, device=cuda)
+    out = host(enc.run(a, b, ws, len(valids), seg_stride, seg_stride, seg_valid=sv, tile_stats=stats))
     torch.cuda.synchronize()
     assert enc.status(arena, ws) == 0
+    st = host(stats).reshape(2, -1, 64)
+    per_seg = seg_stride // 128
     for i, v in enumerate(valids):
         blk = out[i * seg_stride:(i + 1) * seg_stride]
-        want = O.encoder_layer(xs[i], p, v, tau1, tau2)
+        want, _ = _oracle_layer_same_decisions(xs[i], p, v, tau1, tau2, st[:, i * per_seg:(i + 1) * per_seg])
         assert np.all(blk[v:] == 0)
         assert nrmse(blk[:v], want[:v]) <= 1e-2
 
@@ -131,8 +156,10 @@ def test_three_layer_stack_and_product_calibration(pk, cuda):
     cur = x
     for l, p in enumerate(ps):
         a, b = dev16(cur), torch.zeros((rows, 1024), dtype=torch.float16, device=cuda)
-        layer_out = host(enc.run(a, b, ws, 1, rows, valid, first=l, count=1))
-        want = O.encoder_layer(cur, p, valid, enc.layers[l].ff1.tau, enc.layers[l].ff2.tau)
+        stats = torch.zeros((2, rows // 128 * 64), dtype=torch.float32, device=cuda)
+        layer_out = host(enc.run(a, b, ws, 1, rows, valid, tile_stats=stats, first=l, count=1))
+        want, _ = _oracle_layer_same_decisions(cur, p, valid, enc.layers[l].ff1.tau, enc.layers[l].ff2.tau,
+                                               host(stats).reshape(2, -1, 64))
         assert nrmse(layer_out[:valid], want[:valid]) <= 1e-2, l
         cur = layer_out
     # one call over all layers equals the layer-by-layer runs bit for bit
