@@ -291,6 +291,27 @@ int pk100_tdt_decode(void* stream, const pk100_decoder_weights* weights, const v
                      int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
                      int* status);
 
+/* Decoder for hosts that may not allocate device memory.  It has no counterpart in the
+ * reference (there the Rust host allocates the decoder workspace itself,
+ * src/cuda/pipeline.rs:280-350).  Meant for embedders whose process owns a fixed CUDA memory
+ * arena and rejects cudaMalloc from plug-ins: pre-sized serving workers, real-time audio
+ * hosts, code called while another component is capturing the stream.
+ * Same arguments as pk100_tdt_decode minus `workspace`: the exchange scratch is a fixed
+ * 288 KiB device array inside the library image, present on every GPU that loads the
+ * library for the life of the process.  Limits and rules:
+ *   - at most PK100_DECODER_MAX_UTTERANCES utterances; more returns PK100_ERR_LIMIT and
+ *     launches nothing;
+ *   - the first call on each device looks the array's device address up (with that device
+ *     current) and remembers it; make that first call outside any stream capture;
+ *   - the array is shared by every call and keeps the previous call's contents; each call
+ *     clears the part it uses before its kernel starts (stream-ordered), so back-to-back
+ *     calls on one stream are fine, but two calls that overlap on the GPU (different
+ *     streams or threads) race on it -- serialise them;
+ *   - performs no cudaMalloc / cudaFree and calls no allocating library routine. */
+int pk100_tdt_decode_static(void* stream, const pk100_decoder_weights* weights, const void* enc_proj,
+                            int utterances, int seg_stride, const int* frames, int32_t* tokens,
+                            int32_t* durations, int32_t* counts, int max_tokens, int* status);
+
 /* Same contract, earlier design kept as a cross-check: weights in shared memory and a
  * bounded grid barrier between the phases (the structure of the reference kernel,
  * kernels/sm89/decoder.cu:227-414).  pk100_tdt_decode falls back to it on devices whose SM

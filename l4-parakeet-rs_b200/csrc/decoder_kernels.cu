@@ -988,6 +988,56 @@ extern "C" int pk100_tdt_decode_barrier(void* stream_v, const pk100_decoder_weig
     return PK100_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Entry point for callers that cannot allocate device memory.
+//
+// Some embedders of this library run inside a host that owns the CUDA memory pool and
+// forbids cudaMalloc from plug-in code (a serving process with a pre-sized arena, a
+// real-time audio host, code running between the nodes of somebody else's stream
+// capture).  For them the decoder's exchange scratch lives in the library image itself:
+// a file-scope device array of fixed size, resident on every GPU that loads the library
+// until the process exits.
+constexpr size_t kStaticScratchBytes = 288 * 1024;   // covers xch_layout(8) = 279 808 bytes
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address:
+// the address a kernel may dereference is looked up once per device.
+void* g_static_scratch_ptr[64] = {nullptr};
+
+int static_scratch_address(void** out) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    if (dev < 0 || dev >= 64) return PK100_ERR_LIMIT;
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, g_static_scratch);   // with device `dev` current
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            return static_cast<int>(err);
+        }
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return PK100_OK;
+}
+}  // namespace
+
+extern "C" int pk100_tdt_decode_static(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+                                       int utterances, int seg_stride, const int* frames, int32_t* tokens,
+                                       int32_t* durations, int32_t* counts, int max_tokens, int* status) {
+    if (utterances > kMaxUtt) return PK100_ERR_LIMIT;          // scratch is sized for 8 utterances
+    if (utterances > 0 && xch_layout(utterances).total > kStaticScratchBytes) return PK100_ERR_LIMIT;
+    void* scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != PK100_OK) return rc;
+    // pk100_tdt_decode clears the part of the scratch it uses (stream-ordered memset of
+    // existing memory) and launches the kernel: no allocation on this path
+    return pk100_tdt_decode(stream_v, w, enc_proj, utterances, seg_stride, frames, scratch, tokens, durations,
+                            counts, max_tokens, status);
+}
+
 extern "C" int pk100_tdt_decode(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
                                 int utterances, int seg_stride, const int* frames, void* workspace,
                                 int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,

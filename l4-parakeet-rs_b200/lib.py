@@ -57,6 +57,7 @@ SIGNATURES = {
     "pk100_tdt_workspace_bytes": None,
     "pk100_tdt_decode": None,
     "pk100_tdt_decode_barrier": None,
+    "pk100_tdt_decode_static": None,
     "pk100_subsampling_workspace_bytes": None,
     "pk100_run_subsampling": None,
     "pk100_launch_count": None,
