@@ -48,6 +48,12 @@ def parse_args():
                     help="LSTM layers of the prediction network (benchmark config: 1; the reference model: 2)")
     ap.add_argument("--layers", type=int, default=ENCODER_LAYERS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tau-cache", default=None,
+                    help="JSON file with calibrated tile thresholds: loaded if present, written otherwise")
+    ap.add_argument("--micro", default=None,
+                    choices=["ff_expand", "ff_contract", "qkv", "attention", "layer_norm", "decode"],
+                    help="time ONE kernel of the path on synthetic operands (used for ncu captures)")
+    ap.add_argument("--rows", type=int, default=6144, help="rows (M) of the --micro case")
     return ap.parse_args()
 
 
@@ -183,8 +189,109 @@ def workload_config(args):
         parallelism="utterance data-parallel, no collective on the compute path, host gather of tokens")
 
 
+def run_micro(args):
+    """One kernel of the path in isolation: `--micro NAME --rows M --steps K --warmup W`.
+    Prints a JSON line with the average launch time and the achieved rate."""
+    import numpy as np
+    import torch
+    pk = importlib.import_module("l4-parakeet-rs_b200")
+    L = pk.lib
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device="cpu").manual_seed(1)
+    m = args.rows
+    peaks = measured_peaks()
+
+    def rand16(*shape, std=1.0):
+        return (torch.randn(shape, generator=g) * std).half().to(dev)
+
+    if args.micro in ("ff_expand", "ff_contract", "qkv"):
+        if args.micro == "ff_expand":
+            x = rand16(m, 1024)
+            w = rand16(4096, 1024, std=0.02)
+            xq = pk.ops.quantize_fp8_fixed(x, 56.0)
+            wq, ws = pk.ops.pack_weight_rows(w, L.PACK_E4M3)
+            out = torch.empty((m, 4096), dtype=torch.int8, device=dev)
+            keep = torch.zeros(((m + 127) // 128, 64), dtype=torch.uint8, device=dev)
+            stats = torch.zeros(((m + 127) // 128, 64), dtype=torch.float32, device=dev)
+            fn = lambda tau=0.0: pk.ops.gemm(xq, wq, kind=L.KIND_E4M3, epilogue=L.EPI_SPARSE_OUT, out=out,
+                                             out_type=L.OUT_S8, out_scale=32.0, row_scale=8.0 / 448.0,
+                                             col_scales=ws, tau=tau, keep_out=keep, stats_out=stats)
+            fn()
+            torch.cuda.synchronize()
+            tau = pk.encoder.tau_for_zero_fraction(stats.cpu().numpy(), 0.7)
+            call = lambda: fn(tau)
+            flops, nbytes = 2.0 * m * 4096 * 1024, m * 1024 + 4096 * 1024 + m * 4096
+            peak, unit, bound = 2 * peaks["bf16"], "TFLOP/s", "tensor"
+        elif args.micro == "ff_contract":
+            h = torch.randint(-100, 100, (m, 4096), generator=g, dtype=torch.int8).to(dev)
+            keep_h = (torch.rand(((m + 127) // 128, 64), generator=g) < 0.3).to(torch.uint8)
+            mask = keep_h.repeat_interleave(128, 0)[:m].repeat_interleave(64, 1).to(dev)
+            h = h * mask.to(torch.int8)
+            keep = keep_h.to(dev)
+            w = rand16(1024, 4096, std=0.02)
+            wq, ws = pk.ops.pack_weight_rows(w, L.PACK_S8)
+            xres = rand16(m, 1024)
+            call = lambda: pk.ops.gemm(h, wq, kind=L.KIND_S8, out=xres, row_scale=1.0 / 32.0, col_scales=ws,
+                                       residual=xres, alpha=0.5, keep_in=keep)
+            live = float(keep_h.float().mean())
+            flops, nbytes = 2.0 * m * 4096 * 1024 * live, m * 4096 * live + 1024 * 4096 + 2 * m * 1024 * 2
+            peak, unit, bound = 2 * peaks["bf16"], "TOP/s (executed)", "tensor"
+        else:
+            x = rand16(m, 1024)
+            xq, xs = pk.ops.layer_norm(x, torch.ones(1024, device=dev).half(), torch.zeros(1024, device=dev).half(),
+                                       L.LN_S8_ROW)
+            wq, ws = pk.ops.pack_weight_rows(rand16(3072, 1024, std=0.02), L.PACK_S8)
+            out = torch.empty((m, 3072), dtype=torch.float16, device=dev)
+            call = lambda: pk.ops.gemm(xq, wq, kind=L.KIND_S8, out=out, row_scales=xs, col_scales=ws)
+            flops, nbytes = 2.0 * m * 3072 * 1024, m * 1024 + 3072 * 1024 + m * 3072 * 2
+            peak, unit, bound = 2 * peaks["bf16"], "TOP/s", "tensor"
+        work = flops / 1e12
+    elif args.micro == "attention":
+        seg = 768
+        segs = max(1, m // seg)
+        m = segs * seg
+        qkv = rand16(m, 3072)
+        pos, u, v = rand16(8, 272, 128), rand16(8, 128, std=0.02), rand16(8, 128, std=0.02)
+        out = torch.empty((m, 1024), dtype=torch.float16, device=dev)
+        call = lambda: pk.ops.local_attention(qkv[:, :1024], qkv[:, 1024:2048], qkv[:, 2048:], pos, u, v,
+                                              seg_stride=seg, valid_rows=750, out=out)
+        nbytes = m * 1024 * 2 * 4
+        work, peak, unit, bound = nbytes / 1e9, peaks["hbm_gbs"], "GB/s", "hbm"
+    elif args.micro == "layer_norm":
+        x = rand16(m, 1024)
+        gam, bet = torch.ones(1024, device=dev).half(), torch.zeros(1024, device=dev).half()
+        out = torch.empty((m, 1024), dtype=torch.uint8, device=dev)
+        call = lambda: pk.ops.layer_norm(x, gam, bet, L.LN_E4M3_FIXED, inv_scale=56.0, out=out)
+        nbytes = m * 1024 * 3
+        work, peak, unit, bound = nbytes / 1e9, peaks["hbm_gbs"], "GB/s", "hbm"
+    else:
+        dec = pk.decoder.TdtDecoder(pk.synth.decoder_weights(SEED, args.decoder_layers), dev)
+        enc = rand16(8 * 768, 640, std=0.5)
+        fr = torch.full((8,), min(750, max(1, args.rows)), dtype=torch.int32, device=dev)
+        call = lambda: dec.decode(enc, 8, 768, fr, 7500)
+        work, peak, unit, bound, nbytes = 0.0, 1.0, "rounds/s", "latency", 0
+    for _ in range(args.warmup):
+        call()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    achieved = work / (ms * 1e-3) if work else None
+    print(json.dumps(dict(micro=args.micro, rows=m, avg_launch_ms=ms, achieved=achieved, unit=unit, bound=bound,
+                          peak=peak, frac=(achieved / peak if achieved else None),
+                          algorithmic_bytes=nbytes, peak_source=peaks["source"])), flush=True)
+
+
 def main():
     args = parse_args()
+    if args.micro:
+        run_micro(args)
+        return
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -213,7 +320,15 @@ def main():
                                      seed=SEED, max_utterances=UTTERANCES_PER_GPU, mel_frames=MEL_FRAMES)
     mel_host = torch.from_numpy(np.stack([pk.synth.mel_input(100 + u, MEL_FRAMES) for u in my_utts])).pin_memory()
     eng.mel_dev.copy_(mel_host)
-    eng.calibrate(UTTERANCES_PER_GPU)          # load-time: tile thresholds for 70 % zero tiles
+    cache = Path(args.tau_cache) if args.tau_cache else None
+    if cache is not None and cache.exists():
+        taus = json.loads(cache.read_text())
+        for l, (t1, t2) in enumerate(taus):
+            eng.enc.set_tau(l, t1, t2)
+    else:
+        eng.calibrate(UTTERANCES_PER_GPU)      # load-time: tile thresholds for 70 % zero tiles
+        if cache is not None and rank == 0:
+            cache.write_text(json.dumps([[l.ff1.tau, l.ff2.tau] for l in eng.enc.layers]))
     eng.enable_gemm_timing()
     torch.cuda.synchronize()
 

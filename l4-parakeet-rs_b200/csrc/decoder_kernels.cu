@@ -17,6 +17,8 @@
 #include <float.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "pk100_internal.h"
 
 namespace pk100 {
@@ -440,28 +442,35 @@ __device__ __forceinline__ bool xch_wait(const unsigned long long* slot, unsigne
 __device__ __forceinline__ bool xch_wait8(const unsigned long long* base, size_t stride, const unsigned (&want)[8],
                                           const size_t (&offset)[8], float (&value)[8], volatile int* abort_flag) {
     unsigned long long v[8];
+    unsigned pending = 0;
 #pragma unroll
     for (int u = 0; u < 8; ++u)
-        if (want[u] != 0u) v[u] = xch_load(base + u * stride + offset[u]);
-    bool good = true;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-        if (want[u] == 0u) continue;
-        if (static_cast<unsigned>(v[u] >> 32) != want[u]) {
-            const long long start = clock64();
-            unsigned polls = 0;
-            do {
-                v[u] = xch_load(base + u * stride + offset[u]);
-                if ((++polls & 127u) == 0u && (*abort_flag != 0 || clock64() - start > 2000000000ll)) {
-                    *abort_flag = 1;
-                    good = false;
-                    break;
-                }
-            } while (static_cast<unsigned>(v[u] >> 32) != want[u]);
+        if (want[u] != 0u) {
+            pending |= 1u << u;
+            v[u] = xch_load(base + u * stride + offset[u]);
         }
-        value[u] = __uint_as_float(static_cast<unsigned>(v[u]));
+    long long start = 0;
+    unsigned polls = 0;
+    while (true) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if ((pending >> u) & 1u) {
+                if (static_cast<unsigned>(v[u] >> 32) == want[u]) {
+                    pending &= ~(1u << u);
+                    value[u] = __uint_as_float(static_cast<unsigned>(v[u]));
+                }
+            }
+        if (pending == 0u) return true;
+        if (polls == 0u) start = clock64();
+        if ((++polls & 63u) == 0u && (*abort_flag != 0 || clock64() - start > 2000000000ll)) {   // ~1 s
+            *abort_flag = 1;
+            return false;
+        }
+        // reload every entry that is still missing, all loads in flight together
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if ((pending >> u) & 1u) v[u] = xch_load(base + u * stride + offset[u]);
     }
-    return good;
 }
 
 // Sum 8 per-lane partials across the warp with 9 shuffles.  On return every lane holds
@@ -511,25 +520,60 @@ __device__ __forceinline__ void dot8(const __half2 (&w)[10], const float* x, int
     }
 }
 
+// Activations are kept as fp16 (hi, lo) pairs: x = hi + lo to ~2^-22, so the tiny GEMMs of
+// a round run on tensor cores (mma.sync m16n8k16, fp32 accumulate) without losing the fp32
+// state: rows 0-7 of an A tile hold the hi parts of utterances 0-7, rows 8-15 the lo parts,
+// and the two halves of each accumulator column are added after the MMA.
+constexpr int kAct = kHidden + 8;            // padded pitch (halves) of activation / weight rows
+constexpr int kLstmK = 2 * kHidden;          // [input | recurrent]
+constexpr int kLstmPitch = kLstmK + 8;
+constexpr int kLstmRows = 20;                // 5 hidden units x 4 gates per CTA
+
 struct XSmem {
-    float hcur[2][kMaxUtt][kHidden];     // committed hidden state per layer (all units)
-    float x[kMaxUtt][kHidden];           // LSTM input / joint input staging
-    float pred[kMaxUtt][kHidden];        // cached prediction vectors
-    float gate[kMaxUtt][8][4];           // [utt][unit slot][gate]
-    float cstate[2][2][8][kMaxUtt];      // [layer][version parity][unit slot][utt]
-    __half w_lstm[2][5][8][kHidden];     // [layer][unit slot][ih gates 0-3 | hh gates 0-3]
-    __half w_pred[8][kHidden];           // this CTA's prediction-projection rows
-    __half w_joint[8][kHidden];          // this CTA's joint rows
-    float bias[2][8][4];                 // b_ih + b_hh per owned unit and gate
+    __half wl[2][kLstmRows][kLstmPitch];  // [layer][unit slot * 4 + gate][w_ih row | w_hh row]
+    __half wp[8][kAct];                   // this CTA's prediction-projection rows
+    __half wj[8][kAct];                   // this CTA's joint rows
+    __half ax[16][kAct];                  // LSTM input / joint input (hi rows 0-7, lo rows 8-15)
+    __half ah[2][16][kAct];               // committed hidden state per layer, all 640 units
+    float part[kXWarps][8][24];           // per-warp partial sums of the K-split
+    float pred[kMaxUtt][kHidden];         // cached prediction vectors
+    float gate[kMaxUtt][8][4];            // [utt][unit slot][gate]
+    float cstate[2][2][8][kMaxUtt];       // [layer][version parity][unit slot][utt]
+    float bias[2][8][4];                  // b_ih + b_hh per owned unit and gate
     float pred_bias[8];
     float joint_bias[8];
     unsigned long long best[kMaxUtt];
     unsigned long long rowkey[kMaxUtt][8];   // this CTA's joint rows: one key per (utterance, row slot)
     float dur[kMaxUtt][8];
     int frame[kMaxUtt], symbols[kMaxUtt], last[kMaxUtt], count[kMaxUtt], ver[kMaxUtt], pred_ver[kMaxUtt];
+    int total_frames[kMaxUtt];
     unsigned char emitted[kMaxUtt], valid[kMaxUtt], done[kMaxUtt], need[kMaxUtt];
     int ok;
 };
+
+__device__ __forceinline__ void split_store(__half (*buf)[kAct], int u, int col, float v) {
+    const __half hi = __float2half_rn(v);
+    buf[u][col] = hi;
+    buf[u + 8][col] = __float2half_rn(v - __half2float(hi));
+}
+
+__device__ __forceinline__ void dec_ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void dec_ldmatrix_x2(unsigned (&r)[2], const void* smem) {
+    const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
+                 : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void dec_mma(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
 
 #ifdef PK100_DEC_PROFILE
 #define PK_STAMP(i) do { if (tid == 0) { const long long now__ = clock64(); prof[i] += now__ - last_stamp; last_stamp = now__; } } while (0)
@@ -545,6 +589,7 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
     extern __shared__ __align__(16) uint8_t xs_raw[];
     XSmem& sm = *reinterpret_cast<XSmem*>(xs_raw);
     const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
+    const int g = lane / 4, t = lane % 4;
     const int G = gridDim.x, cta = blockIdx.x;
     const int units = (kHidden + G - 1) / G;            // <= 5 (checked on the host)
     const int jrows = (kJointRows + G - 1) / G;         // <= 8
@@ -556,34 +601,32 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
     volatile int* abort_flag = reinterpret_cast<volatile int*>(p.workspace + lay.abort);
     const int U = p.utts;
 
-    // ---- register-resident weight slices
-    const int my_unit_slot = warp / 4, my_gate = warp % 4;
-    const int my_unit = cta + G * my_unit_slot;
-    const bool lstm_warp = my_unit_slot < units && my_unit < kHidden;
-    for (int i = tid; i < 2 * 5 * 8 * kHidden; i += kXThreads) {
-        const int c = i % kHidden, r = (i / kHidden) % 8, slot = (i / (8 * kHidden)) % 5, l = i / (5 * 8 * kHidden);
+    // ---- this CTA's weight slices -> shared memory (once)
+    for (int i = tid; i < 2 * kLstmRows * kLstmPitch; i += kXThreads) {
+        const int c = i % kLstmPitch, n = (i / kLstmPitch) % kLstmRows, l = i / (kLstmRows * kLstmPitch);
+        const int slot = n / 4, gt = n % 4;
         const int unit = cta + G * slot;
         __half v = __float2half(0.0f);
-        if (l < p.layers && slot < units && unit < kHidden)
-            v = (r < 4 ? p.w_ih[l] : p.w_hh[l])[(static_cast<size_t>(r & 3) * kHidden + unit) * kHidden + c];
-        sm.w_lstm[l][slot][r][c] = v;
+        if (l < p.layers && slot < units && unit < kHidden && c < kLstmK) {
+            const __half* src = c < kHidden ? p.w_ih[l] : p.w_hh[l];
+            v = src[(static_cast<size_t>(gt) * kHidden + unit) * kHidden + (c % kHidden)];
+        }
+        sm.wl[l][n][c] = v;
     }
-    const int pred_row = cta + G * warp;
-    const bool pred_warp = warp < units && pred_row < kHidden;
-    const int joint_row = cta + G * warp;
-    const bool joint_warp = warp < jrows && joint_row < kJointRows;
-    for (int i = tid; i < 8 * kHidden; i += kXThreads) {
-        const int slot = i / kHidden, c = i % kHidden;
+    for (int i = tid; i < 8 * kAct; i += kXThreads) {
+        const int slot = i / kAct, c = i % kAct;
         const int row = cta + G * slot;
-        sm.w_pred[slot][c] = (slot < units && row < kHidden) ? p.w_pred[static_cast<size_t>(row) * kHidden + c]
-                                                             : __float2half(0.0f);
-        sm.w_joint[slot][c] = (slot < jrows && row < kJointRows)
+        sm.wp[slot][c] = (slot < units && row < kHidden && c < kHidden)
+            ? p.w_pred[static_cast<size_t>(row) * kHidden + c] : __float2half(0.0f);
+        sm.wj[slot][c] = (slot < jrows && row < kJointRows && c < kHidden)
             ? p.w_joint[static_cast<size_t>(row) * kHidden + c] : __float2half(0.0f);
     }
-
-    // ---- shared state
-    for (int i = tid; i < 2 * kMaxUtt * kHidden; i += kXThreads) (&sm.hcur[0][0][0])[i] = 0.0f;
-    for (int i = tid; i < kMaxUtt * kHidden; i += kXThreads) { (&sm.x[0][0])[i] = 0.0f; (&sm.pred[0][0])[i] = 0.0f; }
+    for (int i = tid; i < 16 * kAct; i += kXThreads) {
+        (&sm.ax[0][0])[i] = __float2half(0.0f);
+        (&sm.ah[0][0][0])[i] = __float2half(0.0f);
+        (&sm.ah[1][0][0])[i] = __float2half(0.0f);
+    }
+    for (int i = tid; i < kMaxUtt * kHidden; i += kXThreads) (&sm.pred[0][0])[i] = 0.0f;
     for (int i = tid; i < 2 * 2 * 8 * kMaxUtt; i += kXThreads) (&sm.cstate[0][0][0][0])[i] = 0.0f;
     if (tid < 2 * 8 * 4) {
         const int l = tid / 32, slot = (tid / 4) % 8, gt = tid % 4;
@@ -599,15 +642,50 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
     if (tid < kMaxUtt) {
         sm.frame[tid] = 0; sm.symbols[tid] = 0; sm.last[tid] = kBlank; sm.count[tid] = 0;
         sm.ver[tid] = 0; sm.pred_ver[tid] = 0; sm.emitted[tid] = 0; sm.valid[tid] = 0;
+        sm.total_frames[tid] = tid < U ? p.frames[tid] : 0;
         sm.done[tid] = tid >= U || p.frames[tid] <= 0;
         sm.need[tid] = 0;
     }
     if (tid == 0) sm.ok = 1;
     __syncthreads();
 
+    // One K-split GEMM: out[u][n] partials of A(16 x 16*ksteps) . B(n x K)^T for this warp's
+    // k-steps, hi/lo rows folded, written to sm.part[warp][u][n].  NT = number of 8-row tiles.
+    auto small_gemm = [&](const __half (*a)[kAct], int a_col0, const __half* b, int b_pitch, int b_rows,
+                          int b_col0, int ksteps, auto nt_tag) {
+        constexpr int NT = decltype(nt_tag)::value;
+        float acc[NT][4];
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[j][e] = 0.0f;
+        for (int ks = 0; ks < ksteps; ++ks) {
+            unsigned af[4];
+            dec_ldmatrix_x4(af, &a[lane % 16][a_col0 + ks * 16 + (lane / 16) * 8]);
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                // B tile j: rows j*8 .. j*8+7 (clamped into the stored rows; surplus columns unused)
+                int row = j * 8 + lane % 8;
+                row = row < b_rows ? row : b_rows - 1;
+                unsigned bf[2];
+                dec_ldmatrix_x2(bf, b + static_cast<size_t>(row) * b_pitch + b_col0 + ks * 16 + ((lane / 8) % 2) * 8);
+                dec_mma(acc[j], af, bf[0], bf[1]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            sm.part[warp][g][j * 8 + 2 * t] = acc[j][0] + acc[j][2];
+            sm.part[warp][g][j * 8 + 2 * t + 1] = acc[j][1] + acc[j][3];
+        }
+    };
+    auto sum_parts = [&](int u, int n, int warps) {
+        float v = 0.0f;
+        for (int w = 0; w < warps; ++w) v += sm.part[w][u][n];
+        return v;
+    };
+
     unsigned round = 0;
     while (true) {
-        // ---- who runs, who needs a new prediction
         bool any_running = false, any_need = false;
         for (int u = 0; u < U; ++u) {
             any_running |= !sm.done[u];
@@ -621,9 +699,8 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
         if (any_need) {
             for (int l = 0; l < p.layers; ++l) {
                 if (sm.ok == 0) break;
-                // input of layer l: embedding of the last token (layer 0) or the lower layer's
-                // fresh hidden state, which arrives through the exchange buffer
-                // (one thread per column: kXThreads == kHidden)
+                // input of layer l (one thread per column: kXThreads == kHidden): the embedding
+                // of the last token, or the lower layer's fresh hidden state from the exchange
                 if (l == 0) {
                     __half e[8];
 #pragma unroll
@@ -632,7 +709,10 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
                             e[u] = __ldg(p.embedding + static_cast<size_t>(sm.last[u]) * kHidden + tid);
 #pragma unroll
                     for (int u = 0; u < 8; ++u)
-                        if (u < U && sm.need[u]) sm.x[u][tid] = sm.emitted[u] ? __half2float(e[u]) : 0.0f;
+                        if (u < U && sm.need[u]) {
+                            sm.ax[u][tid] = sm.emitted[u] ? e[u] : __float2half(0.0f);   // fp16 exactly
+                            sm.ax[u + 8][tid] = __float2half(0.0f);
+                        }
                 } else {
                     unsigned want[8];
                     size_t off[8];
@@ -645,32 +725,25 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
                     if (!xch_wait8(xh, kHidden, want, off, val, abort_flag)) sm.ok = 0;
 #pragma unroll
                     for (int u = 0; u < 8; ++u)
-                        if (want[u] != 0u) sm.x[u][tid] = val[u];
+                        if (want[u] != 0u) {
+                            split_store(sm.ax, u, tid, val[u]);
+                            split_store(sm.ah[l - 1], u, tid, val[u]);   // lower layer's next committed state
+                        }
                 }
                 __syncthreads();
                 PK_STAMP(1);
                 if (sm.ok == 0) break;
-                if (lstm_warp) {
-                    float acc[8];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
-                    __half2 wv[10];
-                    load_row_slices(sm.w_lstm[l][my_unit_slot][my_gate], lane, wv);
-                    dot8(wv, &sm.x[0][0], lane, acc);
-                    load_row_slices(sm.w_lstm[l][my_unit_slot][4 + my_gate], lane, wv);
-                    dot8(wv, &sm.hcur[l][0][0], lane, acc);
-                    const float total = reduce8(acc, lane);
-                    const int u = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-                    if ((lane & 3) == 0) sm.gate[u][my_unit_slot][my_gate] = total + sm.bias[l][my_unit_slot][my_gate];
+                // gates[u][20 rows] = [x | h] . [w_ih | w_hh]^T, K = 1280 split over the 20 warps
+                if (warp < 10) small_gemm(sm.ax, warp * 64, &sm.wl[l][0][0], kLstmPitch, kLstmRows, warp * 64, 4,
+                                          std::integral_constant<int, 3>{});
+                else small_gemm(sm.ah[l], (warp - 10) * 64, &sm.wl[l][0][0], kLstmPitch, kLstmRows,
+                                kHidden + (warp - 10) * 64, 4, std::integral_constant<int, 3>{});
+                __syncthreads();
+                if (tid < 8 * kLstmRows) {
+                    const int u = tid / kLstmRows, n = tid % kLstmRows;
+                    sm.gate[u][n / 4][n % 4] = sum_parts(u, n, kXWarps) + sm.bias[l][n / 4][n % 4];
                 }
                 __syncthreads();
-                // the lower layer's new state becomes that layer's committed state for the next version
-                if (l > 0) {
-                    for (int i = tid; i < U * kHidden; i += kXThreads) {
-                        const int u = i / kHidden, c = i % kHidden;
-                        if (sm.need[u]) sm.hcur[l - 1][u][c] = sm.x[u][c];
-                    }
-                }
                 if (tid < units * U) {
                     const int slot = tid / U, u = tid % U;
                     const int unit = cta + G * slot;
@@ -704,24 +777,22 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
                 if (!xch_wait8(xh, kHidden, want, off, val, abort_flag)) sm.ok = 0;
 #pragma unroll
                 for (int u = 0; u < 8; ++u)
-                    if (want[u] != 0u) sm.hcur[top][u][tid] = val[u];
+                    if (want[u] != 0u) split_store(sm.ah[top], u, tid, val[u]);
             }
             __syncthreads();
             PK_STAMP(3);
             if (sm.ok == 0) break;
-            if (pred_warp) {
-                float acc[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
-                __half2 wp[10];
-                load_row_slices(sm.w_pred[warp], lane, wp);
-                dot8(wp, &sm.hcur[p.layers - 1][0][0], lane, acc);
-                const float total = reduce8(acc, lane);
-                const int u = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-                if ((lane & 3) == 0 && u < U && sm.need[u]) {
+            // pred[u][row] = h_top . w_pred^T, K = 640 split over the 20 warps (2 k-steps each)
+            small_gemm(sm.ah[p.layers - 1], warp * 32, &sm.wp[0][0], kAct, 8, warp * 32, 2,
+                       std::integral_constant<int, 1>{});
+            __syncthreads();
+            if (tid < 8 * 8) {
+                const int u = tid / 8, slot = tid % 8;
+                const int row = cta + G * slot;
+                if (u < U && sm.need[u] && slot < units && row < kHidden) {
                     const unsigned tag = static_cast<unsigned>(sm.ver[u] + 1);
-                    xch_store(xp + (static_cast<size_t>(tag & 1) * U + u) * kHidden + pred_row,
-                              total + sm.pred_bias[warp], tag);
+                    xch_store(xp + (static_cast<size_t>(tag & 1) * U + u) * kHidden + row,
+                              sum_parts(u, slot, kXWarps) + sm.pred_bias[slot], tag);
                 }
             }
             __syncthreads();
@@ -749,7 +820,7 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
             for (int u = 0; u < 8; ++u) {
                 if (u >= U || sm.done[u]) continue;
                 if (want[u] != 0u) sm.pred[u][tid] = val[u];
-                sm.x[u][tid] = fmaxf(__half2float(e[u]) + sm.pred[u][tid], 0.0f);
+                split_store(sm.ax, u, tid, fmaxf(__half2float(e[u]) + sm.pred[u][tid], 0.0f));
             }
         }
         __syncthreads();
@@ -757,33 +828,26 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
         if (sm.ok == 0) break;
         if (tid < U) sm.pred_ver[tid] = sm.ver[tid];
         const unsigned epoch = (round + 1) & kEpochMask;
-        if (joint_warp) {
-            float acc[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
-            __half2 wj[10];
-            load_row_slices(sm.w_joint[warp], lane, wj);
-            dot8(wj, &sm.x[0][0], lane, acc);
-            const float total = reduce8(acc, lane) + sm.joint_bias[warp];
-            const int u = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-            if ((lane & 3) == 0 && u < U && !sm.done[u]) {
-                unsigned long long key = 0ull;
-                if (joint_row >= kTokenOutputs) {
-                    xch_store(xd + (static_cast<size_t>(round & 1) * U + u) * 8 + (joint_row - kTokenOutputs),
-                              total, round + 1);
+        small_gemm(sm.ax, warp * 32, &sm.wj[0][0], kAct, 8, warp * 32, 2, std::integral_constant<int, 1>{});
+        __syncthreads();
+        if (tid < 8 * 8) {
+            const int u = tid / 8, slot = tid % 8;
+            const int row = cta + G * slot;
+            unsigned long long key = 0ull;
+            if (u < U && !sm.done[u] && slot < jrows && row < kJointRows) {
+                const float total = sum_parts(u, slot, kXWarps) + sm.joint_bias[slot];
+                if (row >= kTokenOutputs) {
+                    xch_store(xd + (static_cast<size_t>(round & 1) * U + u) * 8 + (row - kTokenOutputs), total, round + 1);
                 } else if (total == total) {          // NaN never wins
                     float sc = total;
                     if (sc == 0.0f) sc = 0.0f;
                     const unsigned bits = __float_as_uint(sc);
                     const unsigned ordered = (bits & 0x80000000u) ? ~bits : (bits ^ 0x80000000u);
                     key = (static_cast<unsigned long long>(ordered) << 32) |
-                          (static_cast<unsigned long long>(2047 - joint_row) << 21) | epoch;
+                          (static_cast<unsigned long long>(2047 - row) << 21) | epoch;
                 }
-                sm.rowkey[u][warp] = key;
             }
-        } else if (warp < 8 && (lane & 3) == 0) {
-            const int u = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-            sm.rowkey[u][warp] = 0ull;
+            sm.rowkey[u][slot] = key;
         }
         __syncthreads();
         PK_STAMP(6);
@@ -813,35 +877,34 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
             const unsigned long long* dslot = xd + (static_cast<size_t>(round & 1) * U + u) * 8 + lane;
             if (lane < kDurations) dv = xch_load(dslot);
             unsigned long long best = 0ull;
+            {
+                unsigned pending = 0;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int c = lane + 32 * j;
-                if (c >= G) continue;
-                if ((static_cast<unsigned>(v[j]) & kEpochMask) != epoch) {
-                    const long long start = clock64();
-                    unsigned polls = 0;
-                    do {
-                        v[j] = xch_load(row + c);
-                        if ((++polls & 127u) == 0u && (*abort_flag != 0 || clock64() - start > 2000000000ll)) {
-                            *abort_flag = 1;
-                            good = false;
-                            break;
-                        }
-                    } while ((static_cast<unsigned>(v[j]) & kEpochMask) != epoch);
-                }
-                best = v[j] > best ? v[j] : best;
-            }
-            if (lane < kDurations && static_cast<unsigned>(dv >> 32) != round + 1) {
-                const long long start = clock64();
+                for (int j = 0; j < 8; ++j)
+                    if (lane + 32 * j < G) pending |= 1u << j;
+                bool dur_pending = lane < kDurations;
+                long long start = 0;
                 unsigned polls = 0;
-                do {
-                    dv = xch_load(dslot);
-                    if ((++polls & 127u) == 0u && (*abort_flag != 0 || clock64() - start > 2000000000ll)) {
+                while (true) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (((pending >> j) & 1u) && (static_cast<unsigned>(v[j]) & kEpochMask) == epoch) {
+                            pending &= ~(1u << j);
+                            best = v[j] > best ? v[j] : best;
+                        }
+                    if (dur_pending && static_cast<unsigned>(dv >> 32) == round + 1) dur_pending = false;
+                    if (pending == 0u && !dur_pending) break;
+                    if (polls == 0u) start = clock64();
+                    if ((++polls & 63u) == 0u && (*abort_flag != 0 || clock64() - start > 2000000000ll)) {
                         *abort_flag = 1;
                         good = false;
                         break;
                     }
-                } while (static_cast<unsigned>(dv >> 32) != round + 1);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if ((pending >> j) & 1u) v[j] = xch_load(row + lane + 32 * j);
+                    if (dur_pending) dv = xch_load(dslot);
+                }
             }
 #pragma unroll
             for (int off = 16; off > 0; off /= 2) {
@@ -879,7 +942,7 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
                 if (duration == 0) sm.frame[u] += 1;
                 sm.symbols[u] = 0;
             }
-            if (sm.frame[u] >= p.frames[u]) sm.done[u] = 1;
+            if (sm.frame[u] >= sm.total_frames[u]) sm.done[u] = 1;
         }
         __syncthreads();
         PK_STAMP(8);
