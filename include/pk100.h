@@ -42,7 +42,13 @@ enum {
 };
 
 /* Operand kinds of pk100_gemm. */
-enum { PK100_KIND_F16 = 0, PK100_KIND_E4M3 = 1, PK100_KIND_S8 = 2 };
+enum {
+    PK100_KIND_F16 = 0, PK100_KIND_E4M3 = 1, PK100_KIND_S8 = 2,
+    /* A fp16 [m,k]; b = INT4 codes [n, k/2] (low nibble = even k), b_group_scales = fp16
+     * [k/128, n]; the weights are dequantised to fp16 in shared memory by producer warps
+     * (W = f16(code * scale)) and multiplied with kind::f16 MMAs. */
+    PK100_KIND_F16_W4G128 = 3
+};
 /* Output encodings of pk100_gemm. */
 enum { PK100_OUT_F16 = 0, PK100_OUT_F32 = 1, PK100_OUT_E4M3 = 2, PK100_OUT_S8 = 3 };
 /* Activations (kernels/sm89/linear.cu:65-73). */
@@ -106,6 +112,7 @@ typedef struct pk100_gemm_args {
     const uint8_t* keep_in;
     int* status;              /* device int, set to 1 if a bounded wait expired; may be NULL */
     int max_ctas;             /* <= 0: one CTA per SM */
+    const void* b_group_scales; /* PK100_KIND_F16_W4G128 only */
 } pk100_gemm_args;
 
 int pk100_gemm(void* stream, const pk100_gemm_args* args);
@@ -217,7 +224,8 @@ typedef struct pk100_layer_weights {
     const void* wqkv;          const float* wqkv_scales;   /* S8 [3072,1024] rows Q|K|V */
     const void* position;                                   /* fp16 [8,272,128] */
     const void* bias_u;        const void* bias_v;          /* fp16 [8,128] */
-    const void* wo_f16;                                     /* fp16 [1024,1024] (dequantised INT4-g128) */
+    const void* wo_f16;                                     /* fp16 [1024,1024] (dequantised INT4-g128); used when wo_codes == NULL */
+    const void* wo_codes;      const void* wo_group_scales; /* INT4 codes [1024,512] + fp16 scales [8,1024] */
     const void* ln_conv_gamma; const void* ln_conv_beta;
     const void* wpw1;          const float* wpw1_scales;   /* E4M3 [2048,1024] */
     const void* dw_weight;                                  /* fp16 [1024,9] */

@@ -156,7 +156,13 @@ extern "C" int pk100_run_layers(void* stream, const pk100_layer_weights* layers,
                     seg_valid));
             }
         }
-        gemm_base(a, PK100_KIND_F16, g.rows, kWidth, kWidth, ws.att, w.wo_f16);
+        if (w.wo_codes != nullptr) {
+            gemm_base(a, PK100_KIND_F16_W4G128, g.rows, kWidth, kWidth, ws.att, w.wo_codes);
+            a.ldb = kWidth / 2;
+            a.b_group_scales = w.wo_group_scales;
+        } else {
+            gemm_base(a, PK100_KIND_F16, g.rows, kWidth, kWidth, ws.att, w.wo_f16);
+        }
         a.residual = x; a.ld_res = kWidth; a.out = x; a.ld_out = kWidth; a.status = ws.status;
         PK_TRY(pk100_gemm(stream, &a));
 

@@ -87,6 +87,29 @@ static int launch(const pk100_gemm_args& a, const GemmParams& p, cudaStream_t st
     return pk100_launch_status();
 }
 
+// fp16 activations x INT4 group-128 weights, dequantised in shared memory by producer warps.
+static int launch_w4(const pk100_gemm_args& a, const GemmParams& p, cudaStream_t stream) {
+    constexpr int BlockN = 128;
+    using Smem = GemmSmem<BlockN, 128>;
+    auto kernel = gemm_kernel<KIND_F16, BlockN, 128, EPI_LINEAR, BSRC_W4G128>;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t err = cudaFuncSetAttribute(
+            kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
+        if (err != cudaSuccess) return static_cast<int>(err);
+        configured = true;
+    }
+    CUtensorMap map_a;
+    const int rc = make_map(&map_a, a.a, 2, a.m, a.k, a.lda, kBlockM, 128);
+    if (rc != PK100_OK) return rc;
+    const int m_tiles = (a.m + kBlockM - 1) / kBlockM;
+    const int n_tiles = (p.n + BlockN - 1) / BlockN;
+    int ctas = a.max_ctas > 0 ? a.max_ctas : sm_count();
+    if (ctas > m_tiles * n_tiles) ctas = m_tiles * n_tiles;
+    kernel<<<ctas, kGemmThreads, Smem::kTotal, stream>>>(map_a, map_a, p);   // B has no tensor map
+    return pk100_launch_status();
+}
+
 static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
 }  // namespace pk100
@@ -101,12 +124,18 @@ extern "C" int pk100_gemm(void* stream_v, const pk100_gemm_args* a) {
     if (a == nullptr || a->a == nullptr || a->b == nullptr || a->out == nullptr) return PK100_ERR_NULL;
     if (a->m < 0 || a->n <= 0 || a->k <= 0) return PK100_ERR_SHAPE;
     if (a->m == 0) return PK100_OK;
-    if (a->kind < PK100_KIND_F16 || a->kind > PK100_KIND_S8) return PK100_ERR_UNSUPPORTED;
-    const int elem = a->kind == PK100_KIND_F16 ? 2 : 1;
+    if (a->kind < PK100_KIND_F16 || a->kind > PK100_KIND_F16_W4G128) return PK100_ERR_UNSUPPORTED;
+    const bool w4 = a->kind == PK100_KIND_F16_W4G128;
+    const int elem = (a->kind == PK100_KIND_F16 || w4) ? 2 : 1;
     if ((static_cast<long long>(a->k) * elem) % 16 != 0 ||
-        (static_cast<long long>(a->lda) * elem) % 16 != 0 ||
-        (static_cast<long long>(a->ldb) * elem) % 16 != 0 || a->lda < a->k || a->ldb < a->k)
+        (static_cast<long long>(a->lda) * elem) % 16 != 0 || a->lda < a->k)
         return PK100_ERR_SHAPE;
+    if (!w4 && ((static_cast<long long>(a->ldb) * elem) % 16 != 0 || a->ldb < a->k)) return PK100_ERR_SHAPE;
+    if (w4) {
+        if (a->b_group_scales == nullptr) return PK100_ERR_NULL;
+        if (a->k % 128 != 0 || a->epilogue != PK100_EPI_LINEAR || a->keep_in != nullptr)
+            return PK100_ERR_SHAPE;
+    }
     if (a->n % 32 != 0) return PK100_ERR_SHAPE;
     if (!aligned16(a->a) || !aligned16(a->b) || !aligned16(a->out)) return PK100_ERR_ALIGN;
     if (a->out_type < PK100_OUT_F16 || a->out_type > PK100_OUT_S8) return PK100_ERR_UNSUPPORTED;
@@ -149,8 +178,8 @@ extern "C" int pk100_gemm(void* stream_v, const pk100_gemm_args* a) {
     p.keep_out = a->keep_out;
     p.stats_out = a->stats_out;
     p.keep_in = a->keep_in;
-    p.w4_codes = nullptr;
-    p.w4_scales = nullptr;
+    p.w4_codes = w4 ? static_cast<const uint8_t*>(a->b) : nullptr;
+    p.w4_scales = w4 ? static_cast<const __half*>(a->b_group_scales) : nullptr;
     p.status = a->status;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
@@ -158,6 +187,7 @@ extern "C" int pk100_gemm(void* stream_v, const pk100_gemm_args* a) {
     const int m_tiles = (a->m + kBlockM - 1) / kBlockM;
     const bool narrow = (a->n % 256 != 0) || (m_tiles * (a->n / 256) < sm_count());
 
+    if (w4) return launch_w4(*a, p, stream);
     switch (a->epilogue) {
     case PK100_EPI_LINEAR:
         if (a->kind == PK100_KIND_F16) {

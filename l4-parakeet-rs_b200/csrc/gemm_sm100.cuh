@@ -105,8 +105,9 @@ __device__ __forceinline__ float acc_to_float(uint32_t r) {
 }
 
 // Named barrier over the epilogue warps only.
+template <int Warps>
 __device__ __forceinline__ void epilogue_bar_sync() {
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * Warps) : "memory");
 }
 
 // Store 32 consecutive output columns of one row.
@@ -192,7 +193,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     constexpr uint32_t kTmemCols = 2 * BlockN;
     constexpr int kBHalf = BlockN / 2;                       // rows per B load
     static_assert(BlockN == 64 || BlockN == 128 || BlockN == 256, "BlockN");
-    static_assert(BSrc == BSRC_TMA || (Kind == KIND_F16 && SwizzleBytes == 128), "w4 needs f16");
+    static_assert(BSrc == BSRC_TMA || (Kind == KIND_F16 && SwizzleBytes == 128 && BlockN == 128 &&
+                                       Epi == EPI_LINEAR), "w4: fp16 MMA, 128-column tiles, linear epilogue");
+    // INT4 weights: 4 epilogue warps (one per TMEM lane quadrant) + 4 dequantisation warps;
+    // otherwise 8 epilogue warps, two per quadrant, each half of the tile's columns.
+    constexpr int kEpiWarps = BSrc == BSRC_W4G128 ? 4 : kEpilogueWarps;
+    constexpr int kColSplit = kEpiWarps / 4;
+    constexpr int kColsPerWarp = BlockN / kColSplit;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -226,7 +233,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tmem_full_bar + b, 1);
-            mbar_init(tmem_empty_bar + b, kEpilogueWarps);
+            mbar_init(tmem_empty_bar + b, kEpiWarps);
         }
         fence_barrier_init();
         prefetch_tensormap(&map_a);
@@ -336,12 +343,65 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 }
             }
         }
+    } else if (BSrc == BSRC_W4G128 && warp >= 2 + kEpiWarps) {
+        // ------------------------------------- INT4 -> fp16 B-operand producer
+        // Thread dq owns row dq of the 128-row B stage: 32 bytes of codes (64 K values) per K
+        // block, one fp16 scale per 128 K.  W = f16(code * scale) is written straight into the
+        // 128-byte-swizzled layout the MMA descriptor expects (16-byte chunk c of row r lives at
+        // chunk c ^ (r & 7)), made visible to the async proxy, then the warp arrives on `full`.
+        const int dq = static_cast<int>(threadIdx.x) - 32 * (2 + kEpiWarps);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const int nt = tile / m_tiles;
+            const int n = nt * BlockN + dq;
+            const bool row_ok = n < p.n;
+            const uint8_t* codes = p.w4_codes + static_cast<size_t>(row_ok ? n : 0) * (p.k / 2);
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const bool got = mbar_wait_bounded(empty_bar + stage, phase ^ 1u, abort_flag);
+                if (!__all_sync(0xffffffffu, got)) {
+                    ok = false;
+                    break;
+                }
+                uint4 raw[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+                float scale = 0.0f;
+                if (row_ok) {
+                    const uint4* src = reinterpret_cast<const uint4*>(codes + kb * 32);
+                    raw[0] = src[0];
+                    raw[1] = src[1];
+                    scale = __half2float(p.w4_scales[static_cast<size_t>(kb / 2) * p.n + n]);
+                }
+                uint8_t* row_base = smem + stage * Smem::kStageBytes + Smem::kStageA + dq * 128;
+                const uint32_t* words = reinterpret_cast<const uint32_t*>(raw);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {              // chunk c = K values 8c .. 8c+7 = one code word
+                    const uint32_t wbits = words[c];
+                    uint32_t h[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        int lo = (wbits >> (8 * j)) & 15, hi = (wbits >> (8 * j + 4)) & 15;
+                        lo = lo >= 8 ? lo - 16 : lo;
+                        hi = hi >= 8 ? hi - 16 : hi;
+                        h[j] = pack_half2(static_cast<float>(lo) * scale, static_cast<float>(hi) * scale);
+                    }
+                    *reinterpret_cast<uint4*>(row_base + ((c ^ (dq & 7)) * 16)) = make_uint4(h[0], h[1], h[2], h[3]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_bar + stage);
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
     } else {
         // ---------------------------------------------------------- epilogue
         const int ew = warp - 2;                 // 0..7
         const int quad = warp % 4;               // TMEM lane quadrant this warp may read
-        const int half = ew / 4;                 // which half of the tile's columns
-        const int et = static_cast<int>(threadIdx.x) - 64;   // 0..255
+        const int half = ew / 4;                 // which part of the tile's columns
+        const int et = static_cast<int>(threadIdx.x) - 64;   // 0 .. 32*kEpiWarps-1
         int local = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
@@ -352,8 +412,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const int row = mt * kBlockM + quad * 32 + lane;
             const int n0 = Epi == EPI_GLU ? nt * kBHalf : nt * BlockN;   // first output column
             // stage per-column scale / bias for this tile
-            epilogue_bar_sync();
-            for (int c = et; c < BlockN; c += 32 * kEpilogueWarps) {
+            epilogue_bar_sync<kEpiWarps>();
+            for (int c = et; c < BlockN; c += 32 * kEpiWarps) {
                 int src;
                 if constexpr (Epi == EPI_GLU) {
                     src = c < kBHalf ? nt * kBHalf + c : p.n / 2 + nt * kBHalf + (c - kBHalf);
@@ -364,7 +424,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 s_col_scale[c] = (p.col_scales != nullptr && in) ? p.col_scales[src] : 1.0f;
                 s_bias[c] = (p.bias != nullptr && in) ? p.bias[src] : 0.0f;
             }
-            epilogue_bar_sync();
+            epilogue_bar_sync<kEpiWarps>();
 
             bool live = true;
             if (p.keep_in != nullptr) {
@@ -388,10 +448,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const size_t obytes = out_elem_bytes(p.out_type);
 
             if constexpr (Epi == EPI_LINEAR) {
-                constexpr int kChunks = BlockN / 2 / 32;
+                constexpr int kChunks = kColsPerWarp / 32;
 #pragma unroll 1
                 for (int c = 0; c < kChunks; ++c) {
-                    const int col_local = half * (BlockN / 2) + c * 32;
+                    const int col_local = half * kColsPerWarp + c * 32;
                     uint32_t r[32];
                     tmem_ld_32x32(taddr_base + col_local, r);
                     tmem_ld_wait();
@@ -485,7 +545,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     s_reduce[ew * 2 + 0] = tile_max[0];
                     s_reduce[ew * 2 + 1] = tile_max[1];
                 }
-                epilogue_bar_sync();
+                epilogue_bar_sync<kEpiWarps>();
                 bool keep[2];
                 const int n_tiles64 = p.n / 64;
 #pragma unroll

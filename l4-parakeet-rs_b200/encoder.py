@@ -30,6 +30,7 @@ class FfWeights(C.Structure):
 class LayerWeights(C.Structure):
     _fields_ = [("ff1", FfWeights), ("ln_att_gamma", vp), ("ln_att_beta", vp), ("wqkv", vp),
                 ("wqkv_scales", vp), ("position", vp), ("bias_u", vp), ("bias_v", vp), ("wo_f16", vp),
+                ("wo_codes", vp), ("wo_group_scales", vp),
                 ("ln_conv_gamma", vp), ("ln_conv_beta", vp), ("wpw1", vp), ("wpw1_scales", vp),
                 ("dw_weight", vp), ("bn_gamma", vp), ("bn_beta", vp), ("bn_mean", vp), ("bn_var", vp),
                 ("wpw2", vp), ("wpw2_scales", vp), ("ff2", FfWeights), ("ln_out_gamma", vp),
@@ -106,6 +107,7 @@ class EncoderLayers:
         codes, gs = self._keep(*ops.pack_weight_rows(self._dev16(w["wo"]), L.PACK_S4_G128))
         (wo16,) = self._keep(ops.dequant_w4g128(codes, gs))
         lw.wo_f16 = wo16.data_ptr()
+        lw.wo_codes, lw.wo_group_scales = codes.data_ptr(), gs.data_ptr()
         # position table: sinusoid . Wpos^T (fp16 linear), head-major
         proj = torch.empty((POSITION_ROWS_PADDED, 1024), dtype=torch.float16, device=self.device)
         ops.gemm(self._sinus, self._dev16(w["wpos"]), kind=L.KIND_F16, out=proj)

@@ -30,7 +30,7 @@ class GemmArgs(C.Structure):
         ("act", i32), ("residual", vp), ("ld_res", i32), ("alpha", f32), ("valid_rows", i32),
         ("out", vp), ("ld_out", i32), ("out_type", i32), ("out_scale", f32),
         ("tau", f32), ("keep_out", vp), ("stats_out", vp), ("keep_in", vp),
-        ("status", vp), ("max_ctas", i32),
+        ("status", vp), ("max_ctas", i32), ("b_group_scales", vp),
     ]
 
 
@@ -73,7 +73,7 @@ lib.pk100_launch_count.argtypes = []
 
 # enums (include/pk100.h)
 OK, ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_UNSUPPORTED, ERR_DRIVER, ERR_LIMIT = 0, -1, -2, -3, -4, -5, -6
-KIND_F16, KIND_E4M3, KIND_S8 = 0, 1, 2
+KIND_F16, KIND_E4M3, KIND_S8, KIND_F16_W4G128 = 0, 1, 2, 3
 OUT_F16, OUT_F32, OUT_E4M3, OUT_S8 = 0, 1, 2, 3
 ACT_NONE, ACT_SILU, ACT_RELU = 0, 1, 2
 EPI_LINEAR, EPI_GLU, EPI_SPARSE_OUT = 0, 1, 2

@@ -33,7 +33,7 @@ def _need(t, dtype=None):
 def gemm(a, b, *, kind, out, epilogue=L.EPI_LINEAR, row_scales=None, row_scale=1.0,
          col_scales=None, bias=None, act=L.ACT_NONE, residual=None, alpha=1.0, valid_rows=0,
          out_type=L.OUT_F16, out_scale=1.0, tau=0.0, keep_out=None, stats_out=None, keep_in=None,
-         status=None, max_ctas=0, n=None):
+         status=None, max_ctas=0, n=None, b_group_scales=None):
     """D = epilogue(A . B^T); see `pk100_gemm` in include/pk100.h."""
     _need(a), _need(b), _need(out)
     m, k = a.shape
@@ -50,7 +50,8 @@ def gemm(a, b, *, kind, out, epilogue=L.EPI_LINEAR, row_scales=None, row_scale=1
         keep_out=None if keep_out is None else keep_out.data_ptr(),
         stats_out=None if stats_out is None else stats_out.data_ptr(),
         keep_in=None if keep_in is None else keep_in.data_ptr(),
-        status=None if status is None else status.data_ptr(), max_ctas=max_ctas)
+        status=None if status is None else status.data_ptr(), max_ctas=max_ctas,
+        b_group_scales=None if b_group_scales is None else b_group_scales.data_ptr())
     L.check(L.lib.pk100_gemm(_stream(), C.byref(args)), "pk100_gemm")
     return out
 

@@ -200,6 +200,35 @@ def test_ff_block_config1(pk, cuda, m):
     assert nrmse(got, want) <= 1e-2
 
 
+@pytest.mark.parametrize("m,n,k", [(750, 4096, 1024), (130, 1024, 1024), (64, 128, 128)])
+def test_w4g128_in_smem_dequant(pk, cuda, m, n, k):
+    """Benchmark configuration 0: X fp16 [750,1024] x W INT4 symmetric, g=128 along K, fp16
+    scales ~U(0.005,0.02), fp32 accumulate.  The GEMM dequantises the codes in shared memory;
+    its result must equal the fp16 GEMM on the pre-dequantised weights bit for bit."""
+    L = pk.lib
+    rng = np.random.default_rng(0)
+    x = codec.f16_round(rng.standard_normal((m, k)))
+    codes = rng.integers(-7, 8, (n, k), dtype=np.int8)
+    packed = codec.pack_nibbles(codes)
+    scales = rng.uniform(0.005, 0.02, (k // 128, n)).astype(np.float16)
+    st = _status(cuda)
+    out = torch.zeros((m, n), dtype=torch.float16, device=cuda)
+    pk.ops.gemm(dev16(x), dev(packed), kind=L.KIND_F16_W4G128, out=out, b_group_scales=dev(scales), n=n,
+                status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    want = O.linear_w4g128(x, packed, scales)
+    got = host(out)
+    assert np.max(np.abs(got - want)) <= 4e-3 * max(1.0, np.abs(want).max() / 4)
+    # same operands through the pre-dequantised fp16 path
+    w16 = pk.ops.dequant_w4g128(dev(packed), dev(scales))
+    assert np.array_equal(host(w16), codec.dequant_int4_g128(packed, scales))
+    ref = torch.zeros((m, n), dtype=torch.float16, device=cuda)
+    pk.ops.gemm(dev16(x), w16, kind=L.KIND_F16, out=ref, status=st)
+    torch.cuda.synchronize()
+    assert np.array_equal(got, host(ref))
+
+
 def test_gemm_rejects_bad_arguments(pk, cuda):
     L = pk.lib
     a = torch.zeros((8, 24), dtype=torch.float16, device=cuda)     # k*2 = 48 bytes: ok; n bad below
