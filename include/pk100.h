@@ -82,7 +82,8 @@ enum { PK100_PACK_E4M3 = 0, PK100_PACK_S8 = 1, PK100_PACK_S4_ROW = 2, PK100_PACK
  *     f16(value) / (1 + exp(-f16(gate))), out has n/2 columns (encoder.cu:936-944).
  *   PK100_EPI_SPARSE_OUT: v = SiLU(...); per [128-row x 64-col] tile t = max|v|;
  *     keep_out[tile] = t >= tau; kept tiles are stored as INT8
- *     clamp(rne(f16(v) * out_scale)), dropped tiles as zeros; stats_out[tile] = t.
+ *     clamp(rne(v * out_scale)), dropped tiles as zeros; stats_out[tile] = t.  SiLU is
+ *     evaluated as v/2 * (1 + tanh(v/2)) with the hardware tanh approximation (rel. 2^-11).
  *   keep_in: when given ([ceil(m/128), k/64] bytes) K tiles flagged 0 are skipped
  *     (their A bytes must be zero).
  * Constraints: k * elem_size, lda/ldb * elem_size multiples of 16 bytes;

@@ -197,7 +197,7 @@ def ff_expand(xq, w1q, w1_scales, rows, tau, row_scale=FP8_INPUT_SCALE, keep_ove
 
     h32 = SiLU(acc * (8/448) * ws[n]) (kernels/sm89/encoder.cu:973-1005, epilogue 0);
     a tile whose max|h32| < tau is zeroed entirely and flagged 0 in the bitmap;
-    kept tiles are stored as clamp(rne(f32(f16(h32)) * 32), +-127).
+    kept tiles are stored as clamp(rne(h32 * 32), +-127).
     Returns (hq int8 [M,4096], keep uint8 [ceil(M/128), 64], stats fp32)."""
     acc = accumulate(codec.e4m3_decode(xq), codec.e4m3_decode(w1q))
     h32 = epilogue(acc, row_scale, w1_scales, None, 1)
@@ -206,7 +206,7 @@ def ff_expand(xq, w1q, w1_scales, rows, tau, row_scale=FP8_INPUT_SCALE, keep_ove
     keep = (stats >= F32(tau)).astype(np.uint8)
     if keep_override is not None:      # decisions imposed by the caller (ambiguous tiles)
         keep = np.asarray(keep_override, dtype=np.uint8).reshape(keep.shape)
-    hq = codec.quantize_int8(f16_round(h32), INT8_HIDDEN_INV)
+    hq = codec.quantize_int8(h32, INT8_HIDDEN_INV)
     m = hq.shape[0]
     mask = np.repeat(np.repeat(keep, SPARSE_TILE_ROWS, axis=0)[:m], SPARSE_TILE_COLS, axis=1)
     hq = np.where(mask.astype(bool), hq, np.int8(0)).astype(np.int8)

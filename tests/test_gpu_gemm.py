@@ -187,12 +187,12 @@ def test_ff_block_config1(pk, cuda, m):
                 residual=y, alpha=0.5, keep_in=keep, status=st)
     torch.cuda.synchronize()
     assert int(st.item()) == 0
-    assert np.allclose(host(stats_d), mid["stats"], rtol=1e-4, atol=1e-6)
+    assert np.allclose(host(stats_d), mid["stats"], rtol=2e-3, atol=1e-5)    # tanh.approx: rel 2^-11
     assert np.array_equal(host(keep), mid["keep"])
     # INT8 hidden codes: equal except values sitting on a rounding boundary
     hq_h = host(hq)
     diff = hq_h != mid["hq"]
-    assert diff.mean() < 2e-3 and np.max(np.abs(hq_h.astype(int) - mid["hq"].astype(int))) <= 1
+    assert diff.mean() < 3e-2 and np.max(np.abs(hq_h.astype(int) - mid["hq"].astype(int))) <= 1
     # second GEMM fed with the GPU's own codes is exact up to the fp32 epilogue
     want_gpu_codes = O.ff_contract(hq_h, w2q, w2s, x)
     got = host(y)
