@@ -271,15 +271,24 @@ def run_micro(args):
         fr = torch.full((8,), min(750, max(1, args.rows)), dtype=torch.int32, device=dev)
         call = lambda: dec.decode(enc, 8, 768, fr, 7500)
         work, peak, unit, bound, nbytes = 0.0, 1.0, "rounds/s", "latency", 0
-    for _ in range(args.warmup):
+    for _ in range(max(args.warmup, 1)):
         call()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        call()
-    e1.record()
-    torch.cuda.synchronize()
+    # `steps` back-to-back launches replayed from a CUDA graph, so the host-side cost of a
+    # launch (ctypes, tensor-map encoding) stays out of the device timing
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(args.steps):
+                call()
+        graph.replay()
+        side.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(side)
+        graph.replay()
+        e1.record(side)
+        side.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
     achieved = work / (ms * 1e-3) if work else None
     print(json.dumps(dict(micro=args.micro, rows=m, avg_launch_ms=ms, achieved=achieved, unit=unit, bound=bound,

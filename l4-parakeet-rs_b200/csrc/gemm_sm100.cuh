@@ -358,32 +358,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const int n = nt * BlockN + dq;
             const bool row_ok = n < p.n;
             const uint8_t* codes = p.w4_codes + static_cast<size_t>(row_ok ? n : 0) * (p.k / 2);
+            // software pipeline: the codes and scale of K block kb+1 are in flight while block kb
+            // is converted, so the L2 latency is paid once per tile instead of once per block
+            uint4 next_raw[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+            float next_scale = 0.0f;
+            if (row_ok) {
+                const uint4* src = reinterpret_cast<const uint4*>(codes);
+                next_raw[0] = src[0];
+                next_raw[1] = src[1];
+                next_scale = __half2float(p.w4_scales[n]);
+            }
             for (int kb = 0; kb < k_blocks; ++kb) {
+                uint4 raw[2] = {next_raw[0], next_raw[1]};
+                const float scale = next_scale;
+                if (row_ok && kb + 1 < k_blocks) {
+                    const uint4* src = reinterpret_cast<const uint4*>(codes + (kb + 1) * 32);
+                    next_raw[0] = src[0];
+                    next_raw[1] = src[1];
+                    next_scale = __half2float(p.w4_scales[static_cast<size_t>((kb + 1) / 2) * p.n + n]);
+                }
                 const bool got = mbar_wait_bounded(empty_bar + stage, phase ^ 1u, abort_flag);
                 if (!__all_sync(0xffffffffu, got)) {
                     ok = false;
                     break;
                 }
-                uint4 raw[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-                float scale = 0.0f;
-                if (row_ok) {
-                    const uint4* src = reinterpret_cast<const uint4*>(codes + kb * 32);
-                    raw[0] = src[0];
-                    raw[1] = src[1];
-                    scale = __half2float(p.w4_scales[static_cast<size_t>(kb / 2) * p.n + n]);
-                }
                 uint8_t* row_base = smem + stage * Smem::kStageBytes + Smem::kStageA + dq * 128;
                 const uint32_t* words = reinterpret_cast<const uint32_t*>(raw);
+                const __half2 scale2 = __float2half2_rn(scale);
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {              // chunk c = K values 8c .. 8c+7 = one code word
-                    const uint32_t wbits = words[c];
+                    // nibble n -> fp16 (1024 + (n ^ 8)) by OR-ing the biased nibble into the
+                    // mantissa of 1024.0, minus 1032.0 = the signed code, exactly; HMUL2 by the
+                    // fp16 group scale then rounds once, i.e. f16(code * scale).
+                    const uint32_t wbits = words[c] ^ 0x88888888u;       // two's complement -> offset binary
                     uint32_t h[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        int lo = (wbits >> (8 * j)) & 15, hi = (wbits >> (8 * j + 4)) & 15;
-                        lo = lo >= 8 ? lo - 16 : lo;
-                        hi = hi >= 8 ? hi - 16 : hi;
-                        h[j] = pack_half2(static_cast<float>(lo) * scale, static_cast<float>(hi) * scale);
+                        // byte j holds codes (2j, 2j+1): low nibble -> low half, high nibble -> high half
+                        const uint32_t byte = (wbits >> (8 * j)) & 0xFFu;
+                        const uint32_t pair = ((byte & 0x0Fu) | ((byte & 0xF0u) << 12)) | 0x64006400u;
+                        const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&pair),
+                                                  __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408)));
+                        const __half2 w = __hmul2(v, scale2);
+                        h[j] = *reinterpret_cast<const uint32_t*>(&w);
                     }
                     *reinterpret_cast<uint4*>(row_base + ((c ^ (dq & 7)) * 16)) = make_uint4(h[0], h[1], h[2], h[3]);
                 }
