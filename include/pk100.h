@@ -118,6 +118,10 @@ typedef struct pk100_gemm_args {
 
 int pk100_gemm(void* stream, const pk100_gemm_args* args);
 
+/* enable != 0: 256-column GEMM tiles run on CTA pairs (tcgen05 cta_group::2, 2-CTA clusters,
+ * 256 x 256 tiles); default 0 = one CTA per 128 x 256 tile, which measured faster on B200. */
+void pk100_set_gemm_cta_pairs(int enable);
+
 /* Number of kernels this library has launched in the calling process (monotonic). */
 long long pk100_launch_count(void);
 

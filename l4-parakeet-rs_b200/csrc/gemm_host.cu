@@ -62,8 +62,61 @@ static int sm_count() {
     return count;
 }
 
+// CTA pairs (cta_group::2) for the 256-column kernels.  Off by default: on B200 the pair
+// path measured 5-15 % slower than one CTA per tile (the peer's B half arrives over the same
+// SM ingress as the TMA traffic it saves), so it is kept as a validated alternative.
+static std::atomic<int> g_use_pairs{0};
+extern "C" void pk100_set_gemm_cta_pairs(int enable) { g_use_pairs.store(enable != 0); }
+
+template <int Kind, int SwizzleBytes, int Epi>
+static int launch_pair(const pk100_gemm_args& a, const GemmParams& p, cudaStream_t stream) {
+    constexpr int BlockN = 256;
+    using Smem = GemmSmem<BlockN / 2, SwizzleBytes, BlockN>;
+    auto kernel = gemm_kernel<Kind, BlockN, SwizzleBytes, Epi, BSRC_TMA, 2>;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t err = cudaFuncSetAttribute(
+            kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
+        if (err != cudaSuccess) return static_cast<int>(err);
+        configured = true;
+    }
+    constexpr int elem = Kind == KIND_F16 ? 2 : 1;
+    CUtensorMap map_a, map_b;
+    int rc = make_map(&map_a, a.a, elem, a.m, a.k, a.lda, kBlockM, SwizzleBytes);
+    if (rc != PK100_OK) return rc;
+    rc = make_map(&map_b, a.b, elem, a.n, a.k, a.ldb, BlockN / 2, SwizzleBytes);
+    if (rc != PK100_OK) return rc;
+    const int m_groups = (a.m + 2 * kBlockM - 1) / (2 * kBlockM);
+    const int n_tiles = (p.n + BlockN - 1) / BlockN;
+    int pairs = (a.max_ctas > 0 ? a.max_ctas : sm_count()) / 2;
+    if (pairs > m_groups * n_tiles) pairs = m_groups * n_tiles;
+    if (pairs < 1) pairs = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = Smem::kTotal;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, p);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return static_cast<int>(err);
+    }
+    pk100_count_launch();
+    return PK100_OK;
+}
+
 template <int Kind, int BlockN, int SwizzleBytes, int Epi>
 static int launch(const pk100_gemm_args& a, const GemmParams& p, cudaStream_t stream) {
+    if constexpr (BlockN == 256) {
+        if (g_use_pairs.load() != 0 && a.m > kBlockM) return launch_pair<Kind, SwizzleBytes, Epi>(a, p, stream);
+    }
     using Smem = GemmSmem<BlockN, SwizzleBytes>;
     auto kernel = gemm_kernel<Kind, BlockN, SwizzleBytes, Epi, BSRC_TMA>;
     static bool configured = false;

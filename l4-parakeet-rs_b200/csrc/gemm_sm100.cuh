@@ -57,17 +57,18 @@ constexpr int kBlockM = 128;
 constexpr int kEpilogueWarps = 8;
 constexpr int kGemmThreads = 32 * (2 + kEpilogueWarps);
 
-template <int BlockN, int SwizzleBytes>
+// BRows = B rows staged per CTA per stage, EpiCols = accumulator columns of the tile.
+template <int BRows, int SwizzleBytes, int EpiCols = BRows>
 struct GemmSmem {
     static constexpr int kStageA = kBlockM * SwizzleBytes;
-    static constexpr int kStageB = BlockN * SwizzleBytes;
+    static constexpr int kStageB = BRows * SwizzleBytes;
     static constexpr int kStageBytes = kStageA + kStageB;
     static constexpr int kBudget = 196 * 1024;
     static constexpr int kStagesRaw = kBudget / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
     static constexpr int kTileBytes = kStages * kStageBytes;
     // tail: barriers + tmem pointer + abort flag + epilogue staging
-    static constexpr int kTailBytes = 64 * 8 + 16 + 2 * BlockN * 4 + 64 * 4;
+    static constexpr int kTailBytes = 64 * 8 + 16 + 2 * EpiCols * 4 + 64 * 4;
     static constexpr int kTotal = kTileBytes + kTailBytes + 1024;  // + alignment slack
 };
 
@@ -181,11 +182,17 @@ __device__ __forceinline__ bool k_block_live(uint64_t mask, int kb) {
     }
 }
 
-template <int Kind, int BlockN, int SwizzleBytes, int Epi, int BSrc>
+// CtaGroup = 2: the CTAs of a 2-CTA cluster share one 256 x BlockN tile (tcgen05 cta_group::2).
+// Each CTA stages its own 128 rows of A and BlockN/2 rows of B, so a tile costs 2/3 of the
+// operand traffic of two independent 128 x BlockN tiles; the even CTA issues the MMAs, each CTA
+// runs the epilogue of its own 128 accumulator rows.
+template <int Kind, int BlockN, int SwizzleBytes, int Epi, int BSrc, int CtaGroup = 1>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const GemmParams p) {
-    using Smem = GemmSmem<BlockN, SwizzleBytes>;
+    static_assert(CtaGroup == 1 || (CtaGroup == 2 && BlockN == 256 && BSrc == BSRC_TMA), "pairs: 256 columns, TMA");
+    constexpr int kBRows = BlockN / CtaGroup;               // B rows staged by this CTA
+    using Smem = GemmSmem<kBRows, SwizzleBytes, BlockN>;
     constexpr int kStages = Smem::kStages;
     constexpr int kElemBytes = Kind == KIND_F16 ? 2 : 1;
     constexpr int kBlockK = SwizzleBytes / kElemBytes;       // elements per K block
@@ -218,11 +225,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const int warp = static_cast<int>(threadIdx.x) / 32;
     const int lane = static_cast<int>(threadIdx.x) % 32;
 
-    const int m_tiles = (p.m + kBlockM - 1) / kBlockM;
+    const uint32_t rank = CtaGroup == 2 ? cluster_ctarank() : 0u;   // 0 = leader of the pair
+    const int worker = static_cast<int>(blockIdx.x) / CtaGroup;      // pair (or CTA) index
+    const int workers = static_cast<int>(gridDim.x) / CtaGroup;
+    const int m_tiles = (p.m + kBlockM - 1) / kBlockM;                // 128-row tiles
+    const int m_groups = (m_tiles + CtaGroup - 1) / CtaGroup;         // tiles of 128 * CtaGroup rows
     const int n_tiles = (p.n + BlockN - 1) / BlockN;
-    const int num_tiles = m_tiles * n_tiles;
+    const int num_tiles = m_groups * n_tiles;
     const int k_blocks = (p.k + kBlockK - 1) / kBlockK;
     const int k_tiles64 = p.k / 64;
+    // live-K mask of a work item: union over the 128-row tiles it covers
+    auto group_live_mask = [&](int mg) {
+        uint64_t mask = load_live_mask(p.keep_in, mg * CtaGroup, k_tiles64);
+        if (CtaGroup == 2 && p.keep_in != nullptr && mg * 2 + 1 < m_tiles)
+            mask |= load_live_mask(p.keep_in, mg * 2 + 1, k_tiles64);
+        return mask;
+    };
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -233,18 +251,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tmem_full_bar + b, 1);
-            mbar_init(tmem_empty_bar + b, kEpiWarps);
+            mbar_init(tmem_empty_bar + b, kEpiWarps * CtaGroup);
         }
         fence_barrier_init();
         prefetch_tensormap(&map_a);
         if constexpr (BSrc == BSRC_TMA) prefetch_tensormap(&map_b);
     }
     if (warp == 1) {
-        tmem_alloc(tmem_ptr_smem, kTmemCols);
-        tmem_relinquish();
+        if constexpr (CtaGroup == 2) {
+            tmem_alloc_pair(tmem_ptr_smem, kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_ptr_smem, kTmemCols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before_sync();
     __syncthreads();
+    // both CTAs' barriers exist before either one signals the other
+    if constexpr (CtaGroup == 2) cluster_sync_all();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
 
@@ -254,11 +279,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int mt = tile % m_tiles;
-                const int nt = tile / m_tiles;
-                const int m0 = mt * kBlockM;
-                const uint64_t live_mask = load_live_mask(p.keep_in, mt, k_tiles64);
+            for (int tile = worker; tile < num_tiles && ok; tile += workers) {
+                const int mg = tile % m_groups;
+                const int nt = tile / m_groups;
+                const int m0 = (mg * CtaGroup + static_cast<int>(rank)) * kBlockM;
+                const uint64_t live_mask = group_live_mask(mg);
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (p.keep_in != nullptr && !k_block_live<SwizzleBytes>(live_mask, kb)) continue;
                     if (!mbar_wait_bounded(empty_bar + stage, phase ^ 1u, abort_flag)) {
@@ -267,7 +292,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     }
                     uint8_t* sa = smem + stage * Smem::kStageBytes;
                     uint8_t* sb = sa + Smem::kStageA;
-                    if constexpr (BSrc == BSRC_TMA) {
+                    if constexpr (CtaGroup == 2) {
+                        // the leader's barrier counts the bytes of both CTAs
+                        if (rank == 0) mbar_arrive_expect_tx(full_bar + stage, 2 * Smem::kStageBytes);
+                        const uint32_t bar = map_to_cta(smem_u32(full_bar + stage), 0);
+                        int n_rows;
+                        if constexpr (Epi == EPI_GLU) {
+                            n_rows = rank == 0 ? nt * kBRows : p.n / 2 + nt * kBRows;   // values | gates
+                        } else {
+                            n_rows = nt * BlockN + static_cast<int>(rank) * kBRows;
+                        }
+                        tma_load_2d_pair(sa, &map_a, bar, kb * kBlockK, m0);
+                        tma_load_2d_pair(sb, &map_b, bar, kb * kBlockK, n_rows);
+                    } else if constexpr (BSrc == BSRC_TMA) {
                         mbar_arrive_expect_tx(full_bar + stage, Smem::kStageBytes);
                         tma_load_2d(sa, &map_a, full_bar + stage, kb * kBlockK, m0);
                         int n_first, n_second;
@@ -294,17 +331,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_instr_desc<Kind>(kBlockM, BlockN);
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_instr_desc<Kind>(kBlockM * CtaGroup, BlockN);
             int stage = 0;
             uint32_t phase = 0;
             int local = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-                const int mt = tile % m_tiles;
+            for (int tile = worker; tile < num_tiles && ok; tile += workers, ++local) {
+                const int mg = tile % m_groups;
                 const int buf = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
-                const uint64_t live_mask = load_live_mask(p.keep_in, mt, k_tiles64);
+                const uint64_t live_mask = group_live_mask(mg);
                 if (!mbar_wait_bounded(tmem_empty_bar + buf, acc_phase ^ 1u, abort_flag)) {
                     ok = false;
                     break;
@@ -326,17 +363,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
                     for (int j = 0; j < kMmasPerBlock; ++j) {
                         // advance 32 bytes along K inside the swizzle atom: +2 in 16-byte units
-                        tc_mma<Kind>(tmem_d, desc_a + 2u * j, desc_b + 2u * j, idesc, accumulate);
+                        if constexpr (CtaGroup == 2)
+                            tc_mma_pair<Kind>(tmem_d, desc_a + 2u * j, desc_b + 2u * j, idesc, accumulate);
+                        else
+                            tc_mma<Kind>(tmem_d, desc_a + 2u * j, desc_b + 2u * j, idesc, accumulate);
                         accumulate = 1;
                     }
-                    tc_commit(empty_bar + stage);   // frees the stage once the MMAs retire
+                    // free the stage (in both CTAs of a pair) once the MMAs retire
+                    if constexpr (CtaGroup == 2) {
+                        tc_commit_pair(map_to_cta(smem_u32(empty_bar + stage), 0));
+                        tc_commit_pair(map_to_cta(smem_u32(empty_bar + stage), 1));
+                    } else {
+                        tc_commit(empty_bar + stage);
+                    }
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                if (accumulate != 0) {
+                if constexpr (CtaGroup == 2) {
+                    if (accumulate != 0) {
+                        tc_commit_pair(map_to_cta(smem_u32(tmem_full_bar + buf), 0));
+                        tc_commit_pair(map_to_cta(smem_u32(tmem_full_bar + buf), 1));
+                    } else {
+                        mbar_arrive_cluster(map_to_cta(smem_u32(tmem_full_bar + buf), 0));
+                        mbar_arrive_cluster(map_to_cta(smem_u32(tmem_full_bar + buf), 1));
+                    }
+                } else if (accumulate != 0) {
                     tc_commit(tmem_full_bar + buf);
                 } else {
                     mbar_arrive(tmem_full_bar + buf);  // no live K block: accumulator unused
@@ -353,8 +407,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            const int nt = tile / m_tiles;
+        for (int tile = worker; tile < num_tiles && ok; tile += workers) {
+            const int nt = tile / m_groups;
             const int n = nt * BlockN + dq;
             const bool row_ok = n < p.n;
             const uint8_t* codes = p.w4_codes + static_cast<size_t>(row_ok ? n : 0) * (p.k / 2);
@@ -421,9 +475,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const int et = static_cast<int>(threadIdx.x) - 64;   // 0 .. 32*kEpiWarps-1
         int local = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-            const int mt = tile % m_tiles;
-            const int nt = tile / m_tiles;
+        for (int tile = worker; tile < num_tiles && ok; tile += workers, ++local) {
+            const int mg = tile % m_groups;
+            const int mt = mg * CtaGroup + static_cast<int>(rank);    // this CTA's 128-row tile
+            const int nt = tile / m_groups;
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             const int row = mt * kBlockM + quad * 32 + lane;
@@ -445,9 +500,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
             bool live = true;
             if (p.keep_in != nullptr) {
-                const uint8_t* krow = p.keep_in + static_cast<size_t>(mt) * k_tiles64;
+                // MMAs were issued for this work item iff any K tile of any of its rows is live
                 bool any = false;
-                for (int i = lane; i < k_tiles64; i += 32) any |= krow[i] != 0;
+                for (int t = mg * CtaGroup; t < mg * CtaGroup + CtaGroup && t < m_tiles; ++t) {
+                    const uint8_t* krow = p.keep_in + static_cast<size_t>(t) * k_tiles64;
+                    for (int i = lane; i < k_tiles64; i += 32) any |= krow[i] != 0;
+                }
                 live = __any_sync(0xffffffffu, any);
             }
 
@@ -588,7 +646,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     mx *= inv_out_scale;                        // statistic in activation units
                     keep[t] = mx >= p.tau;
                     const int tile64 = (n0 + half * (BlockN / 2)) / 64 + t;
-                    if (quad == 0 && lane == 0 && tile64 < n_tiles64) {
+                    if (quad == 0 && lane == 0 && tile64 < n_tiles64 && mt < m_tiles) {
                         p.keep_out[static_cast<size_t>(mt) * n_tiles64 + tile64] = keep[t] ? 1 : 0;
                         if (p.stats_out != nullptr)
                             p.stats_out[static_cast<size_t>(mt) * n_tiles64 + tile64] = mx;
@@ -610,7 +668,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             // release the accumulator buffer
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_empty_bar + buf);
+            if (lane == 0) {
+                if constexpr (CtaGroup == 2) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty_bar + buf), 0));
+                else mbar_arrive(tmem_empty_bar + buf);
+            }
         }
     }
 
@@ -624,9 +685,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     tc_fence_before_sync();
     __syncthreads();
+    // a pair leaves together: the peer's shared and tensor memory stay valid until the
+    // leader's last MMA and every remote arrive have landed
+    if constexpr (CtaGroup == 2) cluster_sync_all();
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, kTmemCols);
+        if constexpr (CtaGroup == 2) tmem_dealloc_pair(tmem_base, kTmemCols);
+        else tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 

@@ -70,6 +70,8 @@ for _name, _argtypes in SIGNATURES.items():
     _fn.restype = i32
 lib.pk100_launch_count.restype = i64
 lib.pk100_launch_count.argtypes = []
+lib.pk100_set_gemm_cta_pairs.restype = None
+lib.pk100_set_gemm_cta_pairs.argtypes = [i32]
 
 # enums (include/pk100.h)
 OK, ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_UNSUPPORTED, ERR_DRIVER, ERR_LIMIT = 0, -1, -2, -3, -4, -5, -6

@@ -229,6 +229,49 @@ def test_w4g128_in_smem_dequant(pk, cuda, m, n, k):
     assert np.array_equal(got, host(ref))
 
 
+@pytest.mark.parametrize("kind", ["f16", "e4m3", "s8"])
+def test_cta_pair_tiles_match_single_cta_tiles(pk, cuda, kind):
+    """256-column tiles can run on CTA pairs (cta_group::2).  Same operands through both paths:
+    INT8 must agree bit for bit (exact accumulator), fp kinds within one fp16 ulp; the pair
+    result is also checked against the oracle.  M is not a multiple of 256 (odd tile count)."""
+    L = pk.lib
+    rng = np.random.default_rng(21)
+    m, n, k = 4480, 1024, 1024          # 35 row tiles x 4 column tiles = 140... forced to 256-wide below
+    x = codec.f16_round(rng.standard_normal((m, k)))
+    w = codec.f16_round(rng.standard_normal((2048, k)) * 0.02)
+    n = 2048
+    res = codec.f16_round(rng.standard_normal((m, n)))
+    if kind == "f16":
+        a, b, kw, want = dev16(x), dev16(w), dict(kind=L.KIND_F16), O.linear_f16(x, w, residual16=res, alpha=0.5)
+    elif kind == "e4m3":
+        xq, xs = O.quant_rows_fp8_dynamic(x)
+        wq, ws = codec.quantize_rows_fp8(w)
+        a, b = dev(xq), dev(wq)
+        kw = dict(kind=L.KIND_E4M3, row_scales=dev(xs), col_scales=dev(ws))
+        want = O.linear_fp8(xq, wq, ws, xs, residual16=res, alpha=0.5)
+    else:
+        xq, xs = O.quant_rows_int8_dynamic(x)
+        wq, ws = codec.quantize_rows_int8(w)
+        a, b = dev(xq), dev(wq)
+        kw = dict(kind=L.KIND_S8, row_scales=dev(xs), col_scales=dev(ws))
+        want = O.linear_int8(xq, wq, ws, xs, residual16=res, alpha=0.5)
+    outs = []
+    for pairs in (1, 0):
+        L.lib.pk100_set_gemm_cta_pairs(pairs)
+        st = _status(cuda)
+        out = dev16(res).clone()
+        pk.ops.gemm(a, b, out=out, residual=out, alpha=0.5, status=st, **kw)
+        torch.cuda.synchronize()
+        assert int(st.item()) == 0
+        outs.append(host(out))
+    L.lib.pk100_set_gemm_cta_pairs(0)
+    assert np.max(np.abs(outs[0] - want)) <= 4e-3
+    if kind == "s8":
+        assert np.array_equal(outs[0], outs[1])
+    else:
+        assert np.max(np.abs(outs[0] - outs[1])) <= 2e-3
+
+
 def test_gemm_rejects_bad_arguments(pk, cuda):
     L = pk.lib
     a = torch.zeros((8, 24), dtype=torch.float16, device=cuda)     # k*2 = 48 bytes: ok; n bad below
