@@ -291,9 +291,32 @@ def run_micro(args):
         side.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
     achieved = work / (ms * 1e-3) if work else None
-    print(json.dumps(dict(micro=args.micro, rows=m, avg_launch_ms=ms, achieved=achieved, unit=unit, bound=bound,
-                          peak=peak, frac=(achieved / peak if achieved else None),
-                          algorithmic_bytes=nbytes, peak_source=peaks["source"])), flush=True)
+    line = dict(micro=args.micro, rows=m, avg_launch_ms=ms, achieved=achieved, unit=unit, bound=bound,
+                peak=peak, frac=(achieved / peak if achieved else None),
+                algorithmic_bytes=nbytes, peak_source=peaks["source"])
+    if args.micro == "ff_expand":
+        # library bar, same run: cuBLASLt E4M3 GEMM of the same shape with a plain fp16 epilogue
+        # (no SiLU, no tile statistics, no INT8 encoding) -- context for the fraction above
+        try:
+            a8 = torch.randn(m, 1024, device=dev).to(torch.float8_e4m3fn)
+            b8 = torch.randn(4096, 1024, device=dev).to(torch.float8_e4m3fn)
+            one = torch.ones((), device=dev)
+            lib = lambda: torch._scaled_mm(a8, b8.t(), scale_a=one, scale_b=one, out_dtype=torch.float16)
+            for _ in range(3):
+                lib()
+            torch.cuda.synchronize()
+            l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            l0.record()
+            for _ in range(args.steps):
+                lib()
+            l1.record()
+            torch.cuda.synchronize()
+            lib_ms = l0.elapsed_time(l1) / args.steps
+            line["library_bar"] = dict(what="cuBLASLt E4M3 (torch._scaled_mm), plain fp16 epilogue",
+                                       avg_launch_ms=lib_ms, tflops=flops / (lib_ms * 1e-3) / 1e12)
+        except Exception as exc:  # noqa: BLE001 - the bar is optional context
+            line["library_bar"] = dict(unavailable=str(exc)[:120])
+    print(json.dumps(line), flush=True)
 
 
 def main():
