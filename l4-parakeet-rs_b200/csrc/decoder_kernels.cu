@@ -547,7 +547,10 @@ struct XSmem {
     float dur[kMaxUtt][8];
     int frame[kMaxUtt], symbols[kMaxUtt], last[kMaxUtt], count[kMaxUtt], ver[kMaxUtt], pred_ver[kMaxUtt];
     int total_frames[kMaxUtt];
-    unsigned char emitted[kMaxUtt], valid[kMaxUtt], done[kMaxUtt], need[kMaxUtt];
+    alignas(8) unsigned char emitted[kMaxUtt];
+    alignas(8) unsigned char valid[kMaxUtt];
+    alignas(8) unsigned char done[kMaxUtt];      // read as one 64-bit word: entries >= utts are 1
+    alignas(8) unsigned char need[kMaxUtt];      // !done && !valid, refreshed at the end of every round
     int ok;
 };
 
@@ -644,7 +647,7 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
         sm.ver[tid] = 0; sm.pred_ver[tid] = 0; sm.emitted[tid] = 0; sm.valid[tid] = 0;
         sm.total_frames[tid] = tid < U ? p.frames[tid] : 0;
         sm.done[tid] = tid >= U || p.frames[tid] <= 0;
-        sm.need[tid] = 0;
+        sm.need[tid] = !(tid >= U || p.frames[tid] <= 0);
     }
     if (tid == 0) sm.ok = 1;
     __syncthreads();
@@ -686,34 +689,19 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
 
     unsigned round = 0;
     while (true) {
-        bool any_running = false, any_need = false;
-        for (int u = 0; u < U; ++u) {
-            any_running |= !sm.done[u];
-            any_need |= !sm.done[u] && !sm.valid[u];
-        }
-        if (!any_running || sm.ok == 0) break;
-        if (tid < kMaxUtt) sm.need[tid] = tid < U && !sm.done[tid] && !sm.valid[tid];
-        __syncthreads();
+        const unsigned long long done8 = *reinterpret_cast<const unsigned long long*>(sm.done);
+        const unsigned long long need8 = *reinterpret_cast<const unsigned long long*>(sm.need);
+        if (done8 == 0x0101010101010101ull || sm.ok == 0) break;
+        const bool any_need = need8 != 0ull;
         PK_STAMP(0);
 
         if (any_need) {
             for (int l = 0; l < p.layers; ++l) {
                 if (sm.ok == 0) break;
-                // input of layer l (one thread per column: kXThreads == kHidden): the embedding
-                // of the last token, or the lower layer's fresh hidden state from the exchange
-                if (l == 0) {
-                    __half e[8];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        if (u < U && sm.need[u] && sm.emitted[u])
-                            e[u] = __ldg(p.embedding + static_cast<size_t>(sm.last[u]) * kHidden + tid);
-#pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        if (u < U && sm.need[u]) {
-                            sm.ax[u][tid] = sm.emitted[u] ? e[u] : __float2half(0.0f);   // fp16 exactly
-                            sm.ax[u + 8][tid] = __float2half(0.0f);
-                        }
-                } else {
+                // input of layer l (one thread per column: kXThreads == kHidden).  Layer 0 reads
+                // the embedding row that the decision warp staged in sm.ax when the token was
+                // chosen; upper layers take the lower layer's fresh hidden state from the exchange
+                if (l > 0) {
                     unsigned want[8];
                     size_t off[8];
                     float val[8];
@@ -729,8 +717,8 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
                             split_store(sm.ax, u, tid, val[u]);
                             split_store(sm.ah[l - 1], u, tid, val[u]);   // lower layer's next committed state
                         }
+                    __syncthreads();
                 }
-                __syncthreads();
                 PK_STAMP(1);
                 if (sm.ok == 0) break;
                 // gates[u][20 rows] = [x | h] . [w_ih | w_hh]^T, K = 1280 split over the 20 warps
@@ -795,9 +783,6 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
                               sum_parts(u, slot, kXWarps) + sm.pred_bias[slot], tag);
                 }
             }
-            __syncthreads();
-            if (tid < U && sm.need[tid]) { sm.ver[tid] += 1; sm.valid[tid] = 1; }
-            __syncthreads();
             PK_STAMP(4);
         }
 
@@ -810,7 +795,10 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const bool live = u < U && !sm.done[u];
-                want[u] = (live && sm.pred_ver[u] != sm.ver[u]) ? static_cast<unsigned>(sm.ver[u]) : 0u;
+                // sm.ver is bumped in the state update below; a prediction computed in this
+                // round carries version ver + 1
+                const int ver_now = sm.ver[u] + (sm.need[u] ? 1 : 0);
+                want[u] = (live && sm.pred_ver[u] != ver_now) ? static_cast<unsigned>(ver_now) : 0u;
                 off[u] = static_cast<size_t>(want[u] & 1) * U * kHidden + tid;
                 if (live)
                     e[u] = __ldg(p.enc_proj + (static_cast<size_t>(u) * p.seg_stride + sm.frame[u]) * kHidden + tid);
@@ -826,7 +814,7 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
         __syncthreads();
         PK_STAMP(5);
         if (sm.ok == 0) break;
-        if (tid < U) sm.pred_ver[tid] = sm.ver[tid];
+        if (tid < U) sm.pred_ver[tid] = sm.ver[tid] + (sm.need[tid] ? 1 : 0);
         const unsigned epoch = (round + 1) & kEpochMask;
         small_gemm(sm.ax, warp * 32, &sm.wj[0][0], kAct, 8, warp * 32, 2, std::integral_constant<int, 1>{});
         __syncthreads();
@@ -911,38 +899,50 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
                 const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, off);
                 best = other > best ? other : best;
             }
-            if (lane == 0) sm.best[u] = best;
-            if (lane < kDurations) sm.dur[u][lane] = __uint_as_float(static_cast<unsigned>(dv));
             if (!__all_sync(0xffffffffu, good)) sm.ok = 0;
-        }
-        __syncthreads();
-        PK_STAMP(7);
-        if (sm.ok == 0) break;
-        if (tid < U && !sm.done[tid]) {
-            const int u = tid;
-            const int token = 2047 - static_cast<int>((sm.best[u] >> 21) & 0x7FFull);
-            const float* dl = sm.dur[u];
+            const int token = 2047 - static_cast<int>((best >> 21) & 0x7FFull);
+            // first strict maximum of the five duration logits (lanes 0..4 hold one each)
+            const float my_dur = __uint_as_float(static_cast<unsigned>(dv));
             int duration = 0;
-            for (int i = 1; i < kDurations; ++i)
-                if (dl[i] > dl[duration]) duration = i;
+            float best_dur = __shfl_sync(0xffffffffu, my_dur, 0);
+#pragma unroll
+            for (int i = 1; i < kDurations; ++i) {
+                const float v = __shfl_sync(0xffffffffu, my_dur, i);
+                if (v > best_dur) { best_dur = v; duration = i; }
+            }
+            // the token's embedding row is the next LSTM input: fetch it now (fp16 exactly)
             if (token != kBlank) {
-                if (cta == 0 && sm.count[u] < p.max_tokens) {
-                    p.tokens[static_cast<size_t>(u) * p.max_tokens + sm.count[u]] = token;
-                    if (p.durations_out != nullptr)
-                        p.durations_out[static_cast<size_t>(u) * p.max_tokens + sm.count[u]] = duration;
+                const __half* emb = p.embedding + static_cast<size_t>(token) * kHidden;
+                for (int c = lane * 8; c < kHidden; c += 256) {
+                    *reinterpret_cast<uint4*>(&sm.ax[u][c]) = __ldg(reinterpret_cast<const uint4*>(emb + c));
+                    *reinterpret_cast<uint4*>(&sm.ax[u + 8][c]) = make_uint4(0, 0, 0, 0);
                 }
-                sm.count[u] += 1;
-                sm.last[u] = token;
-                sm.emitted[u] = 1;
-                sm.valid[u] = 0;
             }
-            sm.symbols[u] += 1;
-            sm.frame[u] += duration;
-            if (duration != 0 || sm.symbols[u] == kMaxSymbols) {
-                if (duration == 0) sm.frame[u] += 1;
-                sm.symbols[u] = 0;
+            if (lane == 0) {
+                if (sm.need[u]) { sm.ver[u] += 1; sm.valid[u] = 1; }   // this round's prediction is now current
+                if (token != kBlank) {
+                    if (cta == 0 && sm.count[u] < p.max_tokens) {
+                        p.tokens[static_cast<size_t>(u) * p.max_tokens + sm.count[u]] = token;
+                        if (p.durations_out != nullptr)
+                            p.durations_out[static_cast<size_t>(u) * p.max_tokens + sm.count[u]] = duration;
+                    }
+                    sm.count[u] += 1;
+                    sm.last[u] = token;
+                    sm.emitted[u] = 1;
+                    sm.valid[u] = 0;
+                }
+                int frame = sm.frame[u] + duration;
+                int symbols = sm.symbols[u] + 1;
+                if (duration != 0 || symbols == kMaxSymbols) {
+                    if (duration == 0) frame += 1;
+                    symbols = 0;
+                }
+                sm.frame[u] = frame;
+                sm.symbols[u] = symbols;
+                const bool done = frame >= sm.total_frames[u];
+                sm.done[u] = done;
+                sm.need[u] = !done && !sm.valid[u];
             }
-            if (sm.frame[u] >= sm.total_frames[u]) sm.done[u] = 1;
         }
         __syncthreads();
         PK_STAMP(8);
