@@ -1,4 +1,5 @@
 import importlib
+import importlib.util
 import sys
 from pathlib import Path
 
@@ -15,7 +16,13 @@ def pytest_configure(config):
 
 @pytest.fixture(scope="session")
 def pk():
-    """The product package (its directory name is not a Python identifier)."""
+    """The product package (its directory name is not a Python identifier).  The shared
+    library is built first if this is a fresh checkout (nvcc cross-compiles without a GPU)."""
+    if not (ROOT / "l4-parakeet-rs_b200" / "libpk100.so").exists():
+        spec = importlib.util.spec_from_file_location("pk100_build", ROOT / "l4-parakeet-rs_b200" / "build.py")
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.build()
     return importlib.import_module("l4-parakeet-rs_b200")
 
 
