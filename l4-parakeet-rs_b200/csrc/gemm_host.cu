@@ -51,6 +51,22 @@ static int make_map(CUtensorMap* map, const void* base, int elem_bytes, uint64_t
     return res == CUDA_SUCCESS ? PK100_OK : PK100_ERR_DRIVER;
 }
 
+// Tensor map of the output for the staged TMA store of the 256-column kernels: every epilogue
+// warp owns 32 rows x (tile columns / 4).  Only slices with 64- or 128-byte rows leave that way
+// (their swizzle modes); anything else keeps per-thread stores.  Returns the row bytes or 0.
+template <int Epi>
+static int make_out_map(CUtensorMap* map, const GemmParams& p) {
+    const int out_cols = Epi == EPI_GLU ? p.n / 2 : p.n;
+    const int cols_per_warp = (Epi == EPI_GLU ? 128 : 256) / (GemmWarps<BSRC_TMA>::kEpilogue / 4);
+    const int obytes = p.out_type == OUT_F16 ? 2 : (p.out_type == OUT_F32 ? 4 : 1);
+    const int row_bytes = cols_per_warp * obytes;
+    if (row_bytes != 64 && row_bytes != 128) return 0;
+    if ((reinterpret_cast<uintptr_t>(p.out) & 15u) != 0) return 0;
+    if ((static_cast<size_t>(p.ld_out) * obytes) % 16 != 0) return 0;
+    if (make_map(map, p.out, obytes, p.m, out_cols, p.ld_out, 32, row_bytes) != PK100_OK) return 0;
+    return row_bytes;
+}
+
 static int sm_count() {
     static int count = 0;
     if (count == 0) {
@@ -69,9 +85,10 @@ static std::atomic<int> g_use_pairs{0};
 extern "C" void pk100_set_gemm_cta_pairs(int enable) { g_use_pairs.store(enable != 0); }
 
 template <int Kind, int SwizzleBytes, int Epi>
-static int launch_pair(const pk100_gemm_args& a, const GemmParams& p, cudaStream_t stream) {
+static int launch_pair(const pk100_gemm_args& a, const GemmParams& p_in, cudaStream_t stream) {
     constexpr int BlockN = 256;
-    using Smem = GemmSmem<BlockN / 2, SwizzleBytes, BlockN>;
+    using Smem = GemmSmem<BlockN / 2, SwizzleBytes, BlockN, gemm_store_bytes<Epi, BSRC_TMA, BlockN>()>;
+    GemmParams p = p_in;
     auto kernel = gemm_kernel<Kind, BlockN, SwizzleBytes, Epi, BSRC_TMA, 2>;
     static bool configured = false;
     if (!configured) {
@@ -86,6 +103,8 @@ static int launch_pair(const pk100_gemm_args& a, const GemmParams& p, cudaStream
     if (rc != PK100_OK) return rc;
     rc = make_map(&map_b, a.b, elem, a.n, a.k, a.ldb, BlockN / 2, SwizzleBytes);
     if (rc != PK100_OK) return rc;
+    CUtensorMap map_out = map_a;
+    p.store_row_bytes = make_out_map<Epi>(&map_out, p);
     const int m_groups = (a.m + 2 * kBlockM - 1) / (2 * kBlockM);
     const int n_tiles = (p.n + BlockN - 1) / BlockN;
     int pairs = (a.max_ctas > 0 ? a.max_ctas : sm_count()) / 2;
@@ -93,7 +112,7 @@ static int launch_pair(const pk100_gemm_args& a, const GemmParams& p, cudaStream
     if (pairs < 1) pairs = 1;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * pairs);
-    cfg.blockDim = dim3(kGemmThreads);
+    cfg.blockDim = dim3(GemmWarps<BSRC_TMA>::kThreads);
     cfg.dynamicSmemBytes = Smem::kTotal;
     cfg.stream = stream;
     cudaLaunchAttribute attr{};
@@ -103,7 +122,7 @@ static int launch_pair(const pk100_gemm_args& a, const GemmParams& p, cudaStream
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, p);
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_out, p);
     if (err != cudaSuccess) {
         cudaGetLastError();
         return static_cast<int>(err);
@@ -113,11 +132,12 @@ static int launch_pair(const pk100_gemm_args& a, const GemmParams& p, cudaStream
 }
 
 template <int Kind, int BlockN, int SwizzleBytes, int Epi>
-static int launch(const pk100_gemm_args& a, const GemmParams& p, cudaStream_t stream) {
+static int launch(const pk100_gemm_args& a, const GemmParams& p_in, cudaStream_t stream) {
     if constexpr (BlockN == 256) {
-        if (g_use_pairs.load() != 0 && a.m > kBlockM) return launch_pair<Kind, SwizzleBytes, Epi>(a, p, stream);
+        if (g_use_pairs.load() != 0 && a.m > kBlockM) return launch_pair<Kind, SwizzleBytes, Epi>(a, p_in, stream);
     }
-    using Smem = GemmSmem<BlockN, SwizzleBytes>;
+    using Smem = GemmSmem<BlockN, SwizzleBytes, BlockN, gemm_store_bytes<Epi, BSRC_TMA, BlockN>()>;
+    GemmParams p = p_in;
     auto kernel = gemm_kernel<Kind, BlockN, SwizzleBytes, Epi, BSRC_TMA>;
     static bool configured = false;
     if (!configured) {
@@ -132,11 +152,13 @@ static int launch(const pk100_gemm_args& a, const GemmParams& p, cudaStream_t st
     if (rc != PK100_OK) return rc;
     rc = make_map(&map_b, a.b, elem, a.n, a.k, a.ldb, BlockN / 2, SwizzleBytes);
     if (rc != PK100_OK) return rc;
+    CUtensorMap map_out = map_a;
+    if constexpr (BlockN == 256) p.store_row_bytes = make_out_map<Epi>(&map_out, p);
     const int m_tiles = (a.m + kBlockM - 1) / kBlockM;
     const int n_tiles = (p.n + BlockN - 1) / BlockN;
     int ctas = a.max_ctas > 0 ? a.max_ctas : sm_count();
     if (ctas > m_tiles * n_tiles) ctas = m_tiles * n_tiles;
-    kernel<<<ctas, kGemmThreads, Smem::kTotal, stream>>>(map_a, map_b, p);
+    kernel<<<ctas, GemmWarps<BSRC_TMA>::kThreads, Smem::kTotal, stream>>>(map_a, map_b, map_out, p);
     return pk100_launch_status();
 }
 
@@ -159,7 +181,7 @@ static int launch_w4(const pk100_gemm_args& a, const GemmParams& p, cudaStream_t
     const int n_tiles = (p.n + BlockN - 1) / BlockN;
     int ctas = a.max_ctas > 0 ? a.max_ctas : sm_count();
     if (ctas > m_tiles * n_tiles) ctas = m_tiles * n_tiles;
-    kernel<<<ctas, kGemmThreads, Smem::kTotal, stream>>>(map_a, map_a, p);   // B has no tensor map
+    kernel<<<ctas, GemmWarps<BSRC_W4G128>::kThreads, Smem::kTotal, stream>>>(map_a, map_a, map_a, p);   // neither B nor the output has a tensor map
     return pk100_launch_status();
 }
 
@@ -238,7 +260,7 @@ extern "C" int pk100_gemm(void* stream_v, const pk100_gemm_args* a) {
 
     // Tile width: 256 columns unless that leaves too few tiles to fill the SMs.
     const int m_tiles = (a->m + kBlockM - 1) / kBlockM;
-    const bool narrow = (a->n % 256 != 0) || (m_tiles * (a->n / 256) < sm_count());
+    bool narrow = (a->n % 256 != 0) || (m_tiles * (a->n / 256) < sm_count());
 
     if (w4) return launch_w4(*a, p, stream);
     switch (a->epilogue) {

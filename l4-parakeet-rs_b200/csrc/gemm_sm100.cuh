@@ -51,25 +51,49 @@ struct GemmParams {
     const uint8_t* w4_codes;     // [n, k/2], low nibble = even k
     const __half* w4_scales;     // [k/128, n]
     int* status;                 // set non-zero when a bounded wait gave up
+    // Bytes of one output row in a warp's 32-row slice when the slices leave through shared
+    // memory and a TMA store (64 or 128); 0 = each thread stores its row piece directly.
+    int store_row_bytes;
 };
 
 constexpr int kBlockM = 128;
-constexpr int kEpilogueWarps = 8;
-constexpr int kGemmThreads = 32 * (2 + kEpilogueWarps);
+// Warps per CTA: TMA producer + MMA issuer + epilogue warps (+ 4 dequantisation warps for INT4
+// weights).  16 epilogue warps = 4 per TMEM lane quadrant, each a quarter of the tile's
+// columns: the epilogue of a K = 1024 tile has to finish within the ~4k cycles its MMAs take.
+template <int BSrc>
+struct GemmWarps {
+    static constexpr int kEpilogue = BSrc == BSRC_W4G128 ? 4 : 16;
+    static constexpr int kThreads = 32 * (2 + kEpilogue + (BSrc == BSRC_W4G128 ? 4 : 0));
+};
 
-// BRows = B rows staged per CTA per stage, EpiCols = accumulator columns of the tile.
-template <int BRows, int SwizzleBytes, int EpiCols = BRows>
+// Shared memory the epilogue warps stage their output slices in for the TMA store: 32 rows of
+// up to 128 bytes per warp (64 bytes for the INT8 sparse-out tiles).  Only the 256-column TMA
+// kernels use it.
+template <int Epi, int BSrc, int BlockN>
+constexpr int gemm_store_bytes() {
+    if (BSrc != BSRC_TMA || BlockN != 256) return 0;
+    return GemmWarps<BSrc>::kEpilogue * 32 * (Epi == EPI_SPARSE_OUT ? 64 : 128);
+}
+
+// BRows = B rows staged per CTA per stage, EpiCols = accumulator columns of the tile,
+// StoreBytes = output staging for the TMA store.
+template <int BRows, int SwizzleBytes, int EpiCols = BRows, int StoreBytes = 0>
 struct GemmSmem {
     static constexpr int kStageA = kBlockM * SwizzleBytes;
     static constexpr int kStageB = BRows * SwizzleBytes;
     static constexpr int kStageBytes = kStageA + kStageB;
-    static constexpr int kBudget = 196 * 1024;
+    // tail: barriers + tmem pointer + abort flag + epilogue staging
+    // (each epilogue warp keeps a private slice of column scales and biases: 32 bytes per column)
+    static constexpr int kTailBytes = 64 * 8 + 16 + 32 * EpiCols + 64 * 4;
+    static constexpr int kStoreBytes = StoreBytes;
+    // 227 KB per CTA, less the tail, the output staging and 1 KB of alignment slack; the
+    // pipeline is not depth-sensitive (2 and 4 stages measured alike), so staging comes first
+    static constexpr int kBudget = 227 * 1024 - 1024 - kTailBytes - kStoreBytes;
     static constexpr int kStagesRaw = kBudget / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+    static_assert(kStages >= 2, "at least a double-buffered operand pipeline");
     static constexpr int kTileBytes = kStages * kStageBytes;
-    // tail: barriers + tmem pointer + abort flag + epilogue staging
-    static constexpr int kTailBytes = 64 * 8 + 16 + 2 * EpiCols * 4 + 64 * 4;
-    static constexpr int kTotal = kTileBytes + kTailBytes + 1024;  // + alignment slack
+    static constexpr int kTotal = kTileBytes + kStoreBytes + kTailBytes + 1024;
 };
 
 __device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
@@ -105,56 +129,59 @@ __device__ __forceinline__ float acc_to_float(uint32_t r) {
     }
 }
 
-// Named barrier over the epilogue warps only.
-template <int Warps>
-__device__ __forceinline__ void epilogue_bar_sync() {
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * Warps) : "memory");
+// Encode 16 consecutive output columns of one row (fp16: two 16-byte chunks, E4M3 / INT8: one).
+__device__ __forceinline__ int pack_piece(int out_type, float out_scale, const float (&v)[16],
+                                          uint4 (&w)[2]) {
+    if (out_type == OUT_F16) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            w[i] = make_uint4(pack_half2(v[8 * i + 0], v[8 * i + 1]), pack_half2(v[8 * i + 2], v[8 * i + 3]),
+                              pack_half2(v[8 * i + 4], v[8 * i + 5]), pack_half2(v[8 * i + 6], v[8 * i + 7]));
+        }
+        return 2;
+    }
+    uint32_t q[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int b = 4 * j;
+        const float a0 = round_f16(v[b]) * out_scale, a1 = round_f16(v[b + 1]) * out_scale;
+        const float a2 = round_f16(v[b + 2]) * out_scale, a3 = round_f16(v[b + 3]) * out_scale;
+        q[j] = out_type == OUT_E4M3 ? pack_e4m3x4(a0, a1, a2, a3) : pack_s8x4(a0, a1, a2, a3);
+    }
+    w[0] = make_uint4(q[0], q[1], q[2], q[3]);
+    return 1;
 }
 
-// Store 32 consecutive output columns of one row.
-__device__ __forceinline__ void store_chunk(void* out_row, int out_type, float out_scale,
-                                            const float (&v)[32]) {
-    if (out_type == OUT_F16) {
-        uint4* dst = reinterpret_cast<uint4*>(out_row);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            dst[i] = make_uint4(pack_half2(v[8 * i + 0], v[8 * i + 1]),
-                                pack_half2(v[8 * i + 2], v[8 * i + 3]),
-                                pack_half2(v[8 * i + 4], v[8 * i + 5]),
-                                pack_half2(v[8 * i + 6], v[8 * i + 7]));
-        }
-    } else if (out_type == OUT_F32) {
+// Store 16 consecutive output columns of one row straight to global memory.
+__device__ __forceinline__ void store_piece(void* out_row, int out_type, float out_scale,
+                                            const float (&v)[16]) {
+    if (out_type == OUT_F32) {
         float4* dst = reinterpret_cast<float4*>(out_row);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 4; ++i) {
             dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
         }
-    } else if (out_type == OUT_E4M3) {
-        uint4* dst = reinterpret_cast<uint4*>(out_row);
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            uint32_t w[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int b = 16 * i + 4 * j;
-                w[j] = pack_e4m3x4(round_f16(v[b]) * out_scale, round_f16(v[b + 1]) * out_scale,
-                                   round_f16(v[b + 2]) * out_scale, round_f16(v[b + 3]) * out_scale);
-            }
-            dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
-        }
+        return;
+    }
+    uint4 w[2];
+    const int chunks = pack_piece(out_type, out_scale, v, w);
+    uint4* dst = reinterpret_cast<uint4*>(out_row);
+    dst[0] = w[0];
+    if (chunks == 2) dst[1] = w[1];
+}
+
+// Put 16 consecutive output columns (piece `piece` of the warp's slice) into this lane's row
+// of the staging slice.  16-byte chunks are XOR-swizzled with `swz`, the pattern of the TMA
+// store's tensor map (64-byte rows: (row >> 1) & 3, 128-byte rows: row & 7).
+__device__ __forceinline__ void stage_piece(uint8_t* stage_row, int piece, int swz, int out_type,
+                                            float out_scale, const float (&v)[16]) {
+    uint4 w[2];
+    const int chunks = pack_piece(out_type, out_scale, v, w);
+    if (chunks == 2) {
+        *reinterpret_cast<uint4*>(stage_row + (((2 * piece) ^ swz) << 4)) = w[0];
+        *reinterpret_cast<uint4*>(stage_row + (((2 * piece + 1) ^ swz) << 4)) = w[1];
     } else {
-        uint4* dst = reinterpret_cast<uint4*>(out_row);
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            uint32_t w[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int b = 16 * i + 4 * j;
-                w[j] = pack_s8x4(round_f16(v[b]) * out_scale, round_f16(v[b + 1]) * out_scale,
-                                 round_f16(v[b + 2]) * out_scale, round_f16(v[b + 3]) * out_scale);
-            }
-            dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
-        }
+        *reinterpret_cast<uint4*>(stage_row + ((piece ^ swz) << 4)) = w[0];
     }
 }
 
@@ -187,12 +214,13 @@ __device__ __forceinline__ bool k_block_live(uint64_t mask, int kb) {
 // operand traffic of two independent 128 x BlockN tiles; the even CTA issues the MMAs, each CTA
 // runs the epilogue of its own 128 accumulator rows.
 template <int Kind, int BlockN, int SwizzleBytes, int Epi, int BSrc, int CtaGroup = 1>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(GemmWarps<BSrc>::kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const __grid_constant__ CUtensorMap map_out,
             const GemmParams p) {
     static_assert(CtaGroup == 1 || (CtaGroup == 2 && BlockN == 256 && BSrc == BSRC_TMA), "pairs: 256 columns, TMA");
     constexpr int kBRows = BlockN / CtaGroup;               // B rows staged by this CTA
-    using Smem = GemmSmem<kBRows, SwizzleBytes, BlockN>;
+    using Smem = GemmSmem<kBRows, SwizzleBytes, BlockN, gemm_store_bytes<Epi, BSrc, BlockN>()>;
     constexpr int kStages = Smem::kStages;
     constexpr int kElemBytes = Kind == KIND_F16 ? 2 : 1;
     constexpr int kBlockK = SwizzleBytes / kElemBytes;       // elements per K block
@@ -203,24 +231,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     static_assert(BSrc == BSRC_TMA || (Kind == KIND_F16 && SwizzleBytes == 128 && BlockN == 128 &&
                                        Epi == EPI_LINEAR), "w4: fp16 MMA, 128-column tiles, linear epilogue");
     // INT4 weights: 4 epilogue warps (one per TMEM lane quadrant) + 4 dequantisation warps;
-    // otherwise 8 epilogue warps, two per quadrant, each half of the tile's columns.
-    constexpr int kEpiWarps = BSrc == BSRC_W4G128 ? 4 : kEpilogueWarps;
-    constexpr int kColSplit = kEpiWarps / 4;
-    constexpr int kColsPerWarp = BlockN / kColSplit;
+    // otherwise 16 epilogue warps, four per quadrant, each a quarter of the tile's columns.
+    constexpr int kEpiWarps = GemmWarps<BSrc>::kEpilogue;
+    constexpr int kParts = kEpiWarps / 4;
+    constexpr int kOutCols = Epi == EPI_GLU ? BlockN / 2 : BlockN;   // output columns of a tile
+    constexpr int kColsPerWarp = kOutCols / kParts;
+    static_assert(kColsPerWarp % 16 == 0, "each epilogue warp owns whole 16-column pieces");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint8_t* tail = smem + Smem::kTileBytes;
+    uint8_t* store_smem = smem + Smem::kTileBytes;            // 1 KB aligned: stage sizes are
+    uint8_t* tail = store_smem + Smem::kStoreBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);
     uint64_t* empty_bar = full_bar + kStages;
     uint64_t* tmem_full_bar = empty_bar + kStages;
     uint64_t* tmem_empty_bar = tmem_full_bar + 2;
     uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(tail + 64 * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 64 * 8 + 8);
-    float* s_col_scale = reinterpret_cast<float*>(tail + 64 * 8 + 16);
-    float* s_bias = s_col_scale + BlockN;
-    float* s_reduce = s_bias + BlockN;                       // [kEpilogueWarps][4]
+    float* s_cols = reinterpret_cast<float*>(tail + 64 * 8 + 16);   // per-warp scale / bias slices
+    float* s_reduce = s_cols + 8 * BlockN;                    // one float per epilogue warp
 
     const int warp = static_cast<int>(threadIdx.x) / 32;
     const int lane = static_cast<int>(threadIdx.x) % 32;
@@ -469,10 +499,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
     } else {
         // ---------------------------------------------------------- epilogue
-        const int ew = warp - 2;                 // 0..7
+        const int ew = warp - 2;                 // 0 .. kEpiWarps-1
         const int quad = warp % 4;               // TMEM lane quadrant this warp may read
-        const int half = ew / 4;                 // which part of the tile's columns
-        const int et = static_cast<int>(threadIdx.x) - 64;   // 0 .. 32*kEpiWarps-1
+        const int part = ew / 4;                 // which slice of the tile's columns
+        // Slice of the per-column epilogue constants this warp reads: kSlice scales, then kSlice
+        // biases (GLU: value columns first, their gate columns after).  Warp-private, so staging
+        // a tile's constants needs no CTA-wide barrier.
+        constexpr int kSlice = BlockN / kParts;
+        constexpr int kPer = kSlice / 32;
+        float* my_scale = s_cols + ew * 2 * kSlice;
+        float* my_bias = my_scale + kSlice;
+        float pre_s[kPer], pre_b[kPer];
+        auto prefetch_cols = [&](int nt_) {
+#pragma unroll
+            for (int u = 0; u < kPer; ++u) {
+                const int i = u * 32 + lane;
+                int src;
+                if constexpr (Epi == EPI_GLU) {
+                    src = i < kColsPerWarp ? nt_ * kBHalf + part * kColsPerWarp + i
+                                           : p.n / 2 + nt_ * kBHalf + part * kColsPerWarp + (i - kColsPerWarp);
+                } else {
+                    src = nt_ * BlockN + part * kColsPerWarp + i;
+                }
+                const bool in = src < p.n;
+                pre_s[u] = (p.col_scales != nullptr && in) ? __ldg(p.col_scales + src) : 1.0f;
+                pre_b[u] = (p.bias != nullptr && in) ? __ldg(p.bias + src) : 0.0f;
+            }
+        };
+        if (worker < num_tiles) prefetch_cols(worker / m_groups);
         int local = 0;
         bool ok = true;
         for (int tile = worker; tile < num_tiles && ok; tile += workers, ++local) {
@@ -483,20 +537,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const uint32_t acc_phase = (local >> 1) & 1;
             const int row = mt * kBlockM + quad * 32 + lane;
             const int n0 = Epi == EPI_GLU ? nt * kBHalf : nt * BlockN;   // first output column
-            // stage per-column scale / bias for this tile
-            epilogue_bar_sync<kEpiWarps>();
-            for (int c = et; c < BlockN; c += 32 * kEpiWarps) {
-                int src;
-                if constexpr (Epi == EPI_GLU) {
-                    src = c < kBHalf ? nt * kBHalf + c : p.n / 2 + nt * kBHalf + (c - kBHalf);
-                } else {
-                    src = nt * BlockN + c;
-                }
-                const bool in = src < p.n;
-                s_col_scale[c] = (p.col_scales != nullptr && in) ? p.col_scales[src] : 1.0f;
-                s_bias[c] = (p.bias != nullptr && in) ? p.bias[src] : 0.0f;
+            // this warp's column scales / biases: written from the registers prefetched during
+            // the previous tile, then the next tile's are requested
+            __syncwarp();
+#pragma unroll
+            for (int u = 0; u < kPer; ++u) {
+                my_scale[u * 32 + lane] = pre_s[u];
+                my_bias[u * 32 + lane] = pre_b[u];
             }
-            epilogue_bar_sync<kEpiWarps>();
+            __syncwarp();
+            if (tile + workers < num_tiles) prefetch_cols((tile + workers) / m_groups);
+            const float rs = p.row_scales != nullptr ? (row < p.m ? p.row_scales[row] : 0.0f)
+                                                     : p.row_scale;
 
             bool live = true;
             if (p.keep_in != nullptr) {
@@ -516,153 +568,172 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
             tc_fence_after_sync();
 
-            const float rs = p.row_scales != nullptr ? (row < p.m ? p.row_scales[row] : 0.0f)
-                                                     : p.row_scale;
             const uint32_t taddr_base = tmem_base + static_cast<uint32_t>(buf * BlockN) +
                                         (static_cast<uint32_t>(quad * 32) << 16);
             const size_t obytes = out_elem_bytes(p.out_type);
 
+            constexpr int kPieces = kColsPerWarp / 16;
+            const bool zero_row = row >= p.valid_rows;
+            // Output slice of this warp (32 rows x kColsPerWarp columns): staged in shared memory
+            // and written by one TMA store when the host set that up, else stored per thread.
+            const bool staged = Smem::kStoreBytes > 0 && p.store_row_bytes != 0;
+            uint8_t* stage = store_smem + ew * (Smem::kStoreBytes / kEpiWarps);
+            uint8_t* stage_row = stage + lane * p.store_row_bytes;
+            const int swz = p.store_row_bytes == 128 ? (lane & 7) : ((lane >> 1) & 3);
+            if (staged) {
+                if (lane == 0) bulk_wait_read_all();   // the previous tile's store has read the slice
+                __syncwarp();
+            }
             if constexpr (Epi == EPI_LINEAR) {
-                constexpr int kChunks = kColsPerWarp / 32;
 #pragma unroll 1
-                for (int c = 0; c < kChunks; ++c) {
-                    const int col_local = half * kColsPerWarp + c * 32;
-                    uint32_t r[32];
-                    tmem_ld_32x32(taddr_base + col_local, r);
+                for (int c = 0; c < kPieces; ++c) {
+                    const int col_local = part * kColsPerWarp + c * 16;
+                    uint32_t r[16];
+                    tmem_ld_32x16(taddr_base + col_local, r);
                     tmem_ld_wait();
                     const int col = n0 + col_local;
                     if (row < p.m && col < p.n) {
-                        float v[32];
-                        const bool zero_row = row >= p.valid_rows;
-                        uint4 res_raw[4];
+                        float v[16];
+                        uint4 res_raw[2];
                         if (p.residual != nullptr) {
                             const uint4* rp = reinterpret_cast<const uint4*>(
                                 p.residual + static_cast<size_t>(row) * p.ld_res + col);
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) res_raw[i] = rp[i];
+                            res_raw[0] = rp[0];
+                            res_raw[1] = rp[1];
                         }
                         const __half* res_h = reinterpret_cast<const __half*>(res_raw);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
+                        for (int j = 0; j < 16; ++j) {
                             float x = live ? acc_to_float<Kind>(r[j]) : 0.0f;
-                            x = x * rs * s_col_scale[col_local + j] + s_bias[col_local + j];
+                            x = x * rs * my_scale[c * 16 + j] + my_bias[c * 16 + j];
                             if (p.act == ACT_SILU) x = silu_f(x);
                             else if (p.act == ACT_RELU) x = fmaxf(x, 0.0f);
                             if (p.residual != nullptr) x = fmaf(p.alpha, x, __half2float(res_h[j]));
                             else x *= p.alpha;
                             v[j] = zero_row ? 0.0f : x;
                         }
-                        uint8_t* out_row = reinterpret_cast<uint8_t*>(p.out) +
-                            (static_cast<size_t>(row) * p.ld_out + col) * obytes;
-                        store_chunk(out_row, p.out_type, p.out_scale, v);
+                        if (staged) {
+                            stage_piece(stage_row, c, swz, p.out_type, p.out_scale, v);
+                        } else {
+                            uint8_t* out_row = reinterpret_cast<uint8_t*>(p.out) +
+                                (static_cast<size_t>(row) * p.ld_out + col) * obytes;
+                            store_piece(out_row, p.out_type, p.out_scale, v);
+                        }
                     }
                 }
             } else if constexpr (Epi == EPI_GLU) {
-                // columns [0, BlockN/2) hold values, [BlockN/2, BlockN) their gates
-                constexpr int kChunks = BlockN / 4 / 32;
-                static_assert(kChunks >= 1, "GLU needs BlockN >= 128");
+                // accumulator columns [0, BlockN/2) hold values, [BlockN/2, BlockN) their gates
 #pragma unroll 1
-                for (int c = 0; c < kChunks; ++c) {
-                    const int col_local = half * (BlockN / 4) + c * 32;
-                    uint32_t rv[32], rg[32];
-                    tmem_ld_32x32(taddr_base + col_local, rv);
-                    tmem_ld_32x32(taddr_base + kBHalf + col_local, rg);
+                for (int c = 0; c < kPieces; ++c) {
+                    const int col_local = part * kColsPerWarp + c * 16;
+                    uint32_t rv[16], rg[16];
+                    tmem_ld_32x16(taddr_base + col_local, rv);
+                    tmem_ld_32x16(taddr_base + kBHalf + col_local, rg);
                     tmem_ld_wait();
                     const int col = n0 + col_local;
                     if (row < p.m && col < p.n / 2) {
-                        float v[32];
-                        const bool zero_row = row >= p.valid_rows;
+                        float v[16];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
+                        for (int j = 0; j < 16; ++j) {
                             const float value = round_f16(acc_to_float<Kind>(rv[j]) * rs *
-                                                          s_col_scale[col_local + j]);
+                                                          my_scale[c * 16 + j]);
                             const float gate = round_f16(acc_to_float<Kind>(rg[j]) * rs *
-                                                         s_col_scale[kBHalf + col_local + j]);
+                                                         my_scale[kColsPerWarp + c * 16 + j]);
                             v[j] = zero_row ? 0.0f : __fdividef(value, 1.0f + __expf(-gate));
                         }
-                        uint8_t* out_row = reinterpret_cast<uint8_t*>(p.out) +
-                            (static_cast<size_t>(row) * p.ld_out + col) * obytes;
-                        store_chunk(out_row, p.out_type, p.out_scale, v);
+                        if (staged) {
+                            stage_piece(stage_row, c, swz, p.out_type, p.out_scale, v);
+                        } else {
+                            uint8_t* out_row = reinterpret_cast<uint8_t*>(p.out) +
+                                (static_cast<size_t>(row) * p.ld_out + col) * obytes;
+                            store_piece(out_row, p.out_type, p.out_scale, v);
+                        }
                     }
                 }
             } else {
                 // EPI_SPARSE_OUT: SiLU, per-(128 x 64) tile max|a| against tau, INT8 store.
-                // Kept lean (about 8 instructions per element) because with K = 1024 the MMAs of
-                // a tile take only ~4k cycles: SiLU(x) = x/2 * (1 + tanh(x/2)) costs one MUFU
-                // (tanh.approx), the x32 of the INT8 encoding is folded into the same FMA, the
-                // codes are produced in the first pass and held packed (32 registers).
-                static_assert(Epi != EPI_SPARSE_OUT || BlockN == 256, "sparse-out uses BlockN 256");
-                constexpr int kChunks = BlockN / 2 / 32;     // 4 chunks = two 64-wide tiles
-                uint32_t q[kChunks][8];                       // INT8 codes, 4 per register
-                float tile_max[2] = {0.0f, 0.0f};             // max |a * out_scale|
-                const bool row_live = row < p.valid_rows && row < p.m;
-                const float half_scale = 0.5f * p.out_scale;
+                // Each epilogue warp owns one 64-column sparsity tile of its 32 rows.  Kept lean
+                // (about 8 instructions per element) because with K = 1024 the MMAs of a tile take
+                // only ~4k cycles: SiLU(x) = x/2 * (1 + tanh(x/2)) costs one MUFU (tanh.approx),
+                // the x32 of the INT8 encoding is folded into the same FMA, the codes are produced
+                // in the first pass and held packed (16 registers).
+                static_assert(Epi != EPI_SPARSE_OUT || (BlockN == 256 && kColsPerWarp == 64),
+                              "sparse-out: 256-column tiles, one 64-column tile per warp");
+                uint32_t q[kPieces][4];                       // INT8 codes, 4 per register
+                float tile_max = 0.0f;                        // max |a * out_scale|
+                // a * out_scale = s * (1 + tanh(h)) with s = x/2 * out_scale and h = x/2; rows that
+                // must read as zero get a zero row factor
+                const float rso = (!zero_row && row < p.m) ? rs * 0.5f * p.out_scale : 0.0f;
+                const float inv_out = 1.0f / p.out_scale;
 #pragma unroll
-                for (int c = 0; c < kChunks; ++c) {
-                    const int col_local = half * (BlockN / 2) + c * 32;
-                    uint32_t r[32];
-                    tmem_ld_32x32(taddr_base + col_local, r);
+                for (int c = 0; c < kPieces; ++c) {
+                    uint32_t r[16];
+                    tmem_ld_32x16(taddr_base + part * kColsPerWarp + c * 16, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        int code[4];
+                    for (int j = 0; j < 16; j += 4) {
+                        const float4 cs = *reinterpret_cast<const float4*>(my_scale + c * 16 + j);
+                        const float csv[4] = {cs.x, cs.y, cs.z, cs.w};
+                        uint32_t bits[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const float x = acc_to_float<Kind>(r[j + e]) * (rs * s_col_scale[col_local + j + e]);
+                            const float sv = (acc_to_float<Kind>(r[j + e]) * rso) * csv[e];
                             float th;
-                            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * x));
-                            const float xs = x * half_scale;
-                            float a = fmaf(xs, th, xs);          // SiLU(x) * out_scale
-                            a = row_live ? a : 0.0f;
-                            tile_max[c / 2] = fmaxf(tile_max[c / 2], fabsf(a));
-                            // SiLU >= -0.279, so saturation at -128 is never reached: +-127 clamp holds
-                            asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(code[e]) : "f"(a));
+                            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(sv * inv_out));
+                            const float a = fmaf(sv, th, sv);
+                            tile_max = fmaxf(tile_max, fabsf(a));
+                            // round-to-nearest-even INT8 code in the low byte: adding 1.5 * 2^23 leaves
+                            // the integer in the mantissa (two's complement for negatives).  SiLU >=
+                            // -0.279, so only the upper clamp at 127 can bind.
+                            bits[e] = __float_as_uint(fminf(a, 127.0f) + 12582912.0f);
                         }
-                        q[c][j / 4] = (code[0] & 255) | ((code[1] & 255) << 8) | ((code[2] & 255) << 16) |
-                                      (static_cast<uint32_t>(code[3]) << 24);
+                        q[c][j / 4] = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040),
+                                                  __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
                     }
                 }
 #pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    float mx = tile_max[t];
-#pragma unroll
-                    for (int off = 16; off > 0; off /= 2)
-                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-                    tile_max[t] = mx;
-                }
-                if (lane == 0) {
-                    s_reduce[ew * 2 + 0] = tile_max[0];
-                    s_reduce[ew * 2 + 1] = tile_max[1];
-                }
-                epilogue_bar_sync<kEpiWarps>();
-                bool keep[2];
+                for (int off = 16; off > 0; off /= 2)
+                    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, off));
+                // (double-buffered by tile parity: a warp can be a whole tile ahead of its peers)
+                float* red = s_reduce + (local & 1) * kEpiWarps;
+                if (lane == 0) red[ew] = tile_max;
+                // the four warps (one per lane quadrant) that share this 64-column tile
+                asm volatile("bar.sync %0, 128;" ::"r"(2 + part) : "memory");
                 const int n_tiles64 = p.n / 64;
-                const float inv_out_scale = 1.0f / p.out_scale;
+                float mx = 0.0f;
 #pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    float mx = 0.0f;
-#pragma unroll
-                    for (int qd = 0; qd < 4; ++qd) mx = fmaxf(mx, s_reduce[(half * 4 + qd) * 2 + t]);
-                    mx *= inv_out_scale;                        // statistic in activation units
-                    keep[t] = mx >= p.tau;
-                    const int tile64 = (n0 + half * (BlockN / 2)) / 64 + t;
-                    if (quad == 0 && lane == 0 && tile64 < n_tiles64 && mt < m_tiles) {
-                        p.keep_out[static_cast<size_t>(mt) * n_tiles64 + tile64] = keep[t] ? 1 : 0;
-                        if (p.stats_out != nullptr)
-                            p.stats_out[static_cast<size_t>(mt) * n_tiles64 + tile64] = mx;
-                    }
+                for (int qd = 0; qd < 4; ++qd) mx = fmaxf(mx, red[part * 4 + qd]);
+                mx *= 1.0f / p.out_scale;                       // statistic in activation units
+                const bool keep = mx >= p.tau;
+                const int tile64 = n0 / 64 + part;
+                if (quad == 0 && lane == 0 && tile64 < n_tiles64 && mt < m_tiles) {
+                    p.keep_out[static_cast<size_t>(mt) * n_tiles64 + tile64] = keep ? 1 : 0;
+                    if (p.stats_out != nullptr)
+                        p.stats_out[static_cast<size_t>(mt) * n_tiles64 + tile64] = mx;
                 }
-                if (row < p.m) {
+                const int col = n0 + part * kColsPerWarp;
+                if (staged) {
 #pragma unroll
-                    for (int c = 0; c < kChunks; ++c) {
-                        const int col = n0 + half * (BlockN / 2) + c * 32;
-                        if (col >= p.n) continue;
-                        uint4* dst = reinterpret_cast<uint4*>(
-                            reinterpret_cast<uint8_t*>(p.out) + static_cast<size_t>(row) * p.ld_out + col);
-                        const bool k = keep[c / 2];
-                        dst[0] = k ? make_uint4(q[c][0], q[c][1], q[c][2], q[c][3]) : make_uint4(0, 0, 0, 0);
-                        dst[1] = k ? make_uint4(q[c][4], q[c][5], q[c][6], q[c][7]) : make_uint4(0, 0, 0, 0);
-                    }
+                    for (int c = 0; c < kPieces; ++c)
+                        *reinterpret_cast<uint4*>(stage_row + ((c ^ swz) << 4)) =
+                            keep ? make_uint4(q[c][0], q[c][1], q[c][2], q[c][3]) : make_uint4(0, 0, 0, 0);
+                } else if (row < p.m && col < p.n) {
+                    uint4* dst = reinterpret_cast<uint4*>(
+                        reinterpret_cast<uint8_t*>(p.out) + static_cast<size_t>(row) * p.ld_out + col);
+#pragma unroll
+                    for (int c = 0; c < kPieces; ++c)
+                        dst[c] = keep ? make_uint4(q[c][0], q[c][1], q[c][2], q[c][3]) : make_uint4(0, 0, 0, 0);
+                }
+            }
+            if (staged) {
+                // generic-proxy writes of the slice -> visible to the TMA engine
+                fence_proxy_async_smem();
+                __syncwarp();
+                const int col0 = n0 + part * kColsPerWarp;
+                const int row0 = mt * kBlockM + quad * 32;
+                if (lane == 0 && row0 < p.m && col0 < (Epi == EPI_GLU ? p.n / 2 : p.n)) {
+                    tma_store_2d(&map_out, stage, col0, row0);
+                    bulk_commit_group();
                 }
             }
             // release the accumulator buffer
@@ -673,6 +744,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 else mbar_arrive(tmem_empty_bar + buf);
             }
         }
+        if (lane == 0) bulk_wait_all();   // this warp's TMA stores have landed
     }
 
     // ---------------------------------------------------------------- teardown
