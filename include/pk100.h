@@ -291,7 +291,10 @@ typedef struct pk100_decoder_weights {
 /* Scratch bytes for `utterances` (<= PK100_DECODER_MAX_UTTERANCES); 0 if out of range. */
 long long pk100_tdt_workspace_bytes(int utterances);
 
-/* Decodes `utterances` sequences in lockstep.  enc_proj rows of utterance u start at
+/* Decodes `utterances` sequences in lockstep.  Chooses the cluster kernel when the model has
+ * one LSTM layer and the device can host a 16-CTA cluster, else the exchange kernel (both
+ * below; same results up to the summation order of the fp32 partial sums).
+ * enc_proj rows of utterance u start at
  * u * seg_stride; frames[u] (device int array) frames are consumed.  tokens /
  * durations: [utterances, max_tokens] int32 (durations may be NULL), counts:
  * [utterances].  workspace: >= pk100_tdt_workspace_bytes(utterances), 256-byte
@@ -309,7 +312,7 @@ int pk100_tdt_decode(void* stream, const pk100_decoder_weights* weights, const v
  * src/cuda/pipeline.rs:280-350).  Meant for embedders whose process owns a fixed CUDA memory
  * arena and rejects cudaMalloc from plug-ins: pre-sized serving workers, real-time audio
  * hosts, code called while another component is capturing the stream.
- * Same arguments as pk100_tdt_decode minus `workspace`: the exchange scratch is a fixed
+ * Same arguments as pk100_tdt_decode_exchange (whose kernel it runs) minus `workspace`: the exchange scratch is a fixed
  * 288 KiB device array inside the library image, present on every GPU that loads the
  * library for the life of the process.  Limits and rules:
  *   - at most PK100_DECODER_MAX_UTTERANCES utterances; more returns PK100_ERR_LIMIT and
@@ -325,7 +328,25 @@ int pk100_tdt_decode_static(void* stream, const pk100_decoder_weights* weights, 
                             int utterances, int seg_stride, const int* frames, int32_t* tokens,
                             int32_t* durations, int32_t* counts, int max_tokens, int* status);
 
-/* Same contract, earlier design kept as a cross-check: weights in shared memory and a
+/* Same contract, one kernel design each.
+ * _cluster: one thread-block cluster of 16 CTAs; the phases of a round exchange their vectors
+ *   through distributed shared memory and the hardware cluster barrier; joint rows resident in
+ *   shared memory, LSTM / prediction weights streamed from L2 in a fragment-ordered copy that the
+ *   call writes into the workspace.  One LSTM layer only (PK100_ERR_UNSUPPORTED otherwise, or when
+ *   the device cannot co-schedule 16 CTAs of 217 KB shared memory as a cluster).
+ * _exchange: one CTA per SM, all weights resident in shared memory, phases exchange through
+ *   tagged global-memory slots that the consumers poll (bounded).  One or two LSTM layers.  Uses
+ *   only the first 280 KB of the workspace. */
+int pk100_tdt_decode_cluster(void* stream, const pk100_decoder_weights* weights, const void* enc_proj,
+                             int utterances, int seg_stride, const int* frames, void* workspace,
+                             int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                             int* status);
+int pk100_tdt_decode_exchange(void* stream, const pk100_decoder_weights* weights, const void* enc_proj,
+                              int utterances, int seg_stride, const int* frames, void* workspace,
+                              int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                              int* status);
+
+/* Same contract, earliest design kept as a cross-check: weights in shared memory and a
  * bounded grid barrier between the phases (the structure of the reference kernel,
  * kernels/sm89/decoder.cu:227-414).  pk100_tdt_decode falls back to it on devices whose SM
  * count does not fit the register-resident slicing. */

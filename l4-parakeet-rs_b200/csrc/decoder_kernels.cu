@@ -20,6 +20,7 @@
 #include <type_traits>
 
 #include "pk100_internal.h"
+#include "ptx_sm100.cuh"
 
 namespace pk100 {
 
@@ -959,6 +960,553 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
     if (sm.ok == 0 && tid == 0 && p.status != nullptr) atomicExch(p.status, 2);
 }
 
+
+// ---------------------------------------------------------------------------
+// Cluster decoder.
+//
+// One thread-block cluster of 16 CTAs decodes the batch.  The phases of a round hand their
+// vectors to the peers through distributed shared memory: every CTA pushes its slice into all
+// 16 CTAs with st.async, which also credits the bytes to an mbarrier of the receiving CTA, and
+// each CTA waits (bounded) on its own mbarrier only.  An exchange costs one SM-to-SM hop
+// instead of the 2-3 us of global-memory slots polled by 148 CTAs.  The price: 16 CTAs
+// cannot hold the 8 MB of fp16 weights in shared memory, so
+//   - the joint rows (needed every round) stay resident,
+//   - the recurrent LSTM weights and the prediction projection are streamed from L2 on the
+//     rounds that follow a non-blank token, from a copy in "fragment order": the 16 bytes a
+//     lane needs for two k-steps of mma.m16n8k16 are contiguous, so a warp pulls 512
+//     contiguous bytes per load straight into registers, several loads deep,
+//   - the input half of the LSTM, W_ih . embedding[token], is a table [1025, 2560] computed
+//     once per call by one GEMM; a round gathers 4 x 40 floats of the token's row per CTA.
+// Every CTA runs the same control flow on replicated utterance state.
+constexpr int kCl = 16;                          // CTAs per cluster
+constexpr int kClUnits = kHidden / kCl;          // 40 hidden units / prediction rows per CTA
+constexpr int kClJoint = 65;                     // joint rows per CTA (16 x 65 >= 1030)
+constexpr int kClThreads = 640;
+constexpr int kClWarps = kClThreads / 32;
+constexpr int kPartFloats = 6400;                // K-split partial sums of any of the three GEMMs
+
+// A [rows x K] weight slice split over the 20 warps as KG k-groups x NG row-groups; a warp
+// walks KP pairs of k-steps (32 columns each) over up to NT row tiles of 8 (TILES in total).
+template <int KG_, int NG_, int KP_, int NT_, int TILES_>
+struct FragShape {
+    static constexpr int KG = KG_, NG = NG_, KP = KP_, NT = NT_, kTiles = TILES_;
+    static constexpr int kRows = kTiles * 8;
+    // row pitch of the partial sums: = 8 (mod 32) floats, so the 8-byte stores of a half-warp
+    // (4 utterances x 4 column pairs) fall into 16 different bank pairs
+    static constexpr int kPitch = kRows + ((8 - kRows % 32) + 32) % 32;
+    static constexpr int kCols = KG * KP * 32;
+    static constexpr int kPerCta = KG * KP * kTiles * 32;   // uint4 per CTA
+    static_assert(KG * NG == kClWarps, "one (k-group, row-group) per warp");
+    static_assert(NG * NT >= kTiles && (NG - 1) * NT < kTiles, "row groups cover the tiles");
+    static_assert(KG * 8 * kPitch <= kPartFloats, "partials fit");
+    static_assert(kCols == kHidden, "K = 640");
+};
+using LstmShape = FragShape<4, 5, 5, 4, 20>;   // 160 gate rows x 640 (recurrent weights)
+using PredShape = FragShape<20, 1, 1, 5, 5>;   // 40 rows x 640
+using JointShape = FragShape<10, 2, 2, 5, 9>;  // 72 rows (65 used) x 640
+
+struct ClLayout { size_t base, lstm, pred, joint, xtab, total; };
+__host__ __device__ inline ClLayout cl_layout(int utts) {
+    ClLayout l;
+    const size_t a = dec_layout(utts).total, b = xch_layout(utts).total;
+    l.base = ((a > b ? a : b) + 255) / 256 * 256;
+    size_t off = l.base;
+    l.lstm = off; off += static_cast<size_t>(kCl) * LstmShape::kPerCta * 16;
+    l.pred = off; off += static_cast<size_t>(kCl) * PredShape::kPerCta * 16;
+    l.joint = off; off += static_cast<size_t>(kCl) * JointShape::kPerCta * 16;
+    l.xtab = off; off += static_cast<size_t>(kTokenOutputs) * kGates * 4;
+    l.total = off;
+    return l;
+}
+
+enum : int { CLPACK_LSTM = 0, CLPACK_PRED = 1, CLPACK_JOINT = 2 };
+
+// dst[cta][kg][kp][tile][lane] = the B fragments (b0, b1) of k-steps 2*kp and 2*kp+1 of row tile
+// `tile`: lane (g = lane / 4, t = lane % 4) holds W[row g][k0 + 2t, +1, +8, +9] per k-step.
+template <typename Shape, int Mode>
+__global__ void tdt_pack_kernel(uint4* dst, const __half* w) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= kCl * Shape::kPerCta) return;
+    int rest = idx;
+    const int lane = rest % 32; rest /= 32;
+    const int tile = rest % Shape::kTiles; rest /= Shape::kTiles;
+    const int kp = rest % Shape::KP; rest /= Shape::KP;
+    const int kg = rest % Shape::KG; rest /= Shape::KG;
+    const int r = rest;
+    const int g = lane / 4, t = lane % 4;
+    const int n = tile * 8 + g;
+    const int k0 = (kg * Shape::KP + kp) * 32;
+    int row = -1;
+    if (Mode == CLPACK_LSTM) row = (n % 4) * kHidden + r * kClUnits + n / 4;   // gate-major rows of w_hh
+    else if (Mode == CLPACK_PRED) row = r * kClUnits + n;
+    else if (n < kClJoint && r * kClJoint + n < kJointRows) row = r * kClJoint + n;
+    auto pair = [&](int k) -> unsigned {
+        if (row < 0) return 0u;
+        const __half* src = w + static_cast<size_t>(row) * kHidden + k;
+        return static_cast<unsigned>(__half_as_ushort(src[0])) | (static_cast<unsigned>(__half_as_ushort(src[1])) << 16);
+    };
+    dst[idx] = make_uint4(pair(k0 + 2 * t), pair(k0 + 2 * t + 8), pair(k0 + 16 + 2 * t), pair(k0 + 16 + 2 * t + 8));
+}
+
+constexpr int kEncChunks = kHidden / 8;          // 16-byte chunks of one projected encoder row
+
+struct CSmem {
+    uint4 wj[JointShape::kPerCta];        // this CTA's joint rows in fragment order (resident)
+    __half ax[16][kAct];                  // joint input (hi rows 0-7, lo rows 8-15)
+    __half ah[16][kAct];                  // committed hidden state, all 640 units
+    __half hx[16][kAct];                  // fresh hidden state, written by all CTAs of the cluster
+    float pred[kMaxUtt][kHidden];         // prediction vectors, written by all CTAs of the cluster
+    float part[kPartFloats];              // [k-group][utterance][row] partial sums
+    __half enc[kMaxUtt][kHidden];         // projected encoder row of each utterance's current frame
+    float xg[kMaxUtt][kClUnits * 4];      // W_ih . embedding[last token] for this CTA's gate rows
+    float cstate[kMaxUtt][kClUnits];
+    alignas(16) __half stage_h[16][kClUnits];     // this CTA's slice of h (hi / lo) on its way out
+    alignas(16) float stage_p[kMaxUtt][kClUnits]; // this CTA's slice of the prediction vector
+    float lstm_bias[kClUnits][4];
+    float pred_bias[kClUnits];
+    float joint_bias[JointShape::kRows];
+    unsigned long long best2[kMaxUtt][2];
+    unsigned long long keys[2][kCl][kMaxUtt];   // [round parity][source CTA][utterance], written by peers
+    float dur[2][kMaxUtt][8];                   // [round parity][utterance][duration], written by the owner
+    uint64_t hbar, pbar, kbar[2];               // exchange mbarriers (count 1 + transaction bytes)
+    int frame[kMaxUtt], symbols[kMaxUtt], count[kMaxUtt], total_frames[kMaxUtt];
+    alignas(8) unsigned char valid[kMaxUtt];
+    alignas(8) unsigned char done[kMaxUtt];      // read as one 64-bit word: entries >= utts are 1
+    alignas(8) unsigned char need[kMaxUtt];      // !done && !valid
+    int abort;
+#ifdef PK100_DEC_PROFILE
+    long long prof[16], last_stamp;       // per-phase cycle totals of thread 0
+#endif
+};
+static_assert(sizeof(CSmem) <= 227 * 1024, "cluster decoder state fits one CTA's shared memory");
+
+// Remote store that credits its bytes to an mbarrier of the destination CTA.  `addr` and `bar`
+// are shared::cluster addresses of the same CTA.
+__device__ __forceinline__ void st_async_v4(uint32_t addr, uint4 v, uint32_t bar) {
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void st_async_b64(uint32_t addr, unsigned long long v, uint32_t bar) {
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b64 [%0], %1, [%2];"
+                 ::"r"(addr), "l"(v), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void st_async_b32(uint32_t addr, unsigned v, uint32_t bar) {
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                 ::"r"(addr), "r"(v), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float fast_tanh(float x) { return 2.0f * fast_sigmoid(2.0f * x) - 1.0f; }
+
+// part[kg][u][row] = A(16 x 640, hi / lo rows) . W^T for this warp's k-group and row group.
+// The weight fragments run through a register ring `Depth` k-step pairs ahead of the MMAs;
+// frag_prefetch issues the loads of the first `Stages` pairs (weights do not depend on the
+// activations, so this can be done before the activations have arrived), frag_compute the rest.
+template <typename Shape, int Depth>
+struct FragRing { uint4 buf[Depth + 1][Shape::NT]; };
+
+template <typename Shape, bool Global>
+__device__ __forceinline__ uint4 frag_fetch(const uint4* w, int warp, int lane, int kp, int j) {
+    const int kg = warp / Shape::NG, ng = warp % Shape::NG;
+    const uint4* ptr = w + static_cast<size_t>(kg * Shape::KP + kp) * Shape::kTiles * 32 + (ng * Shape::NT + j) * 32 + lane;
+    return Global ? __ldg(ptr) : *ptr;
+}
+template <typename Shape>
+__device__ __forceinline__ bool frag_live(int warp, int j) {
+    return Shape::NG * Shape::NT == Shape::kTiles || (warp % Shape::NG) * Shape::NT + j < Shape::kTiles;
+}
+
+template <typename Shape, bool Global, int Depth, int First, int Stages>
+__device__ __forceinline__ void frag_prefetch(const uint4* w, FragRing<Shape, Depth>& ring, int warp, int lane) {
+#pragma unroll
+    for (int s = First; s < First + Stages && s < Shape::KP && s < Depth; ++s)
+#pragma unroll
+        for (int j = 0; j < Shape::NT; ++j)
+            if (frag_live<Shape>(warp, j)) ring.buf[s][j] = frag_fetch<Shape, Global>(w, warp, lane, s, j);
+}
+
+// `Loaded` = prologue stages already issued by frag_prefetch.
+template <typename Shape, bool Global, int Depth, int Loaded>
+__device__ __forceinline__ void frag_compute(const uint4* w, const __half* a, float* part,
+                                             FragRing<Shape, Depth>& ring, int warp, int lane) {
+    constexpr int KP = Shape::KP, NT = Shape::NT;
+    const int kg = warp / Shape::NG, ng = warp % Shape::NG;
+    const int g = lane / 4, t = lane % 4;
+    frag_prefetch<Shape, Global, Depth, Loaded, Depth - Loaded>(w, ring, warp, lane);
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[j][e] = 0.0f;
+    const __half* arow = a + (lane % 16) * kAct + (lane / 16) * 8 + kg * KP * 32;
+#pragma unroll
+    for (int kp = 0; kp < KP; ++kp) {
+        if (kp + Depth < KP) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+                if (frag_live<Shape>(warp, j))
+                    ring.buf[(kp + Depth) % (Depth + 1)][j] = frag_fetch<Shape, Global>(w, warp, lane, kp + Depth, j);
+        }
+        unsigned a0[4], a1[4];
+        dec_ldmatrix_x4(a0, arow + kp * 32);
+        dec_ldmatrix_x4(a1, arow + kp * 32 + 16);
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            if (!frag_live<Shape>(warp, j)) continue;
+            const uint4 b = ring.buf[kp % (Depth + 1)][j];
+            dec_mma(acc[j], a0, b.x, b.y);
+            dec_mma(acc[j], a1, b.z, b.w);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        if (!frag_live<Shape>(warp, j)) continue;
+        float* dst = part + (kg * 8 + g) * Shape::kPitch + (ng * NT + j) * 8 + 2 * t;
+        // hi row + lo row of utterance g
+        *reinterpret_cast<float2*>(dst) = make_float2(acc[j][0] + acc[j][2], acc[j][1] + acc[j][3]);
+    }
+}
+
+#ifdef PK100_DEC_PROFILE
+#define CL_STAMP(i) do { if (tid == 0) { const long long now__ = clock64(); sm.prof[i] += now__ - sm.last_stamp; sm.last_stamp = now__; } } while (0)
+#else
+#define CL_STAMP(i) do { } while (0)
+#endif
+
+__global__ void __launch_bounds__(kClThreads, 1)
+tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* packed_pred,
+                   const uint4* packed_joint, const float* xtab) {
+    extern __shared__ __align__(16) uint8_t cs_raw[];
+    CSmem& sm = *reinterpret_cast<CSmem*>(cs_raw);
+#ifdef PK100_DEC_PROFILE
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 16; ++i) sm.prof[i] = 0;
+        sm.last_stamp = clock64();
+    }
+#endif
+    const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
+    const int r = static_cast<int>(cluster_ctarank());
+    const int U = p.utts;
+    volatile int* abort_flag = &sm.abort;
+
+    // ---- set-up: resident joint slice, biases, cleared state, first encoder rows
+    {
+        const uint4* src = packed_joint + static_cast<size_t>(r) * JointShape::kPerCta;
+        for (int i = tid; i < JointShape::kPerCta; i += kClThreads) sm.wj[i] = __ldg(src + i);
+    }
+    for (int i = tid; i < 16 * kAct; i += kClThreads) {
+        (&sm.ax[0][0])[i] = __float2half(0.0f);
+        (&sm.ah[0][0])[i] = __float2half(0.0f);
+        (&sm.hx[0][0])[i] = __float2half(0.0f);
+    }
+    for (int i = tid; i < kMaxUtt * kHidden; i += kClThreads) {
+        (&sm.pred[0][0])[i] = 0.0f;
+        (&sm.enc[0][0])[i] = __float2half(0.0f);
+    }
+    for (int i = tid; i < kMaxUtt * kClUnits * 4; i += kClThreads) (&sm.xg[0][0])[i] = 0.0f;   // no token yet: zero input
+    for (int i = tid; i < kMaxUtt * kClUnits; i += kClThreads) (&sm.cstate[0][0])[i] = 0.0f;
+    if (tid < kClUnits * 4) {
+        const int slot = tid / 4, gt = tid % 4;
+        const int row = gt * kHidden + r * kClUnits + slot;
+        sm.lstm_bias[slot][gt] = p.b_ih[0][row] + p.b_hh[0][row];
+    }
+    if (tid < kClUnits) sm.pred_bias[tid] = p.b_pred[r * kClUnits + tid];
+    if (tid < JointShape::kRows) {
+        const int row = r * kClJoint + tid;
+        sm.joint_bias[tid] = (tid < kClJoint && row < kJointRows) ? p.b_joint[row] : 0.0f;
+    }
+    if (tid < kMaxUtt) {
+        sm.frame[tid] = 0; sm.symbols[tid] = 0; sm.count[tid] = 0; sm.valid[tid] = 0;
+        sm.total_frames[tid] = tid < U ? p.frames[tid] : 0;
+        const bool done = tid >= U || p.frames[tid] <= 0;
+        sm.done[tid] = done;
+        sm.need[tid] = !done;
+    }
+    for (int i = tid; i < 2 * kCl * kMaxUtt; i += kClThreads) (&sm.keys[0][0][0])[i] = 0ull;
+    for (int i = tid; i < 2 * kMaxUtt * 8; i += kClThreads) (&sm.dur[0][0][0])[i] = 0.0f;
+    if (tid == 0) {
+        mbar_init(&sm.hbar, 1);
+        mbar_init(&sm.pbar, 1);
+        mbar_init(&sm.kbar[0], 1);
+        mbar_init(&sm.kbar[1], 1);
+        sm.abort = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (warp < U && !sm.done[warp]) {
+        const __half* src = p.enc_proj + static_cast<size_t>(warp) * p.seg_stride * kHidden;
+        for (int c = lane; c < kEncChunks; c += 32) cp_async_16(&sm.enc[warp][c * 8], src + c * 8);
+    }
+    __syncthreads();
+    cluster_sync_all();      // every CTA's shared memory and mbarriers are ready before a peer writes
+
+    const uint4* wl = packed_lstm + static_cast<size_t>(r) * LstmShape::kPerCta;
+    const uint4* wp = packed_pred + static_cast<size_t>(r) * PredShape::kPerCta;
+    // sender role of this thread: peer CTA and two of the 80 16-byte items of a slice
+    const uint32_t peer = static_cast<uint32_t>(tid / kClUnits);
+    const int item0 = tid % kClUnits;
+    uint32_t hphase = 0, pphase = 0, kphase[2] = {0, 0};
+    // first k-step pair of the recurrent weights, requested one decision ahead of its use
+    FragRing<LstmShape, 2> lstm_ring;
+    frag_prefetch<LstmShape, true, 2, 0, 1>(wl, lstm_ring, warp, lane);
+
+    unsigned round = 0;
+    while (true) {
+        const unsigned long long done8 = *reinterpret_cast<const unsigned long long*>(sm.done);
+        const unsigned long long need8 = *reinterpret_cast<const unsigned long long*>(sm.need);
+        // a wait that gave up raised sm.abort; it is read here, after the CTA barrier that ends a
+        // round, so every thread of the CTA takes the same branch
+        if (done8 == 0x0101010101010101ull || sm.abort != 0) break;
+        const int needs = __popcll(need8), lives = 8 - __popcll(done8);
+        CL_STAMP(0);
+
+        if (need8 != 0ull) {
+            // ---- LSTM: gates of this CTA's 40 units = table row + h . w_hh^T + bias
+            frag_compute<LstmShape, true, 2, 1>(wl, &sm.ah[0][0], sm.part, lstm_ring, warp, lane);
+            cp_async_wait_all();             // table rows / encoder rows requested at the last decision
+            __syncthreads();
+            CL_STAMP(1);
+            if (tid < kMaxUtt * kClUnits) {
+                const int slot = tid % kClUnits, u = tid / kClUnits;
+                if (u < U && sm.need[u]) {
+                    const float4 x = *reinterpret_cast<const float4*>(&sm.xg[u][slot * 4]);
+                    float gsum[4] = {sm.lstm_bias[slot][0] + x.x, sm.lstm_bias[slot][1] + x.y,
+                                     sm.lstm_bias[slot][2] + x.z, sm.lstm_bias[slot][3] + x.w};
+#pragma unroll
+                    for (int kg = 0; kg < LstmShape::KG; ++kg) {
+                        const float4 v = *reinterpret_cast<const float4*>(
+                            &sm.part[(kg * 8 + u) * LstmShape::kPitch + slot * 4]);
+                        gsum[0] += v.x; gsum[1] += v.y; gsum[2] += v.z; gsum[3] += v.w;
+                    }
+                    const float cell = fast_sigmoid(gsum[1]) * sm.cstate[u][slot] + fast_sigmoid(gsum[0]) * fast_tanh(gsum[2]);
+                    sm.cstate[u][slot] = cell;
+                    const float h = fast_sigmoid(gsum[3]) * fast_tanh(cell);
+                    const __half hi = __float2half_rn(h);
+                    sm.stage_h[u][slot] = hi;
+                    sm.stage_h[u + 8][slot] = __float2half_rn(h - __half2float(hi));
+                }
+            }
+            if (tid == 0) mbar_arrive_expect_tx(&sm.hbar, static_cast<uint32_t>(needs) * 2 * kHidden * 2);
+            __syncthreads();
+            CL_STAMP(2);
+            {   // h slice (hi and lo rows, 5 chunks of 8 units each) -> every CTA's hx
+                const uint32_t bar = map_to_cta(smem_u32(&sm.hbar), peer);
+#pragma unroll
+                for (int it = 0; it < 2; ++it) {
+                    const int item = item0 + it * kClUnits;         // 0..79
+                    const int row = item / 5, chunk = item % 5;
+                    const int u = row % 8;
+                    if (u < U && sm.need[u]) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(&sm.stage_h[row][chunk * 8]);
+                        st_async_v4(map_to_cta(smem_u32(&sm.hx[row][r * kClUnits + chunk * 8]), peer), v, bar);
+                    }
+                }
+            }
+            // the prediction weights of this warp are requested while the hidden state travels
+            FragRing<PredShape, 1> pred_ring;
+            frag_prefetch<PredShape, true, 1, 0, 1>(wp, pred_ring, warp, lane);
+            mbar_wait_bounded(&sm.hbar, hphase, abort_flag);
+            hphase ^= 1u;
+            CL_STAMP(3);
+            // ---- prediction projection of the new state (A operand: the fresh rows in hx)
+            frag_compute<PredShape, true, 1, 1>(wp, &sm.hx[0][0], sm.part, pred_ring, warp, lane);
+            __syncthreads();
+            CL_STAMP(4);
+            if (tid < kMaxUtt * kClUnits) {
+                const int row = tid % kClUnits, u = tid / kClUnits;
+                if (u < U && sm.need[u]) {
+                    float v = sm.pred_bias[row];
+#pragma unroll
+                    for (int kg = 0; kg < PredShape::KG; ++kg) v += sm.part[(kg * 8 + u) * PredShape::kPitch + row];
+                    sm.stage_p[u][row] = v;
+                }
+            } else {
+                // meanwhile the other threads commit the fresh hidden state for the next LSTM step
+                for (int i = tid - kMaxUtt * kClUnits; i < 16 * kEncChunks; i += kClThreads - kMaxUtt * kClUnits) {
+                    const int row = i / kEncChunks, c = i % kEncChunks;
+                    const int u = row % 8;
+                    if (u < U && sm.need[u])
+                        *reinterpret_cast<uint4*>(&sm.ah[row][c * 8]) = *reinterpret_cast<const uint4*>(&sm.hx[row][c * 8]);
+                }
+            }
+            if (tid == 0) mbar_arrive_expect_tx(&sm.pbar, static_cast<uint32_t>(needs) * kHidden * 4);
+            __syncthreads();
+            CL_STAMP(5);
+            {   // prediction slice (10 chunks of 4 floats per utterance) -> every CTA's pred
+                const uint32_t bar = map_to_cta(smem_u32(&sm.pbar), peer);
+#pragma unroll
+                for (int it = 0; it < 2; ++it) {
+                    const int item = item0 + it * kClUnits;         // 0..79
+                    const int u = item / 10, chunk = item % 10;
+                    if (u < U && sm.need[u]) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(&sm.stage_p[u][chunk * 4]);
+                        st_async_v4(map_to_cta(smem_u32(&sm.pred[u][r * kClUnits + chunk * 4]), peer), v, bar);
+                    }
+                }
+            }
+            mbar_wait_bounded(&sm.pbar, pphase, abort_flag);
+            pphase ^= 1u;
+            CL_STAMP(6);
+        } else {
+            cp_async_wait_all();
+            __syncthreads();
+        }
+
+        // ---- joint input relu(enc + pred), one thread per column
+        {
+            float v[kMaxUtt];
+#pragma unroll
+            for (int u = 0; u < kMaxUtt; ++u) {
+                const bool live = ((done8 >> (8 * u)) & 1ull) == 0ull;
+                v[u] = live ? fmaxf(__half2float(sm.enc[u][tid]) + sm.pred[u][tid], 0.0f) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < kMaxUtt; ++u)
+                if (((done8 >> (8 * u)) & 1ull) == 0ull) split_store(sm.ax, u, tid, v[u]);
+        }
+        __syncthreads();
+        CL_STAMP(7);
+        {
+            FragRing<JointShape, 1> joint_ring;
+            frag_compute<JointShape, false, 1, 0>(sm.wj, &sm.ax[0][0], sm.part, joint_ring, warp, lane);
+        }
+        __syncthreads();
+        CL_STAMP(8);
+        const int par = static_cast<int>(round & 1u);
+        const uint32_t kbar_local = smem_u32(&sm.kbar[par]);
+        if (tid == 0) mbar_arrive_expect_tx(&sm.kbar[par], static_cast<uint32_t>(lives) * (kCl * 8 + kDurations * 4));
+        if (warp < 2 * kMaxUtt) {
+            // warp (u, half): 36 of this CTA's 72 row slots of utterance u
+            const int u = warp / 2, half = warp % 2;
+            unsigned long long best = 0ull;
+            const bool live_u = u < U && !sm.done[u];
+            // two passes for every lane (the second covers rows 32..35 of the half), so the warp
+            // stays converged up to the shuffle reduction
+#pragma unroll
+            for (int it = 0; it < 2; ++it) {
+                const int n = half * 36 + lane + it * 32;
+                const int row = r * kClJoint + n;
+                if (live_u && n < half * 36 + 36 && n < kClJoint && row < kJointRows) {
+                    float total = sm.joint_bias[n];
+#pragma unroll
+                    for (int kg = 0; kg < JointShape::KG; ++kg) total += sm.part[(kg * 8 + u) * JointShape::kPitch + n];
+                    if (row >= kTokenOutputs) {
+                        const uint32_t local = smem_u32(&sm.dur[par][u][row - kTokenOutputs]);
+                        for (uint32_t d = 0; d < kCl; ++d)
+                            st_async_b32(map_to_cta(local, d), __float_as_uint(total), map_to_cta(kbar_local, d));
+                    } else if (total == total) {          // NaN never wins
+                        float sc = total;
+                        if (sc == 0.0f) sc = 0.0f;        // canonicalise -0
+                        const unsigned bits = __float_as_uint(sc);
+                        const unsigned ordered = (bits & 0x80000000u) ? ~bits : (bits ^ 0x80000000u);
+                        const unsigned long long key = (static_cast<unsigned long long>(ordered) << 32) |
+                                                       (static_cast<unsigned long long>(2047 - row) << 21) | 1ull;
+                        best = key > best ? key : best;
+                    }
+                }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int off = 16; off > 0; off /= 2) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, off);
+                best = other > best ? other : best;
+            }
+            if (lane == 0) sm.best2[u][half] = best;
+        }
+        __syncthreads();
+        CL_STAMP(9);
+        // ---- this CTA's best row per utterance -> every CTA of the cluster
+        if (warp < U && !sm.done[warp] && lane < kCl) {
+            const int u = warp;
+            unsigned long long best = sm.best2[u][0] > sm.best2[u][1] ? sm.best2[u][0] : sm.best2[u][1];
+            // a CTA whose rows all produced NaN still publishes a (losing) key
+            if (best == 0ull) best = (static_cast<unsigned long long>(2047 - kTokenOutputs) << 21) | 1ull;
+            st_async_b64(map_to_cta(smem_u32(&sm.keys[par][r][u]), static_cast<uint32_t>(lane)), best,
+                         map_to_cta(kbar_local, static_cast<uint32_t>(lane)));
+        }
+        frag_prefetch<LstmShape, true, 2, 0, 1>(wl, lstm_ring, warp, lane);   // for the next round, if it needs the LSTM
+        mbar_wait_bounded(&sm.kbar[par], kphase[par], abort_flag);
+        kphase[par] ^= 1u;
+        CL_STAMP(10);
+
+        // ---- decision (replicated in every CTA): warp u decides utterance u
+        if (warp < U && !sm.done[warp]) {
+            const int u = warp;
+            unsigned long long best = lane < kCl ? sm.keys[par][lane][u] : 0ull;
+#pragma unroll
+            for (int off = 16; off > 0; off /= 2) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, off);
+                best = other > best ? other : best;
+            }
+            int token = 2047 - static_cast<int>((best >> 21) & 0x7FFull);
+            if (token > kBlank) token = kBlank;     // only after a wait gave up (keys not delivered)
+            // first strict maximum of the five duration logits
+            int duration = 0;
+            float best_dur = sm.dur[par][u][0];
+#pragma unroll
+            for (int i = 1; i < kDurations; ++i) {
+                const float v = sm.dur[par][u][i];
+                if (v > best_dur) { best_dur = v; duration = i; }
+            }
+            int frame = sm.frame[u] + duration;
+            int symbols = sm.symbols[u] + 1;
+            if (duration != 0 || symbols == kMaxSymbols) {
+                if (duration == 0) frame += 1;
+                symbols = 0;
+            }
+            const bool done = frame >= sm.total_frames[u];
+            // requests for the next round, in flight while the state is updated: the token's
+            // table row (this CTA's 4 x 40 gate inputs) and the encoder row of the new frame
+            if (token != kBlank) {
+                const float* row = xtab + static_cast<size_t>(token) * kGates + r * kClUnits;
+                for (int n = lane; n < kClUnits * 4; n += 32) cp_async_4(&sm.xg[u][n], row + (n % 4) * kHidden + n / 4);
+            }
+            if (!done && frame != sm.frame[u]) {
+                const __half* src = p.enc_proj + (static_cast<size_t>(u) * p.seg_stride + frame) * kHidden;
+                for (int c = lane; c < kEncChunks; c += 32) cp_async_16(&sm.enc[u][c * 8], src + c * 8);
+            }
+            __syncwarp();
+            if (lane == 0) {
+                if (sm.need[u]) sm.valid[u] = 1;        // this round's prediction is now current
+                if (token != kBlank) {
+                    if (r == 0 && sm.count[u] < p.max_tokens) {
+                        p.tokens[static_cast<size_t>(u) * p.max_tokens + sm.count[u]] = token;
+                        if (p.durations_out != nullptr)
+                            p.durations_out[static_cast<size_t>(u) * p.max_tokens + sm.count[u]] = duration;
+                    }
+                    sm.count[u] += 1;
+                    sm.valid[u] = 0;
+                }
+                sm.frame[u] = frame;
+                sm.symbols[u] = symbols;
+                sm.done[u] = done;
+                sm.need[u] = !done && !sm.valid[u];
+            }
+        }
+        __syncthreads();
+        CL_STAMP(11);
+        round += 1;
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    cluster_sync_all();      // no CTA leaves while a peer may still address its shared memory
+#ifdef PK100_DEC_PROFILE
+    if (r == 0 && tid == 0)
+        for (int i = 0; i < 16; ++i)
+            reinterpret_cast<volatile long long*>(p.workspace + xch_layout(U).abort)[2 + i] = sm.prof[i];
+#endif
+    if (r == 0 && tid < U) p.counts[tid] = min(sm.count[tid], p.max_tokens);
+    if (r == 0 && tid == 0) reinterpret_cast<volatile int*>(p.workspace + xch_layout(U).abort)[2] = static_cast<int>(round);
+    if (sm.abort != 0 && tid == 0 && p.status != nullptr) atomicExch(p.status, 2);
+}
+
 }  // namespace pk100
 
 using namespace pk100;
@@ -984,8 +1532,8 @@ int check_weights(const pk100_decoder_weights* w) {
 
 extern "C" long long pk100_tdt_workspace_bytes(int utterances) {
     if (utterances <= 0 || utterances > kMaxUtt) return 0;
-    const size_t a = dec_layout(utterances).total, b = pk100::xch_layout(utterances).total;
-    return static_cast<long long>(a > b ? a : b);
+    // barrier / exchange scratch, then the fragment-ordered weight copies of the cluster kernel
+    return static_cast<long long>(cl_layout(utterances).total);
 }
 
 extern "C" int pk100_tdt_decode_barrier(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
@@ -1087,6 +1635,11 @@ int static_scratch_address(void** out) {
 }
 }  // namespace
 
+extern "C" int pk100_tdt_decode_exchange(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+                                         int utterances, int seg_stride, const int* frames, void* workspace,
+                                         int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                                         int* status);
+
 extern "C" int pk100_tdt_decode_static(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
                                        int utterances, int seg_stride, const int* frames, int32_t* tokens,
                                        int32_t* durations, int32_t* counts, int max_tokens, int* status) {
@@ -1095,16 +1648,16 @@ extern "C" int pk100_tdt_decode_static(void* stream_v, const pk100_decoder_weigh
     void* scratch = nullptr;
     const int rc = static_scratch_address(&scratch);
     if (rc != PK100_OK) return rc;
-    // pk100_tdt_decode clears the part of the scratch it uses (stream-ordered memset of
+    // pk100_tdt_decode_exchange clears the part of the scratch it uses (stream-ordered memset of
     // existing memory) and launches the kernel: no allocation on this path
-    return pk100_tdt_decode(stream_v, w, enc_proj, utterances, seg_stride, frames, scratch, tokens, durations,
-                            counts, max_tokens, status);
+    return pk100_tdt_decode_exchange(stream_v, w, enc_proj, utterances, seg_stride, frames, scratch, tokens,
+                                     durations, counts, max_tokens, status);
 }
 
-extern "C" int pk100_tdt_decode(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
-                                int utterances, int seg_stride, const int* frames, void* workspace,
-                                int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
-                                int* status) {
+extern "C" int pk100_tdt_decode_exchange(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+                                         int utterances, int seg_stride, const int* frames, void* workspace,
+                                         int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                                         int* status) {
     const int rc = check_weights(w);
     if (rc != PK100_OK) return rc;
     if (!enc_proj || !frames || !workspace || !tokens || !counts) return PK100_ERR_NULL;
@@ -1160,4 +1713,152 @@ extern "C" int pk100_tdt_decode(void* stream_v, const pk100_decoder_weights* w, 
     }
     pk100_count_launch();
     return PK100_OK;
+}
+
+namespace {
+
+// Can this device run a 16-CTA cluster of the cluster decoder?  Asked once per device.
+bool cluster_decoder_available() {
+    static int cached[64] = {0};      // 0 = unknown, 1 = yes, 2 = no
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (cached[dev] != 0) return cached[dev] == 1;
+    bool ok = false;
+    do {
+        int max_smem = 0;
+        cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        if (sizeof(CSmem) > static_cast<size_t>(max_smem)) break;
+        if (cudaFuncSetAttribute(tdt_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(sizeof(CSmem))) != cudaSuccess) break;
+        if (cudaFuncSetAttribute(tdt_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
+            cudaSuccess) break;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(kCl);
+        cfg.blockDim = dim3(kClThreads);
+        cfg.dynamicSmemBytes = sizeof(CSmem);
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = kCl;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, tdt_cluster_kernel, &cfg) != cudaSuccess) break;
+        ok = clusters >= 1;
+    } while (false);
+    cudaGetLastError();
+    cached[dev] = ok ? 1 : 2;
+    return ok;
+}
+
+}  // namespace
+
+extern "C" int pk100_tdt_decode_cluster(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+                                        int utterances, int seg_stride, const int* frames, void* workspace,
+                                        int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                                        int* status) {
+    const int rc = check_weights(w);
+    if (rc != PK100_OK) return rc;
+    if (!enc_proj || !frames || !workspace || !tokens || !counts) return PK100_ERR_NULL;
+    if (utterances == 0) return PK100_OK;
+    if (utterances < 0 || seg_stride <= 0 || max_tokens <= 0) return PK100_ERR_SHAPE;
+    if (utterances > kMaxUtt) return PK100_ERR_LIMIT;
+    if (w->layers != 1 || !cluster_decoder_available()) return PK100_ERR_UNSUPPORTED;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const ClLayout lay = cl_layout(utterances);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    uint4* packed_lstm = reinterpret_cast<uint4*>(ws + lay.lstm);
+    uint4* packed_pred = reinterpret_cast<uint4*>(ws + lay.pred);
+    uint4* packed_joint = reinterpret_cast<uint4*>(ws + lay.joint);
+    float* xtab = reinterpret_cast<float*>(ws + lay.xtab);
+    const __half* w_ih = static_cast<const __half*>(w->w_ih[0]);
+    const __half* w_hh = static_cast<const __half*>(w->w_hh[0]);
+    const __half* w_pred = static_cast<const __half*>(w->w_pred);
+    const __half* w_joint = static_cast<const __half*>(w->w_joint);
+    // weights -> fragment order (they may change between calls, so this is done every call)
+    tdt_pack_kernel<LstmShape, CLPACK_LSTM><<<(kCl * LstmShape::kPerCta + 255) / 256, 256, 0, stream>>>(
+        packed_lstm, w_hh);
+    tdt_pack_kernel<PredShape, CLPACK_PRED><<<(kCl * PredShape::kPerCta + 255) / 256, 256, 0, stream>>>(
+        packed_pred, w_pred);
+    tdt_pack_kernel<JointShape, CLPACK_JOINT><<<(kCl * JointShape::kPerCta + 255) / 256, 256, 0, stream>>>(
+        packed_joint, w_joint);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return static_cast<int>(err);
+    {   // input table: xtab[token][gate row] = embedding[token] . w_ih[gate row] (fp32, no bias)
+        pk100_gemm_args g{};
+        g.kind = PK100_KIND_F16;
+        g.epilogue = PK100_EPI_LINEAR;
+        g.m = kTokenOutputs; g.n = kGates; g.k = kHidden;
+        g.a = w->embedding; g.lda = kHidden;
+        g.b = w_ih; g.ldb = kHidden;
+        g.row_scale = 1.0f;
+        g.alpha = 1.0f;
+        g.out = xtab; g.ld_out = kGates;
+        g.out_type = PK100_OUT_F32;
+        g.out_scale = 1.0f;
+        g.status = status;
+        const int grc = pk100_gemm(stream_v, &g);
+        if (grc != PK100_OK) return grc;
+    }
+    pk100_count_launch();
+    pk100_count_launch();
+    pk100_count_launch();
+
+    DecParams p{};
+    p.enc_proj = static_cast<const __half*>(enc_proj);
+    p.seg_stride = seg_stride;
+    p.frames = frames;
+    p.utts = utterances;
+    p.layers = 1;
+    p.embedding = static_cast<const __half*>(w->embedding);
+    p.w_ih[0] = w_ih;
+    p.w_hh[0] = w_hh;
+    p.b_ih[0] = w->b_ih[0];
+    p.b_hh[0] = w->b_hh[0];
+    p.w_pred = w_pred;
+    p.b_pred = w->b_pred;
+    p.w_joint = w_joint;
+    p.b_joint = w->b_joint;
+    p.workspace = ws;
+    p.tokens = tokens;
+    p.durations_out = durations;
+    p.counts = counts;
+    p.max_tokens = max_tokens;
+    p.status = status;
+
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(kCl);
+    cfg.blockDim = dim3(kClThreads);
+    cfg.dynamicSmemBytes = sizeof(CSmem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = kCl;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    err = cudaLaunchKernelEx(&cfg, tdt_cluster_kernel, p, static_cast<const uint4*>(packed_lstm),
+                             static_cast<const uint4*>(packed_pred), static_cast<const uint4*>(packed_joint),
+                             static_cast<const float*>(xtab));
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return static_cast<int>(err);
+    }
+    pk100_count_launch();
+    return PK100_OK;
+}
+
+extern "C" int pk100_tdt_decode(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+                                int utterances, int seg_stride, const int* frames, void* workspace,
+                                int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                                int* status) {
+    // one LSTM layer on a device that can host a 16-CTA cluster: the cluster kernel; anything
+    // else: the 148-CTA exchange kernel
+    if (w != nullptr && w->layers == 1 && utterances > 0 && utterances <= kMaxUtt && cluster_decoder_available())
+        return pk100_tdt_decode_cluster(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace, tokens,
+                                        durations, counts, max_tokens, status);
+    return pk100_tdt_decode_exchange(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace, tokens,
+                                     durations, counts, max_tokens, status);
 }

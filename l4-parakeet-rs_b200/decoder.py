@@ -27,8 +27,9 @@ L.lib.pk100_tdt_workspace_bytes.restype = C.c_longlong
 L.lib.pk100_tdt_decode.argtypes = [vp, C.POINTER(DecoderWeightsC), vp, C.c_int, C.c_int, vp, vp, vp, vp,
                                    vp, C.c_int, vp]
 L.lib.pk100_tdt_decode.restype = C.c_int
-L.lib.pk100_tdt_decode_barrier.argtypes = L.lib.pk100_tdt_decode.argtypes
-L.lib.pk100_tdt_decode_barrier.restype = C.c_int
+for _name in ("pk100_tdt_decode_barrier", "pk100_tdt_decode_cluster", "pk100_tdt_decode_exchange"):
+    getattr(L.lib, _name).argtypes = L.lib.pk100_tdt_decode.argtypes
+    getattr(L.lib, _name).restype = C.c_int
 
 
 class TdtDecoder:
@@ -71,15 +72,18 @@ class TdtDecoder:
         return ops.gemm(encoded, self.t["w_enc"], kind=L.KIND_F16, out=out, bias=self.t["b_enc"])
 
     def decode(self, enc_proj, utterances, seg_stride, frames, max_tokens, tokens=None, durations=None,
-               counts=None, barrier_kernel=False):
-        """frames: int32 CUDA tensor [utterances].  Returns (tokens, durations, counts) CUDA tensors."""
+               counts=None, barrier_kernel=False, kernel=None):
+        """frames: int32 CUDA tensor [utterances].  Returns (tokens, durations, counts) CUDA tensors.
+        kernel: None (the library's choice), "cluster", "exchange" or "barrier"."""
         if tokens is None:
             tokens = torch.zeros((utterances, max_tokens), dtype=torch.int32, device=self.device)
         if durations is None:
             durations = torch.zeros((utterances, max_tokens), dtype=torch.int32, device=self.device)
         if counts is None:
             counts = torch.zeros(utterances, dtype=torch.int32, device=self.device)
-        fn = L.lib.pk100_tdt_decode_barrier if barrier_kernel else L.lib.pk100_tdt_decode
+        if barrier_kernel:
+            kernel = "barrier"
+        fn = getattr(L.lib, "pk100_tdt_decode" + ("_" + kernel if kernel else ""))
         rc = fn(torch.cuda.current_stream().cuda_stream, C.byref(self.c),
                                     enc_proj.data_ptr(), utterances, seg_stride, frames.data_ptr(),
                                     self.workspace.data_ptr(), tokens.data_ptr(), durations.data_ptr(),

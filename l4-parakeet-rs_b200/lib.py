@@ -57,6 +57,8 @@ SIGNATURES = {
     "pk100_tdt_workspace_bytes": None,
     "pk100_tdt_decode": None,
     "pk100_tdt_decode_barrier": None,
+    "pk100_tdt_decode_cluster": None,
+    "pk100_tdt_decode_exchange": None,
     "pk100_tdt_decode_static": None,
     "pk100_subsampling_workspace_bytes": None,
     "pk100_run_subsampling": None,

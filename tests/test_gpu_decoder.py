@@ -20,9 +20,11 @@ def _check(tokens_gpu, count, oracle_tokens, ambiguous):
     return n
 
 
-@pytest.mark.parametrize("barrier_kernel", [False, True])
+@pytest.mark.parametrize("kernel", [None, "cluster", "exchange", "barrier"])
 @pytest.mark.parametrize("layers", [2, 1])
-def test_batched_decode_matches_oracle(pk, cuda, layers, barrier_kernel):
+def test_batched_decode_matches_oracle(pk, cuda, layers, kernel):
+    if kernel == "cluster" and layers != 1:
+        pytest.skip("the cluster kernel holds one LSTM layer")
     w = D.make_decoder_weights(11 + layers, layers=layers)
     dec = pk.decoder.TdtDecoder(w, cuda)
     seg_stride, frames = 96, [96, 60, 1, 0, 33]
@@ -30,7 +32,7 @@ def test_batched_decode_matches_oracle(pk, cuda, layers, barrier_kernel):
     enc = codec.f16_round(rng.standard_normal((len(frames) * seg_stride, 640)) * 0.5)
     fr = torch.tensor(frames, dtype=torch.int32, device=cuda)
     tokens, durations, counts = dec.decode(dev16(enc), len(frames), seg_stride, fr, seg_stride * 10,
-                                           barrier_kernel=barrier_kernel)
+                                           kernel=kernel)
     torch.cuda.synchronize()
     assert int(dec.status.item()) == 0
     tokens, counts, durations = host(tokens), host(counts), host(durations)
@@ -77,8 +79,8 @@ def test_decoder_limits(pk, cuda):
         dec.decode(enc, 9, 8, fr, 16)
 
 
-def test_eight_utterances_both_kernels_agree(pk, cuda):
-    """Full batch width; the exchange kernel and the barrier kernel walk the same decisions."""
+def test_eight_utterances_all_kernels_agree(pk, cuda):
+    """Full batch width; the cluster, exchange and barrier kernels walk the same decisions."""
     w = D.make_decoder_weights(31, layers=1)
     dec = pk.decoder.TdtDecoder(w, cuda)
     seg_stride = 128
@@ -86,17 +88,20 @@ def test_eight_utterances_both_kernels_agree(pk, cuda):
     rng = np.random.default_rng(9)
     enc = dev16(codec.f16_round(rng.standard_normal((8 * seg_stride, 640)) * 0.5))
     fr = torch.tensor(frames, dtype=torch.int32, device=cuda)
-    t1, d1, c1 = dec.decode(enc, 8, seg_stride, fr, 1280)
-    t1, d1, c1 = host(t1).copy(), host(d1).copy(), host(c1).copy()
-    t2, d2, c2 = dec.decode(enc, 8, seg_stride, fr, 1280, barrier_kernel=True)
-    torch.cuda.synchronize()
-    assert int(dec.status.item()) == 0
-    t2, c2 = host(t2), host(c2)
+    results = []
+    for kernel in ("cluster", "exchange", "barrier"):
+        t, d, c = dec.decode(enc, 8, seg_stride, fr, 1280, kernel=kernel)
+        torch.cuda.synchronize()
+        assert int(dec.status.item()) == 0
+        results.append((host(t).copy(), host(c).copy()))
     enc_h = host(enc)
+    total = 0
     for u in range(8):
         want, _, amb = D.tdt_greedy(enc_h[u * seg_stride:(u + 1) * seg_stride], w, frames[u])
         n = len(want) if amb is None else amb
-        assert np.array_equal(t1[u][:min(n, c1[u])], want[:min(n, c1[u])])
-        assert np.array_equal(t2[u][:min(n, c2[u])], want[:min(n, c2[u])])
-        if amb is None:
-            assert c1[u] == len(want) and c2[u] == len(want)
+        for t, c in results:
+            assert np.array_equal(t[u][:min(n, c[u])], want[:min(n, c[u])])
+            if amb is None:
+                assert c[u] == len(want)
+        total += n
+    assert total > 100
