@@ -7,7 +7,7 @@ accumulator follows the reference's operation order in float32.
 
 Parity status.  Pinned by the reference's own known answers: E4M3 / INT8 / FP16
 codecs, layout sizes, generator (see codec.py).  Pinned against the reference's
-own kernels executed on a B200 (oracle/_ref cubins, tests/test_ref_kernels.py):
+own kernels executed on a B200 (oracle/_ref cubins, tests/test_gpu_ref_kernels.py):
 LayerNorm, fixed FP8 quantiser, FP8 FF expand, GLU, depthwise+BN+SiLU, scalar
 local attention, TDT greedy decode.  The INT8 tile-sparse FF2, INT8 QKV and
 INT4-g128 operators have no reference implementation ("parity unpinned" beyond
