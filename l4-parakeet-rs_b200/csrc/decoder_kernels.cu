@@ -966,11 +966,9 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
 //
 // One thread-block cluster of 16 CTAs decodes the batch.  The phases of a round hand their
 // vectors to the peers through distributed shared memory: every CTA pushes its slice into all
-// 16 CTAs with one bulk copy per peer (cp.async.bulk shared::cta -> shared::cluster), which
-// also credits the bytes to an mbarrier of the receiving CTA, and each CTA waits (bounded) on
-// its own mbarrier only.  An exchange costs one SM-to-SM hop instead of the 2-3 us of
-// global-memory slots polled by 148 CTAs.  Exchanged vectors are stored blocked by owner CTA
-// ([owner][row][40]) so that a slice is one contiguous 1280-byte copy.  The price: 16 CTAs
+// 16 CTAs with st.async, which also credits the bytes to an mbarrier of the receiving CTA, and
+// each CTA waits (bounded) on its own mbarrier only.  An exchange costs one SM-to-SM hop
+// instead of the 2-3 us of global-memory slots polled by 148 CTAs.  The price: 16 CTAs
 // cannot hold the 8 MB of fp16 weights in shared memory, so
 //   - the joint rows (needed every round) stay resident,
 //   - the recurrent LSTM weights and the prediction projection are streamed from L2 on the
@@ -1054,29 +1052,22 @@ constexpr int kEncChunks = kHidden / 8;          // 16-byte chunks of one projec
 
 struct CSmem {
     uint4 wj[JointShape::kPerCta];        // this CTA's joint rows in fragment order (resident)
-    // Activation vectors are blocked by owner CTA: [owner][row][40 units], rows 0-7 = hi parts of
-    // utterances 0-7, rows 8-15 = lo parts.  One owner's block is one contiguous exchange slice.
-    alignas(16) __half ah[kCl][16][kClUnits];     // committed hidden state
-    // Fresh hidden state, written by all CTAs of the cluster; after the prediction GEMM has
-    // consumed it the same rows hold the joint input.  (A peer's next hidden state can only
-    // arrive after this CTA has published its keys, i.e. after its joint GEMM has read the rows.)
-    alignas(16) __half hx[kCl][16][kClUnits];
-    alignas(16) float pred[kCl][kMaxUtt][kClUnits];   // prediction vectors, written by all CTAs
-    float gates_h[kMaxUtt][kClUnits * 4]; // bias + W_hh . h of the committed state, this CTA's gate rows
+    __half ax[16][kAct];                  // joint input (hi rows 0-7, lo rows 8-15)
+    __half ah[16][kAct];                  // committed hidden state, all 640 units
+    __half hx[16][kAct];                  // fresh hidden state, written by all CTAs of the cluster
+    float pred[kMaxUtt][kHidden];         // prediction vectors, written by all CTAs of the cluster
     float part[kPartFloats];              // [k-group][utterance][row] partial sums
     __half enc[kMaxUtt][kHidden];         // projected encoder row of each utterance's current frame
     float xg[kMaxUtt][kClUnits * 4];      // W_ih . embedding[last token] for this CTA's gate rows
     float cstate[kMaxUtt][kClUnits];
-    // this CTA's latest slices (all utterances, kept current), the sources of the bulk copies
-    alignas(16) __half stage_h[16][kClUnits];
-    alignas(16) float stage_p[kMaxUtt][kClUnits];
-    alignas(16) float dur_stage[2][kMaxUtt][8];
+    alignas(16) __half stage_h[16][kClUnits];     // this CTA's slice of h (hi / lo) on its way out
+    alignas(16) float stage_p[kMaxUtt][kClUnits]; // this CTA's slice of the prediction vector
     float lstm_bias[kClUnits][4];
     float pred_bias[kClUnits];
     float joint_bias[JointShape::kRows];
     unsigned long long best2[kMaxUtt][2];
-    alignas(16) unsigned long long keys[2][kCl][kMaxUtt];   // [round parity][source CTA][utterance], written by peers
-    alignas(16) float dur[2][kMaxUtt][8];                   // [round parity][utterance][duration], written by the owner
+    unsigned long long keys[2][kCl][kMaxUtt];   // [round parity][source CTA][utterance], written by peers
+    float dur[2][kMaxUtt][8];                   // [round parity][utterance][duration], written by the owner
     uint64_t hbar, pbar, kbar[2];               // exchange mbarriers (count 1 + transaction bytes)
     int frame[kMaxUtt], symbols[kMaxUtt], count[kMaxUtt], total_frames[kMaxUtt];
     alignas(8) unsigned char valid[kMaxUtt];
@@ -1089,12 +1080,12 @@ struct CSmem {
 };
 static_assert(sizeof(CSmem) <= 227 * 1024, "cluster decoder state fits one CTA's shared memory");
 
-// Bulk copy of `bytes` (multiple of 16) from this CTA's shared memory into a peer's; the bytes
-// are credited to the peer's mbarrier.  `dst` and `bar` are shared::cluster addresses of the
-// same CTA.  The source must have been made visible to the async proxy (fence.proxy.async by
-// its writers) and must stay unchanged until the peer's barrier phase has completed.
-// Remote 8- / 4-byte store that credits its bytes to an mbarrier of the destination CTA
-// (lower latency than a bulk copy; used for the few bytes of the key exchange).
+// Remote store that credits its bytes to an mbarrier of the destination CTA.  `addr` and `bar`
+// are shared::cluster addresses of the same CTA.
+__device__ __forceinline__ void st_async_v4(uint32_t addr, uint4 v, uint32_t bar) {
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void st_async_b64(uint32_t addr, unsigned long long v, uint32_t bar) {
     asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b64 [%0], %1, [%2];"
                  ::"r"(addr), "l"(v), "r"(bar) : "memory");
@@ -1103,12 +1094,6 @@ __device__ __forceinline__ void st_async_b32(uint32_t addr, unsigned v, uint32_t
     asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
                  ::"r"(addr), "r"(v), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "r"(smem_u32(src)), "r"(bytes), "r"(bar) : "memory");
-}
-constexpr uint32_t kSliceBytes = 16 * kClUnits * 2;      // one owner's block: 16 rows x 40 halves = 8 x 40 floats
-static_assert(kSliceBytes == kMaxUtt * kClUnits * 4, "hidden-state and prediction slices have one size");
 __device__ __forceinline__ void cp_async_4(void* smem_dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(src) : "memory");
 }
@@ -1147,8 +1132,7 @@ __device__ __forceinline__ void frag_prefetch(const uint4* w, FragRing<Shape, De
             if (frag_live<Shape>(warp, j)) ring.buf[s][j] = frag_fetch<Shape, Global>(w, warp, lane, s, j);
 }
 
-// `Loaded` = prologue stages already issued by frag_prefetch.  `a` = the blocked activation
-// buffer [owner][16 rows][40].
+// `Loaded` = prologue stages already issued by frag_prefetch.
 template <typename Shape, bool Global, int Depth, int Loaded>
 __device__ __forceinline__ void frag_compute(const uint4* w, const __half* a, float* part,
                                              FragRing<Shape, Depth>& ring, int warp, int lane) {
@@ -1161,12 +1145,7 @@ __device__ __forceinline__ void frag_compute(const uint4* w, const __half* a, fl
     for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[j][e] = 0.0f;
-    // ldmatrix row address of this lane for the 16 x 16 tile at column k: 8-column chunk
-    // k / 8 + lane / 16 lies in block chunk / 5
-    auto a_addr = [&](int k) -> const __half* {
-        const int chunk = k / 8 + lane / 16;
-        return a + ((chunk / 5) * 16 + lane % 16) * kClUnits + (chunk % 5) * 8;
-    };
+    const __half* arow = a + (lane % 16) * kAct + (lane / 16) * 8 + kg * KP * 32;
 #pragma unroll
     for (int kp = 0; kp < KP; ++kp) {
         if (kp + Depth < KP) {
@@ -1176,8 +1155,8 @@ __device__ __forceinline__ void frag_compute(const uint4* w, const __half* a, fl
                     ring.buf[(kp + Depth) % (Depth + 1)][j] = frag_fetch<Shape, Global>(w, warp, lane, kp + Depth, j);
         }
         unsigned a0[4], a1[4];
-        dec_ldmatrix_x4(a0, a_addr((kg * KP + kp) * 32));
-        dec_ldmatrix_x4(a1, a_addr((kg * KP + kp) * 32 + 16));
+        dec_ldmatrix_x4(a0, arow + kp * 32);
+        dec_ldmatrix_x4(a1, arow + kp * 32 + 16);
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
             if (!frag_live<Shape>(warp, j)) continue;
@@ -1222,17 +1201,15 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
         const uint4* src = packed_joint + static_cast<size_t>(r) * JointShape::kPerCta;
         for (int i = tid; i < JointShape::kPerCta; i += kClThreads) sm.wj[i] = __ldg(src + i);
     }
-    for (int i = tid; i < 16 * kHidden; i += kClThreads) {
-        (&sm.ah[0][0][0])[i] = __float2half(0.0f);
-        (&sm.hx[0][0][0])[i] = __float2half(0.0f);
+    for (int i = tid; i < 16 * kAct; i += kClThreads) {
+        (&sm.ax[0][0])[i] = __float2half(0.0f);
+        (&sm.ah[0][0])[i] = __float2half(0.0f);
+        (&sm.hx[0][0])[i] = __float2half(0.0f);
     }
     for (int i = tid; i < kMaxUtt * kHidden; i += kClThreads) {
-        (&sm.pred[0][0][0])[i] = 0.0f;
+        (&sm.pred[0][0])[i] = 0.0f;
         (&sm.enc[0][0])[i] = __float2half(0.0f);
     }
-    for (int i = tid; i < 16 * kClUnits; i += kClThreads) (&sm.stage_h[0][0])[i] = __float2half(0.0f);
-    for (int i = tid; i < kMaxUtt * kClUnits; i += kClThreads) (&sm.stage_p[0][0])[i] = 0.0f;
-    if (tid < 2 * kMaxUtt * 8) (&sm.dur_stage[0][0][0])[tid] = 0.0f;
     for (int i = tid; i < kMaxUtt * kClUnits * 4; i += kClThreads) (&sm.xg[0][0])[i] = 0.0f;   // no token yet: zero input
     for (int i = tid; i < kMaxUtt * kClUnits; i += kClThreads) (&sm.cstate[0][0])[i] = 0.0f;
     if (tid < kClUnits * 4) {
@@ -1263,9 +1240,6 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
         fence_barrier_init();
     }
     __syncthreads();
-    // zero state: W_hh . h = 0, the gate pre-activations are the biases
-    for (int i = tid; i < kMaxUtt * kClUnits * 4; i += kClThreads)
-        (&sm.gates_h[0][0])[i] = (&sm.lstm_bias[0][0])[i % (kClUnits * 4)];
     if (warp < U && !sm.done[warp]) {
         const __half* src = p.enc_proj + static_cast<size_t>(warp) * p.seg_stride * kHidden;
         for (int c = lane; c < kEncChunks; c += 32) cp_async_16(&sm.enc[warp][c * 8], src + c * 8);
@@ -1275,7 +1249,13 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
 
     const uint4* wl = packed_lstm + static_cast<size_t>(r) * LstmShape::kPerCta;
     const uint4* wp = packed_pred + static_cast<size_t>(r) * PredShape::kPerCta;
+    // sender role of this thread: peer CTA and two of the 80 16-byte items of a slice
+    const uint32_t peer = static_cast<uint32_t>(tid / kClUnits);
+    const int item0 = tid % kClUnits;
     uint32_t hphase = 0, pphase = 0, kphase[2] = {0, 0};
+    // first k-step pair of the recurrent weights, requested one decision ahead of its use
+    FragRing<LstmShape, 2> lstm_ring;
+    frag_prefetch<LstmShape, true, 2, 0, 1>(wl, lstm_ring, warp, lane);
 
     unsigned round = 0;
     while (true) {
@@ -1284,12 +1264,12 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
         // a wait that gave up raised sm.abort; it is read here, after the CTA barrier that ends a
         // round, so every thread of the CTA takes the same branch
         if (done8 == 0x0101010101010101ull || sm.abort != 0) break;
-        const int lives = 8 - __popcll(done8);
+        const int needs = __popcll(need8), lives = 8 - __popcll(done8);
         CL_STAMP(0);
 
         if (need8 != 0ull) {
-            // ---- LSTM cell update: gates = table row of the token + (bias + W_hh . h), the
-            // second term precomputed when h was committed
+            // ---- LSTM: gates of this CTA's 40 units = table row + h . w_hh^T + bias
+            frag_compute<LstmShape, true, 2, 1>(wl, &sm.ah[0][0], sm.part, lstm_ring, warp, lane);
             cp_async_wait_all();             // table rows / encoder rows requested at the last decision
             __syncthreads();
             CL_STAMP(1);
@@ -1297,35 +1277,46 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                 const int slot = tid % kClUnits, u = tid / kClUnits;
                 if (u < U && sm.need[u]) {
                     const float4 x = *reinterpret_cast<const float4*>(&sm.xg[u][slot * 4]);
-                    const float4 gh = *reinterpret_cast<const float4*>(&sm.gates_h[u][slot * 4]);
-                    const float cell = fast_sigmoid(gh.y + x.y) * sm.cstate[u][slot] +
-                                       fast_sigmoid(gh.x + x.x) * fast_tanh(gh.z + x.z);
+                    float gsum[4] = {sm.lstm_bias[slot][0] + x.x, sm.lstm_bias[slot][1] + x.y,
+                                     sm.lstm_bias[slot][2] + x.z, sm.lstm_bias[slot][3] + x.w};
+#pragma unroll
+                    for (int kg = 0; kg < LstmShape::KG; ++kg) {
+                        const float4 v = *reinterpret_cast<const float4*>(
+                            &sm.part[(kg * 8 + u) * LstmShape::kPitch + slot * 4]);
+                        gsum[0] += v.x; gsum[1] += v.y; gsum[2] += v.z; gsum[3] += v.w;
+                    }
+                    const float cell = fast_sigmoid(gsum[1]) * sm.cstate[u][slot] + fast_sigmoid(gsum[0]) * fast_tanh(gsum[2]);
                     sm.cstate[u][slot] = cell;
-                    const float h = fast_sigmoid(gh.w + x.w) * fast_tanh(cell);
+                    const float h = fast_sigmoid(gsum[3]) * fast_tanh(cell);
                     const __half hi = __float2half_rn(h);
                     sm.stage_h[u][slot] = hi;
                     sm.stage_h[u + 8][slot] = __float2half_rn(h - __half2float(hi));
                 }
             }
-            fence_proxy_async_smem();        // stage_h writes -> visible to the bulk copies
-            if (tid == 0) mbar_arrive_expect_tx(&sm.hbar, kCl * kSliceBytes);
+            if (tid == 0) mbar_arrive_expect_tx(&sm.hbar, static_cast<uint32_t>(needs) * 2 * kHidden * 2);
             __syncthreads();
             CL_STAMP(2);
-            // this CTA's h slice (hi and lo rows of every utterance) -> block r of every CTA's hx
-            if (warp < kCl && lane == 0)     // one copy per warp: copies of one warp issue one after the other
-                bulk_copy_to_peer(map_to_cta(smem_u32(&sm.hx[r][0][0]), static_cast<uint32_t>(warp)), &sm.stage_h[0][0],
-                                  kSliceBytes, map_to_cta(smem_u32(&sm.hbar), static_cast<uint32_t>(warp)));
-            // the prediction weights of this warp and the first recurrent weights are requested
-            // while the hidden state travels
+            {   // h slice (hi and lo rows, 5 chunks of 8 units each) -> every CTA's hx
+                const uint32_t bar = map_to_cta(smem_u32(&sm.hbar), peer);
+#pragma unroll
+                for (int it = 0; it < 2; ++it) {
+                    const int item = item0 + it * kClUnits;         // 0..79
+                    const int row = item / 5, chunk = item % 5;
+                    const int u = row % 8;
+                    if (u < U && sm.need[u]) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(&sm.stage_h[row][chunk * 8]);
+                        st_async_v4(map_to_cta(smem_u32(&sm.hx[row][r * kClUnits + chunk * 8]), peer), v, bar);
+                    }
+                }
+            }
+            // the prediction weights of this warp are requested while the hidden state travels
             FragRing<PredShape, 1> pred_ring;
-            FragRing<LstmShape, 2> lstm_ring;
             frag_prefetch<PredShape, true, 1, 0, 1>(wp, pred_ring, warp, lane);
-            frag_prefetch<LstmShape, true, 2, 0, 1>(wl, lstm_ring, warp, lane);
             mbar_wait_bounded(&sm.hbar, hphase, abort_flag);
             hphase ^= 1u;
             CL_STAMP(3);
             // ---- prediction projection of the new state (A operand: the fresh rows in hx)
-            frag_compute<PredShape, true, 1, 1>(wp, &sm.hx[0][0][0], sm.part, pred_ring, warp, lane);
+            frag_compute<PredShape, true, 1, 1>(wp, &sm.hx[0][0], sm.part, pred_ring, warp, lane);
             __syncthreads();
             CL_STAMP(4);
             if (tid < kMaxUtt * kClUnits) {
@@ -1337,33 +1328,29 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                     sm.stage_p[u][row] = v;
                 }
             } else {
-                // meanwhile the other threads commit the hidden state for the next LSTM step (all
-                // utterances: rows that did not step hold the values they already had)
-                for (int i = tid - kMaxUtt * kClUnits; i < 16 * kHidden / 8; i += kClThreads - kMaxUtt * kClUnits)
-                    reinterpret_cast<uint4*>(&sm.ah[0][0][0])[i] = reinterpret_cast<const uint4*>(&sm.hx[0][0][0])[i];
+                // meanwhile the other threads commit the fresh hidden state for the next LSTM step
+                for (int i = tid - kMaxUtt * kClUnits; i < 16 * kEncChunks; i += kClThreads - kMaxUtt * kClUnits) {
+                    const int row = i / kEncChunks, c = i % kEncChunks;
+                    const int u = row % 8;
+                    if (u < U && sm.need[u])
+                        *reinterpret_cast<uint4*>(&sm.ah[row][c * 8]) = *reinterpret_cast<const uint4*>(&sm.hx[row][c * 8]);
+                }
             }
-            fence_proxy_async_smem();        // stage_p writes -> visible to the bulk copies
-            if (tid == 0) mbar_arrive_expect_tx(&sm.pbar, kCl * kSliceBytes);
+            if (tid == 0) mbar_arrive_expect_tx(&sm.pbar, static_cast<uint32_t>(needs) * kHidden * 4);
             __syncthreads();
             CL_STAMP(5);
-            // this CTA's prediction slice (every utterance) -> block r of every CTA's pred
-            if (warp < kCl && lane == 0)
-                bulk_copy_to_peer(map_to_cta(smem_u32(&sm.pred[r][0][0]), static_cast<uint32_t>(warp)), &sm.stage_p[0][0],
-                                  kSliceBytes, map_to_cta(smem_u32(&sm.pbar), static_cast<uint32_t>(warp)));
-            // ---- while the prediction vectors travel: recurrent half of the next LSTM step from
-            // the state just committed (valid until the next token, however many blanks follow)
-            CL_STAMP(12);
-            frag_compute<LstmShape, true, 2, 1>(wl, &sm.ah[0][0][0], sm.part, lstm_ring, warp, lane);
-            __syncthreads();
-            CL_STAMP(13);
-            for (int i = tid; i < kMaxUtt * kClUnits * 4; i += kClThreads) {
-                const int u = i / (kClUnits * 4), n = i % (kClUnits * 4);
-                float v = (&sm.lstm_bias[0][0])[n];
+            {   // prediction slice (10 chunks of 4 floats per utterance) -> every CTA's pred
+                const uint32_t bar = map_to_cta(smem_u32(&sm.pbar), peer);
 #pragma unroll
-                for (int kg = 0; kg < LstmShape::KG; ++kg) v += sm.part[(kg * 8 + u) * LstmShape::kPitch + n];
-                sm.gates_h[u][n] = v;
+                for (int it = 0; it < 2; ++it) {
+                    const int item = item0 + it * kClUnits;         // 0..79
+                    const int u = item / 10, chunk = item % 10;
+                    if (u < U && sm.need[u]) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(&sm.stage_p[u][chunk * 4]);
+                        st_async_v4(map_to_cta(smem_u32(&sm.pred[u][r * kClUnits + chunk * 4]), peer), v, bar);
+                    }
+                }
             }
-            CL_STAMP(14);
             mbar_wait_bounded(&sm.pbar, pphase, abort_flag);
             pphase ^= 1u;
             CL_STAMP(6);
@@ -1372,28 +1359,23 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
             __syncthreads();
         }
 
-        // ---- joint input relu(enc + pred), one thread per column (column tid = unit tid % 40 of owner tid / 40)
+        // ---- joint input relu(enc + pred), one thread per column
         {
-            const int owner = tid / kClUnits, unit = tid % kClUnits;
             float v[kMaxUtt];
 #pragma unroll
             for (int u = 0; u < kMaxUtt; ++u) {
                 const bool live = ((done8 >> (8 * u)) & 1ull) == 0ull;
-                v[u] = live ? fmaxf(__half2float(sm.enc[u][tid]) + sm.pred[owner][u][unit], 0.0f) : 0.0f;
+                v[u] = live ? fmaxf(__half2float(sm.enc[u][tid]) + sm.pred[u][tid], 0.0f) : 0.0f;
             }
 #pragma unroll
-            for (int u = 0; u < kMaxUtt; ++u) {
-                if (((done8 >> (8 * u)) & 1ull) != 0ull) continue;
-                const __half hi = __float2half_rn(v[u]);
-                sm.hx[owner][u][unit] = hi;
-                sm.hx[owner][u + 8][unit] = __float2half_rn(v[u] - __half2float(hi));
-            }
+            for (int u = 0; u < kMaxUtt; ++u)
+                if (((done8 >> (8 * u)) & 1ull) == 0ull) split_store(sm.ax, u, tid, v[u]);
         }
         __syncthreads();
         CL_STAMP(7);
         {
             FragRing<JointShape, 1> joint_ring;
-            frag_compute<JointShape, false, 1, 0>(sm.wj, &sm.hx[0][0][0], sm.part, joint_ring, warp, lane);
+            frag_compute<JointShape, false, 1, 0>(sm.wj, &sm.ax[0][0], sm.part, joint_ring, warp, lane);
         }
         __syncthreads();
         CL_STAMP(8);
@@ -1416,7 +1398,9 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
 #pragma unroll
                     for (int kg = 0; kg < JointShape::KG; ++kg) total += sm.part[(kg * 8 + u) * JointShape::kPitch + n];
                     if (row >= kTokenOutputs) {
-                        sm.dur_stage[par][u][row - kTokenOutputs] = total;     // only in the last CTA
+                        const uint32_t local = smem_u32(&sm.dur[par][u][row - kTokenOutputs]);
+                        for (uint32_t d = 0; d < kCl; ++d)
+                            st_async_b32(map_to_cta(local, d), __float_as_uint(total), map_to_cta(kbar_local, d));
                     } else if (total == total) {          // NaN never wins
                         float sc = total;
                         if (sc == 0.0f) sc = 0.0f;        // canonicalise -0
@@ -1438,22 +1422,16 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
         }
         __syncthreads();
         CL_STAMP(9);
-        // ---- this CTA's best row per utterance (and, from the last CTA, the duration logits)
-        // -> every CTA of the cluster: warp u, lane = destination CTA
-        if (warp < U && ((done8 >> (8 * warp)) & 1ull) == 0ull && lane < kCl) {
+        // ---- this CTA's best row per utterance -> every CTA of the cluster
+        if (warp < U && !sm.done[warp] && lane < kCl) {
             const int u = warp;
-            const uint32_t bar = map_to_cta(kbar_local, static_cast<uint32_t>(lane));
             unsigned long long best = sm.best2[u][0] > sm.best2[u][1] ? sm.best2[u][0] : sm.best2[u][1];
             // a CTA whose rows all produced NaN still publishes a (losing) key
             if (best == 0ull) best = (static_cast<unsigned long long>(2047 - kTokenOutputs) << 21) | 1ull;
-            st_async_b64(map_to_cta(smem_u32(&sm.keys[par][r][u]), static_cast<uint32_t>(lane)), best, bar);
-            if (r == kCl - 1) {
-#pragma unroll
-                for (int d = 0; d < kDurations; ++d)
-                    st_async_b32(map_to_cta(smem_u32(&sm.dur[par][u][d]), static_cast<uint32_t>(lane)),
-                                 __float_as_uint(sm.dur_stage[par][u][d]), bar);
-            }
+            st_async_b64(map_to_cta(smem_u32(&sm.keys[par][r][u]), static_cast<uint32_t>(lane)), best,
+                         map_to_cta(kbar_local, static_cast<uint32_t>(lane)));
         }
+        frag_prefetch<LstmShape, true, 2, 0, 1>(wl, lstm_ring, warp, lane);   // for the next round, if it needs the LSTM
         mbar_wait_bounded(&sm.kbar[par], kphase[par], abort_flag);
         kphase[par] ^= 1u;
         CL_STAMP(10);
