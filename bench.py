@@ -51,7 +51,7 @@ def parse_args():
     ap.add_argument("--tau-cache", default=None,
                     help="JSON file with calibrated tile thresholds: loaded if present, written otherwise")
     ap.add_argument("--micro", default=None,
-                    choices=["ff_expand", "ff_contract", "qkv", "attention", "layer_norm", "decode"],
+                    choices=["ff_expand", "ff_contract", "qkv", "attention", "layer_norm", "depthwise", "decode"],
                     help="time ONE kernel of the path on synthetic operands (used for ncu captures)")
     ap.add_argument("--rows", type=int, default=6144, help="rows (M) of the --micro case")
     return ap.parse_args()
@@ -257,6 +257,16 @@ def run_micro(args):
         call = lambda: pk.ops.local_attention(qkv[:, :1024], qkv[:, 1024:2048], qkv[:, 2048:], pos, u, v,
                                               seg_stride=seg, valid_rows=750, out=out)
         nbytes = m * 1024 * 2 * 4
+        work, peak, unit, bound = nbytes / 1e9, peaks["hbm_gbs"], "GB/s", "hbm"
+    elif args.micro == "depthwise":
+        seg = 768
+        segs = max(1, m // seg)
+        m = segs * seg
+        g_in, wdw = rand16(m, 1024), rand16(1024, 9, std=0.3)
+        one, zero = torch.ones(1024, device=dev), torch.zeros(1024, device=dev)
+        call = lambda: pk.ops.depthwise_bn_silu(g_in, wdw, one, zero, zero, one, quantize=True, seg_stride=seg,
+                                                valid_rows=750)
+        nbytes = m * 1024 * 3 + m * 4
         work, peak, unit, bound = nbytes / 1e9, peaks["hbm_gbs"], "GB/s", "hbm"
     elif args.micro == "layer_norm":
         x = rand16(m, 1024)

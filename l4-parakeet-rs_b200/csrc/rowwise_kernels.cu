@@ -322,9 +322,10 @@ __global__ void glu_masked_kernel(const __half* __restrict__ in, __half* __restr
 }
 
 // ------------------------------------------------- depthwise + BN + SiLU
-// One CTA = 256 threads x 4 channels = all 1024 channels of a strip of rows.
+// One CTA = 256 threads x 4 channels = all 1024 channels of a strip of 8 rows (short strips:
+// 768 CTAs at 6144 rows keep enough loads in flight; the 8 halo rows come from L2).
 // A 9-row window of the thread's 4 channels slides down the strip in registers.
-constexpr int kDwStrip = 32;
+constexpr int kDwStrip = 8;
 
 __global__ void __launch_bounds__(256)
 depthwise_bn_silu_kernel(const __half* __restrict__ in, const __half* __restrict__ wdw,
@@ -343,18 +344,27 @@ depthwise_bn_silu_kernel(const __half* __restrict__ in, const __half* __restrict
     const int rows = segment_valid(seg_valid, seg, valid_rows);
     const size_t base = static_cast<size_t>(seg) * seg_stride;
 
-    float w[4][9], rstd[4], gam[4], add[4];
+    // this thread's 4 x 9 taps are 72 contiguous bytes (8-byte aligned): 9 vector loads
+    float w[4][9], rstd[4], gam[4], add[4], mean[4];
+    {
+        __half taps[36];
+        const uint2* src = reinterpret_cast<const uint2*>(wdw + static_cast<size_t>(c0) * 9);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+        for (int i = 0; i < 9; ++i) reinterpret_cast<uint2*>(taps)[i] = __ldg(src + i);
 #pragma unroll
-        for (int t = 0; t < 9; ++t) w[c][t] = __half2float(wdw[(c0 + c) * 9 + t]);
-        rstd[c] = rsqrtf(bn_var[c0 + c] + eps);
-        gam[c] = bn_gamma[c0 + c];
-        add[c] = bn_beta[c0 + c];
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int t = 0; t < 9; ++t) w[c][t] = __half2float(taps[c * 9 + t]);
+        const float4 var = __ldg(reinterpret_cast<const float4*>(bn_var + c0));
+        const float4 g4 = __ldg(reinterpret_cast<const float4*>(bn_gamma + c0));
+        const float4 b4 = __ldg(reinterpret_cast<const float4*>(bn_beta + c0));
+        const float4 m4 = __ldg(reinterpret_cast<const float4*>(bn_mean + c0));
+        rstd[0] = rsqrtf(var.x + eps); rstd[1] = rsqrtf(var.y + eps);
+        rstd[2] = rsqrtf(var.z + eps); rstd[3] = rsqrtf(var.w + eps);
+        gam[0] = g4.x; gam[1] = g4.y; gam[2] = g4.z; gam[3] = g4.w;
+        add[0] = b4.x; add[1] = b4.y; add[2] = b4.z; add[3] = b4.w;
+        mean[0] = m4.x; mean[1] = m4.y; mean[2] = m4.z; mean[3] = m4.w;
     }
-    float mean[4];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) mean[c] = bn_mean[c0 + c];
 
     auto load_row = [&](int r, float (&dst)[4]) {
         if (r >= 0 && r < rows) {
@@ -555,6 +565,10 @@ extern "C" int pk100_depthwise_bn_silu(void* stream, const void* input, const vo
     if (quantize && !row_scales) return PK100_ERR_NULL;
     if (segments <= 0) return segments == 0 ? PK100_OK : PK100_ERR_SHAPE;
     if (seg_stride <= 0) return PK100_ERR_SHAPE;
+    auto misaligned = [](const void* ptr, uintptr_t mask) { return (reinterpret_cast<uintptr_t>(ptr) & mask) != 0; };
+    if (misaligned(dw_weight, 7) || misaligned(bn_gamma, 15) || misaligned(bn_beta, 15) ||
+        misaligned(bn_mean, 15) || misaligned(bn_var, 15) || misaligned(input, 7))
+        return PK100_ERR_ALIGN;      // the kernel reads taps 8 bytes and BatchNorm vectors 16 bytes at a time
     const int strips = (seg_stride + kDwStrip - 1) / kDwStrip;
     depthwise_bn_silu_kernel<<<segments * strips, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(input), static_cast<const __half*>(dw_weight), bn_gamma,
