@@ -57,6 +57,10 @@ def parse_args():
     return ap.parse_args()
 
 
+# DRAM bytes (read + write) of one FF-expand launch at 32768 rows, from the committed ncu summary.
+NCU_DRAM_BYTES_AT_32768_ROWS = 130.5e6
+
+
 def measured_peaks():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -176,7 +180,7 @@ def run_reference(args, rank):
 
 def workload_config(args):
     return dict(
-        workload=("BASELINE configs[4] per-GPU share: 8 x 60 s utterances (mel [6000,128] ~N(0,1), seeds 100+u) "
+        workload=("end-to-end TDT transcription, per-GPU share of 64 x 60 s utterances over 8 GPUs: 8 x 60 s utterances (mel [6000,128] ~N(0,1), seeds 100+u) "
                   "-> 8x conv subsampling -> 24-block FastConformer encoder (T=750 per utterance, 768-row "
                   "segments, batch M=6144) -> TDT greedy decode"),
         utterances_per_gpu=UTTERANCES_PER_GPU, audio_seconds_per_utterance=AUDIO_SECONDS,
@@ -443,7 +447,12 @@ def main():
         peak_note=(f"2 x {peaks['bf16_sustained']} TFLOP/s: MEASURED_PEAKS.json ({peaks['source']}) holds the "
                    "sustained cuBLAS bf16 figure only; E4M3 runs at twice the bf16 rate on this part"),
         launches_timed=len(gemm_ms), avg_launch_ms=gemm_avg_ms,
-        flops_per_launch=flops, traffic=None)
+        flops_per_launch=flops,
+        # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel at 32768 rows
+        # (profiles/gemm_ff_expand_rows32768_full.md), scaled to this launch by its rows: operand and
+        # output bytes all grow in proportion to the rows except the 4 MB of weights
+        traffic=NCU_DRAM_BYTES_AT_32768_ROWS * rows / 32768.0,
+        traffic_note="scaled from an ncu capture at 32768 rows; inside the step the 36 MB of a launch are largely L2 hits")
 
     line = dict(metric=METRIC, value=value, unit="x real time", n_gpus=world, steps=args.steps,
                 warmup=args.warmup, ms_per_step=ms_resident, higher_is_better=True, scaling="weak",
