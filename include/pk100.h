@@ -38,7 +38,9 @@ enum {
     PK100_ERR_ALIGN = -3,     /* pointer / leading dimension not 16-byte aligned */
     PK100_ERR_UNSUPPORTED = -4,
     PK100_ERR_DRIVER = -5,    /* tensor-map encoding failed */
-    PK100_ERR_LIMIT = -6      /* size beyond a documented fixed capacity */
+    PK100_ERR_LIMIT = -6,     /* size beyond a documented fixed capacity */
+    PK100_ERR_FORMAT = -7,    /* artifact file or packer input violates the format */
+    PK100_ERR_IO = -8         /* artifact file cannot be opened or mapped */
 };
 
 /* Operand kinds of pk100_gemm. */
@@ -379,6 +381,52 @@ long long pk100_subsampling_workspace_bytes(int utterances, int frames, int seg_
 int pk100_run_subsampling(void* stream, const pk100_subsampling_weights* weights, const float* mel,
                           int utterances, int frames, const int* mel_frames, void* workspace,
                           void* output, int seg_stride, int* status);
+
+/* ------------------------------------------------------------------------
+ * ".pkl4" weight artifact: reader and layout packers (host code, no GPU).
+ * Replaces AotArtifactIndex::open / read_f32 and validate_header
+ * (src/artifact.rs:98-187, :514-593, :687-724) and the encoders encode_fp16,
+ * encode_fp16_linear, encode_fp32_bias, align_up (src/artifact.rs:413-484, :734-739).
+ * The file is mapped read-only; `data` pointers stay valid until pk100_artifact_close.
+ * A file written by the reference (target "sm_89") is accepted as is: its storages are the
+ * layouts these kernels read (fp16 [out^128, in^128] row-major, fp32 bias ^128).
+ * Load-time FP8 / INT8 / INT4 packing of the linears is pk100_pack_weight_rows. */
+typedef struct pk100_artifact pk100_artifact;
+enum {
+    PK100_STORAGE_FP16 = 0, PK100_STORAGE_FP32 = 1,
+    PK100_STORAGE_FP16_LINEAR = 2,   /* "sm89_fp16_linear" */
+    PK100_STORAGE_FP32_BIAS = 3      /* "sm89_fp32_bias" */
+};
+typedef struct pk100_artifact_tensor {
+    const char* name;                  /* owned by the artifact */
+    int storage;                       /* PK100_STORAGE_* */
+    int logical_rank, physical_rank;   /* <= 4 */
+    long long logical_shape[4], physical_shape[4];
+    unsigned long long offset, bytes;  /* offset from the start of the payload */
+    const void* data;                  /* host pointer into the mapping, 256-byte aligned */
+} pk100_artifact_tensor;
+
+/* Opens and validates `path`.  On failure returns PK100_ERR_IO / PK100_ERR_FORMAT and writes a
+ * message of the reference's wording into `error` (may be NULL). */
+int pk100_artifact_open(const char* path, pk100_artifact** out, char* error, int error_len);
+void pk100_artifact_close(pk100_artifact* artifact);
+int pk100_artifact_tensor_count(const pk100_artifact* artifact);
+int pk100_artifact_tensor_at(const pk100_artifact* artifact, int index, pk100_artifact_tensor* out);
+int pk100_artifact_find(const pk100_artifact* artifact, const char* name);   /* index or -1 */
+int pk100_artifact_vocabulary_size(const pk100_artifact* artifact);
+const char* pk100_artifact_vocabulary_at(const pk100_artifact* artifact, int index);
+/* key: "target", "profile", "source_repository", "source_revision", "precision_plan" */
+const char* pk100_artifact_field(const pk100_artifact* artifact, const char* key);
+/* Plain FP32 tensors only; fails on a non-finite value (src/artifact.rs:158-187). */
+int pk100_artifact_read_f32(const pk100_artifact* artifact, const char* name, float* out, long long capacity);
+
+/* fp32 -> fp16 round-to-nearest-even; non-finite input is PK100_ERR_FORMAT. */
+int pk100_encode_fp16(const float* source, long long elements, uint16_t* out);
+int pk100_encode_fp16_linear(const float* source, long long logical_out, long long logical_in,
+                             long long padded_out, long long padded_in, uint16_t* out);
+int pk100_encode_fp32_bias(const float* source, long long logical, long long padded, float* out);
+/* Returns 0 and sets *overflow (may be NULL) when the rounded value does not fit 64 bits. */
+unsigned long long pk100_align_up(unsigned long long value, unsigned long long alignment, int* overflow);
 
 #ifdef __cplusplus
 }

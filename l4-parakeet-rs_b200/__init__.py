@@ -11,3 +11,4 @@ from . import decoder  # noqa: F401
 from . import subsampling  # noqa: F401
 from . import pipeline  # noqa: F401
 from . import parallel  # noqa: F401
+from . import artifact  # noqa: F401

@@ -60,6 +60,19 @@ SIGNATURES = {
     "pk100_tdt_decode_cluster": None,
     "pk100_tdt_decode_exchange": None,
     "pk100_tdt_decode_static": None,
+    "pk100_artifact_open": None,
+    "pk100_artifact_close": None,
+    "pk100_artifact_tensor_count": None,
+    "pk100_artifact_tensor_at": None,
+    "pk100_artifact_find": None,
+    "pk100_artifact_vocabulary_size": None,
+    "pk100_artifact_vocabulary_at": None,
+    "pk100_artifact_field": None,
+    "pk100_artifact_read_f32": None,
+    "pk100_encode_fp16": None,
+    "pk100_encode_fp16_linear": None,
+    "pk100_encode_fp32_bias": None,
+    "pk100_align_up": None,
     "pk100_subsampling_workspace_bytes": None,
     "pk100_run_subsampling": None,
     "pk100_launch_count": None,

@@ -9,7 +9,7 @@ ROOT = Path(__file__).resolve().parents[1]
 def declared_symbols():
     text = (ROOT / "include" / "pk100.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(?:int|long long|void)\s+(pk100_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(?:int|long long|void|const char\s*\*)\s*(pk100_\w+)\s*\(", text)))
 
 
 def test_header_declares_entry_points():
