@@ -117,7 +117,7 @@ class Artifact:
 
     # ------------------------------------------------------------ model views
     def _f32(self, name, shape=None):
-        a = np.asarray(self.tensor(name), np.float32)
+        a = np.array(self.tensor(name), dtype=np.float32)     # a writable copy, detached from the mapping
         return a.reshape(shape) if shape is not None else a
 
     def layer_weights(self, layer):
