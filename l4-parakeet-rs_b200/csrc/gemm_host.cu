@@ -273,13 +273,10 @@ extern "C" int pk100_gemm(void* stream_v, const pk100_gemm_args* a) {
             return narrow ? launch<KIND_F8, 128, 128, EPI_LINEAR>(*a, p, stream)
                           : launch<KIND_F8, 256, 128, EPI_LINEAR>(*a, p, stream);
         }
-#ifndef PK100_EXP_CONTRACT128
-        if (a->keep_in != nullptr) {
-            // 64-byte K blocks: skip granularity equals the 64-wide sparsity tile
-            return narrow ? launch<KIND_I8, 128, 64, EPI_LINEAR>(*a, p, stream)
-                          : launch<KIND_I8, 256, 64, EPI_LINEAR>(*a, p, stream);
-        }
-#endif
+        // A tile-sparse A operand (keep_in) runs on the same 128-byte K blocks: a block is skipped
+        // when both of its 64-wide sparsity tiles are dead (dead tiles hold zeros, so a half-dead
+        // block is computed correctly).  64-byte K blocks matched the skip granularity but
+        // measured 14 % slower: TMA moves rows of a box at the same rate whatever their width.
         return narrow ? launch<KIND_I8, 128, 128, EPI_LINEAR>(*a, p, stream)
                       : launch<KIND_I8, 256, 128, EPI_LINEAR>(*a, p, stream);
     case PK100_EPI_GLU:

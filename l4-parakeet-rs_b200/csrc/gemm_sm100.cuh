@@ -593,24 +593,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     tmem_ld_wait();
                     const int col = n0 + col_local;
                     if (row < p.m && col < p.n) {
+                        // The run-time switches (activation, residual, dead rows) are taken once per
+                        // piece, outside the element loops: left inside, every element pays for the
+                        // predicated-off SiLU and residual code (22 instructions per element measured).
                         float v[16];
                         uint4 res_raw[2];
-                        if (p.residual != nullptr) {
+                        const bool has_residual = p.residual != nullptr;
+                        if (has_residual) {
                             const uint4* rp = reinterpret_cast<const uint4*>(
                                 p.residual + static_cast<size_t>(row) * p.ld_res + col);
                             res_raw[0] = rp[0];
                             res_raw[1] = rp[1];
                         }
-                        const __half* res_h = reinterpret_cast<const __half*>(res_raw);
+                        const float rs_live = live ? rs : 0.0f;
+                        if (!live) {              // accumulator never written: any bit pattern
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            float x = live ? acc_to_float<Kind>(r[j]) : 0.0f;
-                            x = x * rs * my_scale[c * 16 + j] + my_bias[c * 16 + j];
-                            if (p.act == ACT_SILU) x = silu_f(x);
-                            else if (p.act == ACT_RELU) x = fmaxf(x, 0.0f);
-                            if (p.residual != nullptr) x = fmaf(p.alpha, x, __half2float(res_h[j]));
-                            else x *= p.alpha;
-                            v[j] = zero_row ? 0.0f : x;
+                            for (int j = 0; j < 16; ++j) r[j] = 0u;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4) {
+                            const float4 cs = *reinterpret_cast<const float4*>(my_scale + c * 16 + j);
+                            const float4 bs = *reinterpret_cast<const float4*>(my_bias + c * 16 + j);
+                            v[j + 0] = fmaf(acc_to_float<Kind>(r[j + 0]) * rs_live, cs.x, bs.x);
+                            v[j + 1] = fmaf(acc_to_float<Kind>(r[j + 1]) * rs_live, cs.y, bs.y);
+                            v[j + 2] = fmaf(acc_to_float<Kind>(r[j + 2]) * rs_live, cs.z, bs.z);
+                            v[j + 3] = fmaf(acc_to_float<Kind>(r[j + 3]) * rs_live, cs.w, bs.w);
+                        }
+                        if (p.act == ACT_SILU) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] = silu_f(v[j]);
+                        } else if (p.act == ACT_RELU) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.0f);
+                        }
+                        if (has_residual) {
+                            const __half2* res_h = reinterpret_cast<const __half2*>(res_raw);
+#pragma unroll
+                            for (int j = 0; j < 16; j += 2) {
+                                const float2 rr = __half22float2(res_h[j / 2]);
+                                v[j] = fmaf(p.alpha, v[j], rr.x);
+                                v[j + 1] = fmaf(p.alpha, v[j + 1], rr.y);
+                            }
+                        } else if (p.alpha != 1.0f) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
+                        }
+                        if (zero_row) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] = 0.0f;
                         }
                         if (staged) {
                             stage_piece(stage_row, c, swz, p.out_type, p.out_scale, v);
