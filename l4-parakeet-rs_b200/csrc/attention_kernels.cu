@@ -149,9 +149,13 @@ constexpr int kKeyBlocks = (kQTile + kLeft + kRight + kKeyBlock - 1) / kKeyBlock
 constexpr int kPosBlocks = (kPositionRowsPadded + kKeyBlock - 1) / kKeyBlock;         // 9
 
 struct AttnSmem {
-    __half q[kQTile][kPitch];
+    // The Q tile is only read once, into register fragments, before the first QP value is
+    // written: both live in the same bytes (71.6 KB per CTA -> 3 CTAs per SM instead of 2).
+    union {
+        __half q[kQTile][kPitch];
+        __half qp[kQTile][kQpPitch];
+    };
     __half kv[2][2][kKeyBlock][kPitch];          // [buffer][0 = K / P block, 1 = V]
-    __half qp[kQTile][kQpPitch];
     float uk[2][kKeyBlock];
     float bias_u[kHeadWidth];
     float bias_v[kHeadWidth];
@@ -200,7 +204,7 @@ __device__ __forceinline__ void stage_rows(__half (*dst)[kPitch], const __half* 
     }
 }
 
-__global__ void __launch_bounds__(128, 2) local_attention_mma_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(128, 3) local_attention_mma_kernel(const AttnParams p) {
     extern __shared__ __align__(16) uint8_t attn_smem_raw[];
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>(attn_smem_raw);
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
