@@ -204,6 +204,26 @@ __device__ __forceinline__ void stage_rows(__half (*dst)[kPitch], const __half* 
     }
 }
 
+// Dot product of 32 consecutive fp32 bias values with 32 consecutive halves of a staged row
+// (16-byte shared-memory loads).
+__device__ __forceinline__ float dot32(const float* bias, const __half* row) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(row + i * 8);
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+        const float4 b0 = *reinterpret_cast<const float4*>(bias + i * 8);
+        const float4 b1 = *reinterpret_cast<const float4*>(bias + i * 8 + 4);
+        const float2 x0 = __half22float2(h[0]), x1 = __half22float2(h[1]);
+        const float2 x2 = __half22float2(h[2]), x3 = __half22float2(h[3]);
+        acc = fmaf(b0.x, x0.x, acc); acc = fmaf(b0.y, x0.y, acc);
+        acc = fmaf(b0.z, x1.x, acc); acc = fmaf(b0.w, x1.y, acc);
+        acc = fmaf(b1.x, x2.x, acc); acc = fmaf(b1.y, x2.y, acc);
+        acc = fmaf(b1.z, x3.x, acc); acc = fmaf(b1.w, x3.y, acc);
+    }
+    return acc;
+}
+
 __global__ void __launch_bounds__(128, 3) local_attention_mma_kernel(const AttnParams p) {
     extern __shared__ __align__(16) uint8_t attn_smem_raw[];
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>(attn_smem_raw);
@@ -255,10 +275,7 @@ __global__ void __launch_bounds__(128, 3) local_attention_mma_kernel(const AttnP
         // v . P_j for the 32 rows of this block: 4 threads per row
         {
             const int r = tid / 4, part = tid % 4;
-            float acc = 0.0f;
-#pragma unroll 8
-            for (int d = part * 32; d < part * 32 + 32; ++d)
-                acc = fmaf(sm.bias_v[d], __half2float(sm.kv[buf][0][r][d]), acc);
+            float acc = dot32(sm.bias_v + part * 32, &sm.kv[buf][0][r][part * 32]);
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
             if (part == 0) sm.uk[buf][r] = acc;
@@ -324,10 +341,7 @@ __global__ void __launch_bounds__(128, 3) local_attention_mma_kernel(const AttnP
         // u . K_k for this block's keys
         {
             const int r = tid / 4, part = tid % 4;
-            float acc = 0.0f;
-#pragma unroll 8
-            for (int d = part * 32; d < part * 32 + 32; ++d)
-                acc = fmaf(sm.bias_u[d], __half2float(sm.kv[buf][0][r][d]), acc);
+            float acc = dot32(sm.bias_u + part * 32, &sm.kv[buf][0][r][part * 32]);
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
             if (part == 0) sm.uk[buf][r] = acc;
