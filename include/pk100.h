@@ -428,6 +428,34 @@ int pk100_encode_fp32_bias(const float* source, long long logical, long long pad
 /* Returns 0 and sets *overflow (may be NULL) when the rounded value does not fit 64 bits. */
 unsigned long long pk100_align_up(unsigned long long value, unsigned long long alignment, int* overflow);
 
+/* ------------------------------------------------------------------------
+ * Log-mel frontend: PCM fp32 [utterances, sample_stride] (sample_counts[u] samples each,
+ * device int array) -> normalised log-mel fp32 [utterances, frame_cap, 128], the input
+ * layout of pk100_run_subsampling.  Utterance u has sample_counts[u] / 160 + 1 frames of
+ * which the first sample_counts[u] / 160 are valid; every other row of its block is zero;
+ * valid_frames (device int [utterances], may be NULL) receives the valid counts.
+ * Needs frame_cap >= sample_stride / 160 + 1.
+ * Replaces run_frontend (src/cuda/frontend.rs:230-316) with pk_sm89_frame_window, the cuFFT
+ * R2C plan, pk_sm89_mel_log_sparse and pk_sm89_normalize_mel (kernels/sm89/frontend.cu);
+ * definition: CpuMelFrontend::compute (src/frontend.rs:114-215).  The pinned configuration
+ * only: 512-point FFT, hop 160, 128 mel bins, centred, power spectrum, per-feature
+ * normalisation (src/config.rs:154-173).
+ * window: the 400-tap window centred in 512 values (center_window, src/frontend.rs:218-223);
+ * filters: the non-zero entries of the [128, 257] filter bank row by row (offsets [129],
+ * bins and values [offsets[128]]), as sparse_filters builds them (src/cuda/frontend.rs:196-228). */
+typedef struct pk100_frontend_weights {
+    const float* window;            /* device fp32 [512] */
+    const int* filter_offsets;      /* device int [129] */
+    const int* filter_bins;         /* device int [nonzeros] */
+    const float* filter_values;     /* device fp32 [nonzeros] */
+    float preemphasis, log_zero_guard, normalize_epsilon;   /* 0.97, 2^-24, 1e-5 */
+} pk100_frontend_weights;
+
+int pk100_mel_frames_for(int samples);   /* samples / 160 + 1, or 0 for no samples */
+int pk100_mel_frontend(void* stream, const pk100_frontend_weights* weights, const float* samples,
+                       int utterances, long long sample_stride, const int* sample_counts, float* mel,
+                       int frame_cap, int* valid_frames);
+
 #ifdef __cplusplus
 }
 #endif

@@ -12,3 +12,4 @@ from . import subsampling  # noqa: F401
 from . import pipeline  # noqa: F401
 from . import parallel  # noqa: F401
 from . import artifact  # noqa: F401
+from . import frontend  # noqa: F401

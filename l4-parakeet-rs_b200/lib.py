@@ -73,6 +73,8 @@ SIGNATURES = {
     "pk100_encode_fp16_linear": None,
     "pk100_encode_fp32_bias": None,
     "pk100_align_up": None,
+    "pk100_mel_frames_for": None,
+    "pk100_mel_frontend": None,
     "pk100_subsampling_workspace_bytes": None,
     "pk100_run_subsampling": None,
     "pk100_launch_count": None,

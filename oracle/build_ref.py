@@ -1,7 +1,7 @@
 """Builds the checker's native pieces (test infrastructure, never shipped):
 
   oracle/_ref/*.cubin   the reference's own CUDA translation units
-                        (kernels/sm89/{linear,encoder,decoder,subsampling}.cu of the
+                        (kernels/sm89/{linear,encoder,decoder,subsampling,frontend}.cu of the
                         reference checkout), compiled where they lie -- no source is
                         copied -- with the flags of the reference's build.rs:91-103
                         (--cubin --std=c++17 -O3 -lineinfo [--use_fast_math]) but for
@@ -21,7 +21,7 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
-UNITS = {"linear": True, "encoder": True, "decoder": True, "subsampling": True}
+UNITS = {"linear": True, "encoder": True, "decoder": True, "subsampling": True, "frontend": True}
 
 
 def reference_root() -> Path | None:

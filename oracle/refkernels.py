@@ -164,3 +164,32 @@ def tdt_decode(enc_proj, w, frames, sms):
     torch.cuda.synchronize()
     n = int(count.item())
     return tokens[:n].cpu().numpy()
+
+
+# ---- frontend.cu -----------------------------------------------------------
+
+def frontend_available() -> bool:
+    return (REF_DIR / "frontend.cubin").exists()
+
+
+def frame_window(samples, window512, frames, preemphasis=0.97):
+    """pk_sm89_frame_window as run_frontend launches it (src/cuda/frontend.rs:262-279)."""
+    out = torch.empty((frames, 512), dtype=torch.float32, device=samples.device)
+    module("frontend").launch("pk_sm89_frame_window", (_cdiv(frames * 512, 256),), (256,), 0,
+                              [samples, window512, out, samples.numel(), frames, 0, float(preemphasis)])
+    return out
+
+
+def mel_log_sparse(spectrum, offsets, bins, values, frames, log_zero_guard):
+    """pk_sm89_mel_log_sparse (src/cuda/frontend.rs:283-300); spectrum: float2 [frames, 257]."""
+    out = torch.empty((frames, 128), dtype=torch.float32, device=spectrum.device)
+    module("frontend").launch("pk_sm89_mel_log_sparse", (frames,), (128,), 0,
+                              [spectrum, offsets, bins, values, out, frames, 0, float(log_zero_guard)])
+    return out
+
+
+def normalize_mel(features, frames, valid_frames, epsilon):
+    """pk_sm89_normalize_mel (src/cuda/frontend.rs:303-315), in place on a copy."""
+    out = features.clone()
+    module("frontend").launch("pk_sm89_normalize_mel", (128,), (256,), 0, [out, frames, valid_frames, float(epsilon)])
+    return out
