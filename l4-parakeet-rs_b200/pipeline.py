@@ -123,5 +123,38 @@ class PipelineEngine:
         counts = self.counts_host.numpy()
         return [self.tokens_host[u, :int(counts[u])].numpy().copy() for u in range(utterances)]
 
+    # ---- optional stage in front: PCM -> log-mel (src/cuda/pipeline.rs:437-470 runs it first)
+    def attach_frontend(self, window, mel_filters):
+        """window [400] and mel_filters [128, 257]: the artifact's frontend.* tensors."""
+        from . import frontend as fe_mod
+        self.frontend = fe_mod.MelFrontend(window, mel_filters, self.device)
+        self.pcm_capacity = (self.mel_frames - 1) * fe_mod.HOP          # mel_frames rows hold that many samples
+        self.pcm_dev = torch.zeros((self.max_utterances, self.pcm_capacity), dtype=torch.float32, device=self.device)
+        self.pcm_counts_dev = torch.zeros(self.max_utterances, dtype=torch.int32, device=self.device)
+
+    def transcribe_pcm(self, pcm_host, sample_counts):
+        """pcm_host: fp32 CPU tensor [U, samples] (zero padded), sample_counts: list of ints.
+        Frontend -> subsampling -> encoder -> decode; returns token arrays like transcribe_batch."""
+        from . import frontend as fe_mod
+        utterances, samples = pcm_host.shape
+        if samples > self.pcm_capacity or max(sample_counts) > samples:
+            raise ValueError("utterance longer than the engine was sized for")
+        self.pcm_dev[:utterances, :samples].copy_(pcm_host, non_blocking=True)
+        if samples < self.pcm_capacity:
+            self.pcm_dev[:utterances, samples:].zero_()
+        self.pcm_counts_dev[:utterances].copy_(torch.tensor(sample_counts, dtype=torch.int32), non_blocking=True)
+        self.frontend.compute(self.pcm_dev[:utterances], self.pcm_counts_dev[:utterances], frame_cap=self.mel_frames,
+                              out=self.mel_dev[:utterances])
+        self.set_lengths([n // fe_mod.HOP for n in sample_counts])       # valid frames are known on the host
+        self.run_resident(utterances)
+        self.counts_host.copy_(self.counts, non_blocking=True)
+        self.tokens_host.copy_(self.tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        status = self.status()
+        if status != 0:
+            raise RuntimeError(f"libpk100 reported an expired bounded wait (status {status})")
+        counts = self.counts_host.numpy()
+        return [self.tokens_host[u, :int(counts[u])].numpy().copy() for u in range(utterances)]
+
     def status(self):
         return (self.enc.status(self.arena, self.ws) | int(self.dec.status.item()) | int(self.sub.status.item()))

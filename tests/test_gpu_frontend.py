@@ -87,3 +87,23 @@ def test_frontend_feeds_subsampling_and_rejects_bad_arguments(pk, cuda):
     assert np.abs(host(out)[:rows]).max() > 0 and np.all(np.isfinite(host(out)))
     with pytest.raises(pk.lib.Pk100Error):
         fe.compute(pcm, counts, frame_cap=10)                              # 4800 samples need 31 rows
+
+
+def test_pipeline_from_pcm_equals_pipeline_from_its_own_mel(pk, cuda):
+    """PCM entry point = frontend + the mel entry point (same tokens), variable lengths."""
+    rng = np.random.default_rng(3)
+    eng = pk.pipeline.PipelineEngine(cuda, layers=2, decoder_layers=1, seed=5, max_utterances=2, mel_frames=201)
+    eng.attach_frontend(F.hann_window(), F.triangular_filters())
+    counts = [32000, 20011]
+    pcm = np.zeros((2, 32000), np.float32)
+    for u, n in enumerate(counts):
+        pcm[u, :n] = (0.3 * rng.standard_normal(n)).astype(np.float32)
+    got = eng.transcribe_pcm(torch.from_numpy(pcm), counts)
+    mel = host(eng.mel_dev).copy()
+    valid = [n // 160 for n in counts]
+    for u in range(2):
+        want, v = F.compute(pcm[u, :counts[u]], F.hann_window(), F.triangular_filters())
+        assert v == valid[u] and np.max(np.abs(mel[u, :v] - want[:v])) <= 2e-3 and not mel[u, v:].any()
+    eng.set_lengths(valid)
+    again = eng.transcribe_batch(torch.from_numpy(mel))
+    assert all(np.array_equal(a, b) for a, b in zip(got, again)) and sum(len(t) for t in got) > 10
