@@ -1,0 +1,95 @@
+"""Generates tests/golden/reference_kernels.npz: outputs of the REFERENCE'S OWN KERNELS
+(oracle/_ref/*.cubin, compiled from the reference checkout by oracle/build_ref.py) on small
+seeded inputs, run on a B200.  The inputs are not stored: tests/test_golden.py regenerates them
+from the same seeds through `cases()` below.  Usage, on a machine with a GPU and the cubins:
+
+    python tests/golden/make_golden.py <output.npz>
+"""
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[2]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from oracle import codec, decoder as D, frontend as F, ops as O   # noqa: E402
+
+
+def cases():
+    """Seeded inputs of every golden case (shared by the generator and the test)."""
+    c = {}
+    rng = np.random.default_rng(100)
+    rows, padded = 15, 16
+    c["ln"] = dict(x=codec.f16_round(rng.standard_normal((padded, 1024)) * 2),
+                   g=codec.f16_round(1 + 0.1 * rng.standard_normal(1024)),
+                   b=codec.f16_round(0.1 * rng.standard_normal(1024)), rows=rows, padded=padded)
+    rng = np.random.default_rng(101)
+    x = codec.f16_round(rng.standard_normal((128, 1024)))
+    w = codec.f16_round(rng.standard_normal((4096, 1024)) * 0.02)
+    wq, ws = codec.quantize_rows_fp8(w)
+    c["ffn"] = dict(xq=codec.quantize_fp8_fixed(x, 56.0), wq=wq, ws=ws, rows=128)
+    rng = np.random.default_rng(102)
+    c["glu"] = dict(e=codec.f16_round(rng.standard_normal((24, 2048)) * 2), rows=22, padded=24, valid=21)
+    c["dw"] = dict(wdw=codec.f16_round(rng.standard_normal((1024, 9)) * 0.3),
+                   bn=[(1 + 0.1 * rng.standard_normal(1024)).astype(np.float32),
+                       (0.1 * rng.standard_normal(1024)).astype(np.float32),
+                       (0.1 * rng.standard_normal(1024)).astype(np.float32),
+                       (1 + 0.2 * rng.random(1024)).astype(np.float32)])
+    rng = np.random.default_rng(103)
+    rows, padded, valid = 40, 40, 37
+    q, k, v = [codec.f16_round(rng.standard_normal((padded, 1024))) for _ in range(3)]
+    wpos = codec.f16_round(rng.standard_normal((1024, 1024)) * 0.02)
+    c["att"] = dict(q=q, k=k, v=v, pos=O.position_table(wpos), u=codec.f16_round(rng.standard_normal((8, 128)) * 0.02),
+                    bv=codec.f16_round(rng.standard_normal((8, 128)) * 0.02), rows=rows, padded=padded, valid=valid)
+    rng = np.random.default_rng(104)
+    c["dec"] = dict(w=D.make_decoder_weights(17, layers=2), enc=codec.f16_round(rng.standard_normal((60, 640)) * 0.5),
+                    frames=60)
+    rng = np.random.default_rng(105)
+    c["fe"] = dict(x=(rng.standard_normal(1700) * 0.3).astype(np.float32))
+    return c
+
+
+def main(out_path):
+    import torch
+    from oracle import refkernels as R
+    from tests.util import dev, dev16, host
+    c = cases()
+    g = {}
+    ln = c["ln"]
+    ref = R.layer_norm(dev16(ln["x"]), dev16(ln["g"]), dev16(ln["b"]), ln["rows"], ln["padded"])
+    g["ln"] = host(ref).astype(np.float16)
+    g["ln_q"] = host(R.quantize_fp8_fixed(ref, 56.0))
+    f = c["ffn"]
+    g["ffn"] = host(R.ffn_expand_fp8(dev(f["xq"]), dev(f["wq"]), dev(f["ws"]), f["rows"]))[:, ::16].astype(np.float16)
+    gl = c["glu"]
+    glu = R.glu_masked(dev16(gl["e"]), gl["rows"], gl["padded"], gl["valid"])
+    g["glu"] = host(glu).astype(np.float16)
+    dw = c["dw"]
+    g["dw"] = host(R.depthwise_bn_silu(glu, dev16(dw["wdw"]), *[dev(t) for t in dw["bn"]], gl["rows"],
+                                       gl["padded"])).astype(np.float16)
+    a = c["att"]
+    g["att"] = host(R.local_attention_scalar(dev16(a["q"]), dev16(a["k"]), dev16(a["v"]), dev16(a["pos"]), dev16(a["u"]),
+                                             dev16(a["bv"]), a["rows"], a["padded"], a["valid"])).astype(np.float16)
+    d = c["dec"]
+    dwts = {k: (dev(v) if k.startswith("b_") else dev16(v)) for k, v in d["w"].items() if k != "layers"}
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    g["dec_tokens"] = R.tdt_decode(dev16(d["enc"]), dwts, d["frames"], sms).astype(np.int32)
+    x = c["fe"]["x"]
+    frames, valid = F.frame_counts(x.size)
+    w512 = F.center_window(F.hann_window())
+    fr = R.frame_window(dev(x), dev(w512), frames)
+    g["fe_frames"] = host(fr)
+    offsets, bins, values = F.sparse_filters(F.triangular_filters())
+    spec = np.fft.rfft(host(fr).astype(np.float64), axis=1)
+    spec2 = np.stack([spec.real, spec.imag], axis=-1).astype(np.float32)
+    mel = R.mel_log_sparse(dev(spec2), dev(offsets), dev(bins), dev(values), frames, float(F.LOG_ZERO_GUARD))
+    g["fe_mel"] = host(mel)
+    g["fe_norm"] = host(R.normalize_mel(mel, frames, valid, float(F.NORMALIZE_EPSILON)))
+    np.savez_compressed(out_path, **g)
+    print("wrote", out_path, {k: v.shape for k, v in g.items()})
+
+
+if __name__ == "__main__":
+    main(sys.argv[1])

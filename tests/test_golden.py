@@ -1,0 +1,70 @@
+"""The CPU oracle against committed outputs of the REFERENCE'S OWN KERNELS
+(tests/golden/reference_kernels.npz, produced on a B200 by tests/golden/make_golden.py from
+the reference's kernels/sm89/*.cu compiled for sm_100a).  Runs without a GPU.
+Tolerances as in tests/test_gpu_ref_kernels.py: one fp16 ulp plus fast-math exp for the
+floating-point kernels, bit-exact for the quantiser and the token ids."""
+import importlib.util
+from pathlib import Path
+
+import numpy as np
+
+from oracle import codec, decoder as D, frontend as F, ops as O
+
+HERE = Path(__file__).resolve().parent
+spec = importlib.util.spec_from_file_location("make_golden", HERE / "golden" / "make_golden.py")
+make_golden = importlib.util.module_from_spec(spec)
+spec.loader.exec_module(make_golden)
+GOLD = np.load(HERE / "golden" / "reference_kernels.npz")
+CASES = make_golden.cases()
+
+
+def test_layer_norm_and_fixed_quantiser():
+    c = CASES["ln"]
+    got = GOLD["ln"].astype(np.float32)
+    want = O.layer_norm(c["x"], c["g"], c["b"], c["rows"])
+    assert np.max(np.abs(got - want)) <= 2.0 ** -7 and np.mean(got != want) < 2e-3
+    assert np.array_equal(GOLD["ln_q"], codec.quantize_fp8_fixed(got, 56.0))
+
+
+def test_ffn_expand_fp8():
+    c = CASES["ffn"]
+    want = O.linear_fp8(c["xq"], c["wq"], c["ws"], O.FP8_INPUT_SCALE, act=1)[:, ::16]
+    assert np.max(np.abs(GOLD["ffn"].astype(np.float32) - want)) <= 4e-3
+
+
+def test_conv_module_elementwise():
+    g, d = CASES["glu"], CASES["dw"]
+    glu = GOLD["glu"].astype(np.float32)
+    assert np.max(np.abs(glu - O.glu_masked(g["e"], g["rows"], g["valid"]))) <= 4e-3
+    want = O.depthwise_bn_silu(glu, d["wdw"], *d["bn"], g["rows"])
+    assert np.max(np.abs(GOLD["dw"].astype(np.float32) - want)) <= 4e-3
+
+
+def test_scalar_attention():
+    a = CASES["att"]
+    want = O.local_attention(a["q"], a["k"], a["v"], a["pos"], a["u"], a["bv"], a["rows"], a["valid"])
+    assert np.max(np.abs(GOLD["att"].astype(np.float32) - want)) <= 3e-3
+
+
+def test_tdt_decoder_tokens():
+    d = CASES["dec"]
+    tokens, _, ambiguous = D.tdt_greedy(d["enc"], d["w"], d["frames"])
+    n = len(tokens) if ambiguous is None else ambiguous
+    ref = GOLD["dec_tokens"]
+    assert n > 10 and np.array_equal(ref[:n], tokens[:n])
+    if ambiguous is None:
+        assert len(ref) == len(tokens)
+
+
+def test_frontend_kernels():
+    x = CASES["fe"]["x"]
+    frames, valid = F.frame_counts(x.size)
+    w512 = F.center_window(F.hann_window())
+    want_frames = F.framed(x, w512)
+    assert GOLD["fe_frames"].shape == (frames, 512)
+    assert np.max(np.abs(GOLD["fe_frames"] - want_frames)) <= 1e-6
+    offsets, bins, values = F.sparse_filters(F.triangular_filters())
+    want_mel = F.log_mel(GOLD["fe_frames"], offsets, bins, values)
+    assert np.max(np.abs(GOLD["fe_mel"] - want_mel)) <= 1e-4
+    assert np.max(np.abs(GOLD["fe_norm"] - F.normalize(GOLD["fe_mel"], valid))) <= 1e-5
+    assert not GOLD["fe_norm"][valid:].any()
