@@ -293,8 +293,8 @@ typedef struct pk100_decoder_weights {
 /* Scratch bytes for `utterances` (<= PK100_DECODER_MAX_UTTERANCES); 0 if out of range. */
 long long pk100_tdt_workspace_bytes(int utterances);
 
-/* Decodes `utterances` sequences in lockstep.  Chooses the cluster kernel when the model has
- * one LSTM layer and the device can host a 16-CTA cluster, else the exchange kernel (both
+/* Decodes `utterances` sequences in lockstep.  Chooses the cluster kernel when the device can
+ * host a 16-CTA cluster, else the exchange kernel (both
  * below; same results up to the summation order of the fp32 partial sums).
  * enc_proj rows of utterance u start at
  * u * seg_stride; frames[u] (device int array) frames are consumed.  tokens /
@@ -334,8 +334,9 @@ int pk100_tdt_decode_static(void* stream, const pk100_decoder_weights* weights, 
  * _cluster: one thread-block cluster of 16 CTAs; the phases of a round exchange their vectors
  *   through distributed shared memory and the hardware cluster barrier; joint rows resident in
  *   shared memory, LSTM / prediction weights streamed from L2 in a fragment-ordered copy that the
- *   call writes into the workspace.  One LSTM layer only (PK100_ERR_UNSUPPORTED otherwise, or when
- *   the device cannot co-schedule 16 CTAs of 217 KB shared memory as a cluster).
+ *   call writes into the workspace.  With two LSTM layers the joint rows are streamed as well (the
+ *   second layer's state takes their room).  PK100_ERR_UNSUPPORTED when the device cannot
+ *   co-schedule 16 CTAs of that much shared memory as a cluster.
  * _exchange: one CTA per SM, all weights resident in shared memory, phases exchange through
  *   tagged global-memory slots that the consumers poll (bounded).  One or two LSTM layers.  Uses
  *   only the first 280 KB of the workspace. */

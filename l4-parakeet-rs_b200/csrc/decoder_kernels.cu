@@ -999,13 +999,14 @@ struct FragShape {
     static_assert(KG * NG == kClWarps, "one (k-group, row-group) per warp");
     static_assert(NG * NT >= kTiles && (NG - 1) * NT < kTiles, "row groups cover the tiles");
     static_assert(KG * 8 * kPitch <= kPartFloats, "partials fit");
-    static_assert(kCols == kHidden, "K = 640");
+    static_assert(kCols % kHidden == 0, "K = 640, or 1280 for [input | recurrent]");
 };
 using LstmShape = FragShape<4, 5, 5, 4, 20>;   // 160 gate rows x 640 (recurrent weights)
 using PredShape = FragShape<20, 1, 1, 5, 5>;   // 40 rows x 640
 using JointShape = FragShape<10, 2, 2, 5, 9>;  // 72 rows (65 used) x 640
+using Lstm1Shape = FragShape<4, 5, 10, 4, 20>; // second LSTM layer: 160 gate rows x 1280 ([h of layer 0 | own h])
 
-struct ClLayout { size_t base, lstm, pred, joint, xtab, total; };
+struct ClLayout { size_t base, lstm, pred, joint, xtab, lstm1, total; };
 __host__ __device__ inline ClLayout cl_layout(int utts) {
     ClLayout l;
     const size_t a = dec_layout(utts).total, b = xch_layout(utts).total;
@@ -1015,16 +1016,17 @@ __host__ __device__ inline ClLayout cl_layout(int utts) {
     l.pred = off; off += static_cast<size_t>(kCl) * PredShape::kPerCta * 16;
     l.joint = off; off += static_cast<size_t>(kCl) * JointShape::kPerCta * 16;
     l.xtab = off; off += static_cast<size_t>(kTokenOutputs) * kGates * 4;
+    l.lstm1 = off; off += static_cast<size_t>(kCl) * Lstm1Shape::kPerCta * 16;
     l.total = off;
     return l;
 }
 
-enum : int { CLPACK_LSTM = 0, CLPACK_PRED = 1, CLPACK_JOINT = 2 };
+enum : int { CLPACK_LSTM = 0, CLPACK_PRED = 1, CLPACK_JOINT = 2, CLPACK_LSTM_IH_HH = 3 };
 
 // dst[cta][kg][kp][tile][lane] = the B fragments (b0, b1) of k-steps 2*kp and 2*kp+1 of row tile
 // `tile`: lane (g = lane / 4, t = lane % 4) holds W[row g][k0 + 2t, +1, +8, +9] per k-step.
 template <typename Shape, int Mode>
-__global__ void tdt_pack_kernel(uint4* dst, const __half* w) {
+__global__ void tdt_pack_kernel(uint4* dst, const __half* w, const __half* w_second) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= kCl * Shape::kPerCta) return;
     int rest = idx;
@@ -1037,12 +1039,15 @@ __global__ void tdt_pack_kernel(uint4* dst, const __half* w) {
     const int n = tile * 8 + g;
     const int k0 = (kg * Shape::KP + kp) * 32;
     int row = -1;
-    if (Mode == CLPACK_LSTM) row = (n % 4) * kHidden + r * kClUnits + n / 4;   // gate-major rows of w_hh
+    if (Mode == CLPACK_LSTM || Mode == CLPACK_LSTM_IH_HH) row = (n % 4) * kHidden + r * kClUnits + n / 4;   // gate-major rows
     else if (Mode == CLPACK_PRED) row = r * kClUnits + n;
     else if (n < kClJoint && r * kClJoint + n < kJointRows) row = r * kClJoint + n;
     auto pair = [&](int k) -> unsigned {
         if (row < 0) return 0u;
-        const __half* src = w + static_cast<size_t>(row) * kHidden + k;
+        // CLPACK_LSTM_IH_HH: columns 0..639 from w (input weights), 640..1279 from w_second (recurrent)
+        const __half* src = (Mode == CLPACK_LSTM_IH_HH && k >= kHidden)
+            ? w_second + static_cast<size_t>(row) * kHidden + (k - kHidden)
+            : w + static_cast<size_t>(row) * kHidden + k;
         return static_cast<unsigned>(__half_as_ushort(src[0])) | (static_cast<unsigned>(__half_as_ushort(src[1])) << 16);
     };
     dst[idx] = make_uint4(pair(k0 + 2 * t), pair(k0 + 2 * t + 8), pair(k0 + 16 + 2 * t), pair(k0 + 16 + 2 * t + 8));
@@ -1050,8 +1055,21 @@ __global__ void tdt_pack_kernel(uint4* dst, const __half* w) {
 
 constexpr int kEncChunks = kHidden / 8;          // 16-byte chunks of one projected encoder row
 
-struct CSmem {
-    uint4 wj[JointShape::kPerCta];        // this CTA's joint rows in fragment order (resident)
+// Two LSTM layers: second committed state, its receive buffer, cell state, bias, barrier.
+template <int Layers> struct CSecondLayer {};
+template <> struct CSecondLayer<2> {
+    __half ah1[16][kAct];
+    __half hx1[16][kAct];
+    float cstate1[kMaxUtt][kClUnits];
+    float lstm_bias1[kClUnits][4];
+    uint64_t hbar1;
+};
+
+// With one layer the joint rows stay resident; with two they are streamed like the other
+// weights (the second layer's state needs the room).
+template <int Layers>
+struct CSmemT {
+    uint4 wj[Layers == 1 ? JointShape::kPerCta : 1];   // this CTA's joint rows in fragment order (resident)
     __half ax[16][kAct];                  // joint input (hi rows 0-7, lo rows 8-15)
     __half ah[16][kAct];                  // committed hidden state, all 640 units
     __half hx[16][kAct];                  // fresh hidden state, written by all CTAs of the cluster
@@ -1074,11 +1092,13 @@ struct CSmem {
     alignas(8) unsigned char done[kMaxUtt];      // read as one 64-bit word: entries >= utts are 1
     alignas(8) unsigned char need[kMaxUtt];      // !done && !valid
     int abort;
+    CSecondLayer<Layers> second;
 #ifdef PK100_DEC_PROFILE
     long long prof[16], last_stamp;       // per-phase cycle totals of thread 0
 #endif
 };
-static_assert(sizeof(CSmem) <= 227 * 1024, "cluster decoder state fits one CTA's shared memory");
+using CSmem = CSmemT<1>;
+static_assert(sizeof(CSmemT<2>) <= 227 * 1024 && sizeof(CSmem) <= 227 * 1024, "cluster decoder state fits one CTA's shared memory");
 
 // Remote store that credits its bytes to an mbarrier of the destination CTA.  `addr` and `bar`
 // are shared::cluster addresses of the same CTA.
@@ -1180,11 +1200,12 @@ __device__ __forceinline__ void frag_compute(const uint4* w, const __half* a, fl
 #define CL_STAMP(i) do { } while (0)
 #endif
 
+template <int Layers>
 __global__ void __launch_bounds__(kClThreads, 1)
 tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* packed_pred,
-                   const uint4* packed_joint, const float* xtab) {
+                   const uint4* packed_joint, const float* xtab, const uint4* packed_lstm1) {
     extern __shared__ __align__(16) uint8_t cs_raw[];
-    CSmem& sm = *reinterpret_cast<CSmem*>(cs_raw);
+    CSmemT<Layers>& sm = *reinterpret_cast<CSmemT<Layers>*>(cs_raw);
 #ifdef PK100_DEC_PROFILE
     if (threadIdx.x == 0) {
         for (int i = 0; i < 16; ++i) sm.prof[i] = 0;
@@ -1197,9 +1218,21 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
     volatile int* abort_flag = &sm.abort;
 
     // ---- set-up: resident joint slice, biases, cleared state, first encoder rows
-    {
-        const uint4* src = packed_joint + static_cast<size_t>(r) * JointShape::kPerCta;
-        for (int i = tid; i < JointShape::kPerCta; i += kClThreads) sm.wj[i] = __ldg(src + i);
+    const uint4* wjoint = packed_joint + static_cast<size_t>(r) * JointShape::kPerCta;
+    if constexpr (Layers == 1) {
+        for (int i = tid; i < JointShape::kPerCta; i += kClThreads) sm.wj[i] = __ldg(wjoint + i);
+    } else {
+        for (int i = tid; i < 16 * kAct; i += kClThreads) {
+            (&sm.second.ah1[0][0])[i] = __float2half(0.0f);
+            (&sm.second.hx1[0][0])[i] = __float2half(0.0f);
+        }
+        for (int i = tid; i < kMaxUtt * kClUnits; i += kClThreads) (&sm.second.cstate1[0][0])[i] = 0.0f;
+        if (tid < kClUnits * 4) {
+            const int slot = tid / 4, gt = tid % 4;
+            const int row = gt * kHidden + r * kClUnits + slot;
+            sm.second.lstm_bias1[slot][gt] = p.b_ih[1][row] + p.b_hh[1][row];
+        }
+        if (tid == 0) mbar_init(&sm.second.hbar1, 1);
     }
     for (int i = tid; i < 16 * kAct; i += kClThreads) {
         (&sm.ax[0][0])[i] = __float2half(0.0f);
@@ -1253,6 +1286,8 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
     const uint32_t peer = static_cast<uint32_t>(tid / kClUnits);
     const int item0 = tid % kClUnits;
     uint32_t hphase = 0, pphase = 0, kphase[2] = {0, 0};
+    [[maybe_unused]] uint32_t h1phase = 0;
+    [[maybe_unused]] const uint4* wl1 = packed_lstm1 + static_cast<size_t>(r) * Lstm1Shape::kPerCta;
     // first k-step pair of the recurrent weights, requested one decision ahead of its use
     FragRing<LstmShape, 2> lstm_ring;
     frag_prefetch<LstmShape, true, 2, 0, 1>(wl, lstm_ring, warp, lane);
@@ -1311,12 +1346,73 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
             }
             // the prediction weights of this warp are requested while the hidden state travels
             FragRing<PredShape, 1> pred_ring;
-            frag_prefetch<PredShape, true, 1, 0, 1>(wp, pred_ring, warp, lane);
+            if constexpr (Layers == 1) frag_prefetch<PredShape, true, 1, 0, 1>(wp, pred_ring, warp, lane);
             mbar_wait_bounded(&sm.hbar, hphase, abort_flag);
             hphase ^= 1u;
             CL_STAMP(3);
-            // ---- prediction projection of the new state (A operand: the fresh rows in hx)
-            frag_compute<PredShape, true, 1, 1>(wp, &sm.hx[0][0], sm.part, pred_ring, warp, lane);
+            const __half* top_fresh = &sm.hx[0][0];       // fresh hidden state of the top layer
+            __half* top_committed = &sm.ah[0][0];
+            if constexpr (Layers == 2) {
+                // ---- second LSTM layer: gates = [fresh h of layer 0 | own h] . [w_ih | w_hh]^T + bias
+                {
+                    FragRing<Lstm1Shape, 2> ring1;
+                    const int kg = warp / Lstm1Shape::NG;
+                    // k-groups 0, 1 read the 640 columns of hx, groups 2, 3 those of ah1
+                    const __half* a = kg < 2 ? &sm.hx[0][0] : &sm.second.ah1[0][0] - kHidden;
+                    frag_compute<Lstm1Shape, true, 2, 0>(wl1, a, sm.part, ring1, warp, lane);
+                }
+                __syncthreads();
+                if (tid < kMaxUtt * kClUnits) {
+                    const int slot = tid % kClUnits, u = tid / kClUnits;
+                    if (u < U && sm.need[u]) {
+                        float gsum[4] = {sm.second.lstm_bias1[slot][0], sm.second.lstm_bias1[slot][1],
+                                         sm.second.lstm_bias1[slot][2], sm.second.lstm_bias1[slot][3]};
+#pragma unroll
+                        for (int kg = 0; kg < Lstm1Shape::KG; ++kg) {
+                            const float4 v = *reinterpret_cast<const float4*>(
+                                &sm.part[(kg * 8 + u) * Lstm1Shape::kPitch + slot * 4]);
+                            gsum[0] += v.x; gsum[1] += v.y; gsum[2] += v.z; gsum[3] += v.w;
+                        }
+                        const float cell = fast_sigmoid(gsum[1]) * sm.second.cstate1[u][slot] +
+                                           fast_sigmoid(gsum[0]) * fast_tanh(gsum[2]);
+                        sm.second.cstate1[u][slot] = cell;
+                        const float h = fast_sigmoid(gsum[3]) * fast_tanh(cell);
+                        const __half hi = __float2half_rn(h);
+                        sm.stage_h[u][slot] = hi;
+                        sm.stage_h[u + 8][slot] = __float2half_rn(h - __half2float(hi));
+                    }
+                } else {
+                    // meanwhile: commit the fresh state of layer 0
+                    for (int i = tid - kMaxUtt * kClUnits; i < 16 * kEncChunks; i += kClThreads - kMaxUtt * kClUnits) {
+                        const int row = i / kEncChunks, c = i % kEncChunks;
+                        const int u = row % 8;
+                        if (u < U && sm.need[u])
+                            *reinterpret_cast<uint4*>(&sm.ah[row][c * 8]) = *reinterpret_cast<const uint4*>(&sm.hx[row][c * 8]);
+                    }
+                }
+                if (tid == 0) mbar_arrive_expect_tx(&sm.second.hbar1, static_cast<uint32_t>(needs) * 2 * kHidden * 2);
+                __syncthreads();
+                {
+                    const uint32_t bar = map_to_cta(smem_u32(&sm.second.hbar1), peer);
+#pragma unroll
+                    for (int it = 0; it < 2; ++it) {
+                        const int item = item0 + it * kClUnits;
+                        const int row = item / 5, chunk = item % 5;
+                        const int u = row % 8;
+                        if (u < U && sm.need[u]) {
+                            const uint4 v = *reinterpret_cast<const uint4*>(&sm.stage_h[row][chunk * 8]);
+                            st_async_v4(map_to_cta(smem_u32(&sm.second.hx1[row][r * kClUnits + chunk * 8]), peer), v, bar);
+                        }
+                    }
+                }
+                frag_prefetch<PredShape, true, 1, 0, 1>(wp, pred_ring, warp, lane);
+                mbar_wait_bounded(&sm.second.hbar1, h1phase, abort_flag);
+                h1phase ^= 1u;
+                top_fresh = &sm.second.hx1[0][0];
+                top_committed = &sm.second.ah1[0][0];
+            }
+            // ---- prediction projection of the new state (A operand: the fresh rows of the top layer)
+            frag_compute<PredShape, true, 1, 1>(wp, top_fresh, sm.part, pred_ring, warp, lane);
             __syncthreads();
             CL_STAMP(4);
             if (tid < kMaxUtt * kClUnits) {
@@ -1333,7 +1429,8 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                     const int row = i / kEncChunks, c = i % kEncChunks;
                     const int u = row % 8;
                     if (u < U && sm.need[u])
-                        *reinterpret_cast<uint4*>(&sm.ah[row][c * 8]) = *reinterpret_cast<const uint4*>(&sm.hx[row][c * 8]);
+                        *reinterpret_cast<uint4*>(top_committed + row * kAct + c * 8) =
+                            *reinterpret_cast<const uint4*>(top_fresh + row * kAct + c * 8);
                 }
             }
             if (tid == 0) mbar_arrive_expect_tx(&sm.pbar, static_cast<uint32_t>(needs) * kHidden * 4);
@@ -1375,7 +1472,8 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
         CL_STAMP(7);
         {
             FragRing<JointShape, 1> joint_ring;
-            frag_compute<JointShape, false, 1, 0>(sm.wj, &sm.ax[0][0], sm.part, joint_ring, warp, lane);
+            if constexpr (Layers == 1) frag_compute<JointShape, false, 1, 0>(sm.wj, &sm.ax[0][0], sm.part, joint_ring, warp, lane);
+            else frag_compute<JointShape, true, 1, 0>(wjoint, &sm.ax[0][0], sm.part, joint_ring, warp, lane);
         }
         __syncthreads();
         CL_STAMP(8);
@@ -1717,7 +1815,9 @@ extern "C" int pk100_tdt_decode_exchange(void* stream_v, const pk100_decoder_wei
 
 namespace {
 
-// Can this device run a 16-CTA cluster of the cluster decoder?  Asked once per device.
+// Can this device run a 16-CTA cluster of the cluster decoder?  Asked once per device and
+// kernel variant (one or two LSTM layers).
+template <int Layers>
 bool cluster_decoder_available() {
     static int cached[64] = {0};      // 0 = unknown, 1 = yes, 2 = no
     int dev = 0;
@@ -1727,15 +1827,15 @@ bool cluster_decoder_available() {
     do {
         int max_smem = 0;
         cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-        if (sizeof(CSmem) > static_cast<size_t>(max_smem)) break;
-        if (cudaFuncSetAttribute(tdt_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(sizeof(CSmem))) != cudaSuccess) break;
-        if (cudaFuncSetAttribute(tdt_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
+        if (sizeof(CSmemT<Layers>) > static_cast<size_t>(max_smem)) break;
+        if (cudaFuncSetAttribute(tdt_cluster_kernel<Layers>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(sizeof(CSmemT<Layers>))) != cudaSuccess) break;
+        if (cudaFuncSetAttribute(tdt_cluster_kernel<Layers>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
             cudaSuccess) break;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(kCl);
         cfg.blockDim = dim3(kClThreads);
-        cfg.dynamicSmemBytes = sizeof(CSmem);
+        cfg.dynamicSmemBytes = sizeof(CSmemT<Layers>);
         cudaLaunchAttribute attr{};
         attr.id = cudaLaunchAttributeClusterDimension;
         attr.val.clusterDim.x = kCl;
@@ -1744,12 +1844,34 @@ bool cluster_decoder_available() {
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, tdt_cluster_kernel, &cfg) != cudaSuccess) break;
+        if (cudaOccupancyMaxActiveClusters(&clusters, tdt_cluster_kernel<Layers>, &cfg) != cudaSuccess) break;
         ok = clusters >= 1;
     } while (false);
     cudaGetLastError();
     cached[dev] = ok ? 1 : 2;
     return ok;
+}
+
+bool cluster_decoder_available_for(int layers) {
+    return layers == 1 ? cluster_decoder_available<1>() : (layers == 2 ? cluster_decoder_available<2>() : false);
+}
+
+template <int Layers>
+cudaError_t launch_cluster_kernel(cudaStream_t stream, const DecParams& p, const uint4* lstm, const uint4* pred,
+                                  const uint4* joint, const float* xtab, const uint4* lstm1) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(kCl);
+    cfg.blockDim = dim3(kClThreads);
+    cfg.dynamicSmemBytes = sizeof(CSmemT<Layers>);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = kCl;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, tdt_cluster_kernel<Layers>, p, lstm, pred, joint, xtab, lstm1);
 }
 
 }  // namespace
@@ -1764,13 +1886,14 @@ extern "C" int pk100_tdt_decode_cluster(void* stream_v, const pk100_decoder_weig
     if (utterances == 0) return PK100_OK;
     if (utterances < 0 || seg_stride <= 0 || max_tokens <= 0) return PK100_ERR_SHAPE;
     if (utterances > kMaxUtt) return PK100_ERR_LIMIT;
-    if (w->layers != 1 || !cluster_decoder_available()) return PK100_ERR_UNSUPPORTED;
+    if (!cluster_decoder_available_for(w->layers)) return PK100_ERR_UNSUPPORTED;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const ClLayout lay = cl_layout(utterances);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     uint4* packed_lstm = reinterpret_cast<uint4*>(ws + lay.lstm);
     uint4* packed_pred = reinterpret_cast<uint4*>(ws + lay.pred);
     uint4* packed_joint = reinterpret_cast<uint4*>(ws + lay.joint);
+    uint4* packed_lstm1 = reinterpret_cast<uint4*>(ws + lay.lstm1);
     float* xtab = reinterpret_cast<float*>(ws + lay.xtab);
     const __half* w_ih = static_cast<const __half*>(w->w_ih[0]);
     const __half* w_hh = static_cast<const __half*>(w->w_hh[0]);
@@ -1778,11 +1901,19 @@ extern "C" int pk100_tdt_decode_cluster(void* stream_v, const pk100_decoder_weig
     const __half* w_joint = static_cast<const __half*>(w->w_joint);
     // weights -> fragment order (they may change between calls, so this is done every call)
     tdt_pack_kernel<LstmShape, CLPACK_LSTM><<<(kCl * LstmShape::kPerCta + 255) / 256, 256, 0, stream>>>(
-        packed_lstm, w_hh);
+        packed_lstm, w_hh, nullptr);
     tdt_pack_kernel<PredShape, CLPACK_PRED><<<(kCl * PredShape::kPerCta + 255) / 256, 256, 0, stream>>>(
-        packed_pred, w_pred);
+        packed_pred, w_pred, nullptr);
     tdt_pack_kernel<JointShape, CLPACK_JOINT><<<(kCl * JointShape::kPerCta + 255) / 256, 256, 0, stream>>>(
-        packed_joint, w_joint);
+        packed_joint, w_joint, nullptr);
+    pk100_count_launch();
+    pk100_count_launch();
+    pk100_count_launch();
+    if (w->layers == 2) {
+        tdt_pack_kernel<Lstm1Shape, CLPACK_LSTM_IH_HH><<<(kCl * Lstm1Shape::kPerCta + 255) / 256, 256, 0, stream>>>(
+            packed_lstm1, static_cast<const __half*>(w->w_ih[1]), static_cast<const __half*>(w->w_hh[1]));
+        pk100_count_launch();
+    }
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return static_cast<int>(err);
     {   // input table: xtab[token][gate row] = embedding[token] . w_ih[gate row] (fp32, no bias)
@@ -1801,21 +1932,20 @@ extern "C" int pk100_tdt_decode_cluster(void* stream_v, const pk100_decoder_weig
         const int grc = pk100_gemm(stream_v, &g);
         if (grc != PK100_OK) return grc;
     }
-    pk100_count_launch();
-    pk100_count_launch();
-    pk100_count_launch();
 
     DecParams p{};
     p.enc_proj = static_cast<const __half*>(enc_proj);
     p.seg_stride = seg_stride;
     p.frames = frames;
     p.utts = utterances;
-    p.layers = 1;
+    p.layers = w->layers;
     p.embedding = static_cast<const __half*>(w->embedding);
-    p.w_ih[0] = w_ih;
-    p.w_hh[0] = w_hh;
-    p.b_ih[0] = w->b_ih[0];
-    p.b_hh[0] = w->b_hh[0];
+    for (int l = 0; l < w->layers; ++l) {
+        p.w_ih[l] = static_cast<const __half*>(w->w_ih[l]);
+        p.w_hh[l] = static_cast<const __half*>(w->w_hh[l]);
+        p.b_ih[l] = w->b_ih[l];
+        p.b_hh[l] = w->b_hh[l];
+    }
     p.w_pred = w_pred;
     p.b_pred = w->b_pred;
     p.w_joint = w_joint;
@@ -1827,21 +1957,9 @@ extern "C" int pk100_tdt_decode_cluster(void* stream_v, const pk100_decoder_weig
     p.max_tokens = max_tokens;
     p.status = status;
 
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(kCl);
-    cfg.blockDim = dim3(kClThreads);
-    cfg.dynamicSmemBytes = sizeof(CSmem);
-    cfg.stream = stream;
-    cudaLaunchAttribute attr{};
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = kCl;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    err = cudaLaunchKernelEx(&cfg, tdt_cluster_kernel, p, static_cast<const uint4*>(packed_lstm),
-                             static_cast<const uint4*>(packed_pred), static_cast<const uint4*>(packed_joint),
-                             static_cast<const float*>(xtab));
+    err = w->layers == 1
+        ? launch_cluster_kernel<1>(stream, p, packed_lstm, packed_pred, packed_joint, xtab, packed_lstm1)
+        : launch_cluster_kernel<2>(stream, p, packed_lstm, packed_pred, packed_joint, xtab, packed_lstm1);
     if (err != cudaSuccess) {
         cudaGetLastError();
         return static_cast<int>(err);
@@ -1854,9 +1972,9 @@ extern "C" int pk100_tdt_decode(void* stream_v, const pk100_decoder_weights* w, 
                                 int utterances, int seg_stride, const int* frames, void* workspace,
                                 int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
                                 int* status) {
-    // one LSTM layer on a device that can host a 16-CTA cluster: the cluster kernel; anything
-    // else: the 148-CTA exchange kernel
-    if (w != nullptr && w->layers == 1 && utterances > 0 && utterances <= kMaxUtt && cluster_decoder_available())
+    // a device that can host a 16-CTA cluster: the cluster kernel; anything else: the 148-CTA
+    // exchange kernel
+    if (w != nullptr && utterances > 0 && utterances <= kMaxUtt && cluster_decoder_available_for(w->layers))
         return pk100_tdt_decode_cluster(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace, tokens,
                                         durations, counts, max_tokens, status);
     return pk100_tdt_decode_exchange(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace, tokens,

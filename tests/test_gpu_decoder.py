@@ -23,8 +23,6 @@ def _check(tokens_gpu, count, oracle_tokens, ambiguous):
 @pytest.mark.parametrize("kernel", [None, "cluster", "exchange", "barrier"])
 @pytest.mark.parametrize("layers", [2, 1])
 def test_batched_decode_matches_oracle(pk, cuda, layers, kernel):
-    if kernel == "cluster" and layers != 1:
-        pytest.skip("the cluster kernel holds one LSTM layer")
     w = D.make_decoder_weights(11 + layers, layers=layers)
     dec = pk.decoder.TdtDecoder(w, cuda)
     seg_stride, frames = 96, [96, 60, 1, 0, 33]
@@ -79,9 +77,10 @@ def test_decoder_limits(pk, cuda):
         dec.decode(enc, 9, 8, fr, 16)
 
 
-def test_eight_utterances_all_kernels_agree(pk, cuda):
+@pytest.mark.parametrize("layers", [1, 2])
+def test_eight_utterances_all_kernels_agree(pk, cuda, layers):
     """Full batch width; the cluster, exchange and barrier kernels walk the same decisions."""
-    w = D.make_decoder_weights(31, layers=1)
+    w = D.make_decoder_weights(31, layers=layers)
     dec = pk.decoder.TdtDecoder(w, cuda)
     seg_stride = 128
     frames = [128, 100, 90, 128, 5, 64, 77, 128]

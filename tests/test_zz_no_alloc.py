@@ -44,7 +44,8 @@ def test_static_scratch_decoder_matches_regular_entry_point(pk, cuda):
         utterances = len(frames)
         enc_d = torch.from_numpy(codec.f16_round(enc * 0.5)).half().to(cuda)
         fr = torch.tensor(frames, dtype=torch.int32, device=cuda)
-        want_t, want_d, want_c = dec.decode(enc_d, utterances, seg_stride, fr, max_tokens)
+        # the workspace-taking entry point of the same kernel
+        want_t, want_d, want_c = dec.decode(enc_d, utterances, seg_stride, fr, max_tokens, kernel="exchange")
         torch.cuda.synchronize()
         want_t, want_d, want_c = want_t.cpu().numpy().copy(), want_d.cpu().numpy().copy(), want_c.cpu().numpy().copy()
         rc, tokens, durations, counts, status = _decode_static(pk, dec, enc_d, utterances, seg_stride, fr, max_tokens)
