@@ -1,6 +1,7 @@
 // 8x depthwise-striding convolution subsampling (mel [frames,128] -> [frames/8, 1024])
-// for a batch of utterances.  The convolutions are simple channel-parallel kernels
-// (thread = channel, coalesced over the 256 channels); the two pointwise layers and
+// for a batch of utterances.  The convolutions are channel-parallel kernels (thread =
+// channel, coalesced over the 256 channels), the first two fused so that the largest
+// intermediate never reaches HBM; the two pointwise layers and
 // the 4096 -> 1024 projection are tcgen05 GEMMs (pk100_gemm).  Semantics follow
 // kernels/sm89/subsampling.cu:11-226 and the host tiling of
 // src/cuda/subsampling.rs:436-804 (without its 256-frame tiles: the whole batch is
@@ -20,45 +21,91 @@ __device__ __forceinline__ int frames_of(const int* per_utt, int utt, int unifor
     return per_utt != nullptr ? per_utt[utt] : uniform;
 }
 
-// conv 3x3, stride 2, pad 1, 1 -> 256 channels, + bias, ReLU.
-// in  [utt][in_stride frames][128] fp32;  out [utt][out_frames_cap][64][256] fp16
+// First two stages in one kernel: conv 3x3 s2 (1 -> 256 channels) + bias + ReLU, rounded to fp16,
+// feeding the depthwise conv 3x3 s2 + bias.  The intermediate [frames/2, 64, 256] tensor (98 KB per
+// output frame, 786 MB for 8 x 60 s) stays in registers instead of making a round trip through HBM.
+// One CTA per output frame f2: thread = channel; the 7 mel rows 4*f2-3 .. 4*f2+3 are staged in shared
+// memory with one zero column on each side; each thread walks the 64 intermediate features of the 3
+// intermediate rows 2*f2-1 .. 2*f2+1 and scatters them into its 32 outputs.  The accumulation order of
+// both convolutions (bias, then taps row by row, out-of-range taps skipped) is the reference's
+// (kernels/sm89/subsampling.cu:11-179), so fusing changes no bit of the result.
+// in [utt][in_stride frames][128] fp32 -> out [utt][out_cap][32][256] fp16
 __global__ void __launch_bounds__(256)
-subsample_first_kernel(const float* __restrict__ in, const __half* __restrict__ w,
-                       const __half* __restrict__ b, __half* __restrict__ out, int in_stride,
-                       int in_frames_uniform, const int* __restrict__ in_frames_per_utt,
-                       int out_frames_cap) {
+subsample_first_fused_kernel(const float* __restrict__ in, const __half* __restrict__ w0,
+                             const __half* __restrict__ b0, const __half* __restrict__ w1,
+                             const __half* __restrict__ b1, __half* __restrict__ out, int in_stride,
+                             int in_frames_uniform, const int* __restrict__ in_frames_per_utt, int out_cap) {
+    __shared__ __align__(8) float smel[7][kMelBins + 4];      // column t of the mel row sits at index t + 1
     const int ch = threadIdx.x;
-    const int feat0 = blockIdx.x * kGroup;
-    const int of = blockIdx.y;
-    const int utt = blockIdx.z;
+    const int f2 = blockIdx.x, utt = blockIdx.y;
     const int in_frames = frames_of(in_frames_per_utt, utt, in_frames_uniform);
-    const int out_frames = (in_frames + 1) / 2;
-    if (of >= out_frames) return;
+    const int f1_frames = (in_frames + 1) / 2;
+    const int f2_frames = (f1_frames + 1) / 2;
+    if (f2 >= f2_frames) return;
     const float* src = in + static_cast<size_t>(utt) * in_stride * kMelBins;
-    float wk[9];
+    for (int i = ch; i < 7 * (kMelBins + 4); i += 256) {
+        const int row = i / (kMelBins + 4), p = i % (kMelBins + 4);
+        const int f = 4 * f2 - 3 + row, t = p - 1;
+        (&smel[0][0])[i] = (f >= 0 && f < in_frames && t >= 0 && t < kMelBins)
+            ? src[static_cast<size_t>(f) * kMelBins + t] : 0.0f;
+    }
+    float wa[9], wb[9];
 #pragma unroll
-    for (int i = 0; i < 9; ++i) wk[i] = __half2float(w[ch * 9 + i]);
-    const float bias = __half2float(b[ch]);
-    float sums[kGroup];
+    for (int i = 0; i < 9; ++i) {
+        wa[i] = __half2float(w0[ch * 9 + i]);
+        wb[i] = __half2float(w1[ch * 9 + i]);
+    }
+    const float bias0 = __half2float(b0[ch]), bias1 = __half2float(b1[ch]);
+    float sums[32];
 #pragma unroll
-    for (int g = 0; g < kGroup; ++g) sums[g] = bias;
+    for (int m = 0; m < 32; ++m) sums[m] = bias1;
+    __syncthreads();
 #pragma unroll
     for (int kf = 0; kf < 3; ++kf) {
-        const int f = of * 2 + kf - 1;
-        if (f < 0 || f >= in_frames) continue;
+        const int f1 = 2 * f2 + kf - 1;
+        if (f1 < 0 || f1 >= f1_frames) continue;             // padding row of the depthwise conv
+        // mel rows of this intermediate row: 2*f1 - 1 + a = smel row 2*kf + a; rows outside the
+        // utterance are skipped like in the separate kernel
+        bool row_ok[3];
 #pragma unroll
-        for (int kt = 0; kt < 3; ++kt) {
+        for (int a = 0; a < 3; ++a) {
+            const int f = 2 * f1 + a - 1;
+            row_ok[a] = f >= 0 && f < in_frames;
+        }
+        // sliding 3-wide windows of the three mel rows: (c0, c1, c2) = columns 2*m1 - 1 .. 2*m1 + 1
+        float c0[3], c1[3];
 #pragma unroll
-            for (int g = 0; g < kGroup; ++g) {
-                const int t = (feat0 + g) * 2 + kt - 1;
-                if (t >= 0 && t < kMelBins)
-                    sums[g] = fmaf(src[static_cast<size_t>(f) * kMelBins + t], wk[kf * 3 + kt], sums[g]);
+        for (int a = 0; a < 3; ++a) {
+            c0[a] = smel[2 * kf + a][0];
+            c1[a] = smel[2 * kf + a][1];
+        }
+#pragma unroll
+        for (int m1 = 0; m1 < 64; ++m1) {
+            float acc = bias0;
+#pragma unroll
+            for (int a = 0; a < 3; ++a) {
+                const float2 nx = *reinterpret_cast<const float2*>(&smel[2 * kf + a][2 * m1 + 2]);
+                if (row_ok[a]) {
+                    if (m1 > 0) acc = fmaf(c0[a], wa[a * 3 + 0], acc);      // column -1 is padding
+                    acc = fmaf(c1[a], wa[a * 3 + 1], acc);
+                    acc = fmaf(nx.x, wa[a * 3 + 2], acc);                   // column 2*m1 + 1 <= 127
+                }
+                c0[a] = nx.x;
+                c1[a] = nx.y;
+            }
+            const float v = __half2float(__float2half_rn(fmaxf(acc, 0.0f)));
+            // intermediate feature m1 is tap kt of output m2 with m1 = 2*m2 + kt - 1
+            if (m1 % 2 == 0) {
+                sums[m1 / 2] = fmaf(v, wb[kf * 3 + 1], sums[m1 / 2]);
+            } else {
+                sums[(m1 - 1) / 2] = fmaf(v, wb[kf * 3 + 2], sums[(m1 - 1) / 2]);
+                if ((m1 + 1) / 2 < 32) sums[(m1 + 1) / 2] = fmaf(v, wb[kf * 3 + 0], sums[(m1 + 1) / 2]);
             }
         }
     }
-    __half* dst = out + ((static_cast<size_t>(utt) * out_frames_cap + of) * 64 + feat0) * kChannels + ch;
+    __half* dst = out + (static_cast<size_t>(utt) * out_cap + f2) * 32 * kChannels + ch;
 #pragma unroll
-    for (int g = 0; g < kGroup; ++g) dst[g * kChannels] = __float2half_rn(fmaxf(sums[g], 0.0f));
+    for (int m = 0; m < 32; ++m) dst[m * kChannels] = __float2half_rn(sums[m]);
 }
 
 // depthwise conv 3x3, stride 2, pad 1, + bias (no activation).
@@ -148,7 +195,7 @@ extern "C" long long pk100_subsampling_workspace_bytes(int utterances, int frame
     if (utterances <= 0 || frames <= 0 || seg_stride <= 0) return 0;
     const Caps c = caps(frames);
     const long long u = utterances;
-    return up256(u * c.f1 * 64 * 256 * 2) + 2 * up256(u * c.f2 * 32 * 256 * 2) +
+    return 2 * up256(u * c.f2 * 32 * 256 * 2) +
            2 * up256(u * c.f3 * 16 * 256 * 2) + up256(u * seg_stride * 4096LL * 2) + 256;
 }
 
@@ -169,22 +216,18 @@ extern "C" int pk100_run_subsampling(void* stream_v, const pk100_subsampling_wei
     const long long u = utterances;
     char* p = static_cast<char*>(workspace);
     auto take = [&p](long long bytes) { char* cur = p; p += up256(bytes); return cur; };
-    __half* s1 = reinterpret_cast<__half*>(take(u * c.f1 * 64 * 256 * 2));
     __half* s2 = reinterpret_cast<__half*>(take(u * c.f2 * 32 * 256 * 2));
     __half* s3 = reinterpret_cast<__half*>(take(u * c.f2 * 32 * 256 * 2));
     __half* s4 = reinterpret_cast<__half*>(take(u * c.f3 * 16 * 256 * 2));
     __half* s5 = reinterpret_cast<__half*>(take(u * c.f3 * 16 * 256 * 2));
     __half* flat = reinterpret_cast<__half*>(take(u * seg_stride * 4096LL * 2));
 
-    subsample_first_kernel<<<dim3(64 / kGroup, c.f1, utterances), 256, 0, stream>>>(
-        mel, static_cast<const __half*>(w->conv0_w), static_cast<const __half*>(w->conv0_b), s1, frames,
-        frames, mel_frames, c.f1);
+    subsample_first_fused_kernel<<<dim3(c.f2, utterances), 256, 0, stream>>>(
+        mel, static_cast<const __half*>(w->conv0_w), static_cast<const __half*>(w->conv0_b),
+        static_cast<const __half*>(w->dw1_w), static_cast<const __half*>(w->dw1_b), s2, frames, frames,
+        mel_frames, c.f2);
     int rc = pk100_launch_status();
     if (rc != PK100_OK) return rc;
-    subsample_depthwise_kernel<<<dim3(32 / kGroup, c.f2, utterances), 256, 0, stream>>>(
-        s1, static_cast<const __half*>(w->dw1_w), static_cast<const __half*>(w->dw1_b), s2, c.f1, 64,
-        c.f2, frames, mel_frames, 1);
-    if ((rc = pk100_launch_status()) != PK100_OK) return rc;
 
     pk100_gemm_args a{};
     a.kind = PK100_KIND_F16; a.epilogue = PK100_EPI_LINEAR;
