@@ -358,6 +358,38 @@ int pk100_tdt_decode_barrier(void* stream, const pk100_decoder_weights* weights,
                              int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
                              int* status);
 
+/* Long-request numerics.  From 1024 encoder frames on (FP8_MIN_FRAMES, src/cuda/decoder.rs:15,
+ * :88, :292-321) the reference launches another kernel (pk_sm89_tdt_persistent_fp8_ih,
+ * kernels/sm89/decoder.cu:452-784, :805-824) that computes a different function: w_hh of both
+ * layers and w_ih of layer 1 become per-tensor symmetric INT8 codes (scale = max|w| / 127, derived
+ * inside every request, :517-575), the hidden state that multiplies them is rne(h * 127) (:644,
+ * :668), and the layer-0 input term is read from an fp16 table embedding . w_ih[0]^T
+ * (launch_input_table, src/cuda/decoder.rs:355-383).  Prediction projection and joint keep the fp32
+ * state.  The entry points below reproduce those numerics (integer dot products exactly), with the
+ * contract of pk100_tdt_decode:
+ * _long: the cluster kernel where available, else the grid-barrier kernel;
+ * _long_cluster / _long_barrier: one kernel each (PK100_ERR_UNSUPPORTED as for _cluster);
+ * _auto: the reference's rule applied per utterance -- utterances with frames[u] < 1024 are decoded
+ *   with the short-request numerics, the others with the long-request numerics, as two launches on
+ *   `stream` that each skip the other's utterances.  A host that knows every utterance is short
+ *   calls pk100_tdt_decode and saves the second launch. */
+int pk100_tdt_decode_long(void* stream, const pk100_decoder_weights* weights, const void* enc_proj,
+                          int utterances, int seg_stride, const int* frames, void* workspace,
+                          int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                          int* status);
+int pk100_tdt_decode_long_cluster(void* stream, const pk100_decoder_weights* weights, const void* enc_proj,
+                                  int utterances, int seg_stride, const int* frames, void* workspace,
+                                  int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                                  int* status);
+int pk100_tdt_decode_long_barrier(void* stream, const pk100_decoder_weights* weights, const void* enc_proj,
+                                  int utterances, int seg_stride, const int* frames, void* workspace,
+                                  int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                                  int* status);
+int pk100_tdt_decode_auto(void* stream, const pk100_decoder_weights* weights, const void* enc_proj,
+                          int utterances, int seg_stride, const int* frames, void* workspace,
+                          int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                          int* status);
+
 /* ------------------------------------------------------------------------
  * 8x convolution subsampling for a batch of utterances: mel fp32
  * [utterances, frames, 128] -> fp16 rows [utterances * seg_stride, 1024].

@@ -14,6 +14,7 @@
 // :431-445 (frame advance, at most 10 symbols per frame, blank keeps the state).
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
+#include <limits.h>
 #include <float.h>
 #include <stdint.h>
 
@@ -78,7 +79,61 @@ struct DecParams {
     int32_t* counts;             // [utts]
     int max_tokens;
     int* status;
+    // Long-request numerics (the reference's kernel for 1024 frames or more): max |w| of
+    // w_hh[0], w_hh[1], w_ih[1] as three floats in device memory; nullptr = fp16 weights.
+    const float* cache_absmax;
+    // Long-request numerics: fp32 [1025, 2560] table embedding . w_ih[0]^T, entries rounded to fp16
+    // (src/cuda/decoder.rs:355-383), built by a tensor-core GEMM like the reference's.
+    const float* input_table;
+    // Only utterances with frames_lo <= frames[u] < frames_hi take part (cluster and barrier
+    // kernels); the others are left alone, their counts unwritten.
+    int frames_lo, frames_hi;
 };
+__device__ __forceinline__ bool in_window(const DecParams& p, int u) {
+    const int f = p.frames[u];
+    return f >= p.frames_lo && f < p.frames_hi;
+}
+
+// INT8 cache of the long-request kernel (kernels/sm89/decoder.cu:96-98, :552-553, :568-572):
+// codes = rne(w / scale) clamped to +-127 with scale = max|w| / 127 per tensor; the hidden state
+// that multiplies them is rne(h * 127).  Codes and their 640-term dot products are integers
+// below 2^24, so fp16 storage and fp32 (or tensor-core) accumulation reproduce the integer
+// arithmetic exactly in any summation order.
+//
+// The reference builds its decoder unit with --use_fast_math (build.rs:78-83, :100-102), which
+// replaces x / y by __fdividef, expf by __expf and tanhf by __tanhf.  The 8-bit rounding of h turns
+// the error of those approximations (tanh: about 2^-11 relative) into different codes, so the
+// long-request numerics are reproduced with the same intrinsics, spelled out here because this
+// library is built without that flag.
+__device__ __forceinline__ int quantize_i8(float v) { return max(-127, min(127, __float2int_rn(v))); }
+__device__ __forceinline__ float cache_scale(const float* absmax, int i) {
+    const float m = absmax[i];
+    return m > 0.0f ? __fdividef(m, 127.0f) : 1.0f;
+}
+__device__ __forceinline__ float cache_mul(float scale) { return __fdividef(scale, 127.0f); }
+__device__ __forceinline__ __half cache_code(__half w, float scale) {
+    return __int2half_rn(quantize_i8(__fdividef(__half2float(w), scale)));
+}
+__device__ __forceinline__ float ref_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float ref_tanh(float x) { return __tanhf(x); }
+// lstm_cell of decoder.cu:148-163 under those substitutions; returns h
+__device__ __forceinline__ float ref_lstm_cell(const float (&gate)[4], float& cstate) {
+    const float ig = ref_sigmoid(gate[0]), fg = ref_sigmoid(gate[1]);
+    const float gg = ref_tanh(gate[2]), og = ref_sigmoid(gate[3]);
+    const float cell = fg * cstate + ig * gg;
+    cstate = cell;
+    return og * ref_tanh(cell);
+}
+
+// max |w| over a tensor; `out` holds the bits of a non-negative float (ordered like unsigned), zeroed before
+__global__ void tdt_absmax_kernel(const __half* __restrict__ w, int n, unsigned* out) {
+    float m = 0.0f;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+        m = fmaxf(m, fabsf(__half2float(w[i])));
+#pragma unroll
+    for (int off = 16; off > 0; off /= 2) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if (threadIdx.x % 32 == 0) atomicMax(out, __float_as_uint(m));
+}
 
 __device__ __forceinline__ bool better(float s, int id, float os, int oid) {
     return s > os || (s == os && id < oid);
@@ -169,7 +224,12 @@ __global__ void __launch_bounds__(kDecThreads, 1) tdt_greedy_kernel(const DecPar
     __shared__ int s_frame[kMaxUtt], s_symbols[kMaxUtt], s_last[kMaxUtt], s_count[kMaxUtt];
     __shared__ uint8_t s_emitted[kMaxUtt], s_valid[kMaxUtt], s_alt[kMaxUtt], s_done[kMaxUtt];
 
-    // ---- load this CTA's weight slices (once)
+    // ---- load this CTA's weight slices (once); long-request numerics: INT8 codes of the
+    // recurrent weights and of layer 1's input weights, held as fp16 integers
+    const bool cache = p.cache_absmax != nullptr;
+    float cscale[3] = {1.0f, 1.0f, 1.0f};       // w_hh[0], w_hh[1], w_ih[1]
+    if (cache)
+        for (int i = 0; i < (p.layers == 2 ? 3 : 1); ++i) cscale[i] = cache_scale(p.cache_absmax, i);
     for (int l = 0; l < p.layers; ++l) {
         for (int i = 0; i < units; ++i) {
             const int unit = cta + G * i;
@@ -177,8 +237,12 @@ __global__ void __launch_bounds__(kDecThreads, 1) tdt_greedy_kernel(const DecPar
                 __half* dst = s_lstm + ((static_cast<size_t>(l) * units + i) * 8 + r) * kHidden;
                 const __half* src = (r < 4 ? p.w_ih[l] : p.w_hh[l]) +
                                     (static_cast<size_t>(r & 3) * kHidden + unit) * kHidden;
-                for (int c = tid; c < kHidden; c += kDecThreads)
-                    dst[c] = unit < kHidden ? src[c] : __float2half(0.0f);
+                const int coded = !cache ? -1 : (r >= 4 ? l : (l == 1 ? 2 : -1));
+                for (int c = tid; c < kHidden; c += kDecThreads) {
+                    __half v = unit < kHidden ? src[c] : __float2half(0.0f);
+                    if (coded >= 0) v = cache_code(v, cscale[coded]);
+                    dst[c] = v;
+                }
             }
         }
     }
@@ -207,7 +271,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) tdt_greedy_kernel(const DecPar
     if (tid < p.utts) {
         s_frame[tid] = 0; s_symbols[tid] = 0; s_last[tid] = kBlank; s_count[tid] = 0;
         s_emitted[tid] = 0; s_valid[tid] = 0; s_alt[tid] = 0;
-        s_done[tid] = p.frames[tid] <= 0;
+        s_done[tid] = p.frames[tid] <= 0 || !in_window(p, tid);
     }
     if (cta == 0 && tid < p.utts * 3) g_dec[tid] = decision_key(-FLT_MAX, kTokenOutputs);
     bool ok = bar.sync();
@@ -238,9 +302,11 @@ __global__ void __launch_bounds__(kDecThreads, 1) tdt_greedy_kernel(const DecPar
                                              : 0.0f;
                         } else {
                             x = __ldcg(candidate + (l - 1) * kHidden + c);
+                            if (cache) x = static_cast<float>(quantize_i8(x * 127.0f));
                         }
                         vec[c] = x;
-                        vec[kHidden + c] = __ldcg(committed + l * kHidden + c);
+                        const float hv = __ldcg(committed + l * kHidden + c);
+                        vec[kHidden + c] = cache ? static_cast<float>(quantize_i8(hv * 127.0f)) : hv;
                     }
                 }
                 __syncthreads();
@@ -253,22 +319,42 @@ __global__ void __launch_bounds__(kDecThreads, 1) tdt_greedy_kernel(const DecPar
                     float gate[4];
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
-                        float acc = dot640(wrow + r * kHidden, vec, lane) +
-                                    dot640(wrow + (4 + r) * kHidden, vec + kHidden, lane);
-                        acc = warp_sum_f(acc);
-                        gate[r] = acc + p.b_ih[l][r * kHidden + unit] + p.b_hh[l][r * kHidden + unit];
+                        if (!cache) {
+                            float acc = dot640(wrow + r * kHidden, vec, lane) +
+                                        dot640(wrow + (4 + r) * kHidden, vec + kHidden, lane);
+                            acc = warp_sum_f(acc);
+                            gate[r] = acc + p.b_ih[l][r * kHidden + unit] + p.b_hh[l][r * kHidden + unit];
+                        } else {
+                            // decoder.cu:626-640 (layer 0: recurrent codes + bias + fp16 table entry),
+                            // :655-663 (layer 1: recurrent + input codes, then bias)
+                            // layer 0: the table entry of the last token (zero before the first one)
+                            const float in = l == 0
+                                ? (s_emitted[u] ? p.input_table[static_cast<size_t>(s_last[u]) * kGates + r * kHidden + unit] : 0.0f)
+                                : warp_sum_f(dot640(wrow + r * kHidden, vec, lane));
+                            const float rec = warp_sum_f(dot640(wrow + (4 + r) * kHidden, vec + kHidden, lane)) *
+                                              cache_mul(cscale[l]);
+                            const float bias = p.b_ih[l][r * kHidden + unit] + p.b_hh[l][r * kHidden + unit];
+                            gate[r] = l == 0 ? (rec + bias) + in : (rec + in * cache_mul(cscale[2])) + bias;
+                        }
                     }
                     if (lane == 0) {
                         float* st = g_state + static_cast<size_t>(u) * kStatePerUtt;
                         const float* committed = st + (s_alt[u] ? 4 * kHidden : 0);
                         float* candidate = st + (s_alt[u] ? 0 : 4 * kHidden);
-                        const float ig = 1.0f / (1.0f + expf(-gate[0]));
-                        const float fg = 1.0f / (1.0f + expf(-gate[1]));
-                        const float gg = tanhf(gate[2]);
-                        const float og = 1.0f / (1.0f + expf(-gate[3]));
-                        const float cell = fg * __ldcg(committed + (2 + l) * kHidden + unit) + ig * gg;
-                        __stcg(candidate + (2 + l) * kHidden + unit, cell);
-                        __stcg(candidate + l * kHidden + unit, og * tanhf(cell));
+                        if (cache) {
+                            float cell = __ldcg(committed + (2 + l) * kHidden + unit);
+                            const float h = ref_lstm_cell(gate, cell);
+                            __stcg(candidate + (2 + l) * kHidden + unit, cell);
+                            __stcg(candidate + l * kHidden + unit, h);
+                        } else {
+                            const float ig = 1.0f / (1.0f + expf(-gate[0]));
+                            const float fg = 1.0f / (1.0f + expf(-gate[1]));
+                            const float gg = tanhf(gate[2]);
+                            const float og = 1.0f / (1.0f + expf(-gate[3]));
+                            const float cell = fg * __ldcg(committed + (2 + l) * kHidden + unit) + ig * gg;
+                            __stcg(candidate + (2 + l) * kHidden + unit, cell);
+                            __stcg(candidate + l * kHidden + unit, og * tanhf(cell));
+                        }
                     }
                 }
                 ok = bar.sync();
@@ -365,7 +451,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) tdt_greedy_kernel(const DecPar
         slot = next_slot;
     }
 
-    if (cta == 0 && tid < p.utts) p.counts[tid] = min(s_count[tid], p.max_tokens);
+    if (cta == 0 && tid < p.utts && in_window(p, tid)) p.counts[tid] = min(s_count[tid], p.max_tokens);
     if (!ok && cta == 0 && tid == 0 && p.status != nullptr) atomicExch(p.status, 2);
 }
 
@@ -1006,7 +1092,7 @@ using PredShape = FragShape<20, 1, 1, 5, 5>;   // 40 rows x 640
 using JointShape = FragShape<10, 2, 2, 5, 9>;  // 72 rows (65 used) x 640
 using Lstm1Shape = FragShape<4, 5, 10, 4, 20>; // second LSTM layer: 160 gate rows x 1280 ([h of layer 0 | own h])
 
-struct ClLayout { size_t base, lstm, pred, joint, xtab, lstm1, total; };
+struct ClLayout { size_t base, lstm, pred, joint, xtab, lstm1, cache, total; };
 __host__ __device__ inline ClLayout cl_layout(int utts) {
     ClLayout l;
     const size_t a = dec_layout(utts).total, b = xch_layout(utts).total;
@@ -1017,6 +1103,7 @@ __host__ __device__ inline ClLayout cl_layout(int utts) {
     l.joint = off; off += static_cast<size_t>(kCl) * JointShape::kPerCta * 16;
     l.xtab = off; off += static_cast<size_t>(kTokenOutputs) * kGates * 4;
     l.lstm1 = off; off += static_cast<size_t>(kCl) * Lstm1Shape::kPerCta * 16;
+    l.cache = off; off += 256;        // max |w| of the three tensors of the INT8 cache
     l.total = off;
     return l;
 }
@@ -1025,8 +1112,11 @@ enum : int { CLPACK_LSTM = 0, CLPACK_PRED = 1, CLPACK_JOINT = 2, CLPACK_LSTM_IH_
 
 // dst[cta][kg][kp][tile][lane] = the B fragments (b0, b1) of k-steps 2*kp and 2*kp+1 of row tile
 // `tile`: lane (g = lane / 4, t = lane % 4) holds W[row g][k0 + 2t, +1, +8, +9] per k-step.
+// With `absmax` (long-request numerics) the values stored are the INT8 codes of the tensor,
+// scale index `scale_first` for w and `scale_second` for w_second.
 template <typename Shape, int Mode>
-__global__ void tdt_pack_kernel(uint4* dst, const __half* w, const __half* w_second) {
+__global__ void tdt_pack_kernel(uint4* dst, const __half* w, const __half* w_second, const float* absmax,
+                                int scale_first, int scale_second) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= kCl * Shape::kPerCta) return;
     int rest = idx;
@@ -1045,10 +1135,16 @@ __global__ void tdt_pack_kernel(uint4* dst, const __half* w, const __half* w_sec
     auto pair = [&](int k) -> unsigned {
         if (row < 0) return 0u;
         // CLPACK_LSTM_IH_HH: columns 0..639 from w (input weights), 640..1279 from w_second (recurrent)
-        const __half* src = (Mode == CLPACK_LSTM_IH_HH && k >= kHidden)
-            ? w_second + static_cast<size_t>(row) * kHidden + (k - kHidden)
-            : w + static_cast<size_t>(row) * kHidden + k;
-        return static_cast<unsigned>(__half_as_ushort(src[0])) | (static_cast<unsigned>(__half_as_ushort(src[1])) << 16);
+        const bool second = Mode == CLPACK_LSTM_IH_HH && k >= kHidden;
+        const __half* src = second ? w_second + static_cast<size_t>(row) * kHidden + (k - kHidden)
+                                   : w + static_cast<size_t>(row) * kHidden + k;
+        __half v0 = src[0], v1 = src[1];
+        if (absmax != nullptr) {
+            const float scale = cache_scale(absmax, second ? scale_second : scale_first);
+            v0 = cache_code(v0, scale);
+            v1 = cache_code(v1, scale);
+        }
+        return static_cast<unsigned>(__half_as_ushort(v0)) | (static_cast<unsigned>(__half_as_ushort(v1)) << 16);
     };
     dst[idx] = make_uint4(pair(k0 + 2 * t), pair(k0 + 2 * t + 8), pair(k0 + 16 + 2 * t), pair(k0 + 16 + 2 * t + 8));
 }
@@ -1079,6 +1175,8 @@ struct CSmemT {
     float xg[kMaxUtt][kClUnits * 4];      // W_ih . embedding[last token] for this CTA's gate rows
     float cstate[kMaxUtt][kClUnits];
     alignas(16) __half stage_h[16][kClUnits];     // this CTA's slice of h (hi / lo) on its way out
+    alignas(16) __half stage_q[kMaxUtt][kClUnits];  // long-request numerics: its INT8 codes rne(h * 127)
+    float cache_mul[3];                           // scale / 127 of w_hh[0], w_hh[1], w_ih[1]
     alignas(16) float stage_p[kMaxUtt][kClUnits]; // this CTA's slice of the prediction vector
     float lstm_bias[kClUnits][4];
     float pred_bias[kClUnits];
@@ -1152,8 +1250,9 @@ __device__ __forceinline__ void frag_prefetch(const uint4* w, FragRing<Shape, De
             if (frag_live<Shape>(warp, j)) ring.buf[s][j] = frag_fetch<Shape, Global>(w, warp, lane, s, j);
 }
 
-// `Loaded` = prologue stages already issued by frag_prefetch.
-template <typename Shape, bool Global, int Depth, int Loaded>
+// `Loaded` = prologue stages already issued by frag_prefetch.  `HiOnly`: A has 8 rows (one per
+// utterance, no low-order rows), as for the integer codes of the long-request numerics.
+template <typename Shape, bool Global, int Depth, int Loaded, bool HiOnly = false>
 __device__ __forceinline__ void frag_compute(const uint4* w, const __half* a, float* part,
                                              FragRing<Shape, Depth>& ring, int warp, int lane) {
     constexpr int KP = Shape::KP, NT = Shape::NT;
@@ -1165,7 +1264,8 @@ __device__ __forceinline__ void frag_compute(const uint4* w, const __half* a, fl
     for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[j][e] = 0.0f;
-    const __half* arow = a + (lane % 16) * kAct + (lane / 16) * 8 + kg * KP * 32;
+    const __half* arow = HiOnly ? a + (lane % 8) * kAct + ((lane / 8) % 2) * 8 + kg * KP * 32
+                                : a + (lane % 16) * kAct + (lane / 16) * 8 + kg * KP * 32;
 #pragma unroll
     for (int kp = 0; kp < KP; ++kp) {
         if (kp + Depth < KP) {
@@ -1175,8 +1275,16 @@ __device__ __forceinline__ void frag_compute(const uint4* w, const __half* a, fl
                     ring.buf[(kp + Depth) % (Depth + 1)][j] = frag_fetch<Shape, Global>(w, warp, lane, kp + Depth, j);
         }
         unsigned a0[4], a1[4];
-        dec_ldmatrix_x4(a0, arow + kp * 32);
-        dec_ldmatrix_x4(a1, arow + kp * 32 + 16);
+        if constexpr (HiOnly) {
+            unsigned lo[2], hi[2];       // rows 0-7: columns k .. k+7 and k+8 .. k+15
+            dec_ldmatrix_x2(lo, arow + kp * 32);
+            dec_ldmatrix_x2(hi, arow + kp * 32 + 16);
+            a0[0] = lo[0]; a0[1] = 0u; a0[2] = lo[1]; a0[3] = 0u;
+            a1[0] = hi[0]; a1[1] = 0u; a1[2] = hi[1]; a1[3] = 0u;
+        } else {
+            dec_ldmatrix_x4(a0, arow + kp * 32);
+            dec_ldmatrix_x4(a1, arow + kp * 32 + 16);
+        }
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
             if (!frag_live<Shape>(warp, j)) continue;
@@ -1190,7 +1298,8 @@ __device__ __forceinline__ void frag_compute(const uint4* w, const __half* a, fl
         if (!frag_live<Shape>(warp, j)) continue;
         float* dst = part + (kg * 8 + g) * Shape::kPitch + (ng * NT + j) * 8 + 2 * t;
         // hi row + lo row of utterance g
-        *reinterpret_cast<float2*>(dst) = make_float2(acc[j][0] + acc[j][2], acc[j][1] + acc[j][3]);
+        *reinterpret_cast<float2*>(dst) = HiOnly ? make_float2(acc[j][0], acc[j][1])
+                                                 : make_float2(acc[j][0] + acc[j][2], acc[j][1] + acc[j][3]);
     }
 }
 
@@ -1200,7 +1309,11 @@ __device__ __forceinline__ void frag_compute(const uint4* w, const __half* a, fl
 #define CL_STAMP(i) do { } while (0)
 #endif
 
-template <int Layers>
+// `Cache` = long-request numerics: recurrent weights (and layer 1's input weights) arrive as INT8
+// codes in the packed copies, `xtab` is rounded to fp16, and every hidden state also travels as
+// codes: rows 0-7 of ah / ah1 hold the committed codes (the A operand of the recurrent GEMMs),
+// rows 8-15 receive the fresh codes from the cluster.
+template <int Layers, bool Cache>
 __global__ void __launch_bounds__(kClThreads, 1)
 tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* packed_pred,
                    const uint4* packed_joint, const float* xtab, const uint4* packed_lstm1) {
@@ -1251,6 +1364,7 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
         sm.lstm_bias[slot][gt] = p.b_ih[0][row] + p.b_hh[0][row];
     }
     if (tid < kClUnits) sm.pred_bias[tid] = p.b_pred[r * kClUnits + tid];
+    if (tid < 3) sm.cache_mul[tid] = (Cache && (tid == 0 || Layers == 2)) ? cache_mul(cache_scale(p.cache_absmax, tid)) : 0.0f;
     if (tid < JointShape::kRows) {
         const int row = r * kClJoint + tid;
         sm.joint_bias[tid] = (tid < kClJoint && row < kJointRows) ? p.b_joint[row] : 0.0f;
@@ -1258,7 +1372,7 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
     if (tid < kMaxUtt) {
         sm.frame[tid] = 0; sm.symbols[tid] = 0; sm.count[tid] = 0; sm.valid[tid] = 0;
         sm.total_frames[tid] = tid < U ? p.frames[tid] : 0;
-        const bool done = tid >= U || p.frames[tid] <= 0;
+        const bool done = tid >= U || p.frames[tid] <= 0 || !in_window(p, tid);
         sm.done[tid] = done;
         sm.need[tid] = !done;
     }
@@ -1292,6 +1406,59 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
     FragRing<LstmShape, 2> lstm_ring;
     frag_prefetch<LstmShape, true, 2, 0, 1>(wl, lstm_ring, warp, lane);
 
+    // LSTM cell of one (utterance, unit) from its four gate sums; stages h for the exchange
+    auto cell_update = [&](const float (&gsum)[4], float& cstate, int u, int slot) {
+        float h;
+        if constexpr (Cache) {
+            // the reference's approximations: h is rounded to 8 bits next, and a code that flips moves a gate
+            h = ref_lstm_cell(gsum, cstate);
+            sm.stage_q[u][slot] = __int2half_rn(quantize_i8(h * 127.0f));
+        } else {
+            const float cell = fast_sigmoid(gsum[1]) * cstate + fast_sigmoid(gsum[0]) * fast_tanh(gsum[2]);
+            cstate = cell;
+            h = fast_sigmoid(gsum[3]) * fast_tanh(cell);
+        }
+        const __half hi = __float2half_rn(h);
+        sm.stage_h[u][slot] = hi;
+        sm.stage_h[u + 8][slot] = __float2half_rn(h - __half2float(hi));
+    };
+    // this CTA's staged slice of a hidden state -> `fresh` (hi / lo rows) of every CTA, and with
+    // Cache its codes -> rows 8-15 of `committed`; all bytes are credited to `bar_local` there
+    auto send_hidden = [&](__half (*fresh)[kAct], __half (*committed)[kAct], uint64_t* bar_local) {
+        const uint32_t bar = map_to_cta(smem_u32(bar_local), peer);
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int item = item0 + it * kClUnits;         // 0..79: 16 rows x 5 chunks of 8 units
+            const int row = item / 5, chunk = item % 5;
+            const int u = row % 8;
+            if (u < U && sm.need[u]) {
+                const uint4 v = *reinterpret_cast<const uint4*>(&sm.stage_h[row][chunk * 8]);
+                st_async_v4(map_to_cta(smem_u32(&fresh[row][r * kClUnits + chunk * 8]), peer), v, bar);
+            }
+        }
+        if constexpr (Cache) {
+            const int u = item0 / 5, chunk = item0 % 5;
+            if (u < U && sm.need[u]) {
+                const uint4 v = *reinterpret_cast<const uint4*>(&sm.stage_q[u][chunk * 8]);
+                st_async_v4(map_to_cta(smem_u32(&committed[8 + u][r * kClUnits + chunk * 8]), peer), v, bar);
+            }
+        }
+    };
+    // bytes one stepping utterance contributes to a hidden-state exchange
+    constexpr uint32_t kHiddenTx = 2 * kHidden * 2 + (Cache ? kHidden * 2 : 0);
+    // the threads from `first` on make the fresh state the committed one
+    auto commit_hidden = [&](const __half (*fresh)[kAct], __half (*committed)[kAct], int first) {
+        constexpr int kRows = Cache ? 8 : 16;
+        for (int i = tid - first; i < kRows * kEncChunks; i += kClThreads - first) {
+            const int row = i / kEncChunks, c = i % kEncChunks;
+            const int u = row % 8;
+            if (u < U && sm.need[u]) {
+                const __half* src = Cache ? &committed[8 + row][c * 8] : &fresh[row][c * 8];
+                *reinterpret_cast<uint4*>(&committed[row][c * 8]) = *reinterpret_cast<const uint4*>(src);
+            }
+        }
+    };
+
     unsigned round = 0;
     while (true) {
         const unsigned long long done8 = *reinterpret_cast<const unsigned long long*>(sm.done);
@@ -1304,7 +1471,7 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
 
         if (need8 != 0ull) {
             // ---- LSTM: gates of this CTA's 40 units = table row + h . w_hh^T + bias
-            frag_compute<LstmShape, true, 2, 1>(wl, &sm.ah[0][0], sm.part, lstm_ring, warp, lane);
+            frag_compute<LstmShape, true, 2, 1, Cache>(wl, &sm.ah[0][0], sm.part, lstm_ring, warp, lane);
             cp_async_wait_all();             // table rows / encoder rows requested at the last decision
             __syncthreads();
             CL_STAMP(1);
@@ -1312,54 +1479,55 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                 const int slot = tid % kClUnits, u = tid / kClUnits;
                 if (u < U && sm.need[u]) {
                     const float4 x = *reinterpret_cast<const float4*>(&sm.xg[u][slot * 4]);
-                    float gsum[4] = {sm.lstm_bias[slot][0] + x.x, sm.lstm_bias[slot][1] + x.y,
-                                     sm.lstm_bias[slot][2] + x.z, sm.lstm_bias[slot][3] + x.w};
+                    float gsum[4];
+                    if constexpr (Cache) {
+                        // exact integer dot products; order of decoder.cu:636-637: (recurrent + bias) + table
+                        float rec[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                    for (int kg = 0; kg < LstmShape::KG; ++kg) {
-                        const float4 v = *reinterpret_cast<const float4*>(
-                            &sm.part[(kg * 8 + u) * LstmShape::kPitch + slot * 4]);
-                        gsum[0] += v.x; gsum[1] += v.y; gsum[2] += v.z; gsum[3] += v.w;
+                        for (int kg = 0; kg < LstmShape::KG; ++kg) {
+                            const float4 v = *reinterpret_cast<const float4*>(
+                                &sm.part[(kg * 8 + u) * LstmShape::kPitch + slot * 4]);
+                            rec[0] += v.x; rec[1] += v.y; rec[2] += v.z; rec[3] += v.w;
+                        }
+                        const float mul = sm.cache_mul[0];
+                        gsum[0] = (rec[0] * mul + sm.lstm_bias[slot][0]) + x.x;
+                        gsum[1] = (rec[1] * mul + sm.lstm_bias[slot][1]) + x.y;
+                        gsum[2] = (rec[2] * mul + sm.lstm_bias[slot][2]) + x.z;
+                        gsum[3] = (rec[3] * mul + sm.lstm_bias[slot][3]) + x.w;
+                    } else {
+                        gsum[0] = sm.lstm_bias[slot][0] + x.x; gsum[1] = sm.lstm_bias[slot][1] + x.y;
+                        gsum[2] = sm.lstm_bias[slot][2] + x.z; gsum[3] = sm.lstm_bias[slot][3] + x.w;
+#pragma unroll
+                        for (int kg = 0; kg < LstmShape::KG; ++kg) {
+                            const float4 v = *reinterpret_cast<const float4*>(
+                                &sm.part[(kg * 8 + u) * LstmShape::kPitch + slot * 4]);
+                            gsum[0] += v.x; gsum[1] += v.y; gsum[2] += v.z; gsum[3] += v.w;
+                        }
                     }
-                    const float cell = fast_sigmoid(gsum[1]) * sm.cstate[u][slot] + fast_sigmoid(gsum[0]) * fast_tanh(gsum[2]);
-                    sm.cstate[u][slot] = cell;
-                    const float h = fast_sigmoid(gsum[3]) * fast_tanh(cell);
-                    const __half hi = __float2half_rn(h);
-                    sm.stage_h[u][slot] = hi;
-                    sm.stage_h[u + 8][slot] = __float2half_rn(h - __half2float(hi));
+                    cell_update(gsum, sm.cstate[u][slot], u, slot);
                 }
             }
-            if (tid == 0) mbar_arrive_expect_tx(&sm.hbar, static_cast<uint32_t>(needs) * 2 * kHidden * 2);
+            if (tid == 0) mbar_arrive_expect_tx(&sm.hbar, static_cast<uint32_t>(needs) * kHiddenTx);
             __syncthreads();
             CL_STAMP(2);
-            {   // h slice (hi and lo rows, 5 chunks of 8 units each) -> every CTA's hx
-                const uint32_t bar = map_to_cta(smem_u32(&sm.hbar), peer);
-#pragma unroll
-                for (int it = 0; it < 2; ++it) {
-                    const int item = item0 + it * kClUnits;         // 0..79
-                    const int row = item / 5, chunk = item % 5;
-                    const int u = row % 8;
-                    if (u < U && sm.need[u]) {
-                        const uint4 v = *reinterpret_cast<const uint4*>(&sm.stage_h[row][chunk * 8]);
-                        st_async_v4(map_to_cta(smem_u32(&sm.hx[row][r * kClUnits + chunk * 8]), peer), v, bar);
-                    }
-                }
-            }
+            send_hidden(sm.hx, sm.ah, &sm.hbar);     // h slice -> every CTA's hx (and codes)
             // the prediction weights of this warp are requested while the hidden state travels
             FragRing<PredShape, 1> pred_ring;
             if constexpr (Layers == 1) frag_prefetch<PredShape, true, 1, 0, 1>(wp, pred_ring, warp, lane);
             mbar_wait_bounded(&sm.hbar, hphase, abort_flag);
             hphase ^= 1u;
             CL_STAMP(3);
-            const __half* top_fresh = &sm.hx[0][0];       // fresh hidden state of the top layer
-            __half* top_committed = &sm.ah[0][0];
+            const __half (*top_fresh)[kAct] = sm.hx;      // fresh hidden state of the top layer
+            __half (*top_committed)[kAct] = sm.ah;
             if constexpr (Layers == 2) {
                 // ---- second LSTM layer: gates = [fresh h of layer 0 | own h] . [w_ih | w_hh]^T + bias
                 {
                     FragRing<Lstm1Shape, 2> ring1;
                     const int kg = warp / Lstm1Shape::NG;
-                    // k-groups 0, 1 read the 640 columns of hx, groups 2, 3 those of ah1
-                    const __half* a = kg < 2 ? &sm.hx[0][0] : &sm.second.ah1[0][0] - kHidden;
-                    frag_compute<Lstm1Shape, true, 2, 0>(wl1, a, sm.part, ring1, warp, lane);
+                    // k-groups 0, 1 read the 640 columns of hx (Cache: the fresh codes of layer 0 in
+                    // rows 8-15 of ah), groups 2, 3 those of ah1
+                    const __half* a = kg < 2 ? (Cache ? &sm.ah[8][0] : &sm.hx[0][0]) : &sm.second.ah1[0][0] - kHidden;
+                    frag_compute<Lstm1Shape, true, 2, 0, Cache>(wl1, a, sm.part, ring1, warp, lane);
                 }
                 __syncthreads();
                 if (tid < kMaxUtt * kClUnits) {
@@ -1367,52 +1535,45 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                     if (u < U && sm.need[u]) {
                         float gsum[4] = {sm.second.lstm_bias1[slot][0], sm.second.lstm_bias1[slot][1],
                                          sm.second.lstm_bias1[slot][2], sm.second.lstm_bias1[slot][3]};
+                        if constexpr (Cache) {
+                            // k-groups 0, 1: input codes (scale of w_ih[1]); 2, 3: recurrent codes;
+                            // decoder.cu:655-663 adds the bias last
+                            float in[4] = {0.0f, 0.0f, 0.0f, 0.0f}, rec[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                        for (int kg = 0; kg < Lstm1Shape::KG; ++kg) {
-                            const float4 v = *reinterpret_cast<const float4*>(
-                                &sm.part[(kg * 8 + u) * Lstm1Shape::kPitch + slot * 4]);
-                            gsum[0] += v.x; gsum[1] += v.y; gsum[2] += v.z; gsum[3] += v.w;
+                            for (int kg = 0; kg < Lstm1Shape::KG; ++kg) {
+                                const float4 v = *reinterpret_cast<const float4*>(
+                                    &sm.part[(kg * 8 + u) * Lstm1Shape::kPitch + slot * 4]);
+                                float (&dst)[4] = kg < 2 ? in : rec;
+                                dst[0] += v.x; dst[1] += v.y; dst[2] += v.z; dst[3] += v.w;
+                            }
+#pragma unroll
+                            for (int g4 = 0; g4 < 4; ++g4)
+                                gsum[g4] = (rec[g4] * sm.cache_mul[1] + in[g4] * sm.cache_mul[2]) + gsum[g4];
+                        } else {
+#pragma unroll
+                            for (int kg = 0; kg < Lstm1Shape::KG; ++kg) {
+                                const float4 v = *reinterpret_cast<const float4*>(
+                                    &sm.part[(kg * 8 + u) * Lstm1Shape::kPitch + slot * 4]);
+                                gsum[0] += v.x; gsum[1] += v.y; gsum[2] += v.z; gsum[3] += v.w;
+                            }
                         }
-                        const float cell = fast_sigmoid(gsum[1]) * sm.second.cstate1[u][slot] +
-                                           fast_sigmoid(gsum[0]) * fast_tanh(gsum[2]);
-                        sm.second.cstate1[u][slot] = cell;
-                        const float h = fast_sigmoid(gsum[3]) * fast_tanh(cell);
-                        const __half hi = __float2half_rn(h);
-                        sm.stage_h[u][slot] = hi;
-                        sm.stage_h[u + 8][slot] = __float2half_rn(h - __half2float(hi));
+                        cell_update(gsum, sm.second.cstate1[u][slot], u, slot);
                     }
                 } else {
                     // meanwhile: commit the fresh state of layer 0
-                    for (int i = tid - kMaxUtt * kClUnits; i < 16 * kEncChunks; i += kClThreads - kMaxUtt * kClUnits) {
-                        const int row = i / kEncChunks, c = i % kEncChunks;
-                        const int u = row % 8;
-                        if (u < U && sm.need[u])
-                            *reinterpret_cast<uint4*>(&sm.ah[row][c * 8]) = *reinterpret_cast<const uint4*>(&sm.hx[row][c * 8]);
-                    }
+                    commit_hidden(sm.hx, sm.ah, kMaxUtt * kClUnits);
                 }
-                if (tid == 0) mbar_arrive_expect_tx(&sm.second.hbar1, static_cast<uint32_t>(needs) * 2 * kHidden * 2);
+                if (tid == 0) mbar_arrive_expect_tx(&sm.second.hbar1, static_cast<uint32_t>(needs) * kHiddenTx);
                 __syncthreads();
-                {
-                    const uint32_t bar = map_to_cta(smem_u32(&sm.second.hbar1), peer);
-#pragma unroll
-                    for (int it = 0; it < 2; ++it) {
-                        const int item = item0 + it * kClUnits;
-                        const int row = item / 5, chunk = item % 5;
-                        const int u = row % 8;
-                        if (u < U && sm.need[u]) {
-                            const uint4 v = *reinterpret_cast<const uint4*>(&sm.stage_h[row][chunk * 8]);
-                            st_async_v4(map_to_cta(smem_u32(&sm.second.hx1[row][r * kClUnits + chunk * 8]), peer), v, bar);
-                        }
-                    }
-                }
+                send_hidden(sm.second.hx1, sm.second.ah1, &sm.second.hbar1);
                 frag_prefetch<PredShape, true, 1, 0, 1>(wp, pred_ring, warp, lane);
                 mbar_wait_bounded(&sm.second.hbar1, h1phase, abort_flag);
                 h1phase ^= 1u;
-                top_fresh = &sm.second.hx1[0][0];
-                top_committed = &sm.second.ah1[0][0];
+                top_fresh = sm.second.hx1;
+                top_committed = sm.second.ah1;
             }
             // ---- prediction projection of the new state (A operand: the fresh rows of the top layer)
-            frag_compute<PredShape, true, 1, 1>(wp, top_fresh, sm.part, pred_ring, warp, lane);
+            frag_compute<PredShape, true, 1, 1>(wp, &top_fresh[0][0], sm.part, pred_ring, warp, lane);
             __syncthreads();
             CL_STAMP(4);
             if (tid < kMaxUtt * kClUnits) {
@@ -1425,13 +1586,7 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                 }
             } else {
                 // meanwhile the other threads commit the fresh hidden state for the next LSTM step
-                for (int i = tid - kMaxUtt * kClUnits; i < 16 * kEncChunks; i += kClThreads - kMaxUtt * kClUnits) {
-                    const int row = i / kEncChunks, c = i % kEncChunks;
-                    const int u = row % 8;
-                    if (u < U && sm.need[u])
-                        *reinterpret_cast<uint4*>(top_committed + row * kAct + c * 8) =
-                            *reinterpret_cast<const uint4*>(top_fresh + row * kAct + c * 8);
-                }
+                commit_hidden(top_fresh, top_committed, kMaxUtt * kClUnits);
             }
             if (tid == 0) mbar_arrive_expect_tx(&sm.pbar, static_cast<uint32_t>(needs) * kHidden * 4);
             __syncthreads();
@@ -1600,7 +1755,7 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
         for (int i = 0; i < 16; ++i)
             reinterpret_cast<volatile long long*>(p.workspace + xch_layout(U).abort)[2 + i] = sm.prof[i];
 #endif
-    if (r == 0 && tid < U) p.counts[tid] = min(sm.count[tid], p.max_tokens);
+    if (r == 0 && tid < U && in_window(p, tid)) p.counts[tid] = min(sm.count[tid], p.max_tokens);
     if (r == 0 && tid == 0) reinterpret_cast<volatile int*>(p.workspace + xch_layout(U).abort)[2] = static_cast<int>(round);
     if (sm.abort != 0 && tid == 0 && p.status != nullptr) atomicExch(p.status, 2);
 }
@@ -1634,10 +1789,67 @@ extern "C" long long pk100_tdt_workspace_bytes(int utterances) {
     return static_cast<long long>(cl_layout(utterances).total);
 }
 
-extern "C" int pk100_tdt_decode_barrier(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+namespace {
+
+// xtab[token][gate row] = embedding[token] . w_ih[0][gate row] (fp32, no bias) by one tensor-core
+// GEMM; `round_fp16`: entries rounded to fp16 precision, as the reference's long-request kernel reads
+// them from an fp16 table that its own tensor-core linear kernel wrote (src/cuda/decoder.rs:355-383)
+__global__ void tdt_round_table_kernel(float* table, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) table[i] = __half2float(__float2half_rn(table[i]));
+}
+
+int build_input_table(void* stream_v, const pk100_decoder_weights* w, float* xtab, int* status, bool round_fp16) {
+    pk100_gemm_args g{};
+    g.kind = PK100_KIND_F16;
+    g.epilogue = PK100_EPI_LINEAR;
+    g.m = kTokenOutputs; g.n = kGates; g.k = kHidden;
+    g.a = w->embedding; g.lda = kHidden;
+    g.b = w->w_ih[0]; g.ldb = kHidden;
+    g.row_scale = 1.0f;
+    g.alpha = 1.0f;
+    g.out = xtab; g.ld_out = kGates;
+    g.out_type = PK100_OUT_F32;
+    g.out_scale = 1.0f;
+    g.status = status;
+    const int grc = pk100_gemm(stream_v, &g);
+    if (grc != PK100_OK) return grc;
+    if (round_fp16) {
+        const int n = kTokenOutputs * kGates;
+        tdt_round_table_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream_v)>>>(xtab, n);
+        pk100_count_launch();
+        const cudaError_t err = cudaGetLastError();
+        if (err != cudaSuccess) return static_cast<int>(err);
+    }
+    return PK100_OK;
+}
+
+// max |w| of w_hh[0], w_hh[1], w_ih[1] -> three floats at cl_layout().cache of the workspace
+// (the per-tensor scales of the INT8 cache are derived inside every request, decoder.cu:517-555)
+int launch_cache_absmax(cudaStream_t stream, const pk100_decoder_weights* w, uint8_t* ws, int utterances,
+                        const float** out) {
+    unsigned* slot = reinterpret_cast<unsigned*>(ws + cl_layout(utterances).cache);
+    cudaError_t err = cudaMemsetAsync(slot, 0, 16, stream);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    const int n = kGates * kHidden;
+    tdt_absmax_kernel<<<160, 256, 0, stream>>>(static_cast<const __half*>(w->w_hh[0]), n, slot);
+    pk100_count_launch();
+    if (w->layers == 2) {
+        tdt_absmax_kernel<<<160, 256, 0, stream>>>(static_cast<const __half*>(w->w_hh[1]), n, slot + 1);
+        tdt_absmax_kernel<<<160, 256, 0, stream>>>(static_cast<const __half*>(w->w_ih[1]), n, slot + 2);
+        pk100_count_launch();
+        pk100_count_launch();
+    }
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return static_cast<int>(err);
+    *out = reinterpret_cast<const float*>(slot);
+    return PK100_OK;
+}
+
+int decode_barrier(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
                                 int utterances, int seg_stride, const int* frames, void* workspace,
                                 int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
-                                int* status) {
+                                int* status, bool cache, int frames_lo = INT_MIN, int frames_hi = INT_MAX) {
     const int rc = check_weights(w);
     if (rc != PK100_OK) return rc;
     if (!enc_proj || !frames || !workspace || !tokens || !counts) return PK100_ERR_NULL;
@@ -1680,6 +1892,16 @@ extern "C" int pk100_tdt_decode_barrier(void* stream_v, const pk100_decoder_weig
     p.counts = counts;
     p.max_tokens = max_tokens;
     p.status = status;
+    p.frames_lo = frames_lo;
+    p.frames_hi = frames_hi;
+    if (cache) {
+        const int crc = launch_cache_absmax(stream, w, p.workspace, utterances, &p.cache_absmax);
+        if (crc != PK100_OK) return crc;
+        float* xtab = reinterpret_cast<float*>(p.workspace + cl_layout(utterances).xtab);
+        const int trc = build_input_table(stream_v, w, xtab, status, true);
+        if (trc != PK100_OK) return trc;
+        p.input_table = xtab;
+    }
 
     // state, decisions and the barrier words start from zero on every call
     err = cudaMemsetAsync(workspace, 0, dec_layout(utterances).total, stream);
@@ -1695,6 +1917,24 @@ extern "C" int pk100_tdt_decode_barrier(void* stream_v, const pk100_decoder_weig
     }
     pk100_count_launch();
     return PK100_OK;
+}
+
+}  // namespace
+
+extern "C" int pk100_tdt_decode_barrier(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+                                        int utterances, int seg_stride, const int* frames, void* workspace,
+                                        int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                                        int* status) {
+    return decode_barrier(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace, tokens, durations,
+                          counts, max_tokens, status, false);
+}
+
+extern "C" int pk100_tdt_decode_long_barrier(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+                                             int utterances, int seg_stride, const int* frames, void* workspace,
+                                             int32_t* tokens, int32_t* durations, int32_t* counts,
+                                             int max_tokens, int* status) {
+    return decode_barrier(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace, tokens, durations,
+                          counts, max_tokens, status, true);
 }
 
 // ---------------------------------------------------------------------------
@@ -1798,6 +2038,8 @@ extern "C" int pk100_tdt_decode_exchange(void* stream_v, const pk100_decoder_wei
     p.counts = counts;
     p.max_tokens = max_tokens;
     p.status = status;
+    p.frames_lo = INT_MIN;
+    p.frames_hi = INT_MAX;
     // tags start at 1, so a cleared workspace holds no valid entry
     err = cudaMemsetAsync(workspace, 0, xch_layout(utterances).total, stream);
     if (err != cudaSuccess) return static_cast<int>(err);
@@ -1817,7 +2059,7 @@ namespace {
 
 // Can this device run a 16-CTA cluster of the cluster decoder?  Asked once per device and
 // kernel variant (one or two LSTM layers).
-template <int Layers>
+template <int Layers, bool Cache>
 bool cluster_decoder_available() {
     static int cached[64] = {0};      // 0 = unknown, 1 = yes, 2 = no
     int dev = 0;
@@ -1828,9 +2070,9 @@ bool cluster_decoder_available() {
         int max_smem = 0;
         cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
         if (sizeof(CSmemT<Layers>) > static_cast<size_t>(max_smem)) break;
-        if (cudaFuncSetAttribute(tdt_cluster_kernel<Layers>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(tdt_cluster_kernel<Layers, Cache>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(sizeof(CSmemT<Layers>))) != cudaSuccess) break;
-        if (cudaFuncSetAttribute(tdt_cluster_kernel<Layers>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
+        if (cudaFuncSetAttribute(tdt_cluster_kernel<Layers, Cache>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
             cudaSuccess) break;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(kCl);
@@ -1844,7 +2086,7 @@ bool cluster_decoder_available() {
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, tdt_cluster_kernel<Layers>, &cfg) != cudaSuccess) break;
+        if (cudaOccupancyMaxActiveClusters(&clusters, tdt_cluster_kernel<Layers, Cache>, &cfg) != cudaSuccess) break;
         ok = clusters >= 1;
     } while (false);
     cudaGetLastError();
@@ -1852,11 +2094,13 @@ bool cluster_decoder_available() {
     return ok;
 }
 
-bool cluster_decoder_available_for(int layers) {
-    return layers == 1 ? cluster_decoder_available<1>() : (layers == 2 ? cluster_decoder_available<2>() : false);
+bool cluster_decoder_available_for(int layers, bool cache) {
+    if (layers == 1) return cache ? cluster_decoder_available<1, true>() : cluster_decoder_available<1, false>();
+    if (layers == 2) return cache ? cluster_decoder_available<2, true>() : cluster_decoder_available<2, false>();
+    return false;
 }
 
-template <int Layers>
+template <int Layers, bool Cache>
 cudaError_t launch_cluster_kernel(cudaStream_t stream, const DecParams& p, const uint4* lstm, const uint4* pred,
                                   const uint4* joint, const float* xtab, const uint4* lstm1) {
     cudaLaunchConfig_t cfg{};
@@ -1871,66 +2115,59 @@ cudaError_t launch_cluster_kernel(cudaStream_t stream, const DecParams& p, const
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, tdt_cluster_kernel<Layers>, p, lstm, pred, joint, xtab, lstm1);
+    return cudaLaunchKernelEx(&cfg, tdt_cluster_kernel<Layers, Cache>, p, lstm, pred, joint, xtab, lstm1);
 }
 
 }  // namespace
 
-extern "C" int pk100_tdt_decode_cluster(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+namespace {
+int decode_cluster(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
                                         int utterances, int seg_stride, const int* frames, void* workspace,
                                         int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
-                                        int* status) {
+                                        int* status, bool cache, int frames_lo = INT_MIN, int frames_hi = INT_MAX) {
     const int rc = check_weights(w);
     if (rc != PK100_OK) return rc;
     if (!enc_proj || !frames || !workspace || !tokens || !counts) return PK100_ERR_NULL;
     if (utterances == 0) return PK100_OK;
     if (utterances < 0 || seg_stride <= 0 || max_tokens <= 0) return PK100_ERR_SHAPE;
     if (utterances > kMaxUtt) return PK100_ERR_LIMIT;
-    if (!cluster_decoder_available_for(w->layers)) return PK100_ERR_UNSUPPORTED;
+    if (!cluster_decoder_available_for(w->layers, cache)) return PK100_ERR_UNSUPPORTED;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const ClLayout lay = cl_layout(utterances);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
+    const float* absmax = nullptr;
+    if (cache) {
+        const int crc = launch_cache_absmax(stream, w, ws, utterances, &absmax);
+        if (crc != PK100_OK) return crc;
+    }
     uint4* packed_lstm = reinterpret_cast<uint4*>(ws + lay.lstm);
     uint4* packed_pred = reinterpret_cast<uint4*>(ws + lay.pred);
     uint4* packed_joint = reinterpret_cast<uint4*>(ws + lay.joint);
     uint4* packed_lstm1 = reinterpret_cast<uint4*>(ws + lay.lstm1);
     float* xtab = reinterpret_cast<float*>(ws + lay.xtab);
-    const __half* w_ih = static_cast<const __half*>(w->w_ih[0]);
     const __half* w_hh = static_cast<const __half*>(w->w_hh[0]);
     const __half* w_pred = static_cast<const __half*>(w->w_pred);
     const __half* w_joint = static_cast<const __half*>(w->w_joint);
     // weights -> fragment order (they may change between calls, so this is done every call)
     tdt_pack_kernel<LstmShape, CLPACK_LSTM><<<(kCl * LstmShape::kPerCta + 255) / 256, 256, 0, stream>>>(
-        packed_lstm, w_hh, nullptr);
+        packed_lstm, w_hh, nullptr, absmax, 0, 0);
     tdt_pack_kernel<PredShape, CLPACK_PRED><<<(kCl * PredShape::kPerCta + 255) / 256, 256, 0, stream>>>(
-        packed_pred, w_pred, nullptr);
+        packed_pred, w_pred, nullptr, nullptr, 0, 0);
     tdt_pack_kernel<JointShape, CLPACK_JOINT><<<(kCl * JointShape::kPerCta + 255) / 256, 256, 0, stream>>>(
-        packed_joint, w_joint, nullptr);
+        packed_joint, w_joint, nullptr, nullptr, 0, 0);
     pk100_count_launch();
     pk100_count_launch();
     pk100_count_launch();
     if (w->layers == 2) {
         tdt_pack_kernel<Lstm1Shape, CLPACK_LSTM_IH_HH><<<(kCl * Lstm1Shape::kPerCta + 255) / 256, 256, 0, stream>>>(
-            packed_lstm1, static_cast<const __half*>(w->w_ih[1]), static_cast<const __half*>(w->w_hh[1]));
+            packed_lstm1, static_cast<const __half*>(w->w_ih[1]), static_cast<const __half*>(w->w_hh[1]), absmax, 2, 1);
         pk100_count_launch();
     }
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return static_cast<int>(err);
-    {   // input table: xtab[token][gate row] = embedding[token] . w_ih[gate row] (fp32, no bias)
-        pk100_gemm_args g{};
-        g.kind = PK100_KIND_F16;
-        g.epilogue = PK100_EPI_LINEAR;
-        g.m = kTokenOutputs; g.n = kGates; g.k = kHidden;
-        g.a = w->embedding; g.lda = kHidden;
-        g.b = w_ih; g.ldb = kHidden;
-        g.row_scale = 1.0f;
-        g.alpha = 1.0f;
-        g.out = xtab; g.ld_out = kGates;
-        g.out_type = PK100_OUT_F32;
-        g.out_scale = 1.0f;
-        g.status = status;
-        const int grc = pk100_gemm(stream_v, &g);
-        if (grc != PK100_OK) return grc;
+    {
+        const int trc = build_input_table(stream_v, w, xtab, status, cache);
+        if (trc != PK100_OK) return trc;
     }
 
     DecParams p{};
@@ -1956,16 +2193,68 @@ extern "C" int pk100_tdt_decode_cluster(void* stream_v, const pk100_decoder_weig
     p.counts = counts;
     p.max_tokens = max_tokens;
     p.status = status;
+    p.cache_absmax = absmax;
+    p.frames_lo = frames_lo;
+    p.frames_hi = frames_hi;
 
-    err = w->layers == 1
-        ? launch_cluster_kernel<1>(stream, p, packed_lstm, packed_pred, packed_joint, xtab, packed_lstm1)
-        : launch_cluster_kernel<2>(stream, p, packed_lstm, packed_pred, packed_joint, xtab, packed_lstm1);
+    if (w->layers == 1)
+        err = cache ? launch_cluster_kernel<1, true>(stream, p, packed_lstm, packed_pred, packed_joint, xtab, packed_lstm1)
+                    : launch_cluster_kernel<1, false>(stream, p, packed_lstm, packed_pred, packed_joint, xtab, packed_lstm1);
+    else
+        err = cache ? launch_cluster_kernel<2, true>(stream, p, packed_lstm, packed_pred, packed_joint, xtab, packed_lstm1)
+                    : launch_cluster_kernel<2, false>(stream, p, packed_lstm, packed_pred, packed_joint, xtab, packed_lstm1);
     if (err != cudaSuccess) {
         cudaGetLastError();
         return static_cast<int>(err);
     }
     pk100_count_launch();
     return PK100_OK;
+}
+}  // namespace
+
+extern "C" int pk100_tdt_decode_cluster(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+                                        int utterances, int seg_stride, const int* frames, void* workspace,
+                                        int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                                        int* status) {
+    return decode_cluster(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace, tokens, durations,
+                          counts, max_tokens, status, false);
+}
+
+extern "C" int pk100_tdt_decode_long_cluster(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+                                             int utterances, int seg_stride, const int* frames, void* workspace,
+                                             int32_t* tokens, int32_t* durations, int32_t* counts,
+                                             int max_tokens, int* status) {
+    return decode_cluster(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace, tokens, durations,
+                          counts, max_tokens, status, true);
+}
+
+extern "C" int pk100_tdt_decode_long(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+                                     int utterances, int seg_stride, const int* frames, void* workspace,
+                                     int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                                     int* status) {
+    // the cluster kernel where a 16-CTA cluster can be hosted, else the grid-barrier kernel
+    if (w != nullptr && utterances > 0 && utterances <= kMaxUtt && cluster_decoder_available_for(w->layers, true))
+        return pk100_tdt_decode_long_cluster(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace,
+                                             tokens, durations, counts, max_tokens, status);
+    return pk100_tdt_decode_long_barrier(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace, tokens,
+                                         durations, counts, max_tokens, status);
+}
+
+extern "C" int pk100_tdt_decode_auto(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
+                                     int utterances, int seg_stride, const int* frames, void* workspace,
+                                     int32_t* tokens, int32_t* durations, int32_t* counts, int max_tokens,
+                                     int* status) {
+    // the reference's rule per request (src/cuda/decoder.rs:15, :88), here per utterance: two
+    // launches on the same stream, each decoding its own utterances and skipping the others
+    constexpr int kLongRequestFrames = 1024;
+    const bool cluster = w != nullptr && utterances > 0 && utterances <= kMaxUtt &&
+                         cluster_decoder_available_for(w->layers, false) && cluster_decoder_available_for(w->layers, true);
+    auto run = cluster ? decode_cluster : decode_barrier;
+    const int rc = run(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace, tokens, durations, counts,
+                       max_tokens, status, false, INT_MIN, kLongRequestFrames);
+    if (rc != PK100_OK) return rc;
+    return run(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace, tokens, durations, counts,
+               max_tokens, status, true, kLongRequestFrames, INT_MAX);
 }
 
 extern "C" int pk100_tdt_decode(void* stream_v, const pk100_decoder_weights* w, const void* enc_proj,
@@ -1974,7 +2263,7 @@ extern "C" int pk100_tdt_decode(void* stream_v, const pk100_decoder_weights* w, 
                                 int* status) {
     // a device that can host a 16-CTA cluster: the cluster kernel; anything else: the 148-CTA
     // exchange kernel
-    if (w != nullptr && utterances > 0 && utterances <= kMaxUtt && cluster_decoder_available_for(w->layers))
+    if (w != nullptr && utterances > 0 && utterances <= kMaxUtt && cluster_decoder_available_for(w->layers, false))
         return pk100_tdt_decode_cluster(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace, tokens,
                                         durations, counts, max_tokens, status);
     return pk100_tdt_decode_exchange(stream_v, w, enc_proj, utterances, seg_stride, frames, workspace, tokens,

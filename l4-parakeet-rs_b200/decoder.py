@@ -14,6 +14,7 @@ from . import ops
 vp = C.c_void_p
 HIDDEN = 640
 MAX_UTTERANCES = 8
+LONG_REQUEST_FRAMES = 1024      # FP8_MIN_FRAMES, src/cuda/decoder.rs:15
 
 
 class DecoderWeightsC(C.Structure):
@@ -27,7 +28,9 @@ L.lib.pk100_tdt_workspace_bytes.restype = C.c_longlong
 L.lib.pk100_tdt_decode.argtypes = [vp, C.POINTER(DecoderWeightsC), vp, C.c_int, C.c_int, vp, vp, vp, vp,
                                    vp, C.c_int, vp]
 L.lib.pk100_tdt_decode.restype = C.c_int
-for _name in ("pk100_tdt_decode_barrier", "pk100_tdt_decode_cluster", "pk100_tdt_decode_exchange"):
+for _name in ("pk100_tdt_decode_barrier", "pk100_tdt_decode_cluster", "pk100_tdt_decode_exchange",
+              "pk100_tdt_decode_long", "pk100_tdt_decode_long_cluster", "pk100_tdt_decode_long_barrier",
+              "pk100_tdt_decode_auto"):
     getattr(L.lib, _name).argtypes = L.lib.pk100_tdt_decode.argtypes
     getattr(L.lib, _name).restype = C.c_int
 
@@ -72,9 +75,12 @@ class TdtDecoder:
         return ops.gemm(encoded, self.t["w_enc"], kind=L.KIND_F16, out=out, bias=self.t["b_enc"])
 
     def decode(self, enc_proj, utterances, seg_stride, frames, max_tokens, tokens=None, durations=None,
-               counts=None, barrier_kernel=False, kernel=None):
+               counts=None, barrier_kernel=False, kernel=None, lstm_cache="fp16"):
         """frames: int32 CUDA tensor [utterances].  Returns (tokens, durations, counts) CUDA tensors.
-        kernel: None (the library's choice), "cluster", "exchange" or "barrier"."""
+        kernel: None (the library's choice), "cluster", "exchange" or "barrier".
+        lstm_cache: "fp16" = the numerics of the reference's short-request kernel, "int8" = those of
+        its kernel for requests of 1024 frames or more (cluster or barrier kernel), "auto" = the
+        reference's rule per utterance (src/cuda/decoder.rs:88; two launches)."""
         if tokens is None:
             tokens = torch.zeros((utterances, max_tokens), dtype=torch.int32, device=self.device)
         if durations is None:
@@ -83,10 +89,22 @@ class TdtDecoder:
             counts = torch.zeros(utterances, dtype=torch.int32, device=self.device)
         if barrier_kernel:
             kernel = "barrier"
-        fn = getattr(L.lib, "pk100_tdt_decode" + ("_" + kernel if kernel else ""))
+        if lstm_cache == "auto":
+            if kernel is not None:
+                raise ValueError("lstm_cache='auto' chooses its own kernels")
+            name = "pk100_tdt_decode_auto"
+        elif lstm_cache == "int8":
+            if kernel not in (None, "cluster", "barrier"):
+                raise ValueError("the long-request numerics exist in the cluster and barrier kernels")
+            name = "pk100_tdt_decode_long" + ("_" + kernel if kernel else "")
+        elif lstm_cache == "fp16":
+            name = "pk100_tdt_decode" + ("_" + kernel if kernel else "")
+        else:
+            raise ValueError(f"lstm_cache: {lstm_cache!r}")
+        fn = getattr(L.lib, name)
         rc = fn(torch.cuda.current_stream().cuda_stream, C.byref(self.c),
                                     enc_proj.data_ptr(), utterances, seg_stride, frames.data_ptr(),
                                     self.workspace.data_ptr(), tokens.data_ptr(), durations.data_ptr(),
                                     counts.data_ptr(), max_tokens, self.status.data_ptr())
-        L.check(rc, "pk100_tdt_decode")
+        L.check(rc, name)
         return tokens, durations, counts

@@ -60,6 +60,10 @@ SIGNATURES = {
     "pk100_tdt_decode_cluster": None,
     "pk100_tdt_decode_exchange": None,
     "pk100_tdt_decode_static": None,
+    "pk100_tdt_decode_long": None,
+    "pk100_tdt_decode_long_cluster": None,
+    "pk100_tdt_decode_long_barrier": None,
+    "pk100_tdt_decode_auto": None,
     "pk100_artifact_open": None,
     "pk100_artifact_close": None,
     "pk100_artifact_tensor_count": None,

@@ -56,6 +56,8 @@ class PipelineEngine:
         self.mel_dev = torch.zeros((max_utterances, mel_frames, 128), dtype=torch.float32, device=dev)
         self.mel_frames_dev = torch.full((max_utterances,), mel_frames, dtype=torch.int32, device=dev)
         self.out_frames_dev = torch.full((max_utterances,), self.frames_out, dtype=torch.int32, device=dev)
+        self.out_frames_host = torch.full((max_utterances,), self.frames_out, dtype=torch.int32)
+        self.longest_out_frames = self.frames_out      # max(out_frames_host)
         # pinned host staging for the two copies of a request
         self.tokens_host = torch.zeros((max_utterances, self.max_tokens), dtype=torch.int32).pin_memory()
         self.counts_host = torch.zeros(max_utterances, dtype=torch.int32).pin_memory()
@@ -83,6 +85,8 @@ class PipelineEngine:
         of = torch.tensor([sub_mod.output_frames(int(f)) for f in mel_frames_per_utt], dtype=torch.int32)
         self.mel_frames_dev[:len(mf)].copy_(mf)
         self.out_frames_dev[:len(of)].copy_(of)
+        self.out_frames_host[:len(of)].copy_(of)
+        self.longest_out_frames = int(self.out_frames_host.max())
 
     def encode(self, utterances):
         self.sub.run(self.mel_dev[:utterances], self.seg_stride, mel_frames=self.mel_frames_dev,
@@ -104,8 +108,11 @@ class PipelineEngine:
         """Hot path with the inputs already in HBM: subsampling -> encoder -> decode."""
         encoded = self.encode(utterances)
         self.dec.project(encoded, out=self.enc_proj)
+        # the reference switches decoder kernels (and numerics) at 1024 frames per request
+        # (src/cuda/decoder.rs:88); a batch of short utterances needs one launch only
+        cache = "auto" if self.longest_out_frames >= dec_mod.LONG_REQUEST_FRAMES else "fp16"
         self.dec.decode(self.enc_proj, utterances, self.seg_stride, self.out_frames_dev, self.max_tokens,
-                        self.tokens, self.durations, self.counts)
+                        self.tokens, self.durations, self.counts, lstm_cache=cache)
 
     def transcribe_batch(self, mel_host):
         """mel_host: pinned fp32 CPU tensor [U, frames, 128].  Returns a list of int32 numpy

@@ -166,6 +166,26 @@ def tdt_decode(enc_proj, w, frames, sms):
     return tokens[:n].cpu().numpy()
 
 
+def tdt_decode_long(enc_proj, w, frames):
+    """launch_decode (src/cuda/decoder.rs:274-353) for a request of 1024 frames or more: the
+    fp16 input table (launch_input_table, :355-383) and the INT8-cache kernel on a
+    cooperative grid of 160 CTAs x 128 threads (:317-321)."""
+    dev = enc_proj.device
+    table = fp16_linear(w["embedding"][:1024].contiguous(), w["w_ih0"], None, None, 1024, 2560, 640)
+    workspace = torch.zeros(9360 + 16 + 2088, dtype=torch.float32, device=dev)
+    control = torch.zeros(9, dtype=torch.int32, device=dev)
+    tokens = torch.zeros(frames * 10 + 16, dtype=torch.int32, device=dev)
+    count = torch.zeros(1, dtype=torch.int32, device=dev)
+    module("decoder").launch(
+        "pk_sm89_tdt_persistent_fp8_ih", (160,), (128,), 0,
+        [enc_proj, w["embedding"], w["w_ih0"], w["w_hh0"], w["b_ih0"], w["b_hh0"], w["w_ih1"],
+         w["w_hh1"], w["b_ih1"], w["b_hh1"], w["w_pred"], w["b_pred"], w["w_joint"], w["b_joint"],
+         table, workspace, control, tokens, count, frames], cooperative=True)
+    torch.cuda.synchronize()
+    n = int(count.item())
+    return tokens[:n].cpu().numpy()
+
+
 # ---- frontend.cu -----------------------------------------------------------
 
 def frontend_available() -> bool:

@@ -46,6 +46,14 @@ def cases():
     rng = np.random.default_rng(104)
     c["dec"] = dict(w=D.make_decoder_weights(17, layers=2), enc=codec.f16_round(rng.standard_normal((60, 640)) * 0.5),
                     frames=60)
+    rng = np.random.default_rng(106)
+    # a request long enough (>= 1024 frames) for the reference to pick its INT8-cache kernel
+    c["dec_long"] = dict(w=c["dec"]["w"], enc=codec.f16_round(rng.standard_normal((1024, 640)) * 0.5), frames=1024)
+    # the same kernel on 16 short independent requests (the kernel itself has no length limit; only
+    # the host's choice depends on the frame count): many decisions before the first near-tie of each
+    rng = np.random.default_rng(107)
+    c["dec_long_short"] = dict(w=c["dec"]["w"], frames=48,
+                               enc=[codec.f16_round(rng.standard_normal((48, 640)) * 0.5) for _ in range(16)])
     rng = np.random.default_rng(105)
     c["fe"] = dict(x=(rng.standard_normal(1700) * 0.3).astype(np.float32))
     return c
@@ -76,6 +84,13 @@ def main(out_path):
     dwts = {k: (dev(v) if k.startswith("b_") else dev16(v)) for k, v in d["w"].items() if k != "layers"}
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     g["dec_tokens"] = R.tdt_decode(dev16(d["enc"]), dwts, d["frames"], sms).astype(np.int32)
+    dl = c["dec_long"]
+    g["dec_long_tokens"] = R.tdt_decode_long(dev16(dl["enc"]), dwts, dl["frames"]).astype(np.int32)
+    dls = c["dec_long_short"]
+    for i, enc in enumerate(dls["enc"]):
+        g[f"dec_long_short_{i}"] = R.tdt_decode_long(dev16(enc), dwts, dls["frames"]).astype(np.int32)
+    # the same request through the short-request kernel, to show that the two kernels differ
+    g["dec_long_tokens_fp16"] = R.tdt_decode(dev16(dl["enc"]), dwts, dl["frames"], sms).astype(np.int32)
     x = c["fe"]["x"]
     frames, valid = F.frame_counts(x.size)
     w512 = F.center_window(F.hann_window())

@@ -56,6 +56,39 @@ def test_tdt_decoder_tokens():
         assert len(ref) == len(tokens)
 
 
+def test_tdt_decoder_tokens_long_request():
+    """The oracle's INT8-cache path against the kernel the reference launches from 1024 frames."""
+    d = CASES["dec_long"]
+    assert d["frames"] >= D.LONG_REQUEST_FRAMES
+    tokens, _, ambiguous = D.tdt_greedy(d["enc"], d["w"], d["frames"], lstm_cache="auto")
+    n = len(tokens) if ambiguous is None else ambiguous
+    ref = GOLD["dec_long_tokens"]
+    assert n >= 15 and np.array_equal(ref[:n], tokens[:n])
+    # past the first near-tie the two streams may part for a few tokens, then the encoder
+    # frames pull them together again: most positions still agree
+    m = min(len(ref), len(tokens))
+    assert abs(len(ref) - len(tokens)) <= 3 and np.mean(ref[:m] == tokens[:m]) > 0.85
+    # and the long-request kernel is not the short-request kernel
+    m = min(len(ref), len(GOLD["dec_long_tokens_fp16"]))
+    assert not np.array_equal(ref[:m], GOLD["dec_long_tokens_fp16"][:m])
+
+
+def test_tdt_decoder_tokens_long_request_kernel_on_short_requests():
+    """16 independent 48-frame requests through the reference's INT8-cache kernel: every decision
+    before each request's first near-tie must match."""
+    d = CASES["dec_long_short"]
+    compared = 0
+    for i, enc in enumerate(d["enc"]):
+        tokens, _, ambiguous = D.tdt_greedy(enc, d["w"], d["frames"], lstm_cache="int8")
+        n = len(tokens) if ambiguous is None else ambiguous
+        ref = GOLD[f"dec_long_short_{i}"]
+        assert np.array_equal(ref[:n], tokens[:n]), i
+        if ambiguous is None:
+            assert len(ref) == len(tokens), i
+        compared += n
+    assert compared > 250
+
+
 def test_frontend_kernels():
     x = CASES["fe"]["x"]
     frames, valid = F.frame_counts(x.size)
