@@ -209,3 +209,34 @@ def test_auto_applies_the_frame_rule_per_utterance(pk, cuda):
     # the two numerics are different functions: on 1100 frames of noise they part ways
     n = min(int(short[2][0]), int(long_[2][0]))
     assert not np.array_equal(short[0][0][:n], long_[0][0][:n])
+
+
+def test_short_request_kernels_against_reference_kernel_tokens(pk, cuda):
+    """Committed outputs of the reference's short-request kernel (pk_sm89_tdt_persistent_v2) on a
+    60-frame and a 1024-frame request: every decoder kernel of this library must give the same tokens
+    up to the first decision the oracle reports as a near-tie, and nearly everywhere after it."""
+    import importlib.util
+    from pathlib import Path
+    gold_dir = Path(__file__).resolve().parent / "golden"
+    spec = importlib.util.spec_from_file_location("make_golden", gold_dir / "make_golden.py")
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    gold = np.load(gold_dir / "reference_kernels.npz")
+    cases = mg.cases()
+    for case, key in (("dec", "dec_tokens"), ("dec_long", "dec_long_tokens_fp16")):
+        d = cases[case]
+        ref = gold[key]
+        dec = pk.decoder.TdtDecoder(d["w"], cuda)
+        fr = torch.tensor([d["frames"]], dtype=torch.int32, device=cuda)
+        _, _, amb = D.tdt_greedy(d["enc"], d["w"], d["frames"])
+        n = len(ref) if amb is None else amb
+        for kernel in ("cluster", "exchange", "barrier"):
+            tokens, _, counts = dec.decode(dev16(d["enc"]), 1, d["frames"], fr, d["frames"] * 10, kernel=kernel)
+            torch.cuda.synchronize()
+            assert int(dec.status.item()) == 0
+            got = host(tokens)[0][:int(host(counts)[0])]
+            assert np.array_equal(got[:n], ref[:n]), (case, kernel)
+            m = min(len(got), len(ref))
+            agree = float(np.mean(got[:m] == ref[:m]))
+            print(f"{case} {kernel}: {len(got)} tokens, reference {len(ref)}, agreement {agree:.4f}")
+            assert abs(len(got) - len(ref)) <= 2 and agree > 0.9, (case, kernel, agree)
