@@ -1177,6 +1177,7 @@ struct CSmemT {
     alignas(16) __half stage_h[16][kClUnits];     // this CTA's slice of h (hi / lo) on its way out
     alignas(16) __half stage_q[kMaxUtt][kClUnits];  // long-request numerics: its INT8 codes rne(h * 127)
     float cache_mul[3];                           // scale / 127 of w_hh[0], w_hh[1], w_ih[1]
+    uint32_t tmem_base;                           // tensor memory holding layer 0's recurrent weights
     alignas(16) float stage_p[kMaxUtt][kClUnits]; // this CTA's slice of the prediction vector
     float lstm_bias[kClUnits][4];
     float pred_bias[kClUnits];
@@ -1303,6 +1304,84 @@ __device__ __forceinline__ void frag_compute(const uint4* w, const __half* a, fl
     }
 }
 
+// Layer 0's recurrent weights live in TENSOR MEMORY for the whole call: the 205 KB slice of a CTA
+// (160 gate rows x 640, fragment order) does not fit beside the joint rows in shared memory, but
+// the 256 KB of TMEM are otherwise unused by this kernel (its MMAs are register-operand
+// mma.sync).  A warp can reach the 32 lanes of its quadrant (warp % 4); the five warps of a quadrant
+// take 80 columns each: lane L, columns 16 * kp + 4 * j .. + 3 = the uint4 that lane L feeds to the
+// MMAs of k-step pair kp and row tile j.  One tcgen05.ld.32x32b.x16 per k-step pair replaces four
+// 512-byte loads from L2, which bounded this GEMM at the SM's L2 port (about 70 bytes per cycle).
+constexpr uint32_t kTmemColumns = 512;
+static_assert(LstmShape::NT == 4 && LstmShape::NG * LstmShape::NT == LstmShape::kTiles, "16 columns per k-step pair");
+static_assert((kClWarps / 4) * LstmShape::KP * 16 <= kTmemColumns && kClWarps % 4 == 0, "recurrent slice fits TMEM");
+
+__device__ __forceinline__ uint32_t lstm_tmem_addr(uint32_t base, int warp) {
+    return base + (static_cast<uint32_t>((warp % 4) * 32) << 16) + static_cast<uint32_t>((warp / 4) * LstmShape::KP * 16);
+}
+
+// set-up: this warp's fragments, global (fragment-ordered copy) -> TMEM
+__device__ __forceinline__ void lstm_tmem_fill(const uint4* w, uint32_t taddr, int warp, int lane) {
+#pragma unroll
+    for (int kp = 0; kp < LstmShape::KP; ++kp) {
+        uint32_t r[16];
+#pragma unroll
+        for (int j = 0; j < LstmShape::NT; ++j) {
+            const uint4 v = frag_fetch<LstmShape, true>(w, warp, lane, kp, j);
+            r[4 * j] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
+        }
+        tmem_st_32x16(taddr + kp * 16, r);
+    }
+    tmem_st_wait();
+}
+
+// part[kg][u][row] = A . W_hh^T with the weights read from TMEM; the load of k-step pair kp + 1 is
+// in flight while the MMAs of pair kp issue
+template <bool HiOnly>
+__device__ __forceinline__ void lstm_compute_tmem(uint32_t taddr, const __half* a, float* part, int warp, int lane) {
+    using Shape = LstmShape;
+    constexpr int KP = Shape::KP, NT = Shape::NT;
+    const int kg = warp / Shape::NG, ng = warp % Shape::NG;
+    const int g = lane / 4, t = lane % 4;
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[j][e] = 0.0f;
+    const __half* arow = HiOnly ? a + (lane % 8) * kAct + ((lane / 8) % 2) * 8 + kg * KP * 32
+                                : a + (lane % 16) * kAct + (lane / 16) * 8 + kg * KP * 32;
+    uint32_t wbuf[2][16];
+    tmem_ld_32x16(taddr, wbuf[0]);
+    tmem_ld_wait();
+#pragma unroll
+    for (int kp = 0; kp < KP; ++kp) {
+        if (kp + 1 < KP) tmem_ld_32x16(taddr + (kp + 1) * 16, wbuf[(kp + 1) % 2]);
+        unsigned a0[4], a1[4];
+        if constexpr (HiOnly) {
+            unsigned lo[2], hi[2];
+            dec_ldmatrix_x2(lo, arow + kp * 32);
+            dec_ldmatrix_x2(hi, arow + kp * 32 + 16);
+            a0[0] = lo[0]; a0[1] = 0u; a0[2] = lo[1]; a0[3] = 0u;
+            a1[0] = hi[0]; a1[1] = 0u; a1[2] = hi[1]; a1[3] = 0u;
+        } else {
+            dec_ldmatrix_x4(a0, arow + kp * 32);
+            dec_ldmatrix_x4(a1, arow + kp * 32 + 16);
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const uint32_t* b = &wbuf[kp % 2][4 * j];
+            dec_mma(acc[j], a0, b[0], b[1]);
+            dec_mma(acc[j], a1, b[2], b[3]);
+        }
+        if (kp + 1 < KP) tmem_ld_wait();
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        float* dst = part + (kg * 8 + g) * Shape::kPitch + (ng * NT + j) * 8 + 2 * t;
+        *reinterpret_cast<float2*>(dst) = HiOnly ? make_float2(acc[j][0], acc[j][1])
+                                                 : make_float2(acc[j][0] + acc[j][2], acc[j][1] + acc[j][3]);
+    }
+}
+
 #ifdef PK100_DEC_PROFILE
 #define CL_STAMP(i) do { if (tid == 0) { const long long now__ = clock64(); sm.prof[i] += now__ - sm.last_stamp; sm.last_stamp = now__; } } while (0)
 #else
@@ -1386,7 +1465,13 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
         sm.abort = 0;
         fence_barrier_init();
     }
+    if (warp == 1) {                 // one warp owns the tensor-memory allocation (all of it; one CTA per SM)
+        tmem_alloc(&sm.tmem_base, kTmemColumns);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
     __syncthreads();
+    tc_fence_after_sync();
     if (warp < U && !sm.done[warp]) {
         const __half* src = p.enc_proj + static_cast<size_t>(warp) * p.seg_stride * kHidden;
         for (int c = lane; c < kEncChunks; c += 32) cp_async_16(&sm.enc[warp][c * 8], src + c * 8);
@@ -1402,9 +1487,9 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
     uint32_t hphase = 0, pphase = 0, kphase[2] = {0, 0};
     [[maybe_unused]] uint32_t h1phase = 0;
     [[maybe_unused]] const uint4* wl1 = packed_lstm1 + static_cast<size_t>(r) * Lstm1Shape::kPerCta;
-    // first k-step pair of the recurrent weights, requested one decision ahead of its use
-    FragRing<LstmShape, 2> lstm_ring;
-    frag_prefetch<LstmShape, true, 2, 0, 1>(wl, lstm_ring, warp, lane);
+    // layer 0's recurrent weights: once from the fragment-ordered copy into tensor memory
+    const uint32_t lstm_taddr = lstm_tmem_addr(sm.tmem_base, warp);
+    lstm_tmem_fill(wl, lstm_taddr, warp, lane);
 
     // LSTM cell of one (utterance, unit) from its four gate sums; stages h for the exchange
     auto cell_update = [&](const float (&gsum)[4], float& cstate, int u, int slot) {
@@ -1471,7 +1556,7 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
 
         if (need8 != 0ull) {
             // ---- LSTM: gates of this CTA's 40 units = table row + h . w_hh^T + bias
-            frag_compute<LstmShape, true, 2, 1, Cache>(wl, &sm.ah[0][0], sm.part, lstm_ring, warp, lane);
+            lstm_compute_tmem<Cache>(lstm_taddr, &sm.ah[0][0], sm.part, warp, lane);
             cp_async_wait_all();             // table rows / encoder rows requested at the last decision
             __syncthreads();
             CL_STAMP(1);
@@ -1684,7 +1769,6 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
             st_async_b64(map_to_cta(smem_u32(&sm.keys[par][r][u]), static_cast<uint32_t>(lane)), best,
                          map_to_cta(kbar_local, static_cast<uint32_t>(lane)));
         }
-        frag_prefetch<LstmShape, true, 2, 0, 1>(wl, lstm_ring, warp, lane);   // for the next round, if it needs the LSTM
         mbar_wait_bounded(&sm.kbar[par], kphase[par], abort_flag);
         kphase[par] ^= 1u;
         CL_STAMP(10);
@@ -1748,7 +1832,12 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
         round += 1;
     }
     cp_async_wait_all();
+    tc_fence_before_sync();
     __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(sm.tmem_base, kTmemColumns);
+    }
     cluster_sync_all();      // no CTA leaves while a peer may still address its shared memory
 #ifdef PK100_DEC_PROFILE
     if (r == 0 && tid == 0)
