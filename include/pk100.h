@@ -332,10 +332,11 @@ int pk100_tdt_decode_static(void* stream, const pk100_decoder_weights* weights, 
 
 /* Same contract, one kernel design each.
  * _cluster: one thread-block cluster of 16 CTAs; the phases of a round exchange their vectors
- *   through distributed shared memory and the hardware cluster barrier; joint rows resident in
- *   shared memory, LSTM / prediction weights streamed from L2 in a fragment-ordered copy that the
- *   call writes into the workspace.  With two LSTM layers the joint rows are streamed as well (the
- *   second layer's state takes their room).  PK100_ERR_UNSUPPORTED when the device cannot
+ *   through distributed shared memory (remote stores that complete on the receiver's mbarrier);
+ *   joint rows resident in shared memory, layer 0's recurrent weights resident in tensor memory,
+ *   prediction weights streamed from L2, all from a fragment-ordered copy that the call writes
+ *   into the workspace.  With two LSTM layers the joint rows and the second layer's weights are
+ *   streamed as well (the second layer's state takes the room of the joint rows).  PK100_ERR_UNSUPPORTED when the device cannot
  *   co-schedule 16 CTAs of that much shared memory as a cluster.
  * _exchange: one CTA per SM, all weights resident in shared memory, phases exchange through
  *   tagged global-memory slots that the consumers poll (bounded).  One or two LSTM layers.  Uses

@@ -1057,10 +1057,12 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
 // instead of the 2-3 us of global-memory slots polled by 148 CTAs.  The price: 16 CTAs
 // cannot hold the 8 MB of fp16 weights in shared memory, so
 //   - the joint rows (needed every round) stay resident,
-//   - the recurrent LSTM weights and the prediction projection are streamed from L2 on the
-//     rounds that follow a non-blank token, from a copy in "fragment order": the 16 bytes a
-//     lane needs for two k-steps of mma.m16n8k16 are contiguous, so a warp pulls 512
-//     contiguous bytes per load straight into registers, several loads deep,
+//   - the recurrent LSTM weights of layer 0 sit in tensor memory (unused otherwise: the MMAs
+//     here are mma.sync), written once per call and read back per k-step pair,
+//   - the prediction projection (and a second LSTM layer) is streamed from L2 on the rounds
+//     that follow a non-blank token, from a copy in "fragment order": the 16 bytes a lane
+//     needs for two k-steps of mma.m16n8k16 are contiguous, so a warp pulls 512 contiguous
+//     bytes per load straight into registers, several loads deep,
 //   - the input half of the LSTM, W_ih . embedding[token], is a table [1025, 2560] computed
 //     once per call by one GEMM; a round gathers 4 x 40 floats of the token's row per CTA.
 // Every CTA runs the same control flow on replicated utterance state.
