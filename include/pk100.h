@@ -300,8 +300,10 @@ long long pk100_tdt_workspace_bytes(int utterances);
  * u * seg_stride; frames[u] (device int array) frames are consumed.  tokens /
  * durations: [utterances, max_tokens] int32 (durations may be NULL), counts:
  * [utterances].  workspace: >= pk100_tdt_workspace_bytes(utterances), 256-byte
- * aligned; it is cleared by the call.  *status (device int, may be NULL) becomes 2 if
- * a bounded grid barrier expired.  Token rule: highest joint score, ties to the lower
+ * aligned; it is cleared by the call.  frames[u] beyond seg_stride is read as seg_stride (a
+ * decode never leaves its utterance's block).  *status (device int, may be NULL) becomes 2 if
+ * a bounded wait expired; bit 4 is set when every token score of a round was NaN (that round
+ * decodes as a blank, so no id outside [0, 1024] is ever produced).  Token rule: highest joint score, ties to the lower
  * id; duration: first strict maximum of 5 logits; at most 10 symbols per frame; blank
  * (1024) never updates the prediction network (kernels/sm89/decoder.cu:35-46, :416-445). */
 int pk100_tdt_decode(void* stream, const pk100_decoder_weights* weights, const void* enc_proj,
@@ -320,7 +322,8 @@ int pk100_tdt_decode(void* stream, const pk100_decoder_weights* weights, const v
  *   - at most PK100_DECODER_MAX_UTTERANCES utterances; more returns PK100_ERR_LIMIT and
  *     launches nothing;
  *   - the first call on each device looks the array's device address up (with that device
- *     current) and remembers it; make that first call outside any stream capture;
+ *     current) and remembers it; make that first call outside any stream capture; the remembered
+ *     address does not survive a cudaDeviceReset (reload the library after one);
  *   - the array is shared by every call and keeps the previous call's contents; each call
  *     clears the part it uses before its kernel starts (stream-ordered), so back-to-back
  *     calls on one stream are fine, but two calls that overlap on the GPU (different

@@ -18,6 +18,7 @@
 #include <float.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "pk100_internal.h"
@@ -331,10 +332,12 @@ __global__ void __launch_bounds__(kDecThreads, 1) tdt_greedy_kernel(const DecPar
                             const float in = l == 0
                                 ? (s_emitted[u] ? p.input_table[static_cast<size_t>(s_last[u]) * kGates + r * kHidden + unit] : 0.0f)
                                 : warp_sum_f(dot640(wrow + r * kHidden, vec, lane));
-                            const float rec = warp_sum_f(dot640(wrow + (4 + r) * kHidden, vec + kHidden, lane)) *
-                                              cache_mul(cscale[l]);
+                            // rounded product, never fused with the additions that follow (see the cluster kernel)
+                            const float rec = __fmul_rn(warp_sum_f(dot640(wrow + (4 + r) * kHidden, vec + kHidden, lane)),
+                                                        cache_mul(cscale[l]));
                             const float bias = p.b_ih[l][r * kHidden + unit] + p.b_hh[l][r * kHidden + unit];
-                            gate[r] = l == 0 ? (rec + bias) + in : (rec + in * cache_mul(cscale[2])) + bias;
+                            gate[r] = l == 0 ? __fadd_rn(__fadd_rn(rec, bias), in)
+                                             : __fadd_rn(fmaf(in, cache_mul(cscale[2]), rec), bias);
                         }
                     }
                     if (lane == 0) {
@@ -419,7 +422,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) tdt_greedy_kernel(const DecPar
         if (tid < p.utts && !s_done[tid]) {
             const int u = tid;
             const unsigned long long key = __ldcg(g_dec + u * 3 + slot);
-            const int token = static_cast<int>(0xffffffffu - static_cast<unsigned>(key));
+            int token = static_cast<int>(0xffffffffu - static_cast<unsigned>(key));
+            // every token score of the round was NaN (no key beat the initial one): a blank, and
+            // the call reports it (status bit 4); 1025 is no row of the embedding table
+            if (token > kBlank) { token = kBlank; if (cta == 0 && p.status != nullptr) atomicOr(p.status, 4); }
             const float* dl = g_dur + (static_cast<size_t>(u) * 3 + slot) * kDurations;
             int duration = 0;
             float best = __ldcg(dl);
@@ -445,7 +451,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) tdt_greedy_kernel(const DecPar
                 if (duration == 0) s_frame[u] += 1;
                 s_symbols[u] = 0;
             }
-            if (s_frame[u] >= p.frames[u]) s_done[u] = 1;
+            if (s_frame[u] >= min(p.frames[u], p.seg_stride)) s_done[u] = 1;   // never past the utterance's block
         }
         __syncthreads();
         slot = next_slot;
@@ -732,7 +738,7 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
     if (tid < kMaxUtt) {
         sm.frame[tid] = 0; sm.symbols[tid] = 0; sm.last[tid] = kBlank; sm.count[tid] = 0;
         sm.ver[tid] = 0; sm.pred_ver[tid] = 0; sm.emitted[tid] = 0; sm.valid[tid] = 0;
-        sm.total_frames[tid] = tid < U ? p.frames[tid] : 0;
+        sm.total_frames[tid] = tid < U ? min(p.frames[tid], p.seg_stride) : 0;   // never past the utterance's block
         sm.done[tid] = tid >= U || p.frames[tid] <= 0;
         sm.need[tid] = !(tid >= U || p.frames[tid] <= 0);
     }
@@ -987,7 +993,13 @@ __global__ void __launch_bounds__(kXThreads, 1) tdt_exchange_kernel(const DecPar
                 best = other > best ? other : best;
             }
             if (!__all_sync(0xffffffffu, good)) sm.ok = 0;
-            const int token = 2047 - static_cast<int>((best >> 21) & 0x7FFull);
+            int token = 2047 - static_cast<int>((best >> 21) & 0x7FFull);
+            // every token score of the round was NaN (only losing keys were published): a blank,
+            // reported as status bit 4; 1025 is no row of the embedding table
+            if (token > kBlank) {
+                token = kBlank;
+                if (cta == 0 && lane == 0 && good && p.status != nullptr) atomicOr(p.status, 4);
+            }
             // first strict maximum of the five duration logits (lanes 0..4 hold one each)
             const float my_dur = __uint_as_float(static_cast<unsigned>(dv));
             int duration = 0;
@@ -1414,7 +1426,9 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
     // ---- set-up: resident joint slice, biases, cleared state, first encoder rows
     const uint4* wjoint = packed_joint + static_cast<size_t>(r) * JointShape::kPerCta;
     if constexpr (Layers == 1) {
-        for (int i = tid; i < JointShape::kPerCta; i += kClThreads) sm.wj[i] = __ldg(wjoint + i);
+        // (the long-request numerics read the joint rows from the caller's matrix instead)
+        if constexpr (!Cache)
+            for (int i = tid; i < JointShape::kPerCta; i += kClThreads) sm.wj[i] = __ldg(wjoint + i);
     } else {
         for (int i = tid; i < 16 * kAct; i += kClThreads) {
             (&sm.second.ah1[0][0])[i] = __float2half(0.0f);
@@ -1452,7 +1466,7 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
     }
     if (tid < kMaxUtt) {
         sm.frame[tid] = 0; sm.symbols[tid] = 0; sm.count[tid] = 0; sm.valid[tid] = 0;
-        sm.total_frames[tid] = tid < U ? p.frames[tid] : 0;
+        sm.total_frames[tid] = tid < U ? min(p.frames[tid], p.seg_stride) : 0;   // never past the utterance's block
         const bool done = tid >= U || p.frames[tid] <= 0 || !in_window(p, tid);
         sm.done[tid] = done;
         sm.need[tid] = !done;
@@ -1500,14 +1514,17 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
             // the reference's approximations: h is rounded to 8 bits next, and a code that flips moves a gate
             h = ref_lstm_cell(gsum, cstate);
             sm.stage_q[u][slot] = __int2half_rn(quantize_i8(h * 127.0f));
+            // the prediction projection of this mode reads the fp32 state (decoder.cu:672-681), so the
+            // slice travels as fp32: stage_h viewed as float[8][40], the same bytes as a hi / lo pair
+            reinterpret_cast<float*>(&sm.stage_h[0][0])[u * kClUnits + slot] = h;
         } else {
             const float cell = fast_sigmoid(gsum[1]) * cstate + fast_sigmoid(gsum[0]) * fast_tanh(gsum[2]);
             cstate = cell;
             h = fast_sigmoid(gsum[3]) * fast_tanh(cell);
+            const __half hi = __float2half_rn(h);
+            sm.stage_h[u][slot] = hi;
+            sm.stage_h[u + 8][slot] = __float2half_rn(h - __half2float(hi));
         }
-        const __half hi = __float2half_rn(h);
-        sm.stage_h[u][slot] = hi;
-        sm.stage_h[u + 8][slot] = __float2half_rn(h - __half2float(hi));
     };
     // this CTA's staged slice of a hidden state -> `fresh` (hi / lo rows) of every CTA, and with
     // Cache its codes -> rows 8-15 of `committed`; all bytes are credited to `bar_local` there
@@ -1515,12 +1532,24 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
         const uint32_t bar = map_to_cta(smem_u32(bar_local), peer);
 #pragma unroll
         for (int it = 0; it < 2; ++it) {
-            const int item = item0 + it * kClUnits;         // 0..79: 16 rows x 5 chunks of 8 units
-            const int row = item / 5, chunk = item % 5;
-            const int u = row % 8;
-            if (u < U && sm.need[u]) {
-                const uint4 v = *reinterpret_cast<const uint4*>(&sm.stage_h[row][chunk * 8]);
-                st_async_v4(map_to_cta(smem_u32(&fresh[row][r * kClUnits + chunk * 8]), peer), v, bar);
+            const int item = item0 + it * kClUnits;
+            if constexpr (Cache) {
+                // 0..79: 8 utterances x 10 chunks of 4 floats into `fresh` viewed as float[8][640]
+                const int u = item / 10, chunk = item % 10;
+                if (u < U && sm.need[u]) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(
+                        reinterpret_cast<const float*>(&sm.stage_h[0][0]) + u * kClUnits + chunk * 4);
+                    float* dst = reinterpret_cast<float*>(&fresh[0][0]) + u * kHidden + r * kClUnits + chunk * 4;
+                    st_async_v4(map_to_cta(smem_u32(dst), peer), v, bar);
+                }
+            } else {
+                // 0..79: 16 rows x 5 chunks of 8 units
+                const int row = item / 5, chunk = item % 5;
+                const int u = row % 8;
+                if (u < U && sm.need[u]) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(&sm.stage_h[row][chunk * 8]);
+                    st_async_v4(map_to_cta(smem_u32(&fresh[row][r * kClUnits + chunk * 8]), peer), v, bar);
+                }
             }
         }
         if constexpr (Cache) {
@@ -1577,10 +1606,13 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                             rec[0] += v.x; rec[1] += v.y; rec[2] += v.z; rec[3] += v.w;
                         }
                         const float mul = sm.cache_mul[0];
-                        gsum[0] = (rec[0] * mul + sm.lstm_bias[slot][0]) + x.x;
-                        gsum[1] = (rec[1] * mul + sm.lstm_bias[slot][1]) + x.y;
-                        gsum[2] = (rec[2] * mul + sm.lstm_bias[slot][2]) + x.z;
-                        gsum[3] = (rec[3] * mul + sm.lstm_bias[slot][3]) + x.w;
+                        const float xin[4] = {x.x, x.y, x.z, x.w};
+                        // the scaled recurrent sum is rounded BEFORE the bias is added, as in the reference
+                        // (decoder.cu:113, :626-640: products rounded per lane, then summed): a fused
+                        // multiply-add here parts from the reference kernel's tokens after a few hundred steps
+#pragma unroll
+                        for (int g4 = 0; g4 < 4; ++g4)
+                            gsum[g4] = __fadd_rn(__fadd_rn(__fmul_rn(rec[g4], mul), sm.lstm_bias[slot][g4]), xin[g4]);
                     } else {
                         gsum[0] = sm.lstm_bias[slot][0] + x.x; gsum[1] = sm.lstm_bias[slot][1] + x.y;
                         gsum[2] = sm.lstm_bias[slot][2] + x.z; gsum[3] = sm.lstm_bias[slot][3] + x.w;
@@ -1599,8 +1631,8 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
             CL_STAMP(2);
             send_hidden(sm.hx, sm.ah, &sm.hbar);     // h slice -> every CTA's hx (and codes)
             // the prediction weights of this warp are requested while the hidden state travels
-            FragRing<PredShape, 1> pred_ring;
-            if constexpr (Layers == 1) frag_prefetch<PredShape, true, 1, 0, 1>(wp, pred_ring, warp, lane);
+            [[maybe_unused]] FragRing<PredShape, 1> pred_ring;
+            if constexpr (Layers == 1 && !Cache) frag_prefetch<PredShape, true, 1, 0, 1>(wp, pred_ring, warp, lane);
             mbar_wait_bounded(&sm.hbar, hphase, abort_flag);
             hphase ^= 1u;
             CL_STAMP(3);
@@ -1634,8 +1666,9 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                                 dst[0] += v.x; dst[1] += v.y; dst[2] += v.z; dst[3] += v.w;
                             }
 #pragma unroll
+                            // rounded recurrent product first, the input product fused onto it (decoder.cu:113, :660)
                             for (int g4 = 0; g4 < 4; ++g4)
-                                gsum[g4] = (rec[g4] * sm.cache_mul[1] + in[g4] * sm.cache_mul[2]) + gsum[g4];
+                                gsum[g4] = __fadd_rn(fmaf(in[g4], sm.cache_mul[2], __fmul_rn(rec[g4], sm.cache_mul[1])), gsum[g4]);
                         } else {
 #pragma unroll
                             for (int kg = 0; kg < Lstm1Shape::KG; ++kg) {
@@ -1653,12 +1686,43 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                 if (tid == 0) mbar_arrive_expect_tx(&sm.second.hbar1, static_cast<uint32_t>(needs) * kHiddenTx);
                 __syncthreads();
                 send_hidden(sm.second.hx1, sm.second.ah1, &sm.second.hbar1);
-                frag_prefetch<PredShape, true, 1, 0, 1>(wp, pred_ring, warp, lane);
+                if constexpr (!Cache) frag_prefetch<PredShape, true, 1, 0, 1>(wp, pred_ring, warp, lane);
                 mbar_wait_bounded(&sm.second.hbar1, h1phase, abort_flag);
                 h1phase ^= 1u;
                 top_fresh = sm.second.hx1;
                 top_committed = sm.second.ah1;
             }
+            if constexpr (Cache) {
+                // ---- prediction projection in fp32 on the fp32 state, in the reference's summation
+                // order (decoder.cu:672-684): lane l takes elements 2l + 64w, w = 0..9, as one fma
+                // chain that starts from the bias in lane 0, then the shuffle tree of warp_sum
+                const float* hf = reinterpret_cast<const float*>(&top_fresh[0][0]);
+#pragma unroll
+                for (int it = 0; it < kClUnits / kClWarps; ++it) {
+                    const int n = warp + it * kClWarps;
+                    const uint32_t* wrow = reinterpret_cast<const uint32_t*>(
+                        p.w_pred + static_cast<size_t>(r * kClUnits + n) * kHidden);
+                    uint32_t words[10];
+#pragma unroll
+                    for (int w = 0; w < 10; ++w) words[w] = __ldg(wrow + lane + 32 * w);
+                    for (int u = 0; u < U; ++u) {
+                        if (!sm.need[u]) continue;
+                        float sum = lane == 0 ? sm.pred_bias[n] : 0.0f;
+#pragma unroll
+                        for (int w = 0; w < 10; ++w) {
+                            const float2 wv = __half22float2(*reinterpret_cast<const __half2*>(&words[w]));
+                            const float2 hv = *reinterpret_cast<const float2*>(hf + u * kHidden + 2 * lane + 64 * w);
+                            sum = fmaf(wv.x, hv.x, sum);
+                            sum = fmaf(wv.y, hv.y, sum);
+                        }
+#pragma unroll
+                        for (int off = 16; off > 0; off /= 2) sum += __shfl_down_sync(0xffffffffu, sum, off);
+                        if (lane == 0) sm.stage_p[u][n] = sum;
+                    }
+                }
+                CL_STAMP(4);
+                commit_hidden(top_fresh, top_committed, 0);
+            } else {
             // ---- prediction projection of the new state (A operand: the fresh rows of the top layer)
             frag_compute<PredShape, true, 1, 1>(wp, &top_fresh[0][0], sm.part, pred_ring, warp, lane);
             __syncthreads();
@@ -1674,6 +1738,7 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
             } else {
                 // meanwhile the other threads commit the fresh hidden state for the next LSTM step
                 commit_hidden(top_fresh, top_committed, kMaxUtt * kClUnits);
+            }
             }
             if (tid == 0) mbar_arrive_expect_tx(&sm.pbar, static_cast<uint32_t>(needs) * kHidden * 4);
             __syncthreads();
@@ -1707,12 +1772,48 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                 v[u] = live ? fmaxf(__half2float(sm.enc[u][tid]) + sm.pred[u][tid], 0.0f) : 0.0f;
             }
 #pragma unroll
-            for (int u = 0; u < kMaxUtt; ++u)
-                if (((done8 >> (8 * u)) & 1ull) == 0ull) split_store(sm.ax, u, tid, v[u]);
+            for (int u = 0; u < kMaxUtt; ++u) {
+                if (((done8 >> (8 * u)) & 1ull) != 0ull) continue;
+                if constexpr (Cache) reinterpret_cast<float*>(&sm.ax[0][0])[u * kHidden + tid] = v[u];   // ax as float[8][640]
+                else split_store(sm.ax, u, tid, v[u]);
+            }
         }
         __syncthreads();
         CL_STAMP(7);
-        {
+        if constexpr (Cache) {
+            // joint rows in fp32 in the reference's summation order (decoder.cu:697-713): one row per
+            // half-warp, half-lane l takes elements 2l + 32s, s = 0..19, as one fma chain that starts from
+            // the bias in half-lane 0, then the shuffle tree of half_warp_sum.  The score (bias included)
+            // lands in the k-group-0 slot of `part`.  Rows come from the caller's [1030, 640] matrix.
+            const float* xf = reinterpret_cast<const float*>(&sm.ax[0][0]);
+            const int hw = tid / 16, hl = tid % 16;
+#pragma unroll 1
+            for (int it = 0; it < 2; ++it) {
+                const int n = hw + it * (kClThreads / 16);
+                const int row = r * kClJoint + n;
+                const bool owned = n < kClJoint && row < kJointRows;
+                const uint32_t* wrow = reinterpret_cast<const uint32_t*>(
+                    p.w_joint + static_cast<size_t>(owned ? row : 0) * kHidden);
+                uint32_t words[20];
+#pragma unroll
+                for (int st = 0; st < 20; ++st) words[st] = __ldg(wrow + hl + 16 * st);
+                const float bias = owned ? sm.joint_bias[n] : 0.0f;
+                for (int u = 0; u < U; ++u) {
+                    if (((done8 >> (8 * u)) & 1ull) != 0ull) continue;
+                    float score = hl == 0 ? bias : 0.0f;
+#pragma unroll
+                    for (int st = 0; st < 20; ++st) {
+                        const float2 wv = __half22float2(*reinterpret_cast<const __half2*>(&words[st]));
+                        const float2 xv = *reinterpret_cast<const float2*>(xf + u * kHidden + 2 * hl + 32 * st);
+                        score = fmaf(wv.x, xv.x, score);
+                        score = fmaf(wv.y, xv.y, score);
+                    }
+#pragma unroll
+                    for (int off = 8; off > 0; off /= 2) score += __shfl_down_sync(0xffffffffu, score, off, 16);
+                    if (hl == 0 && owned) sm.part[u * JointShape::kPitch + n] = score;
+                }
+            }
+        } else {
             FragRing<JointShape, 1> joint_ring;
             if constexpr (Layers == 1) frag_compute<JointShape, false, 1, 0>(sm.wj, &sm.ax[0][0], sm.part, joint_ring, warp, lane);
             else frag_compute<JointShape, true, 1, 0>(wjoint, &sm.ax[0][0], sm.part, joint_ring, warp, lane);
@@ -1734,9 +1835,14 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                 const int n = half * 36 + lane + it * 32;
                 const int row = r * kClJoint + n;
                 if (live_u && n < half * 36 + 36 && n < kClJoint && row < kJointRows) {
-                    float total = sm.joint_bias[n];
+                    float total;
+                    if constexpr (Cache) {
+                        total = sm.part[u * JointShape::kPitch + n];      // finished score of the fp32 joint
+                    } else {
+                        total = sm.joint_bias[n];
 #pragma unroll
-                    for (int kg = 0; kg < JointShape::KG; ++kg) total += sm.part[(kg * 8 + u) * JointShape::kPitch + n];
+                        for (int kg = 0; kg < JointShape::KG; ++kg) total += sm.part[(kg * 8 + u) * JointShape::kPitch + n];
+                    }
                     if (row >= kTokenOutputs) {
                         const uint32_t local = smem_u32(&sm.dur[par][u][row - kTokenOutputs]);
                         for (uint32_t d = 0; d < kCl; ++d)
@@ -1785,7 +1891,12 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                 best = other > best ? other : best;
             }
             int token = 2047 - static_cast<int>((best >> 21) & 0x7FFull);
-            if (token > kBlank) token = kBlank;     // only after a wait gave up (keys not delivered)
+            // keys not delivered (a wait gave up), or every token score of the round was NaN: a
+            // blank; the second case is reported as status bit 4
+            if (token > kBlank) {
+                token = kBlank;
+                if (r == 0 && lane == 0 && sm.abort == 0 && p.status != nullptr) atomicOr(p.status, 4);
+            }
             // first strict maximum of the five duration logits
             int duration = 0;
             float best_dur = sm.dur[par][u][0];
@@ -2043,23 +2154,25 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 namespace {
 // In host code `g_static_scratch` is only a handle for the runtime, not a device address:
 // the address a kernel may dereference is looked up once per device.
-void* g_static_scratch_ptr[64] = {nullptr};
+// Entries are atomic: two host threads that make the first call on a device at once both look the
+// address up and store the same value.  A cudaDeviceReset invalidates the cached address.
+std::atomic<void*> g_static_scratch_ptr[64];
 
 int static_scratch_address(void** out) {
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return static_cast<int>(err);
     if (dev < 0 || dev >= 64) return PK100_ERR_LIMIT;
-    if (g_static_scratch_ptr[dev] == nullptr) {
-        void* ptr = nullptr;
+    void* ptr = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         err = cudaGetSymbolAddress(&ptr, g_static_scratch);   // with device `dev` current
         if (err != cudaSuccess) {
             cudaGetLastError();
             return static_cast<int>(err);
         }
-        g_static_scratch_ptr[dev] = ptr;
+        g_static_scratch_ptr[dev].store(ptr, std::memory_order_release);
     }
-    *out = g_static_scratch_ptr[dev];
+    *out = ptr;
     return PK100_OK;
 }
 }  // namespace

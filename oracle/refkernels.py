@@ -108,6 +108,29 @@ def ffn_expand_fp8(xq, wq, w_scales, rows):
     return out
 
 
+def layer_norm_pair(x, gamma, beta, next_gamma, next_beta, rows, padded_rows, inverse_scale=0.0, eps=1e-5):
+    """launch_norm_pair (src/cuda/encoder.rs:1394-1433): grid padded_rows x 256.  Returns the fp16
+    first output and the second output: fp16 when inverse_scale == 0, else E4M3 bytes."""
+    out = torch.empty_like(x)
+    if inverse_scale != 0.0:
+        nxt = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    else:
+        nxt = torch.empty_like(x)
+    module("encoder").launch("pk_sm89_layer_norm_pair", (padded_rows,), (256,), 0,
+                             [x, gamma, beta, out, next_gamma, next_beta, nxt, rows, padded_rows,
+                              float(eps), float(inverse_scale)])
+    return out, nxt
+
+
+def layer_norm_quantize_fp8_dynamic(x, gamma, beta, rows, padded_rows, eps=1e-5):
+    """launch_norm_quantize_fp8 (src/cuda/encoder.rs:1436-1468): E4M3 bytes + per-row scales."""
+    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    scales = torch.zeros(padded_rows, dtype=torch.float32, device=x.device)
+    module("encoder").launch("pk_sm89_layer_norm_quantize_fp8_dynamic", (padded_rows,), (256,), 0,
+                             [x, gamma, beta, out, scales, rows, padded_rows, float(eps)])
+    return out, scales
+
+
 def glu_masked(e, rows, padded_rows, valid_rows):
     """launch_glu_arena (src/cuda/encoder.rs:1965-1997)."""
     out = torch.empty((padded_rows, 1024), dtype=torch.float16, device=e.device)
@@ -142,6 +165,101 @@ def fp16_linear(x, w, bias, residual, m, n, k, output_scale=1.0, residual_scale=
                             [x, w, bias, residual, out, m, n, k, float(output_scale),
                              float(residual_scale), activation])
     return out
+
+
+def _scaled_linear(name, xq, wq, w_scales, bias, m, n, k, input_scale, activation):
+    """pk_sm89_fp8_linear_epilogue / pk_sm89_int8_linear_epilogue (kernels/sm89/linear.cu:325-429) as the
+    quantisation benchmarks launch them (src/cuda/quant_benchmark.rs): one warp per 16 x 8 output
+    tile, grid (n/32, m/16) x 128; m % 16 == 0, n % 32 == 0, k % 32 == 0, bias required."""
+    assert m % 16 == 0 and n % 32 == 0 and k % 32 == 0
+    out = torch.zeros((m, n), dtype=torch.float16, device=xq.device)
+    module("linear").launch(name, (n // 32, m // 16), (128,), 0,
+                            [xq, wq, w_scales, bias, out, m, n, k, float(input_scale), activation])
+    return out
+
+
+def fp8_linear(xq, wq, w_scales, bias, m, n, k, input_scale, activation=0):
+    return _scaled_linear("pk_sm89_fp8_linear_epilogue", xq, wq, w_scales, bias, m, n, k, input_scale, activation)
+
+
+def int8_linear(xq, wq, w_scales, bias, m, n, k, input_scale, activation=0):
+    return _scaled_linear("pk_sm89_int8_linear_epilogue", xq, wq, w_scales, bias, m, n, k, input_scale, activation)
+
+
+def quantize_fp8(x, inverse_scale):
+    """pk_sm89_quantize_fp8 (kernels/sm89/linear.cu:537-547)."""
+    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    n = x.numel()
+    module("linear").launch("pk_sm89_quantize_fp8", (_cdiv(n, 256),), (256,), 0, [x, out, float(inverse_scale), n])
+    return out
+
+
+def quantize_int8(x, inverse_scale):
+    """pk_sm89_quantize_int8 (kernels/sm89/linear.cu:549-560)."""
+    out = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    n = x.numel()
+    module("linear").launch("pk_sm89_quantize_int8", (_cdiv(n, 256),), (256,), 0, [x, out, float(inverse_scale), n])
+    return out
+
+
+# ---- subsampling.cu -------------------------------------------------------
+
+def subsampling_available() -> bool:
+    return (REF_DIR / "subsampling.cubin").exists()
+
+
+def subsample_first(mel, weight, bias, frames):
+    """launch_first (src/cuda/subsampling.rs) on the whole utterance as one tile: mel fp32
+    [frames, 128] -> fp16 [ceil(frames/2) * 64, 256] (row = frame * 64 + feature), ReLU fused."""
+    f_out, feat = _cdiv(frames, 2), 64
+    out = torch.zeros((f_out * feat, 256), dtype=torch.float16, device=mel.device)
+    module("subsampling").launch("pk_sm89_subsample_first", (_cdiv(feat, 8), f_out), (256,), 0,
+                                 [mel, weight, bias, out, frames, 0, f_out, feat])
+    return out
+
+
+def subsample_depthwise(x, weight, bias, in_frames, in_features, pad_rows_to=16):
+    """launch_depthwise: fp16 [in_frames * in_features, 256] -> [ceil/2 frames * ceil/2 features, 256];
+    the row count is padded (zero rows) to a multiple of 16 for the pointwise linear that follows."""
+    f_out, feat = _cdiv(in_frames, 2), _cdiv(in_features, 2)
+    rows = _cdiv(f_out * feat, pad_rows_to) * pad_rows_to
+    out = torch.zeros((rows, 256), dtype=torch.float16, device=x.device)
+    module("subsampling").launch("pk_sm89_subsample_depthwise", (_cdiv(feat, 8), f_out), (256,), 0,
+                                 [x, weight, bias, out, 0, in_frames, in_features, 0, f_out, feat])
+    return out
+
+
+def subsample_flatten(x, frames, padded_frames, features, valid_frames):
+    """launch_flatten: [frames * features, 256] -> [padded_frames, 256 * features], column =
+    channel * features + feature; rows >= valid_frames are zero."""
+    out = torch.empty((padded_frames, 256 * features), dtype=torch.float16, device=x.device)
+    total = padded_frames * 256 * features
+    module("subsampling").launch("pk_sm89_subsample_flatten", (_cdiv(total, 256),), (256,), 0,
+                                 [x, out, frames, padded_frames, features, 0, valid_frames])
+    return out
+
+
+def subsampling(mel, w, frames):
+    """run_subsampling (src/cuda/subsampling.rs:436-804) for a request that fits one tile, fp16 path:
+    first conv, two (depthwise, pointwise + ReLU) stages, flatten, projection.  `w`: device
+    tensors named as in pk100_subsampling_weights.  Returns (stages, output [ceil(frames/8), 1024])."""
+    stages = {}
+    f1, f2, f3 = _cdiv(frames, 2), _cdiv(_cdiv(frames, 2), 2), _cdiv(_cdiv(_cdiv(frames, 2), 2), 2)
+    x = subsample_first(mel, w["conv0_w"], w["conv0_b"], frames)
+    stages["conv0"] = x
+    x = subsample_depthwise(x, w["dw1_w"], w["dw1_b"], f1, 64)
+    stages["dw1"] = x
+    x = fp16_linear(x, w["pw1_w"], w["pw1_b"], None, x.shape[0], 256, 256, 1.0, 0.0, 2)
+    stages["pw1"] = x
+    x = subsample_depthwise(x, w["dw2_w"], w["dw2_b"], f2, 32)
+    stages["dw2"] = x
+    x = fp16_linear(x, w["pw2_w"], w["pw2_b"], None, x.shape[0], 256, 256, 1.0, 0.0, 2)
+    stages["pw2"] = x
+    padded = _cdiv(f3, 16) * 16
+    flat = subsample_flatten(x, f3, padded, 16, f3)
+    stages["flat"] = flat
+    out = fp16_linear(flat, w["proj_w"], w["proj_b"], None, padded, 1024, 4096)
+    return stages, out[:f3]
 
 
 # ---- decoder.cu -----------------------------------------------------------

@@ -56,6 +56,31 @@ def cases():
                                enc=[codec.f16_round(rng.standard_normal((48, 640)) * 0.5) for _ in range(16)])
     rng = np.random.default_rng(105)
     c["fe"] = dict(x=(rng.standard_normal(1700) * 0.3).astype(np.float32))
+    # per-tensor activation x per-row weight scaled linears and their quantisers (linear.cu:325-429, :537-560)
+    rng = np.random.default_rng(108)
+    m, n, k = 16, 64, 256
+    x = codec.f16_round(rng.standard_normal((m, k)))
+    w = codec.f16_round(rng.standard_normal((n, k)) * 0.02)
+    c["lin"] = dict(x=x, w=w, bias=(0.1 * rng.standard_normal(n)).astype(np.float32), m=m, n=n, k=k,
+                    inv8=float(np.float32(127.0) / np.float32(np.max(np.abs(x)))))
+    # LayerNorm pair / LayerNorm + per-row dynamic E4M3 (encoder.cu:128-306)
+    rng = np.random.default_rng(109)
+    c["lnpair"] = dict(x=codec.f16_round(rng.standard_normal((16, 1024)) * 2),
+                       g=[codec.f16_round(1 + 0.1 * rng.standard_normal(1024)) for _ in range(2)],
+                       b=[codec.f16_round(0.1 * rng.standard_normal(1024)) for _ in range(2)], rows=15, padded=16)
+    # convolution subsampling of a 40-frame request (subsampling.cu, one tile); weights: seeded like
+    # the product's synthetic pre-encode tensors, restated here so the case stands alone
+    rng = np.random.default_rng(110)
+    sw = {"conv0_w": codec.f16_round(rng.standard_normal((256, 9)) * 0.3),
+          "conv0_b": codec.f16_round(rng.standard_normal(256) * 0.1)}
+    for stage in (1, 2):
+        sw[f"dw{stage}_w"] = codec.f16_round(rng.standard_normal((256, 9)) * 0.3)
+        sw[f"dw{stage}_b"] = codec.f16_round(rng.standard_normal(256) * 0.1)
+        sw[f"pw{stage}_w"] = codec.f16_round(rng.standard_normal((256, 256)) * 0.06)
+        sw[f"pw{stage}_b"] = (rng.standard_normal(256) * 0.05).astype(np.float32)
+    sw["proj_w"] = codec.f16_round(rng.standard_normal((1024, 4096)) * 0.02)
+    sw["proj_b"] = (rng.standard_normal(1024) * 0.05).astype(np.float32)
+    c["sub"] = dict(w=sw, mel=rng.standard_normal((40, 128)).astype(np.float32), frames=40)
     return c
 
 
@@ -102,6 +127,30 @@ def main(out_path):
     mel = R.mel_log_sparse(dev(spec2), dev(offsets), dev(bins), dev(values), frames, float(F.LOG_ZERO_GUARD))
     g["fe_mel"] = host(mel)
     g["fe_norm"] = host(R.normalize_mel(mel, frames, valid, float(F.NORMALIZE_EPSILON)))
+    li = c["lin"]
+    q8 = R.quantize_int8(dev16(li["x"]), li["inv8"])
+    qf = R.quantize_fp8(dev16(li["x"]), 56.0)
+    g["lin_q8"], g["lin_qf"] = host(q8), host(qf)
+    w8, w8s = codec.quantize_rows_int8(li["w"])
+    wf, wfs = codec.quantize_rows_fp8(li["w"])
+    for act in (0, 1, 2):
+        g[f"lin_int8_act{act}"] = host(R.int8_linear(q8, dev(w8), dev(w8s), dev(li["bias"]), li["m"], li["n"], li["k"],
+                                                     1.0 / li["inv8"], act)).astype(np.float16)
+    g["lin_fp8"] = host(R.fp8_linear(qf, dev(wf), dev(wfs), dev(li["bias"]), li["m"], li["n"], li["k"],
+                                     8.0 / 448.0, 0)).astype(np.float16)
+    lp = c["lnpair"]
+    args = [dev16(lp["x"]), dev16(lp["g"][0]), dev16(lp["b"][0]), dev16(lp["g"][1]), dev16(lp["b"][1]),
+            lp["rows"], lp["padded"]]
+    first, second = R.layer_norm_pair(*args, 0.0)
+    g["lnpair_first"], g["lnpair_second"] = host(first).astype(np.float16), host(second).astype(np.float16)
+    g["lnpair_second_q"] = host(R.layer_norm_pair(*args, 56.0)[1])
+    dq, ds = R.layer_norm_quantize_fp8_dynamic(dev16(lp["x"]), dev16(lp["g"][0]), dev16(lp["b"][0]), lp["rows"], lp["padded"])
+    g["lndyn_q"], g["lndyn_s"] = host(dq), host(ds)
+    sb = c["sub"]
+    sdev = {k: (dev(v) if k in ("pw1_b", "pw2_b", "proj_b") else dev16(v)) for k, v in sb["w"].items()}
+    stages, out = R.subsampling(dev(sb["mel"]), sdev, sb["frames"])
+    g["sub_conv0"] = host(stages["conv0"]).astype(np.float16)[::7]        # every 7th (frame, feature) row
+    g["sub_out"] = host(out).astype(np.float16)
     np.savez_compressed(out_path, **g)
     print("wrote", out_path, {k: v.shape for k, v in g.items()})
 

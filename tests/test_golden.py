@@ -101,3 +101,48 @@ def test_frontend_kernels():
     assert np.max(np.abs(GOLD["fe_mel"] - want_mel)) <= 1e-4
     assert np.max(np.abs(GOLD["fe_norm"] - F.normalize(GOLD["fe_mel"], valid))) <= 1e-5
     assert not GOLD["fe_norm"][valid:].any()
+
+
+def test_scaled_linears_and_quantisers():
+    """pk_sm89_quantize_int8 / _fp8 and the INT8 / FP8 linears (kernels/sm89/linear.cu:325-429,
+    :537-560): the contract every INT8 GEMM of this build follows."""
+    c = CASES["lin"]
+    assert np.array_equal(GOLD["lin_q8"], codec.quantize_int8(c["x"], c["inv8"]))
+    assert np.array_equal(GOLD["lin_qf"], codec.quantize_fp8_fixed(c["x"], 56.0))
+    w8, w8s = codec.quantize_rows_int8(c["w"])
+    for act in (0, 1, 2):
+        want = O.linear_int8(GOLD["lin_q8"], w8, w8s, np.float32(1.0 / c["inv8"]), bias=c["bias"], act=act)
+        got = GOLD[f"lin_int8_act{act}"].astype(np.float32)
+        assert np.max(np.abs(got - want)) <= 2e-3 and np.mean(got != want) < 5e-3, act
+    wf, wfs = codec.quantize_rows_fp8(c["w"])
+    want = O.linear_fp8(GOLD["lin_qf"], wf, wfs, O.FP8_INPUT_SCALE, bias=c["bias"])
+    assert np.max(np.abs(GOLD["lin_fp8"].astype(np.float32) - want)) <= 4e-3
+
+
+def test_layer_norm_pair_and_dynamic_quantiser():
+    c = CASES["lnpair"]
+    first, second = GOLD["lnpair_first"].astype(np.float32), GOLD["lnpair_second"].astype(np.float32)
+    want1 = O.layer_norm(c["x"], c["g"][0], c["b"][0], c["rows"])
+    assert np.max(np.abs(first - want1)) <= 2.0 ** -7 and np.mean(first != want1) < 2e-3
+    want2 = O.layer_norm(first, c["g"][1], c["b"][1], c["rows"])
+    assert np.max(np.abs(second - want2)) <= 2.0 ** -7 and np.mean(second != want2) < 2e-3
+    assert np.array_equal(GOLD["lnpair_second_q"], codec.quantize_fp8_fixed(second, 56.0))
+    wq, ws = O.quant_rows_fp8_dynamic(first, c["rows"])
+    rows = c["rows"]
+    assert np.allclose(GOLD["lndyn_s"][:rows], ws[:rows], rtol=1e-6, atol=0)
+    assert np.mean(GOLD["lndyn_q"][:rows] != wq[:rows]) < 2e-3 and not GOLD["lndyn_q"][rows:].any()
+
+
+def test_subsampling_stack():
+    c = CASES["sub"]
+    w, mel = c["w"], c["mel"]
+    conv0 = codec.f16_round(np.maximum(O._conv_s2(mel[:, :, None], w["conv0_w"].reshape(256, 3, 3), w["conv0_b"]), 0))
+    got0 = GOLD["sub_conv0"].astype(np.float32)
+    want0 = conv0.reshape(-1, 256)[::7]
+    assert got0.shape == want0.shape
+    assert np.max(np.abs(got0 - want0)) <= 2e-3 and np.mean(got0 != want0) < 1e-2
+    want = O.subsampling(mel, w)
+    got = GOLD["sub_out"].astype(np.float32)
+    assert got.shape == want.shape == (5, 1024)
+    assert np.max(np.abs(got - want)) <= 2e-2
+    assert float(np.sqrt(np.mean((got - want) ** 2)) / np.sqrt(np.mean(want ** 2))) <= 2e-3

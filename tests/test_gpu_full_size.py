@@ -84,3 +84,53 @@ def test_tile_thresholds_drop_seventy_percent_of_the_tiles(pk, cuda, full_engine
         for which, tau in ((0, lw.ff1.tau), (1, lw.ff2.tau)):
             zero_fraction = float((st[l, which] < tau).mean())
             assert 0.62 <= zero_fraction <= 0.78, (l, which, zero_fraction)
+
+
+def test_twenty_four_blocks_match_the_oracle_layer_by_layer(pk, cuda, full_engine):
+    """Benchmark configuration 3 at its real depth: one 60 s utterance (T = 750, 768-row segment),
+    the benchmarked weights (seed 4) and the calibrated tile thresholds.  Every block's output is
+    held to nRMSE <= 1e-2 against the oracle run on the SAME block input (the GPU's own), the
+    free-running oracle stack (tile decisions taken from the GPU run: a threshold is a discontinuous
+    operator) to the reference's layer-stack gate nRMSE <= 3e-2 (src/cuda/encoder.rs:204-239), and
+    the tokens decoded from the GPU's projection of its own encoder output are exact."""
+    from oracle import decoder as D
+    from tests.test_gpu_encoder import _oracle_layer_same_decisions
+    eng, mel = full_engine
+    eng.mel_dev.copy_(mel)
+    rows, valid = eng.seg_stride, eng.frames_out
+    eng.sub.run(eng.mel_dev[:1], eng.seg_stride, mel_frames=eng.mel_frames_dev, out=eng.state_a)
+    cur = host(eng.state_a[:rows]).copy()
+    cur[valid:] = 0                      # rows past the utterance are "don't care" after subsampling: every consumer masks them
+    arena, ws = eng.enc.make_workspace(rows)
+    free = cur.copy()
+    worst = 0.0
+    for l, lw in enumerate(eng.enc.layers):
+        p = O.prepare_layer(pk.synth.layer_weights(4, l))
+        a, b = dev16(cur), torch.zeros((rows, 1024), dtype=torch.float16, device=cuda)
+        stats = torch.zeros((2, rows // 128 * 64), dtype=torch.float32, device=cuda)
+        out = host(eng.enc.run(a, b, ws, 1, rows, valid, tile_stats=stats, first=l, count=1)).copy()
+        st = host(stats).reshape(2, -1, 64)
+        want, _ = _oracle_layer_same_decisions(cur, p, valid, lw.ff1.tau, lw.ff2.tau, st)
+        err = nrmse(out[:valid], want[:valid])
+        worst = max(worst, err)
+        assert err <= 1e-2, (l, err)
+        free = O.encoder_layer(free, p, valid, lw.ff1.tau, lw.ff2.tau,
+                               keep1=(st[0] >= lw.ff1.tau).astype(np.uint8), keep2=(st[1] >= lw.ff2.tau).astype(np.uint8))
+        cur = out
+    assert eng.enc.status(arena, ws) == 0
+    stack = nrmse(cur[:valid], free[:valid])
+    print(f"24 blocks: worst per-layer nRMSE {worst:.2e}, free-running stack nRMSE {stack:.2e}")
+    assert stack <= 3e-2
+    # one call over the 24 blocks gives the layer-by-layer result bit for bit
+    eng.sub.run(eng.mel_dev[:1], eng.seg_stride, mel_frames=eng.mel_frames_dev, out=eng.state_a)
+    whole = eng.enc.run(eng.state_a[:rows], eng.state_b[:rows], ws, 1, rows, valid)
+    assert np.array_equal(host(whole), cur)
+    # tokens: the GPU decoder on the GPU's projection against the oracle decoder on the same rows
+    proj = eng.dec.project(whole)
+    frames = torch.tensor([valid], dtype=torch.int32, device=cuda)
+    tokens, _, counts = eng.dec.decode(proj, 1, rows, frames, eng.max_tokens)
+    torch.cuda.synchronize()
+    got = host(tokens)[0][:int(host(counts)[0])]
+    want_tokens, _, amb = D.tdt_greedy(host(proj)[:valid], pk.synth.decoder_weights(4, 1), valid)
+    n = len(want_tokens) if amb is None else amb
+    assert n > 20 and np.array_equal(got[:n], want_tokens[:n])

@@ -101,3 +101,81 @@ def test_tdt_decoder_tokens(cuda):
     assert np.array_equal(ref[:n], tokens[:n])
     if ambiguous is None:
         assert len(ref) == len(tokens)
+
+
+def test_scaled_linears_and_quantisers(cuda):
+    """pk_sm89_quantize_int8 / _fp8 and pk_sm89_int8_linear_epilogue / _fp8_linear_epilogue
+    (kernels/sm89/linear.cu:325-429, :537-560): codes bit-exact, INT8 linear exact up to the fp16
+    rounding of the scaled sum, FP8 linear within one fp16 ulp of the oracle's float64 sum."""
+    rng = np.random.default_rng(11)
+    m, n, k = 64, 256, 1024
+    x = codec.f16_round(rng.standard_normal((m, k)))
+    w = codec.f16_round(rng.standard_normal((n, k)) * 0.02)
+    bias = (0.1 * rng.standard_normal(n)).astype(np.float32)
+    inv8 = 127.0 / float(np.max(np.abs(x)))
+    q8 = host(R.quantize_int8(dev16(x), inv8))
+    assert np.array_equal(q8, codec.quantize_int8(x, inv8))
+    qf = host(R.quantize_fp8(dev16(x), 56.0))
+    assert np.array_equal(qf, codec.quantize_fp8_fixed(x, 56.0))
+    w8, w8s = codec.quantize_rows_int8(w)
+    for act in (0, 1, 2):
+        ref = host(R.int8_linear(dev(q8), dev(w8), dev(w8s), dev(bias), m, n, k, 1.0 / inv8, act))
+        want = O.linear_int8(q8, w8, w8s, np.float32(1.0 / inv8), bias=bias, act=act)
+        assert np.max(np.abs(ref - want)) <= 2e-3, act
+        assert np.mean(ref != want) < 5e-3, act        # exact integer sums: only fp32 rounding of the scaling differs
+    wf, wfs = codec.quantize_rows_fp8(w)
+    ref = host(R.fp8_linear(dev(qf), dev(wf), dev(wfs), dev(bias), m, n, k, 8.0 / 448.0, 0))
+    want = O.linear_fp8(qf, wf, wfs, O.FP8_INPUT_SCALE, bias=bias)
+    assert np.max(np.abs(ref - want)) <= 4e-3
+
+
+def test_layer_norm_pair_and_dynamic_quantiser(cuda):
+    """pk_sm89_layer_norm_pair and pk_sm89_layer_norm_quantize_fp8_dynamic
+    (kernels/sm89/encoder.cu:128-306)."""
+    rng = np.random.default_rng(12)
+    rows, padded = 45, 48
+    x = codec.f16_round(rng.standard_normal((padded, 1024)) * 2)
+    g1, g2 = [codec.f16_round(1 + 0.1 * rng.standard_normal(1024)) for _ in range(2)]
+    b1, b2 = [codec.f16_round(0.1 * rng.standard_normal(1024)) for _ in range(2)]
+    first, second = R.layer_norm_pair(dev16(x), dev16(g1), dev16(b1), dev16(g2), dev16(b2), rows, padded, 0.0)
+    first, second = host(first), host(second)
+    want1 = O.layer_norm(x, g1, b1, rows)
+    assert np.max(np.abs(first - want1)) <= 2.0 ** -7 and np.mean(first != want1) < 2e-3
+    want2 = O.layer_norm(first, g2, b2, rows)           # the second norm reads the ROUNDED first output
+    assert np.max(np.abs(second - want2)) <= 2.0 ** -7 and np.mean(second != want2) < 2e-3
+    _, second8 = R.layer_norm_pair(dev16(x), dev16(g1), dev16(b1), dev16(g2), dev16(b2), rows, padded, 56.0)
+    assert np.array_equal(host(second8), codec.quantize_fp8_fixed(second, 56.0))
+    q, s = R.layer_norm_quantize_fp8_dynamic(dev16(x), dev16(g1), dev16(b1), rows, padded)
+    q, s = host(q), host(s)
+    wq, wsc = O.quant_rows_fp8_dynamic(first, rows)      # `first` is the reference's own fp16 LayerNorm
+    assert np.allclose(s[:rows], wsc[:rows], rtol=1e-6, atol=0)
+    assert np.mean(q[:rows] != wq[:rows]) < 2e-3 and not q[rows:].any()
+    # a differing byte is a neighbouring code (the division by the row scale is not fused in numpy)
+    d = np.abs(codec.e4m3_decode(q[:rows]) - codec.e4m3_decode(wq[:rows]))
+    assert np.all(d <= 0.125 * np.abs(codec.e4m3_decode(wq[:rows])) + 2.0 ** -9)
+
+
+def test_subsampling_stack(cuda):
+    """pk_sm89_subsample_first / _depthwise / _flatten with the fp16 pointwise and projection
+    linears (kernels/sm89/subsampling.cu:11-226, src/cuda/subsampling.rs:436-804), one tile."""
+    if not R.subsampling_available():
+        pytest.skip("subsampling.cubin was not built")
+    import importlib
+    synth = importlib.import_module("l4-parakeet-rs_b200.synth")
+    frames = 203
+    w = synth.subsampling_weights(2)
+    mel = synth.mel_input(31, frames)
+    dw = {k: (dev(np.ascontiguousarray(v, dtype=np.float32)) if k in ("pw1_b", "pw2_b", "proj_b") else dev16(v))
+          for k, v in w.items()}
+    stages, out = R.subsampling(dev(mel), dw, frames)
+    f1 = (frames + 1) // 2
+    conv0 = np.maximum(O._conv_s2(mel[:, :, None], w["conv0_w"].reshape(256, 3, 3), w["conv0_b"]), 0)
+    got0 = host(stages["conv0"]).reshape(f1, 64, 256)
+    want0 = codec.f16_round(conv0)
+    assert np.max(np.abs(got0 - want0)) <= 2e-3 and np.mean(got0 != want0) < 1e-2
+    want = O.subsampling(mel, w)
+    got = host(out)
+    assert got.shape == want.shape
+    # the reference's own gate for this stage is max abs <= 2.0, nRMSE <= 0.002 (src/cuda/subsampling.rs:375)
+    assert np.max(np.abs(got - want)) <= 2e-2
+    assert float(np.sqrt(np.mean((got - want) ** 2)) / np.sqrt(np.mean(want ** 2))) <= 2e-3

@@ -51,6 +51,16 @@ def test_static_scratch_decoder_matches_regular_entry_point(pk, cuda):
         rc, tokens, durations, counts, status = _decode_static(pk, dec, enc_d, utterances, seg_stride, fr, max_tokens)
         torch.cuda.synchronize()
         assert rc == 0 and int(status.item()) == 0
+        # the property the entry point exists for: with every buffer already in the caller's hands
+        # (here: reused), a further call leaves the device's free memory untouched
+        free_before, _ = torch.cuda.mem_get_info()
+        fn = pk.lib.lib.pk100_tdt_decode_static
+        rc2 = fn(torch.cuda.current_stream().cuda_stream, C.byref(dec.c), enc_d.data_ptr(), utterances, seg_stride,
+                 fr.data_ptr(), tokens.data_ptr(), durations.data_ptr(), counts.data_ptr(), max_tokens,
+                 status.data_ptr())
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert rc2 == 0 and free_after == free_before
         counts = counts.cpu().numpy()
         assert np.array_equal(counts, want_c) and counts.max() > 10
         for u in range(utterances):
