@@ -54,6 +54,13 @@ def parse_args():
                     choices=["ff_expand", "ff_contract", "qkv", "attention", "layer_norm", "depthwise", "decode"],
                     help="time ONE kernel of the path on synthetic operands (used for ncu captures)")
     ap.add_argument("--rows", type=int, default=6144, help="rows (M) of the --micro case")
+    ap.add_argument("--utterances", type=int, default=UTTERANCES_PER_GPU,
+                    help="utterances per GPU and step (8 = benchmark configuration 4; 1 = configuration 3, "
+                         "the batch-1 encoder + decode)")
+    ap.add_argument("--decode-groups", type=int, default=2,
+                    help="groups the batch is cut into so that a group's decode overlaps the next group's encode")
+    ap.add_argument("--no-reference-kernels", action="store_true",
+                    help="skip the timing of the reference's own kernels (oracle/_ref) beside this build's")
     return ap.parse_args()
 
 
@@ -123,13 +130,30 @@ class ClockSampler:
                     reasons=sorted(reasons), samples=len(sm))
 
 
+def load_synth():
+    """The seeded synthetic tensors (l4-parakeet-rs_b200/synth.py) loaded by file path: the CPU arms
+    need the same weights as the GPU arm without importing the package, which would map libpk100.so
+    into a process that must not touch it."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("pk100_synth", ROOT / "l4-parakeet-rs_b200" / "synth.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 class CpuReference:
-    """The CPU restatement of the path (oracle/) timed on the host cores on a bounded sample
-    of one utterance, extrapolated to one whole utterance."""
+    """The CPU restatement of the path (oracle/) timed on the host cores: torch fp32 matmuls on all
+    host threads for the GEMMs and the attention, numpy for the bit-exact quantisers (the oracle's
+    timing mode; its parity mode accumulates in float64).  `sample()` times a bounded sample of one
+    utterance and extrapolates; `whole()` runs one whole utterance."""
 
     def __init__(self, synth, layers_total, decoder_layers, sample_layers=1, sample_frames=100):
+        import torch
         from oracle import ops as O
+        torch.set_num_threads(os.cpu_count() or 1)
+        O.set_timing_mode(True)
         self.layers_total, self.sample_layers, self.sample_frames = layers_total, sample_layers, sample_frames
+        self.synth, self.decoder_layers = synth, decoder_layers
         self.mel = synth.mel_input(100, MEL_FRAMES)
         self.sub_w = synth.subsampling_weights(SEED)
         self.prepared = [O.prepare_layer(synth.layer_weights(SEED, l)) for l in range(sample_layers)]
@@ -144,7 +168,21 @@ class CpuReference:
                 f"x4), {self.sample_layers} of {self.layers_total} encoder blocks at T={parts['frames']} "
                 f"({parts['layers_s']:.2f} s, scaled x{self.layers_total // self.sample_layers}), projection, "
                 f"{parts['sample_frames']} of {parts['frames']} decoder frames ({parts['decoder_s']:.2f} s, "
-                f"scaled); numpy float64 GEMMs on all host threads")
+                f"scaled); torch fp32 matmuls on all host threads + numpy quantisers")
+        return AUDIO_SECONDS / total_s, what
+
+    def whole(self):
+        """One whole 60 s utterance, nothing extrapolated (about 20-30 s of CPU work)."""
+        from oracle import ops as O, pipeline as P
+        prepared = self.prepared + [O.prepare_layer(self.synth.layer_weights(SEED, l))
+                                    for l in range(len(self.prepared), self.layers_total)]
+        taus = [(0.0, 0.0)] * self.layers_total
+        t0 = time.perf_counter()
+        tokens, _, _ = P.transcribe(self.mel, self.sub_w, prepared, taus, self.dec_w)
+        total_s = time.perf_counter() - t0
+        what = (f"1 whole 60 s utterance of the 8 (subsampling, {self.layers_total} encoder blocks at T=750, projection, "
+                f"TDT greedy decode of {len(tokens)} tokens; tile thresholds off) in {total_s:.1f} s; torch fp32 "
+                f"matmuls on all host threads + numpy quantisers")
         return AUDIO_SECONDS / total_s, what
 
 
@@ -154,7 +192,7 @@ def run_reference(args, rank):
     built here, so this arm times the CPU restatement of the same path (oracle/)."""
     if rank != 0:
         return
-    pk_cpu = importlib.import_module("l4-parakeet-rs_b200.synth")
+    pk_cpu = load_synth()
 
     values, sample = [], ""
     ref = CpuReference(pk_cpu, args.layers, args.decoder_layers)
@@ -169,7 +207,7 @@ def run_reference(args, rank):
     cores = os.cpu_count()
     line = dict(impl="reference", metric=METRIC, value=value, unit="x real time", n_gpus=args.gpus,
                 steps=args.steps, warmup=args.warmup, ms_per_step=wall / args.steps * 1e3,
-                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f64 (CPU restatement)",
+                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32 (CPU restatement)",
                 data="synthetic",
                 config=workload_config(args),
                 cpu_baseline=dict(value=value, unit="x real time", cores=cores, kind="port", sample=sample),
@@ -180,10 +218,13 @@ def run_reference(args, rank):
 
 def workload_config(args):
     return dict(
-        workload=("end-to-end TDT transcription, per-GPU share of 64 x 60 s utterances over 8 GPUs: 8 x 60 s utterances (mel [6000,128] ~N(0,1), seeds 100+u) "
+        workload=((f"end-to-end TDT transcription, per-GPU share of 64 x 60 s utterances over 8 GPUs: 8 x 60 s utterances "
+                   "(mel [6000,128] ~N(0,1), seeds 100+u) " if args.utterances >= UTTERANCES_PER_GPU else
+                   f"24-block encoder + TDT decode, batch {args.utterances} x 60 s (benchmark configuration 3 at batch 1) ") +
                   "-> 8x conv subsampling -> 24-block FastConformer encoder (T=750 per utterance, 768-row "
-                  "segments, batch M=6144) -> TDT greedy decode"),
-        utterances_per_gpu=UTTERANCES_PER_GPU, audio_seconds_per_utterance=AUDIO_SECONDS,
+                  "segments) -> TDT greedy decode"),
+        utterances_per_gpu=min(args.utterances, UTTERANCES_PER_GPU), audio_seconds_per_utterance=AUDIO_SECONDS,
+        decode_groups=args.decode_groups,
         encoder_layers=args.layers, decoder_lstm_layers=args.decoder_layers,
         precision_map=("FF: E4M3 x E4M3 expand + SiLU + 70% zero 128x64 tiles -> INT8 x INT8 contract with "
                        "tile skip; QKV INT8; out-proj INT4-g128 (fp16 MMA); conv pointwise E4M3; attention fp16"),
@@ -333,6 +374,203 @@ def run_micro(args):
     print(json.dumps(line), flush=True)
 
 
+def time_device(call, iters, warmup=20, samples=7):
+    """Median device time of one `call` in ms (CUDA events; the reference's protocol,
+    src/cuda.rs:574-618: >= 20 warm-ups, 7 samples of `iters` back-to-back launches, median).  The
+    launches of a sample are replayed from a CUDA graph so that host-side launch cost stays out."""
+    import torch
+    for _ in range(warmup):
+        call()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(iters):
+                call()
+        graph.replay()
+        side.synchronize()
+        times = []
+        for _ in range(samples):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(side)
+            graph.replay()
+            e1.record(side)
+            side.synchronize()
+            times.append(e0.elapsed_time(e1) / iters)
+    return statistics.median(times)
+
+
+def measure_tensor_peaks(dev):
+    """Same-run library GEMM rates at 8192^3: cuBLASLt E4M3 (torch._scaled_mm) and INT8
+    (torch._int_mm), burst (best of 10) and sustained (back to back for about a second)."""
+    import torch
+    n = 8192
+    out = {}
+    cases = {}
+    try:
+        a8 = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        b8 = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        one = torch.ones((), device=dev)
+        cases["fp8_e4m3"] = lambda: torch._scaled_mm(a8, b8.t(), scale_a=one, scale_b=one, out_dtype=torch.float16)
+    except Exception as exc:  # noqa: BLE001
+        out["fp8_e4m3"] = dict(unavailable=str(exc)[:120])
+    try:
+        ai = torch.randint(-100, 100, (n, n), device=dev, dtype=torch.int8)
+        bi = torch.randint(-100, 100, (n, n), device=dev, dtype=torch.int8)
+        cases["int8"] = lambda: torch._int_mm(ai, bi.t())
+    except Exception as exc:  # noqa: BLE001
+        out["int8"] = dict(unavailable=str(exc)[:120])
+    for name, fn in cases.items():
+        try:
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            best = 1e9
+            for _ in range(10):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                best = min(best, e0.elapsed_time(e1))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(10, int(1000.0 / best))
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            flop = 2.0 * n ** 3
+            out[name] = dict(burst_tops=flop / (best * 1e-3) / 1e12,
+                             sustained_tops=flop / (e0.elapsed_time(e1) / reps * 1e-3) / 1e12, shape=f"{n}^3")
+        except Exception as exc:  # noqa: BLE001
+            out[name] = dict(unavailable=str(exc)[:120])
+    return out
+
+
+def reference_kernel_times(pk, dev):
+    """The reference's own kernels (kernels/sm89/*.cu compiled for sm_100a into oracle/_ref/ by
+    oracle/build_ref.py), launched the way its Rust host launches them, timed beside this build's
+    kernel for the same operator on the same operands: the "kernel to beat" on this GPU.  A checker
+    leg like the CPU baseline; nothing here is on the product path."""
+    import numpy as np
+    import torch
+    try:
+        from oracle import refkernels as R
+    except Exception as exc:  # noqa: BLE001 - cuda-python absent
+        return dict(unavailable=f"oracle.refkernels cannot be imported: {str(exc)[:80]}")
+    if not R.available():
+        return dict(unavailable="oracle/_ref/*.cubin not built (no reference checkout at build time)")
+    L = pk.lib
+    g = torch.Generator(device="cpu").manual_seed(7)
+    r16 = lambda *shape, std=1.0: (torch.randn(shape, generator=g) * std).half().to(dev)
+    ones, zeros = torch.ones(1024, device=dev), torch.zeros(1024, device=dev)
+    rows_out = {}
+    for rows in (752, 6144):
+        seg = 768 if rows % 768 == 0 else rows
+        valid = 750 if seg == 768 else rows - 2
+        x = r16(rows, 1024)
+        gam, bet = ones.half(), zeros.half()
+        w1 = r16(4096, 1024, std=0.02)
+        xq = pk.ops.quantize_fp8_fixed(x, 56.0)
+        w1q, w1s = pk.ops.pack_weight_rows(w1, L.PACK_E4M3)
+        h16 = torch.empty((rows, 4096), dtype=torch.float16, device=dev)
+        wqkv = r16(3072, 1024, std=0.02)
+        x8, x8s = pk.ops.layer_norm(x, gam, bet, L.LN_S8_ROW)
+        wq8, wq8s = pk.ops.pack_weight_rows(wqkv, L.PACK_S8)
+        qkv = torch.empty((rows, 3072), dtype=torch.float16, device=dev)
+        bias3 = torch.zeros(3072, device=dev)
+        wo = r16(1024, 1024, std=0.02)
+        o16 = torch.empty((rows, 1024), dtype=torch.float16, device=dev)
+        e = r16(rows, 2048)
+        wdw = r16(1024, 9, std=0.3)
+        pos, bu, bv = r16(8, 272, 128), r16(8, 128, std=0.02), r16(8, 128, std=0.02)
+        att = torch.empty((rows, 1024), dtype=torch.float16, device=dev)
+        glu = pk.ops.glu_masked(e, seg_stride=seg, valid_rows=valid)
+        ops = {
+            "layer_norm": (lambda: R.layer_norm(x, gam, bet, rows, rows),
+                           lambda: pk.ops.layer_norm(x, gam, bet, L.LN_F16, out=o16), "pk_sm89_layer_norm"),
+            "ff_expand_fp8_silu": (lambda: R.ffn_expand_fp8(xq, w1q, w1s, rows),
+                                   lambda: pk.ops.gemm(xq, w1q, kind=L.KIND_E4M3, out=h16, row_scale=8.0 / 448.0,
+                                                       col_scales=w1s, act=L.ACT_SILU),
+                                   "pk_sm89_ffn_expand_fp8_async"),
+            "qkv_int8_linear": (lambda: R.int8_linear(x8, wq8, wq8s, bias3, rows, 3072, 1024, 0.01),
+                                lambda: pk.ops.gemm(x8, wq8, kind=L.KIND_S8, out=qkv, row_scales=x8s, col_scales=wq8s),
+                                "pk_sm89_int8_linear_epilogue"),
+            "fp16_linear_1024": (lambda: R.fp16_linear(x, wo, None, None, rows, 1024, 1024),
+                                 lambda: pk.ops.gemm(x, wo, kind=L.KIND_F16, out=o16), "pk_sm89_fp16_linear_epilogue"),
+            "glu_masked": (lambda: R.glu_masked(e, rows, rows, valid), lambda: pk.ops.glu_masked(e, seg, valid),
+                           "pk_sm89_glu_masked"),
+            "depthwise_bn_silu": (lambda: R.depthwise_bn_silu(glu, wdw, ones, zeros, zeros, ones, rows, rows),
+                                  lambda: pk.ops.depthwise_bn_silu(glu, wdw, ones, zeros, zeros, ones, seg_stride=seg,
+                                                                   valid_rows=valid),
+                                  "pk_sm89_depthwise_batchnorm_silu"),
+            "local_attention": (lambda: R.local_attention_scalar(qkv[:, :1024].contiguous(), qkv[:, 1024:2048].contiguous(),
+                                                                 qkv[:, 2048:].contiguous(), pos, bu, bv, rows, rows, rows),
+                                lambda: pk.ops.local_attention(qkv[:, :1024], qkv[:, 1024:2048], qkv[:, 2048:], pos, bu, bv,
+                                                               seg_stride=seg, valid_rows=valid, out=att),
+                                "pk_sm89_local_relpos_attention (its fp32 scalar kernel; the reference's T=750 kernel "
+                                "_tc_scores needs its FP8 V repack and is not launched here)"),
+        }
+        pk.ops.gemm(x8, wq8, kind=L.KIND_S8, out=qkv, row_scales=x8s, col_scales=wq8s)
+        res = {}
+        for name, (ref_call, own_call, ref_name) in ops.items():
+            try:
+                slow = name == "local_attention" or name == "fp16_linear_1024"
+                iters = 2 if (slow and rows > 1000) else 10
+                ref_ms = time_device(ref_call, iters, warmup=20 if not slow else 3)
+                own_ms = time_device(own_call, 10)
+                res[name] = dict(reference_us=ref_ms * 1e3, this_build_us=own_ms * 1e3, reference_kernel=ref_name,
+                                 speedup=ref_ms / own_ms)
+            except Exception as exc:  # noqa: BLE001
+                res[name] = dict(unavailable=str(exc)[:120])
+        rows_out[f"rows_{rows}"] = res
+    # decoder: one 120-frame request through the reference's cooperative kernel and through this build's
+    try:
+        from oracle import decoder as D
+        from oracle import codec
+        w = D.make_decoder_weights(7, layers=2)
+        rng = np.random.default_rng(8)
+        frames = 120
+        enc = torch.from_numpy(codec.f16_round(rng.standard_normal((frames, 640)) * 0.5)).half().to(dev)
+        dw = {k: (torch.from_numpy(np.ascontiguousarray(v)).to(dev) if k.startswith("b_")
+                  else torch.from_numpy(np.ascontiguousarray(v, dtype=np.float32)).half().to(dev))
+              for k, v in w.items() if k != "layers"}
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+
+        def timed(fn, reps=5):
+            fn()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(reps):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out = fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            return statistics.median(ts), out
+        ref_ms, ref_tokens = timed(lambda: R.tdt_decode(enc, dw, frames, sms))
+        dec = pk.decoder.TdtDecoder(w, dev)
+        fr = torch.tensor([frames], dtype=torch.int32, device=dev)
+        own_ms, own = timed(lambda: dec.decode(enc, 1, frames, fr, frames * 10))
+        steps = frames + len(ref_tokens)
+        rows_out["tdt_decode_120_frames"] = dict(
+            reference_kernel="pk_sm89_tdt_persistent_v2 (cooperative, one grid barrier per step)",
+            reference_ms=ref_ms, this_build_ms=own_ms, steps=steps, reference_us_per_step=ref_ms * 1e3 / steps,
+            this_build_us_per_step=own_ms * 1e3 / steps, speedup=ref_ms / own_ms,
+            note="whole call: this build's figure includes its per-call weight packing and input-table GEMM")
+    except Exception as exc:  # noqa: BLE001
+        rows_out["tdt_decode_120_frames"] = dict(unavailable=str(exc)[:120])
+    rows_out["protocol"] = ("CUDA events, warm-up, 7 samples x N graph-replayed launches, median (src/cuda.rs:574-618); "
+                            "reference kernels compiled unmodified for sm_100a")
+    return rows_out
+
+
+DATASHEET_FP8_DENSE_TFLOPS = 4500.0      # B200 dense FP8 / INT8 (NVIDIA datasheet, HGX B200 per-GPU figure)
+
+
 def main():
     args = parse_args()
     if args.micro:
@@ -360,10 +598,12 @@ def main():
         dist.init_process_group("nccl", device_id=device)
         gloo = dist.new_group(backend="gloo")
 
-    total_utts = UTTERANCES_PER_GPU * world
+    per_gpu = max(1, min(args.utterances, UTTERANCES_PER_GPU))
+    total_utts = per_gpu * world
     my_utts = pk.parallel.shard_utterances(total_utts, world, rank)
     eng = pk.pipeline.PipelineEngine(device, layers=args.layers, decoder_layers=args.decoder_layers,
-                                     seed=SEED, max_utterances=UTTERANCES_PER_GPU, mel_frames=MEL_FRAMES)
+                                     seed=SEED, max_utterances=per_gpu, mel_frames=MEL_FRAMES,
+                                     decode_groups=args.decode_groups)
     mel_host = torch.from_numpy(np.stack([pk.synth.mel_input(100 + u, MEL_FRAMES) for u in my_utts])).pin_memory()
     eng.mel_dev.copy_(mel_host)
     cache = Path(args.tau_cache) if args.tau_cache else None
@@ -372,10 +612,11 @@ def main():
         for l, (t1, t2) in enumerate(taus):
             eng.enc.set_tau(l, t1, t2)
     else:
-        eng.calibrate(UTTERANCES_PER_GPU)      # load-time: tile thresholds for 70 % zero tiles
+        eng.calibrate(per_gpu)      # load-time: tile thresholds for 70 % zero tiles
         if cache is not None and rank == 0:
             cache.write_text(json.dumps([[l.ff1.tau, l.ff2.tau] for l in eng.enc.layers]))
     eng.enable_gemm_timing()
+    eng.enable_stage_timing()
     torch.cuda.synchronize()
 
     def sync_all():
@@ -409,12 +650,14 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        eng.run_resident(UTTERANCES_PER_GPU)
+        eng.run_resident(per_gpu)
     e1.record()
     sync_all()
     launches = pk.lib.lib.pk100_launch_count() - launches0
-    ms_resident = max_over_ranks(e0.elapsed_time(e1)) / args.steps
-    gemm_ms = eng.gemm_times_ms()                      # the last step's 48 FF-expand launches
+    own_ms_resident = e0.elapsed_time(e1) / args.steps
+    ms_resident = max_over_ranks(own_ms_resident)
+    gemm_ms = eng.gemm_times_ms()                      # (ms, rows) of every FF-expand launch of the last step
+    stages = eng.stage_times()                         # per decode group of the last step
 
     # ---- timed: end to end through the public API (host buffers, copies inside)
     sync_all()
@@ -434,11 +677,33 @@ def main():
     value = audio_per_step / (ms_resident / 1e3)
     e2e_value = audio_per_step / (ms_e2e / 1e3)
 
-    # ---- roofline of the dominant kernel: FF expand (E4M3 tcgen05 GEMM + SiLU + tile threshold)
+    # ---- the decoder: the sequential chain that bounds the step.  A round = one joint evaluation
+    # per live utterance; an utterance needs (frames + tokens) rounds, the batch as many as its longest.
+    dec_rounds = sum(s["rounds"] for s in stages)
+    dec_ms = sum(s["decode_ms"] for s in stages)
+    longest = max(s["rounds"] for s in stages)
+    mine = dict(rank=rank, ms_per_step=own_ms_resident, longest_chain_rounds=longest, groups=stages,
+                decode_us_per_round=dec_ms * 1e3 / max(dec_rounds, 1),
+                decode_end_ms=max(s["decode_end_ms"] for s in stages),
+                encode_ms=sum(s["encode_ms"] for s in stages))
+    per_rank = [mine]
+    if world > 1:
+        per_rank = [None] * world
+        dist.all_gather_object(per_rank, mine, group=gloo)
+    decoder = dict(kernel="tdt_cluster_kernel (one 16-CTA cluster per decode group)",
+                   decode_groups=len(stages), rounds=dec_rounds, decode_ms=dec_ms,
+                   us_per_round=mine["decode_us_per_round"], longest_chain_rounds=longest,
+                   share_of_step=max(s["decode_end_ms"] - s["decode_start_ms"] for s in stages) / own_ms_resident,
+                   note=("rank 0, last timed step; a round = one joint evaluation per live utterance (a token or a "
+                         "blank), the groups decode side by side; the step ends when the slowest group's chain ends: "
+                         "ms_per_step ~ that group's decode_start_ms + its rounds x us_per_round"))
+
+    # ---- roofline of the designated kernel: FF expand (E4M3 tcgen05 GEMM + SiLU + tile threshold)
     peaks = measured_peaks()
-    rows = UTTERANCES_PER_GPU * eng.seg_stride
+    # every FF-expand launch of the last timed step (all groups): total flops / total time
+    rows = sum(r for _, r in gemm_ms) / len(gemm_ms)
     flops = 2.0 * rows * 4096 * 1024
-    gemm_avg_ms = sum(gemm_ms) / len(gemm_ms)
+    gemm_avg_ms = sum(ms for ms, _ in gemm_ms) / len(gemm_ms)
     achieved = flops / (gemm_avg_ms * 1e-3) / 1e12
     fp8_peak = 2.0 * peaks["bf16_sustained"]
     roofline = dict(
@@ -446,13 +711,14 @@ def main():
         achieved=achieved, peak=fp8_peak, unit="TFLOP/s", frac=achieved / fp8_peak,
         peak_note=(f"2 x {peaks['bf16_sustained']} TFLOP/s: MEASURED_PEAKS.json ({peaks['source']}) holds the "
                    "sustained cuBLAS bf16 figure only; E4M3 runs at twice the bf16 rate on this part"),
-        launches_timed=len(gemm_ms), avg_launch_ms=gemm_avg_ms,
+        frac_datasheet=achieved / DATASHEET_FP8_DENSE_TFLOPS, datasheet_peak=DATASHEET_FP8_DENSE_TFLOPS,
+        launches_timed=len(gemm_ms), avg_launch_ms=gemm_avg_ms, rows_per_launch=rows,
         flops_per_launch=flops,
-        # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel at 32768 rows
-        # (profiles/gemm_ff_expand_rows32768_full.md), scaled to this launch by its rows: operand and
-        # output bytes all grow in proportion to the rows except the 4 MB of weights
+        # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel at 32768 rows,
+        # scaled to this launch by its rows: operand and output bytes all grow in proportion to the
+        # rows except the 4 MB of weights
         traffic=NCU_DRAM_BYTES_AT_32768_ROWS * rows / 32768.0,
-        traffic_note="scaled from an ncu capture at 32768 rows; inside the step the 36 MB of a launch are largely L2 hits")
+        traffic_note="scaled from an ncu capture at 32768 rows; inside the step the bytes of a launch are largely L2 hits")
 
     line = dict(metric=METRIC, value=value, unit="x real time", n_gpus=world, steps=args.steps,
                 warmup=args.warmup, ms_per_step=ms_resident, higher_is_better=True, scaling="weak",
@@ -461,11 +727,24 @@ def main():
                 e2e=dict(value=e2e_value, unit="x real time", ms_per_step=ms_e2e,
                          h2d_bytes_per_step=int(mel_host.numel() * 4),
                          d2h_bytes_per_step=int(eng.tokens_host.numel() * 4 + eng.counts_host.numel() * 4)),
-                gpu_launches=int(launches), roofline=roofline,
+                gpu_launches=int(launches), roofline=roofline, decoder=decoder, per_rank=per_rank,
+                tensor_map_cache=dict(zip(("hits", "misses"), pk.lib.tensor_map_cache_stats())),
                 tokens_per_utterance=[int(len(t)) for t in tokens])
 
+    if rank == 0:
+        # same-run library rates: the measured FP8 / INT8 denominators MEASURED_PEAKS.json lacks
+        lib_peaks = measure_tensor_peaks(device)
+        line["peaks"] = dict(library_8192=lib_peaks, datasheet_fp8_int8_dense_tops=DATASHEET_FP8_DENSE_TFLOPS,
+                             measured_file=dict(bf16_tflops=peaks["bf16"], bf16_tflops_sustained=peaks["bf16_sustained"],
+                                                hbm_gbs=peaks["hbm_gbs"], source=peaks["source"]))
+        fp8 = lib_peaks.get("fp8_e4m3", {})
+        if "sustained_tops" in fp8:
+            roofline["frac_measured_fp8"] = achieved / fp8["sustained_tops"]
+            roofline["measured_fp8_peak"] = fp8["sustained_tops"]
+    if rank == 0 and world == 1 and not args.no_reference_kernels:
+        line["reference_kernels"] = reference_kernel_times(pk, device)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        v, sample = CpuReference(pk.synth, args.layers, args.decoder_layers).sample()
+        v, sample = CpuReference(load_synth(), args.layers, args.decoder_layers).whole()
         line["cpu_baseline"] = dict(value=v, unit="x real time", cores=os.cpu_count(), kind="port", sample=sample)
     if rank == 0:
         print(json.dumps(line), flush=True)

@@ -124,6 +124,17 @@ int pk100_gemm(void* stream, const pk100_gemm_args* args);
  * 256 x 256 tiles); default 0 = one CTA per 128 x 256 tile, which measured faster on B200. */
 void pk100_set_gemm_cta_pairs(int enable);
 
+/* Process-wide cap on the persistent CTAs of every pk100_gemm launch whose own max_ctas is <= 0
+ * (the sequencers pk100_run_layers / pk100_run_subsampling included); 0 = one CTA per SM.  For a
+ * host that keeps another persistent kernel resident beside the encoder (the cluster decoder holds
+ * 16 SMs per call): persistent GEMM CTAs that cannot be placed at once queue behind the first wave
+ * and double the kernel's time, a smaller grid does not.  Takes effect on launches issued after it. */
+void pk100_set_gemm_cta_cap(int ctas);
+
+/* Tensor maps (TMA descriptors) are cached per (pointer, shape, leading dimension, box): hits and
+ * misses of that cache since the library was loaded.  Either pointer may be NULL. */
+void pk100_tensor_map_cache_stats(long long* hits, long long* misses);
+
 /* Number of kernels this library has launched in the calling process (monotonic). */
 long long pk100_launch_count(void);
 
@@ -292,6 +303,13 @@ typedef struct pk100_decoder_weights {
 
 /* Scratch bytes for `utterances` (<= PK100_DECODER_MAX_UTTERANCES); 0 if out of range. */
 long long pk100_tdt_workspace_bytes(int utterances);
+
+/* Byte offset inside the workspace of an int32 that the cluster and exchange kernels set, when they
+ * finish, to the number of lockstep rounds the call took (a round = one joint evaluation per live
+ * utterance; the latency unit of the decoder: src/cuda/decoder.rs:274-353 has one grid barrier per
+ * such step).  -1 when `utterances` is out of range.  For measurement; the grid-barrier kernel
+ * leaves the word at zero. */
+long long pk100_tdt_rounds_offset(int utterances);
 
 /* Decodes `utterances` sequences in lockstep.  Chooses the cluster kernel when the device can
  * host a 16-CTA cluster, else the exchange kernel (both
@@ -464,6 +482,34 @@ int pk100_encode_fp16_linear(const float* source, long long logical_out, long lo
 int pk100_encode_fp32_bias(const float* source, long long logical, long long padded, float* out);
 /* Returns 0 and sets *overflow (may be NULL) when the rounded value does not fit 64 bits. */
 unsigned long long pk100_align_up(unsigned long long value, unsigned long long alignment, int* overflow);
+
+/* ------------------------------------------------------------------------
+ * Packed-layout size contract: padded shapes and byte counts of the candidate weight formats
+ * (host code, pure integers).  Replaces LinearFormat / LinearLayout / estimate_linear /
+ * TILE_ALIGNMENT (src/packing.rs:5-130) and Exl3Layout (src/exl3.rs:14-75), with which a host
+ * sizes weight buffers before anything is packed.
+ *   FP16: 2 * in^128 * out^128 payload bytes; FP8_E4M3 / INT8: in^128 * out^128 payload + 4 * out^128
+ *   bytes of fp32 row scales; Q4_K: out * (in / 256) * 144 bytes, unpadded, not available when
+ *   in % 256 != 0 (`available` = 0, the reference's Ok(None)); EXL3: in^128 * out^128 * bits / 8
+ *   trellis bytes + 2 * (in^128 + out^128) scale bytes, trellis shape [in^128/16, out^128/16, 16*bits].
+ * Errors: PK100_ERR_SHAPE for a zero dimension (PackingError::Empty), PK100_ERR_UNSUPPORTED for an
+ * unknown format or an EXL3 rate outside 1..8 bits (InvalidBitRate), PK100_ERR_LIMIT on overflow. */
+enum {
+    PK100_FORMAT_FP16 = 0, PK100_FORMAT_FP8_E4M3 = 1, PK100_FORMAT_INT8 = 2,
+    PK100_FORMAT_Q4_K = 3, PK100_FORMAT_EXL3 = 4
+};
+typedef struct pk100_linear_layout {
+    long long logical_in, logical_out, padded_in, padded_out;
+    unsigned long long payload_bytes, metadata_bytes;
+    int available;
+} pk100_linear_layout;
+typedef struct pk100_exl3_layout_t {
+    long long padded_in, padded_out, trellis_shape[3];
+    unsigned long long trellis_bytes, scale_bytes;
+} pk100_exl3_layout_t;
+int pk100_estimate_linear(int format, long long logical_in, long long logical_out, int exl3_bits,
+                          pk100_linear_layout* out);
+int pk100_exl3_layout(long long logical_in, long long logical_out, int qbits, pk100_exl3_layout_t* out);
 
 /* ------------------------------------------------------------------------
  * Log-mel frontend: PCM fp32 [utterances, sample_stride] (sample_counts[u] samples each,

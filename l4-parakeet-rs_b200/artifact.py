@@ -206,3 +206,48 @@ def align_up(value, alignment):
     if overflow.value:
         raise ArtifactError(ERR_FORMAT, "alignment overflow")
     return int(out)
+
+
+# ---- packed-layout size contract (src/packing.rs:71-130, src/exl3.rs:38-75) ----
+
+FORMATS = {"fp16": 0, "fp8_e4m3": 1, "int8": 2, "q4_k": 3, "exl3": 4}
+
+
+class LinearLayoutC(C.Structure):
+    _fields_ = [("logical_in", C.c_longlong), ("logical_out", C.c_longlong), ("padded_in", C.c_longlong),
+                ("padded_out", C.c_longlong), ("payload_bytes", C.c_ulonglong), ("metadata_bytes", C.c_ulonglong),
+                ("available", C.c_int)]
+
+
+class Exl3LayoutC(C.Structure):
+    _fields_ = [("padded_in", C.c_longlong), ("padded_out", C.c_longlong), ("trellis_shape", C.c_longlong * 3),
+                ("trellis_bytes", C.c_ulonglong), ("scale_bytes", C.c_ulonglong)]
+
+
+_l.pk100_estimate_linear.argtypes = [C.c_int, C.c_longlong, C.c_longlong, C.c_int, C.POINTER(LinearLayoutC)]
+_l.pk100_estimate_linear.restype = C.c_int
+_l.pk100_exl3_layout.argtypes = [C.c_longlong, C.c_longlong, C.c_int, C.POINTER(Exl3LayoutC)]
+_l.pk100_exl3_layout.restype = C.c_int
+
+
+def estimate_linear(fmt, logical_in, logical_out, exl3_bits=4):
+    """`estimate_linear`: dict of padded shape and byte counts, or None where the format has no
+    layout for this shape (Q4_K with K % 256 != 0)."""
+    out = LinearLayoutC()
+    rc = _l.pk100_estimate_linear(FORMATS[fmt], logical_in, logical_out, exl3_bits, C.byref(out))
+    if rc != 0:
+        raise ValueError("linear dimensions must be nonzero" if rc == -2 else f"estimate_linear: error {rc}")
+    if not out.available:
+        return None
+    return dict(padded_in=out.padded_in, padded_out=out.padded_out, payload_bytes=out.payload_bytes,
+                metadata_bytes=out.metadata_bytes)
+
+
+def exl3_layout(logical_in, logical_out, qbits):
+    out = Exl3LayoutC()
+    rc = _l.pk100_exl3_layout(logical_in, logical_out, qbits, C.byref(out))
+    if rc != 0:
+        raise ValueError("linear dimensions must be nonzero" if rc == -2 else
+                         f"EXL3 supports integer rates from 1 through 8 bpw, got {qbits}")
+    return dict(padded_in=out.padded_in, padded_out=out.padded_out, trellis_shape=list(out.trellis_shape),
+                trellis_bytes=out.trellis_bytes, scale_bytes=out.scale_bytes)

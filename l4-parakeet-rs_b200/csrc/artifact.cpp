@@ -69,7 +69,20 @@ struct Json {
             if (m.first == key) return &m.second;
         return nullptr;
     }
+    // How often `key` occurs: the header and the tensor records are serde-derived structs in the
+    // reference (src/artifact.rs:30-60), which refuse a field given twice ("duplicate field")
+    // while repeated unknown keys are ignored like any unknown key.
+    int count(const char* key) const {
+        int n = 0;
+        for (const auto& m : members) n += m.first == key ? 1 : 0;
+        return n;
+    }
 };
+
+void reject_duplicate_fields(const Json& object, std::initializer_list<const char*> fields) {
+    for (const char* key : fields)
+        if (object.count(key) > 1) invalid(std::string("header: duplicate field `") + key + "`");
+}
 
 class JsonParser {
 public:
@@ -402,6 +415,9 @@ void load(pk100_artifact& a, const char* path) {
 
     const Json header = JsonParser(reinterpret_cast<const char*>(a.map + kPrefixBytes), header_bytes).parse_document();
     if (header.kind != Json::Object) invalid("header: not a JSON object");
+    reject_duplicate_fields(header, {"schema_version", "target", "profile", "source_repository", "source_revision",
+                                     "source_payload_bytes", "precision_plan", "tensor_alignment", "payload_bytes",
+                                     "vocabulary", "tensors"});
 
     if (need_unsigned(header, "schema_version", "header") != kSchemaVersion)
         invalid("header schema is " + std::to_string(need_unsigned(header, "schema_version", "header")) +
@@ -444,6 +460,7 @@ void load(pk100_artifact& a, const char* path) {
     uint64_t cursor = 0;
     for (const Json& record : tensors->items) {
         if (record.kind != Json::Object) invalid("header: tensor record is not an object");
+        reject_duplicate_fields(record, {"name", "storage", "logical_shape", "physical_shape", "offset", "bytes"});
         Tensor t;
         const Json* name = record.get("name");
         if (name == nullptr || name->kind != Json::String) invalid("header: tensor record without a name");
@@ -629,4 +646,83 @@ extern "C" unsigned long long pk100_align_up(unsigned long long value, unsigned 
     const bool ok = align_up_checked(value, alignment, &out);
     if (overflow != nullptr) *overflow = ok ? 0 : 1;
     return ok ? out : 0;
+}
+
+// ---------------------------------------------------------------------------
+// Packed-layout size contract (src/packing.rs:5-130, src/exl3.rs:14-75): byte counts and padded
+// shapes of the five candidate weight formats.  Pure integer arithmetic with overflow checks.
+namespace {
+constexpr uint64_t kTileAlignment = 128;      // TILE_ALIGNMENT, HADAMARD_BLOCK, OUTPUT_ALIGNMENT
+constexpr uint64_t kTrellisTile = 16;
+constexpr uint64_t kQ4kBlockElements = 256, kQ4kBlockBytes = 144;
+
+bool mul3(uint64_t a, uint64_t b, uint64_t c, uint64_t* out) {
+    uint64_t ab = 0;
+    if (__builtin_mul_overflow(a, b, &ab)) return false;
+    return !__builtin_mul_overflow(ab, c, out);
+}
+}  // namespace
+
+extern "C" int pk100_exl3_layout(long long logical_in, long long logical_out, int qbits, pk100_exl3_layout_t* out) {
+    if (out == nullptr) return PK100_ERR_NULL;
+    if (logical_in <= 0 || logical_out <= 0) return PK100_ERR_SHAPE;          // Exl3LayoutError::Empty
+    if (qbits < 1 || qbits > 8) return PK100_ERR_UNSUPPORTED;                  // InvalidBitRate
+    uint64_t pi = 0, po = 0, bits = 0;
+    if (!align_up_checked(static_cast<uint64_t>(logical_in), kTileAlignment, &pi) ||
+        !align_up_checked(static_cast<uint64_t>(logical_out), kTileAlignment, &po) ||
+        !mul3(pi, po, static_cast<uint64_t>(qbits), &bits))
+        return PK100_ERR_LIMIT;
+    out->padded_in = static_cast<long long>(pi);
+    out->padded_out = static_cast<long long>(po);
+    out->trellis_shape[0] = static_cast<long long>(pi / kTrellisTile);
+    out->trellis_shape[1] = static_cast<long long>(po / kTrellisTile);
+    out->trellis_shape[2] = static_cast<long long>(kTrellisTile * static_cast<uint64_t>(qbits));
+    out->trellis_bytes = bits / 8;
+    out->scale_bytes = 2 * (pi + po);
+    return PK100_OK;
+}
+
+extern "C" int pk100_estimate_linear(int format, long long logical_in, long long logical_out, int exl3_bits,
+                                     pk100_linear_layout* out) {
+    if (out == nullptr) return PK100_ERR_NULL;
+    if (logical_in <= 0 || logical_out <= 0) return PK100_ERR_SHAPE;          // PackingError::Empty
+    const uint64_t in = static_cast<uint64_t>(logical_in), outw = static_cast<uint64_t>(logical_out);
+    uint64_t pi = 0, po = 0, payload = 0, meta = 0;
+    out->logical_in = logical_in;
+    out->logical_out = logical_out;
+    out->available = 1;
+    switch (format) {
+    case PK100_FORMAT_FP16:
+    case PK100_FORMAT_FP8_E4M3:
+    case PK100_FORMAT_INT8:
+        if (!align_up_checked(in, kTileAlignment, &pi) || !align_up_checked(outw, kTileAlignment, &po)) return PK100_ERR_LIMIT;
+        if (!mul3(pi, po, format == PK100_FORMAT_FP16 ? 2 : 1, &payload)) return PK100_ERR_LIMIT;
+        if (format != PK100_FORMAT_FP16 && __builtin_mul_overflow(po, uint64_t{4}, &meta)) return PK100_ERR_LIMIT;
+        break;
+    case PK100_FORMAT_Q4_K:
+        pi = in; po = outw;
+        if (in % kQ4kBlockElements != 0) {            // Ok(None): the format has no layout for this K
+            out->available = 0;
+            out->padded_in = out->padded_out = 0;
+            out->payload_bytes = out->metadata_bytes = 0;
+            return PK100_OK;
+        }
+        if (!mul3(outw, in / kQ4kBlockElements, kQ4kBlockBytes, &payload)) return PK100_ERR_LIMIT;
+        break;
+    case PK100_FORMAT_EXL3: {
+        pk100_exl3_layout_t lay;
+        const int rc = pk100_exl3_layout(logical_in, logical_out, exl3_bits, &lay);
+        if (rc != PK100_OK) return rc;
+        pi = static_cast<uint64_t>(lay.padded_in); po = static_cast<uint64_t>(lay.padded_out);
+        payload = lay.trellis_bytes; meta = lay.scale_bytes;
+        break;
+    }
+    default:
+        return PK100_ERR_UNSUPPORTED;
+    }
+    out->padded_in = static_cast<long long>(pi);
+    out->padded_out = static_cast<long long>(po);
+    out->payload_bytes = payload;
+    out->metadata_bytes = meta;
+    return PK100_OK;
 }

@@ -121,9 +121,12 @@ __device__ __forceinline__ float ref_tanh(float x) { return __tanhf(x); }
 __device__ __forceinline__ float ref_lstm_cell(const float (&gate)[4], float& cstate) {
     const float ig = ref_sigmoid(gate[0]), fg = ref_sigmoid(gate[1]);
     const float gg = ref_tanh(gate[2]), og = ref_sigmoid(gate[3]);
-    const float cell = fg * cstate + ig * gg;
+    // The reference's compiled form of `forget * c + input * g` fuses the input-gate product onto
+    // the ROUNDED forget-gate product; found by running its kernel beside this one: the other two
+    // forms part from its tokens after a few hundred steps (the 8-bit rounding of h amplifies one ulp).
+    const float cell = fmaf(ig, gg, __fmul_rn(fg, cstate));
     cstate = cell;
-    return og * ref_tanh(cell);
+    return __fmul_rn(og, ref_tanh(cell));
 }
 
 // max |w| over a tensor; `out` holds the bits of a non-negative float (ordered like unsigned), zeroed before
@@ -206,6 +209,40 @@ __device__ __forceinline__ float dot640(const __half* w_smem, const float* x_sme
         acc = fmaf(w.y, x.y, acc);
     }
     return acc;
+}
+
+// The same dot products in the summation order of the reference's long-request kernel
+// (decoder.cu:672-684, :697-713): the bias starts the fma chain of lane 0; a prediction row is
+// spread over the 32 lanes (elements 2l + 64w), a joint row over a half-warp (elements 2l + 32s).
+// Every lane returns the sum.
+__device__ __forceinline__ float dot640_ref_warp(const __half* w_smem, const float* x_smem, int lane, float bias) {
+    float acc = lane == 0 ? bias : 0.0f;
+#pragma unroll
+    for (int i = 0; i < kHidden / 64; ++i) {
+        const int idx = 2 * lane + 64 * i;
+        const float2 w = __half22float2(*reinterpret_cast<const __half2*>(w_smem + idx));
+        const float2 x = *reinterpret_cast<const float2*>(x_smem + idx);
+        acc = fmaf(w.x, x.x, acc);
+        acc = fmaf(w.y, x.y, acc);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off /= 2) acc += __shfl_down_sync(0xffffffffu, acc, off);
+    return __shfl_sync(0xffffffffu, acc, 0);
+}
+__device__ __forceinline__ float dot640_ref_half_warp(const __half* w_smem, const float* x_smem, int lane, float bias) {
+    const int hl = lane % 16;               // both halves of the warp compute the same row
+    float acc = hl == 0 ? bias : 0.0f;
+#pragma unroll
+    for (int i = 0; i < kHidden / 32; ++i) {
+        const int idx = 2 * hl + 32 * i;
+        const float2 w = __half22float2(*reinterpret_cast<const __half2*>(w_smem + idx));
+        const float2 x = *reinterpret_cast<const float2*>(x_smem + idx);
+        acc = fmaf(w.x, x.x, acc);
+        acc = fmaf(w.y, x.y, acc);
+    }
+#pragma unroll
+    for (int off = 8; off > 0; off /= 2) acc += __shfl_down_sync(0xffffffffu, acc, off, 16);
+    return __shfl_sync(0xffffffffu, acc, 0);
 }
 
 __global__ void __launch_bounds__(kDecThreads, 1) tdt_greedy_kernel(const DecParams p) {
@@ -376,8 +413,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) tdt_greedy_kernel(const DecPar
                 const int i = task / p.utts, u = task % p.utts;
                 const int row = cta + G * i;
                 if (row >= kHidden || s_done[u] || s_valid[u]) continue;
-                float acc = warp_sum_f(dot640(s_pred + i * kHidden, s_vec + u * 2 * kHidden, lane));
-                if (lane == 0) __stcg(g_pred + static_cast<size_t>(u) * kHidden + row, acc + p.b_pred[row]);
+                const float acc = cache
+                    ? dot640_ref_warp(s_pred + i * kHidden, s_vec + u * 2 * kHidden, lane, p.b_pred[row])
+                    : warp_sum_f(dot640(s_pred + i * kHidden, s_vec + u * 2 * kHidden, lane)) + p.b_pred[row];
+                if (lane == 0) __stcg(g_pred + static_cast<size_t>(u) * kHidden + row, acc);
             }
             ok = bar.sync();
             if (!ok) break;
@@ -403,9 +442,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) tdt_greedy_kernel(const DecPar
             const int i = task / p.utts, u = task % p.utts;
             const int row = cta + G * i;
             if (row >= kJointRows || s_done[u]) continue;
-            float acc = warp_sum_f(dot640(s_joint + i * kHidden, s_vec + u * 2 * kHidden, lane));
+            float acc = cache
+                ? dot640_ref_half_warp(s_joint + i * kHidden, s_vec + u * 2 * kHidden, lane, p.b_joint[row])
+                : warp_sum_f(dot640(s_joint + i * kHidden, s_vec + u * 2 * kHidden, lane)) + p.b_joint[row];
             if (lane == 0) {
-                acc += p.b_joint[row];
                 if (row >= kTokenOutputs) {
                     __stcg(g_dur + (static_cast<size_t>(u) * 3 + slot) * kDurations + (row - kTokenOutputs), acc);
                 } else if (acc == acc) {          // NaN never wins
@@ -1105,6 +1145,10 @@ using LstmShape = FragShape<4, 5, 5, 4, 20>;   // 160 gate rows x 640 (recurrent
 using PredShape = FragShape<20, 1, 1, 5, 5>;   // 40 rows x 640
 using JointShape = FragShape<10, 2, 2, 5, 9>;  // 72 rows (65 used) x 640
 using Lstm1Shape = FragShape<4, 5, 10, 4, 20>; // second LSTM layer: 160 gate rows x 1280 ([h of layer 0 | own h])
+// Measured alternatives that were not kept: four k-groups for the prediction and joint GEMMs (fewer
+// partial sums to add, but longer dependent MMA chains: 8.7 instead of 8.0 us per round), and layer 0's
+// recurrent GEMM moved into the wait for the keys (it overlaps little: the keys arrive within a few
+// hundred cycles, and the token's table row is then waited for at the top of the next round).
 
 struct ClLayout { size_t base, lstm, pred, joint, xtab, lstm1, cache, total; };
 __host__ __device__ inline ClLayout cl_layout(int utts) {
@@ -1196,7 +1240,6 @@ struct CSmemT {
     float lstm_bias[kClUnits][4];
     float pred_bias[kClUnits];
     float joint_bias[JointShape::kRows];
-    unsigned long long best2[kMaxUtt][2];
     unsigned long long keys[2][kCl][kMaxUtt];   // [round parity][source CTA][utterance], written by peers
     float dur[2][kMaxUtt][8];                   // [round parity][utterance][duration], written by the owner
     uint64_t hbar, pbar, kbar[2];               // exchange mbarriers (count 1 + transaction bytes)
@@ -1705,19 +1748,27 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                     uint32_t words[10];
 #pragma unroll
                     for (int w = 0; w < 10; ++w) words[w] = __ldg(wrow + lane + 32 * w);
-                    for (int u = 0; u < U; ++u) {
-                        if (!sm.need[u]) continue;
-                        float sum = lane == 0 ? sm.pred_bias[n] : 0.0f;
+                    // the utterances run side by side: eight independent chains, each in its own order
+                    float sum[kMaxUtt];
 #pragma unroll
-                        for (int w = 0; w < 10; ++w) {
-                            const float2 wv = __half22float2(*reinterpret_cast<const __half2*>(&words[w]));
+                    for (int u = 0; u < kMaxUtt; ++u) sum[u] = lane == 0 ? sm.pred_bias[n] : 0.0f;
+#pragma unroll
+                    for (int w = 0; w < 10; ++w) {
+                        const float2 wv = __half22float2(*reinterpret_cast<const __half2*>(&words[w]));
+#pragma unroll
+                        for (int u = 0; u < kMaxUtt; ++u) {
+                            if (((need8 >> (8 * u)) & 1ull) == 0ull) continue;
                             const float2 hv = *reinterpret_cast<const float2*>(hf + u * kHidden + 2 * lane + 64 * w);
-                            sum = fmaf(wv.x, hv.x, sum);
-                            sum = fmaf(wv.y, hv.y, sum);
+                            sum[u] = fmaf(wv.x, hv.x, sum[u]);
+                            sum[u] = fmaf(wv.y, hv.y, sum[u]);
                         }
+                    }
 #pragma unroll
-                        for (int off = 16; off > 0; off /= 2) sum += __shfl_down_sync(0xffffffffu, sum, off);
-                        if (lane == 0) sm.stage_p[u][n] = sum;
+                    for (int u = 0; u < kMaxUtt; ++u) {
+                        if (((need8 >> (8 * u)) & 1ull) == 0ull) continue;
+#pragma unroll
+                        for (int off = 16; off > 0; off /= 2) sum[u] += __shfl_down_sync(0xffffffffu, sum[u], off);
+                        if (lane == 0) sm.stage_p[u][n] = sum[u];
                     }
                 }
                 CL_STAMP(4);
@@ -1798,19 +1849,26 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
 #pragma unroll
                 for (int st = 0; st < 20; ++st) words[st] = __ldg(wrow + hl + 16 * st);
                 const float bias = owned ? sm.joint_bias[n] : 0.0f;
-                for (int u = 0; u < U; ++u) {
-                    if (((done8 >> (8 * u)) & 1ull) != 0ull) continue;
-                    float score = hl == 0 ? bias : 0.0f;
+                float score[kMaxUtt];
 #pragma unroll
-                    for (int st = 0; st < 20; ++st) {
-                        const float2 wv = __half22float2(*reinterpret_cast<const __half2*>(&words[st]));
+                for (int u = 0; u < kMaxUtt; ++u) score[u] = hl == 0 ? bias : 0.0f;
+#pragma unroll
+                for (int st = 0; st < 20; ++st) {
+                    const float2 wv = __half22float2(*reinterpret_cast<const __half2*>(&words[st]));
+#pragma unroll
+                    for (int u = 0; u < kMaxUtt; ++u) {
+                        if (((done8 >> (8 * u)) & 1ull) != 0ull) continue;
                         const float2 xv = *reinterpret_cast<const float2*>(xf + u * kHidden + 2 * hl + 32 * st);
-                        score = fmaf(wv.x, xv.x, score);
-                        score = fmaf(wv.y, xv.y, score);
+                        score[u] = fmaf(wv.x, xv.x, score[u]);
+                        score[u] = fmaf(wv.y, xv.y, score[u]);
                     }
+                }
 #pragma unroll
-                    for (int off = 8; off > 0; off /= 2) score += __shfl_down_sync(0xffffffffu, score, off, 16);
-                    if (hl == 0 && owned) sm.part[u * JointShape::kPitch + n] = score;
+                for (int u = 0; u < kMaxUtt; ++u) {
+                    if (((done8 >> (8 * u)) & 1ull) != 0ull) continue;
+#pragma unroll
+                    for (int off = 8; off > 0; off /= 2) score[u] += __shfl_down_sync(0xffffffffu, score[u], off, 16);
+                    if (hl == 0 && owned) sm.part[u * JointShape::kPitch + n] = score[u];
                 }
             }
         } else {
@@ -1823,18 +1881,20 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
         const int par = static_cast<int>(round & 1u);
         const uint32_t kbar_local = smem_u32(&sm.kbar[par]);
         if (tid == 0) mbar_arrive_expect_tx(&sm.kbar[par], static_cast<uint32_t>(lives) * (kCl * 8 + kDurations * 4));
-        if (warp < 2 * kMaxUtt) {
-            // warp (u, half): 36 of this CTA's 72 row slots of utterance u
-            const int u = warp / 2, half = warp % 2;
+        // warp u: this CTA's 65 rows of utterance u -> its best key, sent by the same warp (a version
+        // with two warps per utterance, a merge through shared memory and a CTA barrier before the
+        // send cost 0.3 us more per round)
+        if (warp < kMaxUtt) {
+            const int u = warp;
             unsigned long long best = 0ull;
             const bool live_u = u < U && !sm.done[u];
-            // two passes for every lane (the second covers rows 32..35 of the half), so the warp
-            // stays converged up to the shuffle reduction
+            // three passes for every lane (the third covers row 64), so the warp stays converged up
+            // to the shuffle reduction
 #pragma unroll
-            for (int it = 0; it < 2; ++it) {
-                const int n = half * 36 + lane + it * 32;
+            for (int it = 0; it < 3; ++it) {
+                const int n = lane + it * 32;
                 const int row = r * kClJoint + n;
-                if (live_u && n < half * 36 + 36 && n < kClJoint && row < kJointRows) {
+                if (live_u && n < kClJoint && row < kJointRows) {
                     float total;
                     if constexpr (Cache) {
                         total = sm.part[u * JointShape::kPitch + n];      // finished score of the fp32 joint
@@ -1864,19 +1924,15 @@ tdt_cluster_kernel(const DecParams p, const uint4* packed_lstm, const uint4* pac
                 const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, off);
                 best = other > best ? other : best;
             }
-            if (lane == 0) sm.best2[u][half] = best;
+            // ---- this CTA's best row of utterance u -> every CTA of the cluster
+            if (live_u && lane < kCl) {
+                // a CTA whose rows all produced NaN still publishes a (losing) key
+                if (best == 0ull) best = (static_cast<unsigned long long>(2047 - kTokenOutputs) << 21) | 1ull;
+                st_async_b64(map_to_cta(smem_u32(&sm.keys[par][r][u]), static_cast<uint32_t>(lane)), best,
+                             map_to_cta(kbar_local, static_cast<uint32_t>(lane)));
+            }
         }
-        __syncthreads();
         CL_STAMP(9);
-        // ---- this CTA's best row per utterance -> every CTA of the cluster
-        if (warp < U && !sm.done[warp] && lane < kCl) {
-            const int u = warp;
-            unsigned long long best = sm.best2[u][0] > sm.best2[u][1] ? sm.best2[u][0] : sm.best2[u][1];
-            // a CTA whose rows all produced NaN still publishes a (losing) key
-            if (best == 0ull) best = (static_cast<unsigned long long>(2047 - kTokenOutputs) << 21) | 1ull;
-            st_async_b64(map_to_cta(smem_u32(&sm.keys[par][r][u]), static_cast<uint32_t>(lane)), best,
-                         map_to_cta(kbar_local, static_cast<uint32_t>(lane)));
-        }
         mbar_wait_bounded(&sm.kbar[par], kphase[par], abort_flag);
         kphase[par] ^= 1u;
         CL_STAMP(10);
@@ -1984,6 +2040,11 @@ int check_weights(const pk100_decoder_weights* w) {
 }
 
 }  // namespace
+
+extern "C" long long pk100_tdt_rounds_offset(int utterances) {
+    if (utterances <= 0 || utterances > kMaxUtt) return -1;
+    return static_cast<long long>(xch_layout(utterances).abort) + 8;
+}
 
 extern "C" long long pk100_tdt_workspace_bytes(int utterances) {
     if (utterances <= 0 || utterances > kMaxUtt) return 0;

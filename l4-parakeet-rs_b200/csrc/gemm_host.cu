@@ -30,10 +30,63 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// Descriptor cache.  A tensor map is a pure function of (base, element size, extents, leading
+// dimension, box, swizzle), and a host that runs the same layers on the same buffers request after
+// request asks for the same few hundred maps again and again; encoding one costs a driver call.
+// Direct-mapped table keyed by a hash of those fields, guarded by one mutex (launchers are
+// thread-compatible, not thread-hot).  The 128-byte maps are copied out, so an evicted entry
+// never invalidates a launch already issued.
+struct MapKey {
+    const void* base; uint64_t rows, cols, ld; int elem_bytes, box_rows, swizzle_bytes;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld &&
+               elem_bytes == o.elem_bytes && box_rows == o.box_rows && swizzle_bytes == o.swizzle_bytes;
+    }
+};
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+constexpr int kMapSlots = 4096;
+static MapSlot* g_map_slots = nullptr;
+static std::mutex g_map_mutex;
+static std::atomic<long long> g_map_hits{0}, g_map_misses{0};
+
+static size_t map_hash(const MapKey& k) {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.rows * 0xC2B2AE3D27D4EB4Full) ^ (k.cols << 17) ^ (k.ld << 29);
+    h ^= static_cast<uint64_t>(k.elem_bytes * 31 + k.box_rows * 7 + k.swizzle_bytes);
+    h ^= h >> 29;
+    return static_cast<size_t>(h * 0xBF58476D1CE4E5B9ull >> 32) % kMapSlots;
+}
+
+static int encode_map(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows,
+                      uint64_t cols, uint64_t ld, int box_rows, int swizzle_bytes);
+
 // 2-D row-major matrix [rows, cols] with `ld` elements between rows; box =
 // [box_rows, swizzle_bytes / elem_bytes] elements, swizzle mode = box width.
 static int make_map(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows,
                     uint64_t cols, uint64_t ld, int box_rows, int swizzle_bytes) {
+    const MapKey key{base, rows, cols, ld, elem_bytes, box_rows, swizzle_bytes};
+    const size_t slot = map_hash(key);
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        if (g_map_slots == nullptr) g_map_slots = new MapSlot[kMapSlots]();
+        MapSlot& s = g_map_slots[slot];
+        if (s.used && s.key == key) {
+            *map = s.map;
+            g_map_hits.fetch_add(1, std::memory_order_relaxed);
+            return PK100_OK;
+        }
+    }
+    const int rc = encode_map(map, base, elem_bytes, rows, cols, ld, box_rows, swizzle_bytes);
+    if (rc != PK100_OK) return rc;
+    g_map_misses.fetch_add(1, std::memory_order_relaxed);
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    MapSlot& s = g_map_slots[slot];
+    s.key = key; s.map = *map; s.used = true;
+    return PK100_OK;
+}
+
+static int encode_map(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows,
+                      uint64_t cols, uint64_t ld, int box_rows, int swizzle_bytes) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return PK100_ERR_DRIVER;
     const cuuint64_t dims[2] = {cols, rows};
@@ -84,6 +137,19 @@ static int sm_count() {
 static std::atomic<int> g_use_pairs{0};
 extern "C" void pk100_set_gemm_cta_pairs(int enable) { g_use_pairs.store(enable != 0); }
 
+// Process-wide cap on the persistent CTAs of a GEMM whose own max_ctas is <= 0 (0 = one per SM).
+static std::atomic<int> g_cta_cap{0};
+extern "C" void pk100_set_gemm_cta_cap(int ctas) { g_cta_cap.store(ctas > 0 ? ctas : 0); }
+static int cta_budget(const pk100_gemm_args& a) {
+    if (a.max_ctas > 0) return a.max_ctas;
+    const int cap = g_cta_cap.load(std::memory_order_relaxed);
+    return cap > 0 && cap < sm_count() ? cap : sm_count();
+}
+extern "C" void pk100_tensor_map_cache_stats(long long* hits, long long* misses) {
+    if (hits != nullptr) *hits = g_map_hits.load(std::memory_order_relaxed);
+    if (misses != nullptr) *misses = g_map_misses.load(std::memory_order_relaxed);
+}
+
 template <int Kind, int SwizzleBytes, int Epi>
 static int launch_pair(const pk100_gemm_args& a, const GemmParams& p_in, cudaStream_t stream) {
     constexpr int BlockN = 256;
@@ -107,7 +173,7 @@ static int launch_pair(const pk100_gemm_args& a, const GemmParams& p_in, cudaStr
     p.store_row_bytes = make_out_map<Epi>(&map_out, p);
     const int m_groups = (a.m + 2 * kBlockM - 1) / (2 * kBlockM);
     const int n_tiles = (p.n + BlockN - 1) / BlockN;
-    int pairs = (a.max_ctas > 0 ? a.max_ctas : sm_count()) / 2;
+    int pairs = cta_budget(a) / 2;
     if (pairs > m_groups * n_tiles) pairs = m_groups * n_tiles;
     if (pairs < 1) pairs = 1;
     cudaLaunchConfig_t cfg{};
@@ -156,7 +222,7 @@ static int launch(const pk100_gemm_args& a, const GemmParams& p_in, cudaStream_t
     if constexpr (BlockN == 256) p.store_row_bytes = make_out_map<Epi>(&map_out, p);
     const int m_tiles = (a.m + kBlockM - 1) / kBlockM;
     const int n_tiles = (p.n + BlockN - 1) / BlockN;
-    int ctas = a.max_ctas > 0 ? a.max_ctas : sm_count();
+    int ctas = cta_budget(a);
     if (ctas > m_tiles * n_tiles) ctas = m_tiles * n_tiles;
     kernel<<<ctas, GemmWarps<BSRC_TMA>::kThreads, Smem::kTotal, stream>>>(map_a, map_b, map_out, p);
     return pk100_launch_status();
@@ -179,7 +245,7 @@ static int launch_w4(const pk100_gemm_args& a, const GemmParams& p, cudaStream_t
     if (rc != PK100_OK) return rc;
     const int m_tiles = (a.m + kBlockM - 1) / kBlockM;
     const int n_tiles = (p.n + BlockN - 1) / BlockN;
-    int ctas = a.max_ctas > 0 ? a.max_ctas : sm_count();
+    int ctas = cta_budget(a);
     if (ctas > m_tiles * n_tiles) ctas = m_tiles * n_tiles;
     kernel<<<ctas, GemmWarps<BSRC_W4G128>::kThreads, Smem::kTotal, stream>>>(map_a, map_a, map_a, p);   // neither B nor the output has a tensor map
     return pk100_launch_status();

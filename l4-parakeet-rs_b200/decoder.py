@@ -25,6 +25,8 @@ class DecoderWeightsC(C.Structure):
 
 L.lib.pk100_tdt_workspace_bytes.argtypes = [C.c_int]
 L.lib.pk100_tdt_workspace_bytes.restype = C.c_longlong
+L.lib.pk100_tdt_rounds_offset.argtypes = [C.c_int]
+L.lib.pk100_tdt_rounds_offset.restype = C.c_longlong
 L.lib.pk100_tdt_decode.argtypes = [vp, C.POINTER(DecoderWeightsC), vp, C.c_int, C.c_int, vp, vp, vp, vp,
                                    vp, C.c_int, vp]
 L.lib.pk100_tdt_decode.restype = C.c_int
@@ -67,6 +69,13 @@ class TdtDecoder:
                                      device=self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
 
+    def last_rounds(self, utterances, scratch=None):
+        """Lockstep rounds of the last cluster / exchange decode of `utterances` sequences
+        (synchronises: reads one int from the workspace)."""
+        off = int(L.lib.pk100_tdt_rounds_offset(utterances))
+        workspace = self.workspace if scratch is None else scratch[0]
+        return int(workspace[off:off + 4].view(torch.int32).item())
+
     def project(self, encoded, out=None):
         """enc_proj = f16(encoded . W_enc^T + b_enc) (src/cuda/decoder.rs:298-313)."""
         rows = encoded.shape[0]
@@ -74,8 +83,13 @@ class TdtDecoder:
             out = torch.empty((rows, HIDDEN), dtype=torch.float16, device=self.device)
         return ops.gemm(encoded, self.t["w_enc"], kind=L.KIND_F16, out=out, bias=self.t["b_enc"])
 
+    def make_scratch(self):
+        """A further (workspace, status) pair, for a decode that runs beside another one on a second
+        stream: concurrent calls must not share either."""
+        return (torch.zeros_like(self.workspace), torch.zeros(1, dtype=torch.int32, device=self.device))
+
     def decode(self, enc_proj, utterances, seg_stride, frames, max_tokens, tokens=None, durations=None,
-               counts=None, barrier_kernel=False, kernel=None, lstm_cache="fp16"):
+               counts=None, barrier_kernel=False, kernel=None, lstm_cache="fp16", scratch=None):
         """frames: int32 CUDA tensor [utterances].  Returns (tokens, durations, counts) CUDA tensors.
         kernel: None (the library's choice), "cluster", "exchange" or "barrier".
         lstm_cache: "fp16" = the numerics of the reference's short-request kernel, "int8" = those of
@@ -102,9 +116,10 @@ class TdtDecoder:
         else:
             raise ValueError(f"lstm_cache: {lstm_cache!r}")
         fn = getattr(L.lib, name)
+        workspace, status = (self.workspace, self.status) if scratch is None else scratch
         rc = fn(torch.cuda.current_stream().cuda_stream, C.byref(self.c),
                                     enc_proj.data_ptr(), utterances, seg_stride, frames.data_ptr(),
-                                    self.workspace.data_ptr(), tokens.data_ptr(), durations.data_ptr(),
-                                    counts.data_ptr(), max_tokens, self.status.data_ptr())
+                                    workspace.data_ptr(), tokens.data_ptr(), durations.data_ptr(),
+                                    counts.data_ptr(), max_tokens, status.data_ptr())
         L.check(rc, name)
         return tokens, durations, counts

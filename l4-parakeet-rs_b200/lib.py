@@ -55,6 +55,7 @@ SIGNATURES = {
     "pk100_encoder_workspace_carve": None,
     "pk100_run_layers": None,
     "pk100_tdt_workspace_bytes": None,
+    "pk100_tdt_rounds_offset": None,
     "pk100_tdt_decode": None,
     "pk100_tdt_decode_barrier": None,
     "pk100_tdt_decode_cluster": None,
@@ -77,6 +78,8 @@ SIGNATURES = {
     "pk100_encode_fp16_linear": None,
     "pk100_encode_fp32_bias": None,
     "pk100_align_up": None,
+    "pk100_estimate_linear": None,
+    "pk100_exl3_layout": None,
     "pk100_mel_frames_for": None,
     "pk100_mel_frontend": None,
     "pk100_subsampling_workspace_bytes": None,
@@ -93,6 +96,16 @@ lib.pk100_launch_count.restype = i64
 lib.pk100_launch_count.argtypes = []
 lib.pk100_set_gemm_cta_pairs.restype = None
 lib.pk100_set_gemm_cta_pairs.argtypes = [i32]
+lib.pk100_set_gemm_cta_cap.restype = None
+lib.pk100_set_gemm_cta_cap.argtypes = [i32]
+lib.pk100_tensor_map_cache_stats.restype = None
+lib.pk100_tensor_map_cache_stats.argtypes = [C.POINTER(i64), C.POINTER(i64)]
+
+
+def tensor_map_cache_stats():
+    hits, misses = i64(0), i64(0)
+    lib.pk100_tensor_map_cache_stats(C.byref(hits), C.byref(misses))
+    return int(hits.value), int(misses.value)
 
 # enums (include/pk100.h)
 OK, ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_UNSUPPORTED, ERR_DRIVER, ERR_LIMIT = 0, -1, -2, -3, -4, -5, -6

@@ -1,13 +1,20 @@
 """Host-side mirror of the reference's pipeline engine
 (src/cuda/pipeline.rs: PipelineEngine::load :121-395, transcribe :397-417,
 run_prepared :437-608) for a batch of utterances on one GPU, starting from log-mel
-frames (the audio frontend is outside this build's scope).
+frames (`transcribe_batch`) or from PCM through the log-mel frontend (`transcribe_pcm`).
 
     mel [U, frames, 128] fp32 (host) --H2D--> subsampling -> 24 encoder blocks
         -> encoder projection -> TDT greedy decode --D2H--> token ids
 
 Everything between the two copies is stream-ordered launches of libpk100 kernels
-without host synchronisation."""
+without host synchronisation.
+
+Decode is a latency-bound chain on 16 SMs (one thread-block cluster); the encoder wants the
+other 132.  With `decode_groups` > 1 the batch is cut into that many groups of utterances:
+group g is encoded on the caller's stream, then decoded on a high-priority side stream
+while group g + 1 is being encoded, the encoder's persistent GEMMs capped at the SMs the
+decoders in flight leave free.  Results are identical to the ungrouped run (every kernel
+is batch-invariant); only the schedule changes."""
 from __future__ import annotations
 
 import ctypes as C
@@ -16,6 +23,7 @@ import numpy as np
 import torch
 
 from . import decoder as dec_mod
+from . import lib as L
 from . import encoder as enc_mod
 from . import subsampling as sub_mod
 from . import synth
@@ -31,10 +39,12 @@ def seg_stride_for(frames_out: int) -> int:
 
 class PipelineEngine:
     def __init__(self, device, layers=24, decoder_layers=2, seed=4, max_utterances=8, mel_frames=6000,
-                 randomize_norms=False):
+                 randomize_norms=False, decode_groups=2):
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
         self.max_utterances = max_utterances
+        self.decode_groups = max(1, min(int(decode_groups), max_utterances))
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.mel_frames = mel_frames
         self.frames_out = sub_mod.output_frames(mel_frames)
         self.seg_stride = seg_stride_for(self.frames_out)
@@ -63,24 +73,57 @@ class PipelineEngine:
         self.counts_host = torch.zeros(max_utterances, dtype=torch.int32).pin_memory()
         self.calibrated = False
         self._events = None
+        self._lengths = tuple([mel_frames] * max_utterances)
+        # one side stream, scratch and event set per decode group
+        self.dec_streams = [torch.cuda.Stream(device=self.device, priority=-1) for _ in range(self.decode_groups)]
+        self.dec_scratch = [None] + [self.dec.make_scratch() for _ in range(self.decode_groups - 1)]
+        self._stage_events = None
+        self.last_groups = []
 
     # ---- profiling hook: CUDA events around the FF-expand GEMMs
     def enable_gemm_timing(self):
+        """CUDA events around every FF-expand GEMM (two per block), one set per decode group."""
         n = 2 * 2 * len(self.enc.layers)
-        self._events = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
-        for e in self._events:
-            e.record()                       # creates the underlying cudaEvent_t
+        self._events, self._event_arrays = [], []
+        for _ in range(self.decode_groups):
+            events = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+            for e in events:
+                e.record()                   # creates the underlying cudaEvent_t
+            self._events.append(events)
+            self._event_arrays.append((C.c_void_p * n)(*[e.cuda_event for e in events]))
         torch.cuda.synchronize()
-        arr = (C.c_void_p * n)(*[e.cuda_event for e in self._events])
-        self._event_array = arr
-        self.ws.profile_events = C.cast(arr, C.POINTER(C.c_void_p))
         self.ws.profile_events_len = n
 
     def gemm_times_ms(self):
-        return [self._events[2 * i].elapsed_time(self._events[2 * i + 1]) for i in range(len(self._events) // 2)]
+        """[(milliseconds, rows of that launch)] for every FF-expand launch of the last request."""
+        out = []
+        for g, (u0, u1) in enumerate(self.last_groups):
+            ev = self._events[g]
+            out += [(ev[2 * i].elapsed_time(ev[2 * i + 1]), (u1 - u0) * self.seg_stride) for i in range(len(ev) // 2)]
+        return out
 
     # ---- stages
+    def enable_stage_timing(self):
+        """CUDA events around the encode and the decode of every group (recording does not synchronise)."""
+        mk = lambda: torch.cuda.Event(enable_timing=True)
+        self._stage_events = [dict(enc0=mk(), enc1=mk(), dec0=mk(), dec1=mk()) for _ in range(self.decode_groups)]
+
+    def stage_times(self):
+        """After a synchronise: per decode group of the last request, its utterance range, encode
+        and decode milliseconds, the decode's lockstep rounds, and when the decode started and
+        ended relative to the start of the request."""
+        out = []
+        first = self._stage_events[0]["enc0"]
+        for g, (u0, u1) in enumerate(self.last_groups):
+            ev = self._stage_events[g]
+            out.append(dict(utterances=[u0, u1], encode_ms=ev["enc0"].elapsed_time(ev["enc1"]),
+                            decode_ms=ev["dec0"].elapsed_time(ev["dec1"]),
+                            decode_start_ms=first.elapsed_time(ev["dec0"]), decode_end_ms=first.elapsed_time(ev["dec1"]),
+                            rounds=self.dec.last_rounds(u1 - u0, self.dec_scratch[g])))
+        return out
+
     def set_lengths(self, mel_frames_per_utt):
+        self._lengths = tuple(int(f) for f in mel_frames_per_utt) + self._lengths[len(mel_frames_per_utt):]
         mf = torch.tensor(mel_frames_per_utt, dtype=torch.int32)
         of = torch.tensor([sub_mod.output_frames(int(f)) for f in mel_frames_per_utt], dtype=torch.int32)
         self.mel_frames_dev[:len(mf)].copy_(mf)
@@ -104,22 +147,72 @@ class PipelineEngine:
                                           seg_valid=self.out_frames_dev)
         self.calibrated = True
 
+    def _group_bounds(self, utterances):
+        groups = min(self.decode_groups, utterances)
+        base, extra = divmod(utterances, groups)
+        bounds, u = [], 0
+        for g in range(groups):
+            n = base + (1 if g < extra else 0)
+            bounds.append((u, u + n))
+            u += n
+        return bounds
+
     def run_resident(self, utterances):
-        """Hot path with the inputs already in HBM: subsampling -> encoder -> decode."""
-        encoded = self.encode(utterances)
-        self.dec.project(encoded, out=self.enc_proj)
+        """Hot path with the inputs already in HBM: subsampling -> encoder -> projection -> decode,
+        group by group (see the module text); returns with everything queued on the caller's
+        stream, which waits for the side streams."""
         # the reference switches decoder kernels (and numerics) at 1024 frames per request
         # (src/cuda/decoder.rs:88); a batch of short utterances needs one launch only
         cache = "auto" if self.longest_out_frames >= dec_mod.LONG_REQUEST_FRAMES else "fp16"
-        self.dec.decode(self.enc_proj, utterances, self.seg_stride, self.out_frames_dev, self.max_tokens,
-                        self.tokens, self.durations, self.counts, lstm_cache=cache)
+        main = torch.cuda.current_stream()
+        bounds = self._group_bounds(utterances)
+        self.last_groups = bounds
+        seg = self.seg_stride
+        for g, (u0, u1) in enumerate(bounds):
+            ev = self._stage_events[g] if self._stage_events is not None else None
+            r0, r1 = u0 * seg, u1 * seg
+            if g > 0:
+                # decoders of the earlier groups hold 16 SMs each while this group is encoded
+                L.lib.pk100_set_gemm_cta_cap(max(self.sm_count - 16 * g, 16))
+            if ev:
+                ev["enc0"].record(main)
+            if self._events is not None:
+                self.ws.profile_events = C.cast(self._event_arrays[g], C.POINTER(C.c_void_p))
+            self.sub.run(self.mel_dev[u0:u1], seg, mel_frames=self.mel_frames_dev[u0:u1], out=self.state_a[r0:r1])
+            encoded = self.enc.run(self.state_a[r0:r1], self.state_b[r0:r1], self.ws, u1 - u0, seg,
+                                   self.frames_out, seg_valid=self.out_frames_dev[u0:u1])
+            self.dec.project(encoded, out=self.enc_proj[r0:r1])
+            if ev:
+                ev["enc1"].record(main)
+            side = self.dec_streams[g] if len(bounds) > 1 else main
+            if side is not main:
+                side.wait_stream(main)
+            with torch.cuda.stream(side):
+                if ev:
+                    ev["dec0"].record(side)
+                self.dec.decode(self.enc_proj[r0:r1], u1 - u0, seg, self.out_frames_dev[u0:u1], self.max_tokens,
+                                self.tokens[u0:u1], self.durations[u0:u1], self.counts[u0:u1], lstm_cache=cache,
+                                scratch=self.dec_scratch[g])
+                if ev:
+                    ev["dec1"].record(side)
+        if len(bounds) > 1:
+            L.lib.pk100_set_gemm_cta_cap(0)
+            for g in range(len(bounds)):
+                main.wait_stream(self.dec_streams[g])
 
-    def transcribe_batch(self, mel_host):
-        """mel_host: pinned fp32 CPU tensor [U, frames, 128].  Returns a list of int32 numpy
-        token arrays (one per utterance).  Includes the H2D copy of the inputs and the D2H
-        read of the result (pipeline.rs:398, :409)."""
+    def transcribe_batch(self, mel_host, mel_frames_per_utt=None):
+        """mel_host: pinned fp32 CPU tensor [U, frames, 128]; mel_frames_per_utt: true frame
+        count of every utterance (default: all of mel_host's frames).  Returns a list of int32
+        numpy token arrays (one per utterance).  Includes the H2D copy of the inputs and the
+        D2H read of the result (pipeline.rs:398, :409)."""
         utterances = mel_host.shape[0]
-        self.mel_dev[:utterances].copy_(mel_host, non_blocking=True)
+        lengths = tuple([int(mel_host.shape[1])] * utterances if mel_frames_per_utt is None
+                        else [int(f) for f in mel_frames_per_utt])
+        if max(lengths) > mel_host.shape[1] or mel_host.shape[1] > self.mel_frames:
+            raise ValueError("utterance longer than the engine was sized for")
+        if lengths != self._lengths[:utterances]:
+            self.set_lengths(lengths)          # never reuse the lengths an earlier request left behind
+        self.mel_dev[:utterances, :mel_host.shape[1]].copy_(mel_host, non_blocking=True)
         self.run_resident(utterances)
         self.counts_host.copy_(self.counts, non_blocking=True)
         self.tokens_host.copy_(self.tokens, non_blocking=True)
@@ -164,4 +257,7 @@ class PipelineEngine:
         return [self.tokens_host[u, :int(counts[u])].numpy().copy() for u in range(utterances)]
 
     def status(self):
-        return (self.enc.status(self.arena, self.ws) | int(self.dec.status.item()) | int(self.sub.status.item()))
+        dec = int(self.dec.status.item())
+        for scratch in self.dec_scratch[1:]:
+            dec |= int(scratch[1].item())
+        return self.enc.status(self.arena, self.ws) | dec | int(self.sub.status.item())

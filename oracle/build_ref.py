@@ -24,13 +24,17 @@ OUT = HERE / "_ref"
 UNITS = {"linear": True, "encoder": True, "decoder": True, "subsampling": True, "frontend": True}
 
 
-def reference_root() -> Path | None:
-    root = Path(os.environ.get("PK_REFERENCE_ROOT", "/root/reference"))
+def reference_root(root: str | os.PathLike | None = None) -> Path | None:
+    """The reference checkout: the argument, else $PK_REFERENCE_ROOT, else a directory named
+    `reference` beside this repository.  None when its kernels are not there."""
+    if root is None:
+        root = os.environ.get("PK_REFERENCE_ROOT") or HERE.parent.parent / "reference"
+    root = Path(root)
     return root if (root / "kernels" / "sm89" / "encoder.cu").exists() else None
 
 
-def build_reference_cubins(force: bool = False) -> list[Path]:
-    root = reference_root()
+def build_reference_cubins(force: bool = False, root: str | os.PathLike | None = None) -> list[Path]:
+    root = reference_root(root)
     if root is None:
         return sorted(OUT.glob("*.cubin"))          # prebuilt files travel with the tree
     nvcc = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
@@ -69,6 +73,7 @@ def build_c_oracle(force: bool = False) -> Path:
 
 if __name__ == "__main__":
     force = "--force" in sys.argv
+    roots = [a for a in sys.argv[1:] if not a.startswith("--")]
     print(build_c_oracle(force))
-    for p in build_reference_cubins(force):
+    for p in build_reference_cubins(force, roots[0] if roots else None):
         print(p)

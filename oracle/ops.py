@@ -105,8 +105,25 @@ def quant_rows_int8_dynamic(y16, rows=None):
 # GEMM with the reference's epilogue algebra
 # ----------------------------------------------------------------------------
 
+# Timing mode.  Parity runs accumulate in float64 with numpy (exact for the integer GEMMs).  When
+# the benchmark times this restatement as the CPU baseline it switches the two heavy operators, the
+# GEMM accumulation and the attention, to torch fp32 on all host threads; every quantiser stays the
+# bit-exact numpy code.  Never set by a parity test.
+_TIMING_MODE = False
+
+
+def set_timing_mode(on: bool) -> None:
+    global _TIMING_MODE
+    _TIMING_MODE = bool(on)
+
+
 def accumulate(a, b):
     """acc[m,n] = sum_k a[m,k]*b[n,k] in float64 (exact for INT8/INT4 codes)."""
+    if _TIMING_MODE:
+        import torch
+        ta = torch.from_numpy(np.ascontiguousarray(a, dtype=F32))
+        tb = torch.from_numpy(np.ascontiguousarray(b, dtype=F32))
+        return (ta @ tb.T).numpy()
     return np.asarray(a, dtype=np.float64) @ np.asarray(b, dtype=np.float64).T
 
 
@@ -259,6 +276,8 @@ def local_attention(q16, k16, v16, pos16, bias_u16, bias_v16, rows, valid_rows,
       score[q,k] = ((Q_q+u).K_k + (Q_q+v).P[128-q+k]) / sqrt(128),
       keys clipped to [max(0,q-128), min(valid-1,q+128)], fp32 softmax with max
       subtraction, ctx = sum p.V, rows >= min(rows, valid) -> 0."""
+    if _TIMING_MODE:
+        return _local_attention_torch(q16, k16, v16, pos16, bias_u16, bias_v16, rows, valid_rows, left, right)
     q = np.asarray(q16, dtype=F32)
     k = np.asarray(k16, dtype=F32)
     v = np.asarray(v16, dtype=F32)
@@ -284,6 +303,31 @@ def local_attention(q16, k16, v16, pos16, bias_u16, bias_v16, rows, valid_rows,
         p = e / e.sum(axis=1, keepdims=True, dtype=F32)
         out[:nq, sl] = np.einsum("qj,qjd->qd", p.astype(np.float64),
                                  v[:, sl].astype(np.float64)[kc]).astype(F32)
+    return f16_round(out)
+
+
+def _local_attention_torch(q16, k16, v16, pos16, bias_u16, bias_v16, rows, valid_rows, left, right):
+    """The same operator as batched fp32 torch (timing mode): dense [heads, nq, keys] scores with
+    the band mask, the position term gathered at 128 - q + k."""
+    import torch
+    m = np.asarray(q16).shape[0]
+    nq = min(rows, valid_rows)
+    band = left + right + 1
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=F32))
+    q = t(q16)[:nq].reshape(nq, HEADS, HEAD_WIDTH).permute(1, 0, 2)                  # [h, nq, d]
+    k = t(k16)[:valid_rows].reshape(valid_rows, HEADS, HEAD_WIDTH).permute(1, 0, 2)  # [h, keys, d]
+    v = t(v16)[:valid_rows].reshape(valid_rows, HEADS, HEAD_WIDTH).permute(1, 0, 2)
+    u, bv, pos = t(bias_u16)[:, None, :], t(bias_v16)[:, None, :], t(pos16)[:, :band]  # pos [h, band, d]
+    content = (q + u) @ k.transpose(1, 2)                                             # [h, nq, keys]
+    posit = (q + bv) @ pos.transpose(1, 2)                                            # [h, nq, band]
+    rel = torch.arange(valid_rows)[None, :] - torch.arange(nq)[:, None] + left        # [nq, keys]
+    ok = (rel >= 0) & (rel < band)
+    idx = rel.clamp(0, band - 1)[None].expand(HEADS, -1, -1)
+    s = (content + torch.gather(posit, 2, idx)) * float(SOFTMAX_SCALE)
+    s = s.masked_fill(~ok[None], float("-inf"))
+    p = torch.softmax(s, dim=2)
+    out = np.zeros((m, MODEL_WIDTH), dtype=F32)
+    out[:nq] = (p @ v).permute(1, 0, 2).reshape(nq, MODEL_WIDTH).numpy()
     return f16_round(out)
 
 

@@ -54,6 +54,13 @@ def cases():
     rng = np.random.default_rng(107)
     c["dec_long_short"] = dict(w=c["dec"]["w"], frames=48,
                                enc=[codec.f16_round(rng.standard_normal((48, 640)) * 0.5) for _ in range(16)])
+    # three more requests through the long-request kernel, other weights and lengths (the arithmetic
+    # of this kernel feeds every rounding back through 8-bit codes: each extra request pins it further)
+    c["dec_long_more"] = []
+    for seed, wseed, nframes in ((8, 33, 128), (21, 33, 200), (23, 45, 256)):
+        rng = np.random.default_rng(seed)
+        c["dec_long_more"].append(dict(w=D.make_decoder_weights(wseed, layers=2), frames=nframes,
+                                       enc=codec.f16_round(rng.standard_normal((nframes, 640)) * 0.5)))
     rng = np.random.default_rng(105)
     c["fe"] = dict(x=(rng.standard_normal(1700) * 0.3).astype(np.float32))
     # per-tensor activation x per-row weight scaled linears and their quantisers (linear.cu:325-429, :537-560)
@@ -114,6 +121,9 @@ def main(out_path):
     dls = c["dec_long_short"]
     for i, enc in enumerate(dls["enc"]):
         g[f"dec_long_short_{i}"] = R.tdt_decode_long(dev16(enc), dwts, dls["frames"]).astype(np.int32)
+    for i, m in enumerate(c["dec_long_more"]):
+        mw = {k: (dev(v) if k.startswith("b_") else dev16(v)) for k, v in m["w"].items() if k != "layers"}
+        g[f"dec_long_more_{i}"] = R.tdt_decode_long(dev16(m["enc"]), mw, m["frames"]).astype(np.int32)
     # the same request through the short-request kernel, to show that the two kernels differ
     g["dec_long_tokens_fp16"] = R.tdt_decode(dev16(dl["enc"]), dwts, dl["frames"], sms).astype(np.int32)
     x = c["fe"]["x"]

@@ -215,6 +215,36 @@ def test_reader_rejects_what_the_reference_rejects(pk, tmp_path, message, mutate
     assert info.value.code == pk.artifact.ERR_FORMAT and message in info.value.message
 
 
+def test_reader_rejects_a_field_given_twice(pk, tmp_path):
+    """serde refuses a struct field that occurs twice (src/artifact.rs:30-60, :147); a repeated
+    unknown key is ignored like any unknown key."""
+    good = tmp_path / "good.pkl4"
+    A.write(good, small_model(np.random.default_rng(4)), "v2_english", VOCAB)
+    blob = open(good, "rb").read()
+    header_bytes = struct.unpack("<Q", blob[16:24])[0]
+    doc = blob[24:24 + header_bytes].decode()
+    payload = blob[A.align_up(24 + header_bytes, 4096):]
+
+    def rewrite(text, name):
+        enc = text.encode()
+        body = bytearray(A.align_up(24 + len(enc), 4096)) + payload
+        body[:24] = A.MAGIC + struct.pack("<IIQ", 2, 0, len(enc))
+        body[24:24 + len(enc)] = enc
+        path = tmp_path / name
+        open(path, "wb").write(body)
+        return path
+
+    assert doc.startswith("{") and '"payload_bytes":' in doc and '"offset":' in doc
+    value = json.loads(doc)["payload_bytes"]
+    for name, text in (("top.pkl4", '{"payload_bytes":%d,' % value + doc[1:]),
+                       ("tensor.pkl4", doc.replace('"offset":', '"offset":0,"offset":', 1))):
+        with pytest.raises(pk.artifact.ArtifactError) as info:
+            pk.artifact.Artifact(rewrite(text, name))
+        assert info.value.code == pk.artifact.ERR_FORMAT and "duplicate field" in info.value.message
+    ok = rewrite('{"x_unknown":1,"x_unknown":2,' + doc[1:], "unknown.pkl4")
+    assert len(pk.artifact.Artifact(ok).records) > 0
+
+
 def test_reader_io_errors_and_escapes(pk, tmp_path):
     with pytest.raises(pk.artifact.ArtifactError) as info:
         pk.artifact.Artifact(tmp_path / "absent.pkl4")
@@ -273,3 +303,33 @@ def test_model_views_follow_the_manifest(pk, tmp_path):
     assert d["embedding"].shape == (1025, 640) and d["w_joint"].shape == (1030, 640)
     assert np.array_equal(d["b_hh1"], tensors["decoder.lstm.bias_hh_l1"])
     assert np.array_equal(d["w_ih0"], f16(tensors["decoder.lstm.weight_ih_l0"]))
+
+
+def test_size_contract_known_answers_through_the_c_abi(pk):
+    """estimate_linear / Exl3Layout behind libpk100 (src/packing.rs:168-199, src/exl3.rs:82-95),
+    and equal to the oracle's restatement on a sweep of shapes."""
+    from oracle import codec
+    A = pk.artifact
+    fp16 = A.estimate_linear("fp16", 1024, 4096)
+    fp8 = A.estimate_linear("fp8_e4m3", 1024, 4096)
+    assert fp16["payload_bytes"] + fp16["metadata_bytes"] == 8 * 1024 * 1024
+    assert fp8["payload_bytes"] == 4 * 1024 * 1024 and fp8["metadata_bytes"] == 16 * 1024
+    assert A.estimate_linear("q4_k", 640, 8198) is None
+    q4 = A.estimate_linear("q4_k", 1024, 4096)
+    assert q4["payload_bytes"] + q4["metadata_bytes"] == 4096 * 4 * 144
+    j = A.estimate_linear("fp8_e4m3", 640, 8198)
+    assert (j["padded_in"], j["padded_out"]) == (640, 8320)
+    lay = A.exl3_layout(4096, 1024, 4)
+    assert lay["trellis_shape"] == [256, 64, 64]
+    assert lay["trellis_bytes"] == 2 * 1024 * 1024 and lay["scale_bytes"] == 10 * 1024
+    j = A.exl3_layout(640, 8198, 4)
+    assert j["padded_in"] == 640 and j["padded_out"] == 8320 and j["trellis_shape"] == [40, 520, 64]
+    with pytest.raises(ValueError):
+        A.estimate_linear("fp16", 0, 4)
+    with pytest.raises(ValueError):
+        A.exl3_layout(16, 16, 9)
+    for fmt in ("fp16", "fp8_e4m3", "int8", "q4_k", "exl3"):
+        for k, n in ((1, 1), (127, 129), (256, 640), (1024, 3072), (4096, 1024), (640, 1030)):
+            for bits in ((2, 4, 8) if fmt == "exl3" else (4,)):
+                assert A.estimate_linear(fmt, k, n, bits) == codec.estimate_linear(fmt, k, n, bits), (fmt, k, n, bits)
+    assert A.exl3_layout(1000, 70, 3) == codec.exl3_layout(1000, 70, 3)

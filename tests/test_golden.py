@@ -89,6 +89,19 @@ def test_tdt_decoder_tokens_long_request_kernel_on_short_requests():
     assert compared > 250
 
 
+def test_tdt_decoder_tokens_long_request_kernel_more_requests():
+    """Three further requests through the reference's INT8-cache kernel: the oracle agrees with
+    every decision before each request's first near-tie (its trust band, see oracle/decoder.py)."""
+    compared = 0
+    for i, m in enumerate(CASES["dec_long_more"]):
+        tokens, _, ambiguous = D.tdt_greedy(m["enc"], m["w"], m["frames"], lstm_cache="int8")
+        n = min(len(tokens) if ambiguous is None else ambiguous, 100)
+        ref = GOLD[f"dec_long_more_{i}"]
+        assert np.array_equal(ref[:n], tokens[:n]), i
+        compared += n
+    assert compared > 20
+
+
 def test_frontend_kernels():
     x = CASES["fe"]["x"]
     frames, valid = F.frame_counts(x.size)

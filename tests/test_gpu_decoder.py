@@ -183,6 +183,31 @@ def test_long_request_against_reference_kernel_tokens(pk, cuda):
         assert equal == 16, (kernel, equal)
 
 
+def test_long_request_kernels_against_more_reference_kernel_requests(pk, cuda):
+    """Three further requests (other weights, 128 / 200 / 256 frames) through the reference's
+    long-request kernel: the cluster and the grid-barrier kernel reproduce every token."""
+    import importlib.util
+    from pathlib import Path
+    gold_dir = Path(__file__).resolve().parent / "golden"
+    spec = importlib.util.spec_from_file_location("make_golden", gold_dir / "make_golden.py")
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    gold = np.load(gold_dir / "reference_kernels.npz")
+    total = 0
+    for i, m in enumerate(mg.cases()["dec_long_more"]):
+        ref = gold[f"dec_long_more_{i}"]
+        dec = pk.decoder.TdtDecoder(m["w"], cuda)
+        fr = torch.tensor([m["frames"]], dtype=torch.int32, device=cuda)
+        for kernel in ("cluster", "barrier"):
+            tokens, _, counts = dec.decode(dev16(m["enc"]), 1, m["frames"], fr, m["frames"] * 10, kernel=kernel,
+                                           lstm_cache="int8")
+            torch.cuda.synchronize()
+            assert int(dec.status.item()) == 0
+            assert np.array_equal(host(tokens)[0][:int(host(counts)[0])], ref), (i, kernel)
+        total += len(ref)
+    assert total > 1000
+
+
 def test_auto_applies_the_frame_rule_per_utterance(pk, cuda):
     """frames < 1024 -> short-request numerics, otherwise long-request numerics, in one call."""
     w = D.make_decoder_weights(41, layers=2)

@@ -104,6 +104,13 @@ def test_pipeline_from_pcm_equals_pipeline_from_its_own_mel(pk, cuda):
     for u in range(2):
         want, v = F.compute(pcm[u, :counts[u]], F.hann_window(), F.triangular_filters())
         assert v == valid[u] and np.max(np.abs(mel[u, :v] - want[:v])) <= 2e-3 and not mel[u, v:].any()
-    eng.set_lengths(valid)
-    again = eng.transcribe_batch(torch.from_numpy(mel))
+    again = eng.transcribe_batch(torch.from_numpy(mel), valid)
     assert all(np.array_equal(a, b) for a, b in zip(got, again)) and sum(len(t) for t in got) > 10
+    # a mel request right after a PCM request with short clips does not inherit their lengths:
+    # without lengths it covers all 201 frames of the mel it is given
+    eng.transcribe_pcm(torch.from_numpy(pcm[:, :8000].copy()), [8000, 4000])
+    assert eng.longest_out_frames < eng.frames_out
+    full = eng.transcribe_batch(torch.from_numpy(mel))
+    assert eng.longest_out_frames == eng.frames_out
+    want_full = eng.transcribe_batch(torch.from_numpy(mel), [201, 201])
+    assert all(np.array_equal(a, b) for a, b in zip(full, want_full))

@@ -29,7 +29,6 @@ def test_transcribe_batch_matches_oracle(pk, cuda, engine):
     frames = [1000, 1000, 1000]
     mels = np.stack([pk.synth.mel_input(100 + u, 1000) for u in range(3)])
     mel_host = torch.from_numpy(mels).pin_memory()
-    eng.set_lengths(frames)
     # tile thresholds stay 0 here: the free-running stack is compared as a continuous
     # operator (per-block parity WITH thresholds is covered in test_gpu_encoder.py)
     tokens = eng.transcribe_batch(mel_host)
@@ -64,11 +63,21 @@ def test_resident_path_is_deterministic_and_ragged_lengths(pk, cuda, engine):
     eng.mel_dev.copy_(mel_host)
     eng.calibrate(3)                       # 70 % zero tiles from here on
     assert all(l.ff1.tau > 0 and l.ff2.tau > 0 for l in eng.enc.layers)
-    a = eng.transcribe_batch(mel_host)
-    b = eng.transcribe_batch(mel_host)
+    a = eng.transcribe_batch(mel_host, frames)
+    b = eng.transcribe_batch(mel_host, frames)
     assert all(np.array_equal(x, y) for x, y in zip(a, b))
     # a shorter utterance in a batch decodes like the same utterance alone
-    eng.set_lengths([617, 617, 617])
-    solo = eng.transcribe_batch(torch.from_numpy(np.stack([mels[1]] * 3)).pin_memory())
+    solo = eng.transcribe_batch(torch.from_numpy(np.stack([mels[1]] * 3)).pin_memory(), [617, 617, 617])
     assert np.array_equal(solo[0], a[1])
-    eng.set_lengths([1000, 1000, 1000])
+    # a request without lengths means "all frames": nothing is inherited from the request before
+    full = eng.transcribe_batch(mel_host)
+    assert tuple(eng.out_frames_host.tolist()) == (eng.frames_out,) * 3
+    again = eng.transcribe_batch(mel_host, [1000, 1000, 1000])
+    assert all(np.array_equal(x, y) for x, y in zip(full, again))
+    # and the grouped schedule (a group's decode beside the next group's encode) changes no token
+    one = pk.pipeline.PipelineEngine(cuda, layers=2, decoder_layers=2, seed=9, max_utterances=3,
+                                     mel_frames=1000, randomize_norms=True, decode_groups=1)
+    for l, lw in enumerate(eng.enc.layers):
+        one.enc.set_tau(l, lw.ff1.tau, lw.ff2.tau)
+    ungrouped = one.transcribe_batch(mel_host, frames)
+    assert one.status() == 0 and all(np.array_equal(x, y) for x, y in zip(ungrouped, a))
