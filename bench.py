@@ -54,6 +54,8 @@ def parse_args():
                     choices=["ff_expand", "ff_contract", "qkv", "attention", "layer_norm", "depthwise", "decode"],
                     help="time ONE kernel of the path on synthetic operands (used for ncu captures)")
     ap.add_argument("--rows", type=int, default=6144, help="rows (M) of the --micro case")
+    ap.add_argument("--cta-pairs", action="store_true",
+                    help="256-column GEMM tiles on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles)")
     ap.add_argument("--utterances", type=int, default=UTTERANCES_PER_GPU,
                     help="utterances per GPU and step (8 = benchmark configuration 4; 1 = configuration 3, "
                          "the batch-1 encoder + decode)")
@@ -243,6 +245,8 @@ def run_micro(args):
     L = pk.lib
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
+    if args.cta_pairs:
+        L.lib.pk100_set_gemm_cta_pairs(1)
     g = torch.Generator(device="cpu").manual_seed(1)
     m = args.rows
     peaks = measured_peaks()
@@ -601,6 +605,8 @@ def main():
     per_gpu = max(1, min(args.utterances, UTTERANCES_PER_GPU))
     total_utts = per_gpu * world
     my_utts = pk.parallel.shard_utterances(total_utts, world, rank)
+    if args.cta_pairs:
+        pk.lib.lib.pk100_set_gemm_cta_pairs(1)
     eng = pk.pipeline.PipelineEngine(device, layers=args.layers, decoder_layers=args.decoder_layers,
                                      seed=SEED, max_utterances=per_gpu, mel_frames=MEL_FRAMES,
                                      decode_groups=args.decode_groups)

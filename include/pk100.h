@@ -113,7 +113,9 @@ typedef struct pk100_gemm_args {
     uint8_t* keep_out;
     float* stats_out;
     const uint8_t* keep_in;
-    int* status;              /* device int, set to 1 if a bounded wait expired; may be NULL */
+    int* status;              /* device int, may be NULL: becomes 1 if a bounded wait expired; bit 3 (value 8) is
+                               * OR-ed in when PK100_EPI_SPARSE_OUT clamped a code of a kept tile at +127
+                               * (|v * out_scale| > 127: choose a smaller out_scale) */
     int max_ctas;             /* <= 0: one CTA per SM */
     const void* b_group_scales; /* PK100_KIND_F16_W4G128 only */
 } pk100_gemm_args;

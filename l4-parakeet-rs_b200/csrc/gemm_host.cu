@@ -104,16 +104,17 @@ static int encode_map(CUtensorMap* map, const void* base, int elem_bytes, uint64
     return res == CUDA_SUCCESS ? PK100_OK : PK100_ERR_DRIVER;
 }
 
-// Tensor map of the output for the staged TMA store of the 256-column kernels: every epilogue
+// Tensor map of the output for the staged TMA store (256-column kernels, 128-column linear kernels): every epilogue
 // warp owns 32 rows x (tile columns / 4).  Only slices with 64- or 128-byte rows leave that way
 // (their swizzle modes); anything else keeps per-thread stores.  Returns the row bytes or 0.
-template <int Epi>
+template <int Epi, int BlockN = 256>
 static int make_out_map(CUtensorMap* map, const GemmParams& p) {
     const int out_cols = Epi == EPI_GLU ? p.n / 2 : p.n;
-    const int cols_per_warp = (Epi == EPI_GLU ? 128 : 256) / (GemmWarps<BSRC_TMA>::kEpilogue / 4);
+    const int cols_per_warp = (Epi == EPI_GLU ? BlockN / 2 : BlockN) / (GemmWarps<BSRC_TMA>::kEpilogue / 4);
     const int obytes = p.out_type == OUT_F16 ? 2 : (p.out_type == OUT_F32 ? 4 : 1);
     const int row_bytes = cols_per_warp * obytes;
     if (row_bytes != 64 && row_bytes != 128) return 0;
+    if (BlockN == 128 && row_bytes != 64) return 0;      // its staging holds 64-byte rows only
     if ((reinterpret_cast<uintptr_t>(p.out) & 15u) != 0) return 0;
     if ((static_cast<size_t>(p.ld_out) * obytes) % 16 != 0) return 0;
     if (make_map(map, p.out, obytes, p.m, out_cols, p.ld_out, 32, row_bytes) != PK100_OK) return 0;
@@ -219,7 +220,7 @@ static int launch(const pk100_gemm_args& a, const GemmParams& p_in, cudaStream_t
     rc = make_map(&map_b, a.b, elem, a.n, a.k, a.ldb, BlockN / 2, SwizzleBytes);
     if (rc != PK100_OK) return rc;
     CUtensorMap map_out = map_a;
-    if constexpr (BlockN == 256) p.store_row_bytes = make_out_map<Epi>(&map_out, p);
+    if constexpr (gemm_store_bytes<Epi, BSRC_TMA, BlockN>() > 0) p.store_row_bytes = make_out_map<Epi, BlockN>(&map_out, p);
     const int m_tiles = (a.m + kBlockM - 1) / kBlockM;
     const int n_tiles = (p.n + BlockN - 1) / BlockN;
     int ctas = cta_budget(a);

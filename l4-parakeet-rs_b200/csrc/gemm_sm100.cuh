@@ -71,7 +71,10 @@ struct GemmWarps {
 // kernels use it.
 template <int Epi, int BSrc, int BlockN>
 constexpr int gemm_store_bytes() {
-    if (BSrc != BSRC_TMA || BlockN != 256) return 0;
+    if (BSrc != BSRC_TMA) return 0;
+    // 128-column linear tiles: 32 columns per warp, 64-byte rows for fp16 output
+    if (BlockN == 128 && Epi == EPI_LINEAR) return GemmWarps<BSrc>::kEpilogue * 32 * 64;
+    if (BlockN != 256) return 0;
     return GemmWarps<BSrc>::kEpilogue * 32 * (Epi == EPI_SPARSE_OUT ? 64 : 128);
 }
 
@@ -199,6 +202,43 @@ __device__ __forceinline__ uint64_t load_live_mask(const uint8_t* keep_in, int m
     return mask;
 }
 
+// The same mask for the single-lane roles (TMA producer, MMA issuer), which walk it once per tile:
+// the bitmap row is fetched as 16-byte words one tile AHEAD (`fetch`), and compressed to bits when
+// its tile starts (`mask`), so that the walk never waits for a chain of byte loads from L2.
+struct LiveMaskRow {
+    uint4 w[4];          // up to 64 flag bytes
+    bool vector;
+    __device__ __forceinline__ void fetch(const uint8_t* keep_in, int mt, int k_tiles64) {
+        vector = false;
+        if (keep_in == nullptr) return;
+        const uint8_t* row = keep_in + static_cast<size_t>(mt) * k_tiles64;
+        if (k_tiles64 % 16 == 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
+            vector = true;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                w[i] = 16 * i < k_tiles64 ? __ldg(reinterpret_cast<const uint4*>(row) + i) : make_uint4(0, 0, 0, 0);
+        }
+    }
+    // bit i of the result = byte i of a 4-byte word is non-zero
+    static __device__ __forceinline__ uint32_t nonzero_bytes(uint32_t x) {
+        const uint32_t t = (((x & 0x7f7f7f7fu) + 0x7f7f7f7fu) | x) & 0x80808080u;   // 0x80 per non-zero byte
+        return ((t >> 7) * 0x00204081u >> 21) & 0xFu;                              // gather the four flags
+    }
+    __device__ __forceinline__ uint64_t mask(const uint8_t* keep_in, int mt, int k_tiles64) const {
+        if (keep_in == nullptr) return ~0ull;
+        if (!vector) return load_live_mask(keep_in, mt, k_tiles64);
+        uint64_t m = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t words[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                m |= static_cast<uint64_t>(nonzero_bytes(words[j])) << (16 * i + 4 * j);
+        }
+        return m;
+    }
+};
+
 // Is K block `kb` (SwizzleBytes wide, 8-bit elements) live?
 template <int SwizzleBytes>
 __device__ __forceinline__ bool k_block_live(uint64_t mask, int kb) {
@@ -309,11 +349,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            [[maybe_unused]] LiveMaskRow ahead;
+            if (CtaGroup == 1 && worker < num_tiles) ahead.fetch(p.keep_in, worker % m_groups, k_tiles64);
             for (int tile = worker; tile < num_tiles && ok; tile += workers) {
                 const int mg = tile % m_groups;
                 const int nt = tile / m_groups;
                 const int m0 = (mg * CtaGroup + static_cast<int>(rank)) * kBlockM;
-                const uint64_t live_mask = group_live_mask(mg);
+                uint64_t live_mask;
+                if constexpr (CtaGroup == 1) {
+                    live_mask = ahead.mask(p.keep_in, mg, k_tiles64);
+                    if (tile + workers < num_tiles) ahead.fetch(p.keep_in, (tile + workers) % m_groups, k_tiles64);
+                } else {
+                    live_mask = group_live_mask(mg);
+                }
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (p.keep_in != nullptr && !k_block_live<SwizzleBytes>(live_mask, kb)) continue;
                     if (!mbar_wait_bounded(empty_bar + stage, phase ^ 1u, abort_flag)) {
@@ -367,11 +415,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             uint32_t phase = 0;
             int local = 0;
             bool ok = true;
+            [[maybe_unused]] LiveMaskRow ahead;
+            if (CtaGroup == 1 && worker < num_tiles) ahead.fetch(p.keep_in, worker % m_groups, k_tiles64);
             for (int tile = worker; tile < num_tiles && ok; tile += workers, ++local) {
                 const int mg = tile % m_groups;
                 const int buf = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
-                const uint64_t live_mask = group_live_mask(mg);
+                uint64_t live_mask;
+                if constexpr (CtaGroup == 1) {
+                    live_mask = ahead.mask(p.keep_in, mg, k_tiles64);
+                    if (tile + workers < num_tiles) ahead.fetch(p.keep_in, (tile + workers) % m_groups, k_tiles64);
+                } else {
+                    live_mask = group_live_mask(mg);
+                }
                 if (!mbar_wait_bounded(tmem_empty_bar + buf, acc_phase ^ 1u, abort_flag)) {
                     ok = false;
                     break;
@@ -735,6 +791,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 for (int qd = 0; qd < 4; ++qd) mx = fmaxf(mx, red[part * 4 + qd]);
                 mx *= 1.0f / p.out_scale;                       // statistic in activation units
                 const bool keep = mx >= p.tau;
+                // a kept tile whose largest |a * out_scale| exceeds 127 lost information to the clamp:
+                // reported as status bit 3 (value 8), nothing else changes
+                if (keep && mx * p.out_scale > 127.0f && quad == 0 && lane == 0 && p.status != nullptr)
+                    atomicOr(p.status, 8);
                 const int tile64 = n0 / 64 + part;
                 if (quad == 0 && lane == 0 && tile64 < n_tiles64 && mt < m_tiles) {
                     p.keep_out[static_cast<size_t>(mt) * n_tiles64 + tile64] = keep ? 1 : 0;

@@ -223,6 +223,32 @@ class PipelineEngine:
         counts = self.counts_host.numpy()
         return [self.tokens_host[u, :int(counts[u])].numpy().copy() for u in range(utterances)]
 
+    # ---- one long utterance cut into chunks over several GPUs (see parallel.py)
+    def encode_chunk(self, mel_chunk_host, lead_rows, rows):
+        """Encodes `rows` encoder rows of a long utterance from the mel frames that cover them
+        (`parallel.mel_range`): subsampling, the `lead_rows` rows in front dropped, the blocks
+        on the rest as ONE sequence of `rows` rows, the encoder projection.  Needs an engine
+        built for one utterance of at least mel_chunk_host.shape[0] frames.  Returns the
+        projected rows [rows, 640] (fp16, device)."""
+        frames = int(mel_chunk_host.shape[0])
+        if frames > self.mel_frames or self.max_utterances < 1:
+            raise ValueError("chunk longer than the engine was sized for")
+        if lead_rows + rows > self.seg_stride or rows > sub_mod.output_frames(frames) - lead_rows:
+            raise ValueError("the mel frames do not cover the requested rows")
+        self.mel_dev[0, :frames].copy_(mel_chunk_host, non_blocking=True)
+        self.set_lengths([frames])
+        if not hasattr(self, "_chunk_rows"):
+            # subsampling output with room for the dropped rows in front of a 128-aligned block
+            self._chunk_rows = torch.zeros((self.seg_stride + 128, 1024), dtype=torch.float16, device=self.device)
+            self._chunk_valid = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.sub.run(self.mel_dev[:1], self.seg_stride + 128, mel_frames=self.mel_frames_dev[:1], out=self._chunk_rows)
+        x = self._chunk_rows[lead_rows:lead_rows + self.seg_stride]
+        self._chunk_valid.fill_(rows)
+        encoded = self.enc.run(x, self.state_b[:self.seg_stride], self.ws, 1, self.seg_stride, rows,
+                               seg_valid=self._chunk_valid)
+        self.dec.project(encoded, out=self.enc_proj[:self.seg_stride])
+        return self.enc_proj[:rows]
+
     # ---- optional stage in front: PCM -> log-mel (src/cuda/pipeline.rs:437-470 runs it first)
     def attach_frontend(self, window, mel_filters):
         """window [400] and mel_filters [128, 257]: the artifact's frontend.* tensors."""
@@ -256,8 +282,56 @@ class PipelineEngine:
         counts = self.counts_host.numpy()
         return [self.tokens_host[u, :int(counts[u])].numpy().copy() for u in range(utterances)]
 
+    HIDDEN_SATURATED = 8      # status bit of the encoder: an FF hidden activation was clamped at INT8 +127
+
+    def hidden_saturated(self):
+        """True when an FF hidden activation exceeded the INT8 range (x 1/32) since the engine was
+        built: harmless for N(0, 0.02) weights, a sign of a wrong hidden scale on a real checkpoint."""
+        return bool(self.enc.status(self.arena, self.ws) & self.HIDDEN_SATURATED)
+
     def status(self):
-        dec = int(self.dec.status.item())
+        """Non-zero when a bounded wait expired inside a kernel (saturation is reported separately)."""
+        dec = int(self.dec.status.item()) & ~4          # bit 4: a decode round had only NaN scores
         for scratch in self.dec_scratch[1:]:
             dec |= int(scratch[1].item())
-        return self.enc.status(self.arena, self.ws) | dec | int(self.sub.status.item())
+        return (self.enc.status(self.arena, self.ws) & ~self.HIDDEN_SATURATED) | dec | int(self.sub.status.item())
+
+
+def transcribe_long(eng, mel_host, rank=0, world_size=1, group=None, halo=None, decoder=None):
+    """One long utterance over `world_size` GPUs, no collective on the compute path: every rank
+    encodes its chunk of encoder rows with a halo (`parallel.chunk_plan`), the projected rows
+    of the chunk interiors are gathered on the host, rank 0 decodes them as one sequence and
+    returns the token ids (the other ranks return None).
+    eng: this rank's PipelineEngine for ONE utterance, sized for the longest extended chunk;
+    mel_host: fp32 CPU tensor [frames, 128], the same on every rank; halo: rows beside a chunk
+    (default: the exact halo of the engine's depth); decoder: (TdtDecoder, its device) on rank 0
+    when the decode should not use eng.dec."""
+    from . import parallel
+    frames = int(mel_host.shape[0])
+    total_rows = sub_mod.output_frames(frames)
+    if halo is None:
+        halo = parallel.exact_halo_rows(len(eng.enc.layers), tile_sparse=any(l.ff1.tau > 0 or l.ff2.tau > 0
+                                                                              for l in eng.enc.layers))
+    chunk = parallel.chunk_plan(total_rows, world_size, halo)[rank]
+    rows = chunk.extended[1] - chunk.extended[0]
+    if rows > 0:
+        first, last, lead = parallel.mel_range(chunk, frames)
+        proj = eng.encode_chunk(mel_host[first:last], lead, rows)
+        mine = proj[chunk.interior].float().cpu().numpy()
+    else:
+        mine = np.zeros((0, dec_mod.HIDDEN), np.float32)
+    if eng.status() != 0:
+        raise RuntimeError("libpk100 reported an expired bounded wait")
+    parts = parallel.gather_rows(mine, group=group)
+    if parts is None:
+        return None
+    whole = parallel.stitch_rows(parts)
+    dec = eng.dec if decoder is None else decoder
+    stride = seg_stride_for(total_rows)
+    rows_dev = torch.zeros((stride, dec_mod.HIDDEN), dtype=torch.float16, device=eng.device)
+    rows_dev[:total_rows].copy_(torch.from_numpy(whole).to(torch.float16))
+    fr = torch.tensor([total_rows], dtype=torch.int32, device=eng.device)
+    cache = "int8" if total_rows >= dec_mod.LONG_REQUEST_FRAMES else "fp16"
+    tokens, _, counts = dec.decode(rows_dev, 1, stride, fr, total_rows * MAX_SYMBOLS_PER_FRAME, lstm_cache=cache)
+    torch.cuda.synchronize()
+    return tokens[0, :int(counts[0].item())].cpu().numpy()

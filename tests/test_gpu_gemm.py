@@ -284,3 +284,114 @@ def test_gemm_rejects_bad_arguments(pk, cuda):
     out = torch.zeros((8, 64), dtype=torch.float16, device=cuda)
     with pytest.raises(L.Pk100Error):
         pk.ops.gemm(a, b, kind=L.KIND_F16, out=out)
+
+
+@pytest.mark.parametrize("n", [4096, 1024])
+def test_fp8_expand_e4m3_out(pk, cuda, n):
+    """The reference's packed FFN chain writes the expand output as E4M3(f16(SiLU(v)) * 16)
+    (epilogue 1, kernels/sm89/encoder.cu:1006-1022, pk_sm89_ffn_expand_fp8_packed :1071-1077):
+    PK100_OUT_E4M3 with out_scale = 16.  n = 4096 takes the 256-column tiles (staged TMA store of
+    64-byte rows), n = 1024 the 128-column tiles (per-thread stores)."""
+    L = pk.lib
+    rng = np.random.default_rng(31)
+    m = 300
+    x = codec.f16_round(rng.standard_normal((m, 1024)))
+    w = codec.f16_round(rng.standard_normal((n, 1024)) * 0.02)
+    xq = codec.quantize_fp8_fixed(x, 56.0)
+    wq, ws = codec.quantize_rows_fp8(w)
+    st = _status(cuda)
+    out = torch.zeros((m, n), dtype=torch.uint8, device=cuda)
+    pk.ops.gemm(dev(xq), dev(wq), kind=L.KIND_E4M3, out=out, out_type=L.OUT_E4M3, out_scale=16.0,
+                row_scale=8.0 / 448.0, col_scales=dev(ws), act=L.ACT_SILU, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    silu16 = O.linear_fp8(xq, wq, ws, O.FP8_INPUT_SCALE, act=1)          # f16(SiLU(v))
+    want = codec.e4m3_encode((silu16 * np.float32(16.0)).astype(np.float32))
+    got = host(out)
+    # a code differs only where the fp16 value before it differs by an ulp (fast-math exp)
+    assert np.mean(got != want) < 2e-2
+    d = np.abs(codec.e4m3_decode(got) - codec.e4m3_decode(want))
+    assert np.all(d <= 0.125 * np.abs(codec.e4m3_decode(want)) + 2.0 ** -9)
+
+
+def test_f16_operands_with_silu_glu_and_sparse_out(pk, cuda):
+    """The epilogue families on kind::f16 operands (pk_sm89_ffn_expand_async, the reference's fp16
+    FF expand with SiLU, kernels/sm89/encoder.cu:427-547; fp16 conv pointwise + GLU)."""
+    L = pk.lib
+    rng = np.random.default_rng(32)
+    m, valid = 260, 250
+    x = codec.f16_round(rng.standard_normal((m, 1024)))
+    w = codec.f16_round(rng.standard_normal((2048, 1024)) * 0.03)
+    st = _status(cuda)
+    # SiLU
+    out = torch.zeros((m, 2048), dtype=torch.float16, device=cuda)
+    pk.ops.gemm(dev16(x), dev16(w), kind=L.KIND_F16, out=out, act=L.ACT_SILU, status=st)
+    torch.cuda.synchronize()
+    assert np.max(np.abs(host(out) - O.linear_f16(x, w, act=1))) <= 4e-3
+    # GLU (+ pad-row mask)
+    glu = torch.zeros((m, 1024), dtype=torch.float16, device=cuda)
+    pk.ops.gemm(dev16(x), dev16(w), kind=L.KIND_F16, epilogue=L.EPI_GLU, out=glu, valid_rows=valid, status=st)
+    torch.cuda.synchronize()
+    want = O.glu_masked(O.linear_f16(x, w), m, valid)
+    assert np.all(host(glu)[valid:] == 0) and np.max(np.abs(host(glu) - want)) <= 4e-3
+    # SPARSE_OUT: SiLU, tile statistic, INT8 codes of the kept tiles
+    mt = (m + 127) // 128
+    hq = torch.zeros((m, 2048), dtype=torch.int8, device=cuda)
+    keep = torch.zeros((mt, 32), dtype=torch.uint8, device=cuda)
+    stats = torch.zeros((mt, 32), dtype=torch.float32, device=cuda)
+    h32 = O.silu(O.epilogue(O.accumulate(x, w)))
+    want_stats = O.tile_stats(h32, m)
+    tau = float(np.sort(want_stats.ravel())[int(0.5 * want_stats.size)])
+    pk.ops.gemm(dev16(x), dev16(w), kind=L.KIND_F16, epilogue=L.EPI_SPARSE_OUT, out=hq, out_type=L.OUT_S8,
+                out_scale=32.0, tau=tau, keep_out=keep, stats_out=stats, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert np.allclose(host(stats), want_stats, rtol=2e-3, atol=1e-5)
+    near = np.abs(want_stats / tau - 1.0) < 2e-3
+    assert np.array_equal(host(keep)[~near], (want_stats >= tau).astype(np.uint8)[~near])
+    mask = np.repeat(np.repeat(host(keep), 128, axis=0)[:m], 64, axis=1).astype(bool)
+    codes = np.clip(np.rint(h32 * 32.0), -127, 127).astype(np.int8)
+    got = host(hq)
+    assert not got[~mask].any()
+    assert np.max(np.abs(got[mask].astype(int) - codes[mask].astype(int))) <= 1 and np.mean(got[mask] != codes[mask]) < 3e-2
+
+
+def test_cta_limits_do_not_change_results(pk, cuda):
+    """max_ctas (per call) and the process-wide cap shrink the persistent grid; every tile is still
+    computed, bit for bit the same."""
+    L = pk.lib
+    rng = np.random.default_rng(33)
+    m, n, k = 700, 1024, 1024
+    xq = dev(rng.integers(-127, 128, (m, k), dtype=np.int8))
+    wq = dev(rng.integers(-127, 128, (n, k), dtype=np.int8))
+    outs = []
+    for max_ctas, cap in ((0, 0), (7, 0), (0, 20), (1, 0)):
+        L.lib.pk100_set_gemm_cta_cap(cap)
+        st = _status(cuda)
+        out = torch.zeros((m, n), dtype=torch.float32, device=cuda)
+        pk.ops.gemm(xq, wq, kind=L.KIND_S8, out=out, out_type=L.OUT_F32, max_ctas=max_ctas, status=st)
+        torch.cuda.synchronize()
+        assert int(st.item()) == 0
+        outs.append(host(out).copy())
+    L.lib.pk100_set_gemm_cta_cap(0)
+    assert all(np.array_equal(outs[0], o) for o in outs[1:])
+    hits, misses = L.tensor_map_cache_stats()
+    assert hits > 0 and misses > 0          # the four calls share their three descriptors
+
+
+def test_sparse_out_reports_clamped_codes(pk, cuda):
+    """|SiLU| * out_scale beyond 127 is clamped, and status bit 3 says so."""
+    L = pk.lib
+    rng = np.random.default_rng(34)
+    m = 128
+    x = codec.f16_round(rng.standard_normal((m, 1024)))
+    w = codec.f16_round(rng.standard_normal((256, 1024)) * 0.02)
+    hq = torch.zeros((m, 256), dtype=torch.int8, device=cuda)
+    keep = torch.zeros((1, 4), dtype=torch.uint8, device=cuda)
+    for out_scale, clipped in ((32.0, False), (4096.0, True)):
+        st = _status(cuda)
+        pk.ops.gemm(dev16(x), dev16(w), kind=L.KIND_F16, epilogue=L.EPI_SPARSE_OUT, out=hq, out_type=L.OUT_S8,
+                    out_scale=out_scale, tau=0.0, keep_out=keep, status=st)
+        torch.cuda.synchronize()
+        assert bool(int(st.item()) & 8) == clipped and not int(st.item()) & 1
+        assert int(host(hq).max()) == (127 if clipped else int(host(hq).max()))
