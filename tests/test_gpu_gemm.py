@@ -345,7 +345,9 @@ def test_f16_operands_with_silu_glu_and_sparse_out(pk, cuda):
     pk.ops.gemm(dev16(x), dev16(w), kind=L.KIND_F16, epilogue=L.EPI_SPARSE_OUT, out=hq, out_type=L.OUT_S8,
                 out_scale=32.0, tau=tau, keep_out=keep, stats_out=stats, status=st)
     torch.cuda.synchronize()
-    assert int(st.item()) == 0
+    assert int(st.item()) & 1 == 0
+    # N(0, 0.03) weights push a few SiLU values beyond 127 / 32: the clamp is reported (bit 3)
+    assert bool(int(st.item()) & 8) == bool(np.max(h32[:m]) * 32.0 > 127.0)
     assert np.allclose(host(stats), want_stats, rtol=2e-3, atol=1e-5)
     near = np.abs(want_stats / tau - 1.0) < 2e-3
     assert np.array_equal(host(keep)[~near], (want_stats >= tau).astype(np.uint8)[~near])
