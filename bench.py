@@ -51,7 +51,7 @@ def parse_args():
     ap.add_argument("--tau-cache", default=None,
                     help="JSON file with calibrated tile thresholds: loaded if present, written otherwise")
     ap.add_argument("--micro", default=None,
-                    choices=["ff_expand", "ff_contract", "qkv", "attention", "layer_norm", "depthwise", "decode"],
+                    choices=["ff_expand", "ff_contract", "qkv", "out_proj", "attention", "layer_norm", "depthwise", "decode"],
                     help="time ONE kernel of the path on synthetic operands (used for ncu captures)")
     ap.add_argument("--rows", type=int, default=6144, help="rows (M) of the --micro case")
     ap.add_argument("--cta-pairs", action="store_true",
@@ -254,7 +254,16 @@ def run_micro(args):
     def rand16(*shape, std=1.0):
         return (torch.randn(shape, generator=g) * std).half().to(dev)
 
-    if args.micro in ("ff_expand", "ff_contract", "qkv"):
+    if args.micro == "out_proj":
+        # attention output projection: fp16 activations x INT4 group-128 weights dequantised in shared memory
+        x = rand16(m, 1024)
+        codes, gs = pk.ops.pack_weight_rows(rand16(1024, 1024, std=0.02), L.PACK_S4_G128)
+        res = rand16(m, 1024)
+        call = lambda: pk.ops.gemm(x, codes, kind=L.KIND_F16_W4G128, out=res, residual=res, b_group_scales=gs, n=1024)
+        flops, nbytes = 2.0 * m * 1024 * 1024, m * 1024 * 2 * 3 + 1024 * 512 + 8 * 1024 * 2
+        peak, unit, bound = peaks["bf16"], "TFLOP/s", "tensor"
+        work = flops / 1e12
+    elif args.micro in ("ff_expand", "ff_contract", "qkv"):
         if args.micro == "ff_expand":
             x = rand16(m, 1024)
             w = rand16(4096, 1024, std=0.02)
@@ -303,8 +312,13 @@ def run_micro(args):
         qkv = rand16(m, 3072)
         pos, u, v = rand16(8, 272, 128), rand16(8, 128, std=0.02), rand16(8, 128, std=0.02)
         out = torch.empty((m, 1024), dtype=torch.float16, device=dev)
-        call = lambda: pk.ops.local_attention(qkv[:, :1024], qkv[:, 1024:2048], qkv[:, 2048:], pos, u, v,
-                                              seg_stride=seg, valid_rows=750, out=out)
+        if os.environ.get("PK100_ATTENTION") == "mma":
+            call = lambda: pk.ops.local_attention(qkv[:, :1024], qkv[:, 1024:2048], qkv[:, 2048:], pos, u, v,
+                                                  seg_stride=seg, valid_rows=750, out=out)
+        else:
+            scratch = torch.empty(m * 1024 * 2, dtype=torch.uint8, device=dev)
+            call = lambda: pk.ops.local_attention_tcgen05(qkv[:, :1024], qkv[:, 1024:2048], qkv[:, 2048:], pos, u, v,
+                                                          seg_stride=seg, valid_rows=750, out=out, scratch=scratch)
         nbytes = m * 1024 * 2 * 4
         work, peak, unit, bound = nbytes / 1e9, peaks["hbm_gbs"], "GB/s", "hbm"
     elif args.micro == "depthwise":

@@ -258,6 +258,11 @@ static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr
 
 using namespace pk100;
 
+int pk100_tensor_map_2d(void* map, const void* base, int elem_bytes, unsigned long long rows,
+                        unsigned long long cols, unsigned long long ld, int box_rows, int swizzle_bytes) {
+    return make_map(static_cast<CUtensorMap*>(map), base, elem_bytes, rows, cols, ld, box_rows, swizzle_bytes);
+}
+
 static std::atomic<long long> g_launches{0};
 void pk100_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 extern "C" long long pk100_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -21,3 +21,9 @@ static inline int pk100_launch_status() {
     cudaGetLastError();   // clear the non-sticky launch error so later calls are not poisoned
     return static_cast<int>(err);
 }
+
+// 2-D TMA descriptor of a row-major matrix [rows, cols] (`ld` elements between rows) with a box of
+// [box_rows, swizzle_bytes / elem_bytes] elements; served from the library's descriptor cache
+// (gemm_host.cu).  `map` points to a CUtensorMap.
+int pk100_tensor_map_2d(void* map, const void* base, int elem_bytes, unsigned long long rows,
+                        unsigned long long cols, unsigned long long ld, int box_rows, int swizzle_bytes);
