@@ -51,9 +51,14 @@ def parse_args():
     ap.add_argument("--tau-cache", default=None,
                     help="JSON file with calibrated tile thresholds: loaded if present, written otherwise")
     ap.add_argument("--micro", default=None,
-                    choices=["ff_expand", "ff_contract", "qkv", "out_proj", "attention", "layer_norm", "depthwise", "decode"],
+                    choices=["ff_expand", "ff_contract", "qkv", "out_proj", "out_proj_f16", "attention", "layer_norm", "depthwise", "decode"],
                     help="time ONE kernel of the path on synthetic operands (used for ncu captures)")
     ap.add_argument("--rows", type=int, default=6144, help="rows (M) of the --micro case")
+    ap.add_argument("--out-proj", default="f16", choices=["f16", "int4"],
+                    help="resident form of the INT4-g128 out-proj weights: expanded fp16 (default) or packed codes "
+                         "dequantised inside the GEMM; same bits")
+    ap.add_argument("--plain-launch", action="store_true",
+                    help="launch the kernels of the block chain in plain stream order (no programmatic dependent launch)")
     ap.add_argument("--cta-pairs", action="store_true",
                     help="256-column GEMM tiles on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles)")
     ap.add_argument("--utterances", type=int, default=UTTERANCES_PER_GPU,
@@ -229,7 +234,9 @@ def workload_config(args):
         decode_groups=args.decode_groups,
         encoder_layers=args.layers, decoder_lstm_layers=args.decoder_layers,
         precision_map=("FF: E4M3 x E4M3 expand + SiLU + 70% zero 128x64 tiles -> INT8 x INT8 contract with "
-                       "tile skip; QKV INT8; out-proj INT4-g128 (fp16 MMA); conv pointwise E4M3; attention fp16"),
+                       "tile skip; QKV INT8; out-proj INT4-g128 values, fp16 MMA (" +
+                       ("expanded to fp16 at load" if args.out_proj == "f16" else "dequantised inside the GEMM") +
+                       "); conv pointwise E4M3; attention fp16 (tcgen05)"),
         weights="random-init N(0,0.02), seed 4",
         l2=("no flush: each step streams ~0.6 GB of weights and ~0.3 GB of activations, "
             "several times the 126 MB L2"),
@@ -247,6 +254,8 @@ def run_micro(args):
     torch.cuda.set_device(dev)
     if args.cta_pairs:
         L.lib.pk100_set_gemm_cta_pairs(1)
+    if args.plain_launch:
+        L.lib.pk100_set_dependent_launch(0)
     g = torch.Generator(device="cpu").manual_seed(1)
     m = args.rows
     peaks = measured_peaks()
@@ -254,12 +263,17 @@ def run_micro(args):
     def rand16(*shape, std=1.0):
         return (torch.randn(shape, generator=g) * std).half().to(dev)
 
-    if args.micro == "out_proj":
+    if args.micro in ("out_proj", "out_proj_f16"):
         # attention output projection: fp16 activations x INT4 group-128 weights dequantised in shared memory
+        # (out_proj_f16: the same product with the weights expanded to fp16 beforehand, for comparison)
         x = rand16(m, 1024)
         codes, gs = pk.ops.pack_weight_rows(rand16(1024, 1024, std=0.02), L.PACK_S4_G128)
         res = rand16(m, 1024)
-        call = lambda: pk.ops.gemm(x, codes, kind=L.KIND_F16_W4G128, out=res, residual=res, b_group_scales=gs, n=1024)
+        if args.micro == "out_proj":
+            call = lambda: pk.ops.gemm(x, codes, kind=L.KIND_F16_W4G128, out=res, residual=res, b_group_scales=gs, n=1024)
+        else:
+            w16 = pk.ops.dequant_w4g128(codes, gs)
+            call = lambda: pk.ops.gemm(x, w16, kind=L.KIND_F16, out=res, residual=res)
         flops, nbytes = 2.0 * m * 1024 * 1024, m * 1024 * 2 * 3 + 1024 * 512 + 8 * 1024 * 2
         peak, unit, bound = peaks["bf16"], "TFLOP/s", "tensor"
         work = flops / 1e12
@@ -621,9 +635,11 @@ def main():
     my_utts = pk.parallel.shard_utterances(total_utts, world, rank)
     if args.cta_pairs:
         pk.lib.lib.pk100_set_gemm_cta_pairs(1)
+    if args.plain_launch:
+        pk.lib.lib.pk100_set_dependent_launch(0)
     eng = pk.pipeline.PipelineEngine(device, layers=args.layers, decoder_layers=args.decoder_layers,
                                      seed=SEED, max_utterances=per_gpu, mel_frames=MEL_FRAMES,
-                                     decode_groups=args.decode_groups)
+                                     decode_groups=args.decode_groups, out_proj_resident=args.out_proj)
     mel_host = torch.from_numpy(np.stack([pk.synth.mel_input(100 + u, MEL_FRAMES) for u in my_utts])).pin_memory()
     eng.mel_dev.copy_(mel_host)
     cache = Path(args.tau_cache) if args.tau_cache else None

@@ -133,6 +133,12 @@ void pk100_set_gemm_cta_pairs(int enable);
  * and double the kernel's time, a smaller grid does not.  Takes effect on launches issued after it. */
 void pk100_set_gemm_cta_cap(int ctas);
 
+/* Programmatic dependent launch of the kernels of the per-block chain (LayerNorm, GEMMs,
+ * attention, depthwise convolution): each launch may become resident while its predecessor in the
+ * stream drains (its set-up overlaps that tail) and waits for the whole predecessor grid before it
+ * touches global memory, so results do not change.  Default 1; 0 = plain stream order. */
+void pk100_set_dependent_launch(int enable);
+
 /* Tensor maps (TMA descriptors) are cached per (pointer, shape, leading dimension, box): hits and
  * misses of that cache since the library was loaded.  Either pointer may be NULL. */
 void pk100_tensor_map_cache_stats(long long* hits, long long* misses);

@@ -139,7 +139,10 @@ local_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const 
     const int base = seg * p.seg_stride;
     const int rows_here = min(kTile, p.seg_stride - q0);
 
+    // (the segment lengths, biases and position rows are constant over the kernel chain)
+    grid_dependents_launch();
     if (q0 >= valid) {                       // the whole tile is padding: zero-fill and leave
+        grid_dependency_wait();
         for (int c = tid; c < rows_here * 16; c += kThreads)
             *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(base + q0 + c / 16) * p.ldo + head * kDim + (c % 16) * 8) =
                 make_uint4(0, 0, 0, 0);
@@ -176,6 +179,7 @@ local_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const 
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sm.tmem_base;
+    grid_dependency_wait();                  // Q, K and the transposed V come from the kernels before
     const int key_first = q0 - kReach;       // window index kk <-> key key_first + kk
     // slot of key block b, and of value block b after it
     auto slot_of = [](int b) { return b == 0 ? 2 : b - 1; };
@@ -509,6 +513,8 @@ local_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const 
 __global__ void __launch_bounds__(256) transpose_value_kernel(const __half* __restrict__ v, int ldv, __half* __restrict__ vt,
                                                               int rows) {
     __shared__ __half tile[64][66];
+    grid_dependents_launch();
+    grid_dependency_wait();
     const int r0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
     const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;       // 8 row groups
     for (int i = ty; i < 64; i += 8) {
@@ -562,7 +568,7 @@ extern "C" int pk100_local_relpos_attention_tcgen05(
     if (rc == PK100_OK) rc = pk100_tensor_map_2d(&map_vt, scratch, 2, 1024, rows, rows, kDim, 128);
     if (rc != PK100_OK) return rc;
 
-    transpose_value_kernel<<<dim3(static_cast<unsigned>((rows + 63) / 64), 1024 / 64), 256, 0, stream>>>(
+    pk100_launch_chained(transpose_value_kernel, dim3(static_cast<unsigned>((rows + 63) / 64), 1024 / 64), dim3(256), 0, stream,
         static_cast<const __half*>(value), ldv, static_cast<__half*>(scratch), static_cast<int>(rows));
     rc = pk100_launch_status();
     if (rc != PK100_OK) return rc;
@@ -578,6 +584,6 @@ extern "C" int pk100_local_relpos_attention_tcgen05(
     Params p{static_cast<const __half*>(bias_u), static_cast<const __half*>(bias_v), static_cast<__half*>(output), ldo,
              segments, seg_stride, valid_rows, seg_valid, status};
     dim3 grid(seg_stride / kTile, kHeads, segments);
-    local_attention_tcgen05_kernel<<<grid, kThreads, smem_bytes, stream>>>(map_q, map_k, map_p, map_p16, map_vt, p);
+    pk100_launch_chained(local_attention_tcgen05_kernel, grid, dim3(kThreads), smem_bytes, stream, map_q, map_k, map_p, map_p16, map_vt, p);
     return pk100_launch_status();
 }

@@ -139,6 +139,7 @@ static std::atomic<int> g_use_pairs{0};
 extern "C" void pk100_set_gemm_cta_pairs(int enable) { g_use_pairs.store(enable != 0); }
 
 // Process-wide cap on the persistent CTAs of a GEMM whose own max_ctas is <= 0 (0 = one per SM).
+static std::atomic<int> g_dependent_launch{1};
 static std::atomic<int> g_cta_cap{0};
 extern "C" void pk100_set_gemm_cta_cap(int ctas) { g_cta_cap.store(ctas > 0 ? ctas : 0); }
 static int cta_budget(const pk100_gemm_args& a) {
@@ -146,6 +147,7 @@ static int cta_budget(const pk100_gemm_args& a) {
     const int cap = g_cta_cap.load(std::memory_order_relaxed);
     return cap > 0 && cap < sm_count() ? cap : sm_count();
 }
+extern "C" void pk100_set_dependent_launch(int enable) { g_dependent_launch.store(enable != 0); }
 extern "C" void pk100_tensor_map_cache_stats(long long* hits, long long* misses) {
     if (hits != nullptr) *hits = g_map_hits.load(std::memory_order_relaxed);
     if (misses != nullptr) *misses = g_map_misses.load(std::memory_order_relaxed);
@@ -225,14 +227,15 @@ static int launch(const pk100_gemm_args& a, const GemmParams& p_in, cudaStream_t
     const int n_tiles = (p.n + BlockN - 1) / BlockN;
     int ctas = cta_budget(a);
     if (ctas > m_tiles * n_tiles) ctas = m_tiles * n_tiles;
-    kernel<<<ctas, GemmWarps<BSRC_TMA>::kThreads, Smem::kTotal, stream>>>(map_a, map_b, map_out, p);
+    pk100_launch_chained(kernel, dim3(ctas), dim3(GemmWarps<BSRC_TMA>::kThreads), Smem::kTotal, stream, map_a, map_b, map_out, p);
     return pk100_launch_status();
 }
 
 // fp16 activations x INT4 group-128 weights, dequantised in shared memory by producer warps.
 static int launch_w4(const pk100_gemm_args& a, const GemmParams& p, cudaStream_t stream) {
     constexpr int BlockN = 128;
-    using Smem = GemmSmem<BlockN, 128>;
+    constexpr int kMTiles = GemmWarps<BSRC_W4G128>::kMTiles;
+    using Smem = GemmSmem<BlockN, 128, BlockN * kMTiles, 0, kBlockM * kMTiles>;
     auto kernel = gemm_kernel<KIND_F16, BlockN, 128, EPI_LINEAR, BSRC_W4G128>;
     static bool configured = false;
     if (!configured) {
@@ -244,11 +247,12 @@ static int launch_w4(const pk100_gemm_args& a, const GemmParams& p, cudaStream_t
     CUtensorMap map_a;
     const int rc = make_map(&map_a, a.a, 2, a.m, a.k, a.lda, kBlockM, 128);
     if (rc != PK100_OK) return rc;
-    const int m_tiles = (a.m + kBlockM - 1) / kBlockM;
+    const int m_items = (a.m + kBlockM * kMTiles - 1) / (kBlockM * kMTiles);   // 256-row work items
     const int n_tiles = (p.n + BlockN - 1) / BlockN;
     int ctas = cta_budget(a);
-    if (ctas > m_tiles * n_tiles) ctas = m_tiles * n_tiles;
-    kernel<<<ctas, GemmWarps<BSRC_W4G128>::kThreads, Smem::kTotal, stream>>>(map_a, map_a, map_a, p);   // neither B nor the output has a tensor map
+    if (ctas > m_items * n_tiles) ctas = m_items * n_tiles;
+    // neither B nor the output has a tensor map
+    pk100_launch_chained(kernel, dim3(ctas), dim3(GemmWarps<BSRC_W4G128>::kThreads), Smem::kTotal, stream, map_a, map_a, map_a, p);
     return pk100_launch_status();
 }
 
@@ -262,6 +266,8 @@ int pk100_tensor_map_2d(void* map, const void* base, int elem_bytes, unsigned lo
                         unsigned long long cols, unsigned long long ld, int box_rows, int swizzle_bytes) {
     return make_map(static_cast<CUtensorMap*>(map), base, elem_bytes, rows, cols, ld, box_rows, swizzle_bytes);
 }
+
+bool pk100_dependent_launch_enabled() { return pk100::g_dependent_launch.load(std::memory_order_relaxed) != 0; }
 
 static std::atomic<long long> g_launches{0};
 void pk100_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }

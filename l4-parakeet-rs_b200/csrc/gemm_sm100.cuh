@@ -5,10 +5,13 @@
 // One CTA per SM loops over 128 x BLOCK_N output tiles.
 //   warp 0      TMA producer: global -> swizzled shared-memory stage ring
 //   warp 1      tcgen05.mma issuer (one elected lane); owns the TMEM allocation
-//   warps 2..9  epilogue: tcgen05.ld the fp32/s32 accumulator, apply scales /
-//               bias / activation / residual / quantisation, store to global
-// Accumulators are double-buffered in TMEM (2 x BLOCK_N columns) so the MMAs of
-// tile i+1 overlap the epilogue of tile i.  All waits are bounded (ptx_sm100.cuh).
+//   warps 2..17 epilogue (16 warps, four per TMEM lane quadrant): tcgen05.ld the fp32/s32
+//               accumulator, apply scales / bias / activation / residual / quantisation, store
+//               through shared memory and a TMA store (or per thread)
+// INT4 group-128 weights: 8 epilogue warps + 8 warps that dequantise the B stage into shared
+// memory; a work item is 256 x 128 (two 128-row accumulators share every dequantised B stage).
+// Accumulators are double-buffered in TMEM so the MMAs of tile i+1 overlap the epilogue of
+// tile i.  All waits are bounded (ptx_sm100.cuh).
 #pragma once
 
 #include <cuda_fp8.h>
@@ -57,13 +60,18 @@ struct GemmParams {
 };
 
 constexpr int kBlockM = 128;
-// Warps per CTA: TMA producer + MMA issuer + epilogue warps (+ 4 dequantisation warps for INT4
+// Warps per CTA: TMA producer + MMA issuer + epilogue warps (+ 8 dequantisation warps for INT4
 // weights).  16 epilogue warps = 4 per TMEM lane quadrant, each a quarter of the tile's
 // columns: the epilogue of a K = 1024 tile has to finish within the ~4k cycles its MMAs take.
+// INT4 weights: kMTiles = 2 accumulators of 128 rows share each dequantised B stage (the
+// conversion, not the MMA, bounds that kernel, so its cost is spread over twice the rows);
+// 4 epilogue warps per accumulator, each all 128 columns of its 32 rows.
 template <int BSrc>
 struct GemmWarps {
-    static constexpr int kEpilogue = BSrc == BSRC_W4G128 ? 4 : 16;
-    static constexpr int kThreads = 32 * (2 + kEpilogue + (BSrc == BSRC_W4G128 ? 4 : 0));
+    static constexpr int kMTiles = BSrc == BSRC_W4G128 ? 2 : 1;
+    static constexpr int kEpilogue = BSrc == BSRC_W4G128 ? 8 : 16;
+    static constexpr int kDequant = BSrc == BSRC_W4G128 ? 8 : 0;
+    static constexpr int kThreads = 32 * (2 + kEpilogue + kDequant);
 };
 
 // Shared memory the epilogue warps stage their output slices in for the TMA store: 32 rows of
@@ -80,14 +88,17 @@ constexpr int gemm_store_bytes() {
 
 // BRows = B rows staged per CTA per stage, EpiCols = accumulator columns of the tile,
 // StoreBytes = output staging for the TMA store.
-template <int BRows, int SwizzleBytes, int EpiCols = BRows, int StoreBytes = 0>
+template <int BRows, int SwizzleBytes, int EpiCols = BRows, int StoreBytes = 0, int ARows = kBlockM>
 struct GemmSmem {
-    static constexpr int kStageA = kBlockM * SwizzleBytes;
+    static constexpr int kStageA = ARows * SwizzleBytes;
     static constexpr int kStageB = BRows * SwizzleBytes;
     static constexpr int kStageBytes = kStageA + kStageB;
     // tail: barriers + tmem pointer + abort flag + epilogue staging
     // (each epilogue warp keeps a private slice of column scales and biases: 32 bytes per column)
-    static constexpr int kTailBytes = 64 * 8 + 16 + 32 * EpiCols + 64 * 4;
+    // + the tile-skip schedule: one 64-bit live mask and one 16-bit rank per 128-row tile
+    static constexpr int kSchedTiles = 512;
+    static constexpr int kSchedOffset = 64 * 8 + 16 + 32 * EpiCols + 64 * 4;
+    static constexpr int kTailBytes = kSchedOffset + kSchedTiles * (8 + 2);
     static constexpr int kStoreBytes = StoreBytes;
     // 227 KB per CTA, less the tail, the output staging and 1 KB of alignment slack; the
     // pipeline is not depth-sensitive (2 and 4 stages measured alike), so staging comes first
@@ -202,9 +213,8 @@ __device__ __forceinline__ uint64_t load_live_mask(const uint8_t* keep_in, int m
     return mask;
 }
 
-// The same mask for the single-lane roles (TMA producer, MMA issuer), which walk it once per tile:
-// the bitmap row is fetched as 16-byte words one tile AHEAD (`fetch`), and compressed to bits when
-// its tile starts (`mask`), so that the walk never waits for a chain of byte loads from L2.
+// The same mask from 16-byte loads (`fetch`) compressed to bits (`mask`): one thread per 128-row
+// tile fills the CTA's shared-memory copy of the bitmap with it when the kernel starts.
 struct LiveMaskRow {
     uint4 w[4];          // up to 64 flag bytes
     bool vector;
@@ -249,6 +259,16 @@ __device__ __forceinline__ bool k_block_live(uint64_t mask, int kb) {
     }
 }
 
+// Number of live K blocks in a tile's mask.
+template <int SwizzleBytes>
+__device__ __forceinline__ int live_k_blocks(uint64_t mask) {
+    if constexpr (SwizzleBytes == 64) {
+        return __popcll(mask);
+    } else {
+        return __popcll((mask | (mask >> 1)) & 0x5555555555555555ull);
+    }
+}
+
 // CtaGroup = 2: the CTAs of a 2-CTA cluster share one 256 x BlockN tile (tcgen05 cta_group::2).
 // Each CTA stages its own 128 rows of A and BlockN/2 rows of B, so a tile costs 2/3 of the
 // operand traffic of two independent 128 x BlockN tiles; the even CTA issues the MMAs, each CTA
@@ -260,20 +280,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const GemmParams p) {
     static_assert(CtaGroup == 1 || (CtaGroup == 2 && BlockN == 256 && BSrc == BSRC_TMA), "pairs: 256 columns, TMA");
     constexpr int kBRows = BlockN / CtaGroup;               // B rows staged by this CTA
-    using Smem = GemmSmem<kBRows, SwizzleBytes, BlockN, gemm_store_bytes<Epi, BSrc, BlockN>()>;
+    constexpr int kMTiles = GemmWarps<BSrc>::kMTiles;       // 128-row accumulators per work item
+    using Smem = GemmSmem<kBRows, SwizzleBytes, BlockN * kMTiles, gemm_store_bytes<Epi, BSrc, BlockN>(),
+                          kBlockM * kMTiles>;
     constexpr int kStages = Smem::kStages;
     constexpr int kElemBytes = Kind == KIND_F16 ? 2 : 1;
     constexpr int kBlockK = SwizzleBytes / kElemBytes;       // elements per K block
     constexpr int kMmasPerBlock = SwizzleBytes / 32;         // 32 bytes of K per MMA
-    constexpr uint32_t kTmemCols = 2 * BlockN;
+    constexpr uint32_t kTmemCols = 2 * kMTiles * BlockN;
     constexpr int kBHalf = BlockN / 2;                       // rows per B load
     static_assert(BlockN == 64 || BlockN == 128 || BlockN == 256, "BlockN");
     static_assert(BSrc == BSRC_TMA || (Kind == KIND_F16 && SwizzleBytes == 128 && BlockN == 128 &&
                                        Epi == EPI_LINEAR), "w4: fp16 MMA, 128-column tiles, linear epilogue");
-    // INT4 weights: 4 epilogue warps (one per TMEM lane quadrant) + 4 dequantisation warps;
-    // otherwise 16 epilogue warps, four per quadrant, each a quarter of the tile's columns.
+    // 16 epilogue warps, four per TMEM lane quadrant, each a quarter of the tile's columns; INT4
+    // weights: 8 epilogue warps, four per 128-row accumulator, + 8 dequantisation warps.
     constexpr int kEpiWarps = GemmWarps<BSrc>::kEpilogue;
-    constexpr int kParts = kEpiWarps / 4;
+    constexpr int kParts = kEpiWarps / 4 / kMTiles;          // column slices of one accumulator
     constexpr int kOutCols = Epi == EPI_GLU ? BlockN / 2 : BlockN;   // output columns of a tile
     constexpr int kColsPerWarp = kOutCols / kParts;
     static_assert(kColsPerWarp % 16 == 0, "each epilogue warp owns whole 16-column pieces");
@@ -290,7 +312,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(tail + 64 * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 64 * 8 + 8);
     float* s_cols = reinterpret_cast<float*>(tail + 64 * 8 + 16);   // per-warp scale / bias slices
-    float* s_reduce = s_cols + 8 * BlockN;                    // one float per epilogue warp
+    float* s_reduce = s_cols + kEpiWarps * 2 * (BlockN / kParts);   // one float per epilogue warp
+    uint64_t* s_live = reinterpret_cast<uint64_t*>(tail + Smem::kSchedOffset);   // live mask per 128-row tile
+    uint16_t* s_order = reinterpret_cast<uint16_t*>(s_live + Smem::kSchedTiles);  // tiles, most live K blocks first
 
     const int warp = static_cast<int>(threadIdx.x) / 32;
     const int lane = static_cast<int>(threadIdx.x) % 32;
@@ -299,24 +323,48 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const int worker = static_cast<int>(blockIdx.x) / CtaGroup;      // pair (or CTA) index
     const int workers = static_cast<int>(gridDim.x) / CtaGroup;
     const int m_tiles = (p.m + kBlockM - 1) / kBlockM;                // 128-row tiles
-    const int m_groups = (m_tiles + CtaGroup - 1) / CtaGroup;         // tiles of 128 * CtaGroup rows
+    constexpr int kItemTiles = CtaGroup * kMTiles;                    // 128-row tiles per work item
+    const int m_groups = (m_tiles + kItemTiles - 1) / kItemTiles;
     const int n_tiles = (p.n + BlockN - 1) / BlockN;
     const int num_tiles = m_groups * n_tiles;
     const int k_blocks = (p.k + kBlockK - 1) / kBlockK;
     const int k_tiles64 = p.k / 64;
+    // Tile skip with one CTA per 128-row tile: the bitmap is read once into shared memory, and the
+    // work items are dealt in order of their live K blocks (most first), forwards in even passes over
+    // the CTAs and backwards in odd ones, so the CTA that drew the heaviest item of one pass draws the
+    // lightest of the next (tiles differ several-fold in live blocks; dealt round-robin by index the
+    // slowest CTA ran 1.45x the mean).
+    const bool balanced = CtaGroup == 1 && kMTiles == 1 && p.keep_in != nullptr && m_tiles <= Smem::kSchedTiles;
     // live-K mask of a work item: union over the 128-row tiles it covers
     auto group_live_mask = [&](int mg) {
+        if (balanced) return s_live[mg];
         uint64_t mask = load_live_mask(p.keep_in, mg * CtaGroup, k_tiles64);
         if (CtaGroup == 2 && p.keep_in != nullptr && mg * 2 + 1 < m_tiles)
             mask |= load_live_mask(p.keep_in, mg * 2 + 1, k_tiles64);
         return mask;
     };
+    // i-th work item of this worker (false: none left)
+    auto work_item = [&](int i, int& mg, int& nt) {
+        if (balanced) {
+            const int pos = i * workers + ((i & 1) ? workers - 1 - worker : worker);
+            if (pos >= num_tiles) return false;
+            mg = s_order[pos / n_tiles];
+            nt = pos % n_tiles;
+            return true;
+        }
+        const int tile = worker + i * workers;
+        if (tile >= num_tiles) return false;
+        mg = tile % m_groups;
+        nt = tile / m_groups;
+        return true;
+    };
 
+    grid_dependents_launch();
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int s = 0; s < kStages; ++s) {
-            // full: one arrive.expect_tx from the TMA lane (+ 4 producer warps for W4)
-            mbar_init(full_bar + s, BSrc == BSRC_W4G128 ? 1 + 4 : 1);
+            // full: one arrive.expect_tx from the TMA lane (+ the dequantisation warps)
+            mbar_init(full_bar + s, 1 + GemmWarps<BSrc>::kDequant);
             mbar_init(empty_bar + s, 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -342,6 +390,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if constexpr (CtaGroup == 2) cluster_sync_all();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
+    // everything above touched only shared / tensor memory and kernel parameters: under a
+    // programmatic dependent launch it overlapped the previous kernel's tail
+    grid_dependency_wait();
+    if (balanced) {
+        for (int t = static_cast<int>(threadIdx.x); t < m_tiles; t += static_cast<int>(blockDim.x)) {
+            LiveMaskRow row;
+            row.fetch(p.keep_in, t, k_tiles64);
+            s_live[t] = row.mask(p.keep_in, t, k_tiles64);
+        }
+        __syncthreads();
+        for (int t = static_cast<int>(threadIdx.x); t < m_tiles; t += static_cast<int>(blockDim.x)) {
+            const int mine = live_k_blocks<SwizzleBytes>(s_live[t]);
+            int rank_t = 0;
+            for (int u = 0; u < m_tiles; ++u) {
+                const int other = live_k_blocks<SwizzleBytes>(s_live[u]);
+                rank_t += (other > mine || (other == mine && u < t)) ? 1 : 0;
+            }
+            s_order[rank_t] = static_cast<uint16_t>(t);
+        }
+        __syncthreads();
+    }
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
@@ -349,19 +418,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            [[maybe_unused]] LiveMaskRow ahead;
-            if (CtaGroup == 1 && worker < num_tiles) ahead.fetch(p.keep_in, worker % m_groups, k_tiles64);
-            for (int tile = worker; tile < num_tiles && ok; tile += workers) {
-                const int mg = tile % m_groups;
-                const int nt = tile / m_groups;
-                const int m0 = (mg * CtaGroup + static_cast<int>(rank)) * kBlockM;
-                uint64_t live_mask;
-                if constexpr (CtaGroup == 1) {
-                    live_mask = ahead.mask(p.keep_in, mg, k_tiles64);
-                    if (tile + workers < num_tiles) ahead.fetch(p.keep_in, (tile + workers) % m_groups, k_tiles64);
-                } else {
-                    live_mask = group_live_mask(mg);
-                }
+            int mg, nt;
+            for (int it = 0; ok && work_item(it, mg, nt); ++it) {
+                const int m0 = (mg * CtaGroup + static_cast<int>(rank)) * kBlockM * kMTiles;
+                const uint64_t live_mask = group_live_mask(mg);
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (p.keep_in != nullptr && !k_block_live<SwizzleBytes>(live_mask, kb)) continue;
                     if (!mbar_wait_bounded(empty_bar + stage, phase ^ 1u, abort_flag)) {
@@ -397,8 +457,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         tma_load_2d(sb + kBHalf * SwizzleBytes, &map_b, full_bar + stage,
                                     kb * kBlockK, n_second);
                     } else {
-                        mbar_arrive_expect_tx(full_bar + stage, Smem::kStageA);
+                        // 128-row boxes of A, one per accumulator that has rows
+                        const bool second = m0 + kBlockM < p.m;
+                        mbar_arrive_expect_tx(full_bar + stage, second ? Smem::kStageA : Smem::kStageA / 2);
                         tma_load_2d(sa, &map_a, full_bar + stage, kb * kBlockK, m0);
+                        if (second)
+                            tma_load_2d(sa + Smem::kStageA / 2, &map_a, full_bar + stage, kb * kBlockK, m0 + kBlockM);
                     }
                     if (++stage == kStages) {
                         stage = 0;
@@ -415,25 +479,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             uint32_t phase = 0;
             int local = 0;
             bool ok = true;
-            [[maybe_unused]] LiveMaskRow ahead;
-            if (CtaGroup == 1 && worker < num_tiles) ahead.fetch(p.keep_in, worker % m_groups, k_tiles64);
-            for (int tile = worker; tile < num_tiles && ok; tile += workers, ++local) {
-                const int mg = tile % m_groups;
+            int mg, nt;
+            for (; ok && work_item(local, mg, nt); ++local) {
                 const int buf = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
-                uint64_t live_mask;
-                if constexpr (CtaGroup == 1) {
-                    live_mask = ahead.mask(p.keep_in, mg, k_tiles64);
-                    if (tile + workers < num_tiles) ahead.fetch(p.keep_in, (tile + workers) % m_groups, k_tiles64);
-                } else {
-                    live_mask = group_live_mask(mg);
-                }
+                const uint64_t live_mask = group_live_mask(mg);
                 if (!mbar_wait_bounded(tmem_empty_bar + buf, acc_phase ^ 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BlockN);
+                const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kMTiles * BlockN);
+                [[maybe_unused]] const bool second = (mg * kItemTiles + 1) * kBlockM < p.m;
                 uint32_t accumulate = 0;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (p.keep_in != nullptr && !k_block_live<SwizzleBytes>(live_mask, kb)) continue;
@@ -453,6 +510,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             tc_mma_pair<Kind>(tmem_d, desc_a + 2u * j, desc_b + 2u * j, idesc, accumulate);
                         else
                             tc_mma<Kind>(tmem_d, desc_a + 2u * j, desc_b + 2u * j, idesc, accumulate);
+                        if constexpr (kMTiles == 2) {
+                            // the second 128 rows of A (16 KB on: 1024 descriptor units) against the same B
+                            if (second)
+                                tc_mma<Kind>(tmem_d + BlockN, desc_a + 1024u + 2u * j, desc_b + 2u * j, idesc, accumulate);
+                        }
                         accumulate = 1;
                     }
                     // free the stage (in both CTAs of a pair) once the MMAs retire
@@ -485,71 +547,88 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
     } else if (BSrc == BSRC_W4G128 && warp >= 2 + kEpiWarps) {
         // ------------------------------------- INT4 -> fp16 B-operand producer
-        // Thread dq owns row dq of the 128-row B stage: 32 bytes of codes (64 K values) per K
-        // block, one fp16 scale per 128 K.  W = f16(code * scale) is written straight into the
-        // 128-byte-swizzled layout the MMA descriptor expects (16-byte chunk c of row r lives at
-        // chunk c ^ (r & 7)), made visible to the async proxy, then the warp arrives on `full`.
+        // 256 threads: thread dq converts half h = dq / 128 (32 K values = 16 bytes of codes) of
+        // row dq % 128 of the 128-row B stage per K block, one fp16 scale per 128 K.
+        // W = f16(code * scale) is written straight into the 128-byte-swizzled layout the MMA
+        // descriptor expects (16-byte chunk c of row r lives at chunk c ^ (r & 7)), made visible to
+        // the async proxy, then the warp arrives on `full`.
         const int dq = static_cast<int>(threadIdx.x) - 32 * (2 + kEpiWarps);
+        const int brow = dq & 127;
+        const int half = dq >> 7;                 // warp-uniform
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int tile = worker; tile < num_tiles && ok; tile += workers) {
-            const int nt = tile / m_groups;
-            const int n = nt * BlockN + dq;
+        int mg, nt;
+        for (int it = 0; ok && work_item(it, mg, nt); ++it) {
+            const int n = nt * BlockN + brow;
             const bool row_ok = n < p.n;
-            const uint8_t* codes = p.w4_codes + static_cast<size_t>(row_ok ? n : 0) * (p.k / 2);
-            // software pipeline: the codes and scale of K block kb+1 are in flight while block kb
-            // is converted, so the L2 latency is paid once per tile instead of once per block
-            uint4 next_raw[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-            float next_scale = 0.0f;
-            if (row_ok) {
-                const uint4* src = reinterpret_cast<const uint4*>(codes);
-                next_raw[0] = src[0];
-                next_raw[1] = src[1];
-                next_scale = __half2float(p.w4_scales[n]);
-            }
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                uint4 raw[2] = {next_raw[0], next_raw[1]};
-                const float scale = next_scale;
-                if (row_ok && kb + 1 < k_blocks) {
-                    const uint4* src = reinterpret_cast<const uint4*>(codes + (kb + 1) * 32);
-                    next_raw[0] = src[0];
-                    next_raw[1] = src[1];
-                    next_scale = __half2float(p.w4_scales[static_cast<size_t>((kb + 1) / 2) * p.n + n]);
-                }
-                const bool got = mbar_wait_bounded(empty_bar + stage, phase ^ 1u, abort_flag);
-                if (!__all_sync(0xffffffffu, got)) {
-                    ok = false;
-                    break;
-                }
-                uint8_t* row_base = smem + stage * Smem::kStageBytes + Smem::kStageA + dq * 128;
-                const uint32_t* words = reinterpret_cast<const uint32_t*>(raw);
-                const __half2 scale2 = __float2half2_rn(scale);
+            const uint8_t* codes = p.w4_codes + static_cast<size_t>(row_ok ? n : 0) * (p.k / 2) + half * 16;
+            // Software pipeline over groups of 4 K blocks (= one 128-byte line of this row's codes, two
+            // scale groups): the next group's codes and scales are in flight while this group is
+            // converted, so neither the L2 nor the DRAM latency of the weight stream is exposed.
+            uint4 next_raw[4];
+            float next_scale[2];
+            auto fetch_group = [&](int kg) {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {              // chunk c = K values 8c .. 8c+7 = one code word
-                    // nibble n -> fp16 (1024 + (n ^ 8)) by OR-ing the biased nibble into the
-                    // mantissa of 1024.0, minus 1032.0 = the signed code, exactly; HMUL2 by the
-                    // fp16 group scale then rounds once, i.e. f16(code * scale).
-                    const uint32_t wbits = words[c] ^ 0x88888888u;       // two's complement -> offset binary
-                    uint32_t h[4];
+                for (int j = 0; j < 4; ++j)
+                    next_raw[j] = (row_ok && kg + j < k_blocks)
+                        ? __ldg(reinterpret_cast<const uint4*>(codes + (kg + j) * 32)) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        // byte j holds codes (2j, 2j+1): low nibble -> low half, high nibble -> high half
-                        const uint32_t byte = (wbits >> (8 * j)) & 0xFFu;
-                        const uint32_t pair = ((byte & 0x0Fu) | ((byte & 0xF0u) << 12)) | 0x64006400u;
-                        const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&pair),
-                                                  __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408)));
-                        const __half2 w = __hmul2(v, scale2);
-                        h[j] = *reinterpret_cast<const uint32_t*>(&w);
+                for (int i = 0; i < 2; ++i)
+                    next_scale[i] = (row_ok && kg + 2 * i < k_blocks)
+                        ? __half2float(p.w4_scales[static_cast<size_t>(kg / 2 + i) * p.n + n]) : 0.0f;
+            };
+            fetch_group(0);
+            const __half2 bias2 = __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408));
+            for (int kg = 0; kg < k_blocks && ok; kg += 4) {
+                uint4 cur[4];
+                float cur_scale[2];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) cur[j] = next_raw[j];
+                cur_scale[0] = next_scale[0];
+                cur_scale[1] = next_scale[1];
+                if (kg + 4 < k_blocks) fetch_group(kg + 4);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (kg + j >= k_blocks) break;
+                    const bool got = mbar_wait_bounded(empty_bar + stage, phase ^ 1u, abort_flag);
+                    if (!__all_sync(0xffffffffu, got)) {
+                        ok = false;
+                        break;
                     }
-                    *reinterpret_cast<uint4*>(row_base + ((c ^ (dq & 7)) * 16)) = make_uint4(h[0], h[1], h[2], h[3]);
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full_bar + stage);
-                if (++stage == kStages) {
-                    stage = 0;
-                    phase ^= 1u;
+                    uint8_t* row_base = smem + stage * Smem::kStageBytes + Smem::kStageA + brow * 128;
+                    const uint32_t words[4] = {cur[j].x, cur[j].y, cur[j].z, cur[j].w};
+                    const __half2 scale2 = __float2half2_rn(cur_scale[j / 2]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {          // chunk c = K values 8c .. 8c+7 = one code word
+                        const int c = 4 * half + i;
+                        // nibble n -> fp16 (1024 + (n ^ 8)) by OR-ing the biased nibble into the
+                        // mantissa of 1024.0, minus 1032.0 = the signed code, exactly; HMUL2 by the
+                        // fp16 group scale then rounds once, i.e. f16(code * scale).
+                        const uint32_t wbits = words[i] ^ 0x88888888u;   // two's complement -> offset binary
+                        // nibbles (e, e + 4) of the word land in the two halves of one register with
+                        // one shift and one AND-OR; the byte permutes below put K back in order
+                        __half2 v[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t pair = ((wbits >> (4 * e)) & 0x000F000Fu) | 0x64006400u;
+                            v[e] = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&pair), bias2), scale2);
+                        }
+                        const uint32_t* vb = reinterpret_cast<const uint32_t*>(v);
+                        uint32_t h[4];
+                        h[0] = __byte_perm(vb[0], vb[1], 0x5410);        // K 0, 1
+                        h[1] = __byte_perm(vb[2], vb[3], 0x5410);        // K 2, 3
+                        h[2] = __byte_perm(vb[0], vb[1], 0x7632);        // K 4, 5
+                        h[3] = __byte_perm(vb[2], vb[3], 0x7632);        // K 6, 7
+                        *reinterpret_cast<uint4*>(row_base + ((c ^ (brow & 7)) * 16)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full_bar + stage);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
                 }
             }
         }
@@ -557,7 +636,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         // ---------------------------------------------------------- epilogue
         const int ew = warp - 2;                 // 0 .. kEpiWarps-1
         const int quad = warp % 4;               // TMEM lane quadrant this warp may read
-        const int part = ew / 4;                 // which slice of the tile's columns
+        const int sub = (ew / 4) / kParts;       // which 128-row accumulator of the work item
+        const int part = (ew / 4) % kParts;      // which slice of its columns
         // Slice of the per-column epilogue constants this warp reads: kSlice scales, then kSlice
         // biases (GLU: value columns first, their gate columns after).  Warp-private, so staging
         // a tile's constants needs no CTA-wide barrier.
@@ -582,13 +662,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 pre_b[u] = (p.bias != nullptr && in) ? __ldg(p.bias + src) : 0.0f;
             }
         };
-        if (worker < num_tiles) prefetch_cols(worker / m_groups);
+        int mg, nt;
+        if (work_item(0, mg, nt)) prefetch_cols(nt);
         int local = 0;
         bool ok = true;
-        for (int tile = worker; tile < num_tiles && ok; tile += workers, ++local) {
-            const int mg = tile % m_groups;
-            const int mt = mg * CtaGroup + static_cast<int>(rank);    // this CTA's 128-row tile
-            const int nt = tile / m_groups;
+        for (; ok && work_item(local, mg, nt); ++local) {
+            const int mt = (mg * CtaGroup + static_cast<int>(rank)) * kMTiles + sub;   // this warp's 128-row tile
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             const int row = mt * kBlockM + quad * 32 + lane;
@@ -602,19 +681,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 my_bias[u * 32 + lane] = pre_b[u];
             }
             __syncwarp();
-            if (tile + workers < num_tiles) prefetch_cols((tile + workers) / m_groups);
+            {
+                int mg_next, nt_next;
+                if (work_item(local + 1, mg_next, nt_next)) prefetch_cols(nt_next);
+            }
             const float rs = p.row_scales != nullptr ? (row < p.m ? p.row_scales[row] : 0.0f)
                                                      : p.row_scale;
 
             bool live = true;
-            if (p.keep_in != nullptr) {
+            if (balanced) {
+                live = s_live[mt] != 0;
+            } else if (p.keep_in != nullptr) {
                 // MMAs were issued for this work item iff any K tile of any of its rows is live
                 bool any = false;
-                for (int t = mg * CtaGroup; t < mg * CtaGroup + CtaGroup && t < m_tiles; ++t) {
+                for (int t = mg * kItemTiles; t < (mg + 1) * kItemTiles && t < m_tiles; ++t) {
                     const uint8_t* krow = p.keep_in + static_cast<size_t>(t) * k_tiles64;
                     for (int i = lane; i < k_tiles64; i += 32) any |= krow[i] != 0;
                 }
                 live = __any_sync(0xffffffffu, any);
+            }
+
+            // The residual rows of this warp's slice do not depend on the accumulator: the first two
+            // pieces are requested before the wait for it and arrive while the MMAs run; each
+            // later piece is requested two pieces ahead, into the buffer just consumed.
+            constexpr int kPieces = kColsPerWarp / 16;
+            constexpr int kAhead = kPieces < 2 ? kPieces : 2;
+            [[maybe_unused]] uint4 res_pre[kAhead][2];
+            const bool has_residual = Epi == EPI_LINEAR && p.residual != nullptr;
+            auto fetch_residual = [&](uint4 (&dst)[2], int c) {
+                const int col = n0 + part * kColsPerWarp + c * 16;
+                if (has_residual && row < p.m && col < p.n) {
+                    const uint4* rp = reinterpret_cast<const uint4*>(
+                        p.residual + static_cast<size_t>(row) * p.ld_res + col);
+                    dst[0] = rp[0];
+                    dst[1] = rp[1];
+                }
+            };
+            if constexpr (Epi == EPI_LINEAR) {
+#pragma unroll
+                for (int i = 0; i < kAhead; ++i) fetch_residual(res_pre[i], i);
             }
 
             const bool got = mbar_wait_bounded(tmem_full_bar + buf, acc_phase, abort_flag);
@@ -624,11 +729,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
             tc_fence_after_sync();
 
-            const uint32_t taddr_base = tmem_base + static_cast<uint32_t>(buf * BlockN) +
+            const uint32_t taddr_base = tmem_base + static_cast<uint32_t>((buf * kMTiles + sub) * BlockN) +
                                         (static_cast<uint32_t>(quad * 32) << 16);
             const size_t obytes = out_elem_bytes(p.out_type);
 
-            constexpr int kPieces = kColsPerWarp / 16;
             const bool zero_row = row >= p.valid_rows;
             // Output slice of this warp (32 rows x kColsPerWarp columns): staged in shared memory
             // and written by one TMA store when the host set that up, else stored per thread.
@@ -642,7 +746,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
             if constexpr (Epi == EPI_LINEAR) {
 #pragma unroll 1
-                for (int c = 0; c < kPieces; ++c) {
+                for (int cg = 0; cg < kPieces; cg += kAhead) {
+#pragma unroll
+                for (int ci = 0; ci < kAhead; ++ci) {
+                    const int c = cg + ci;
                     const int col_local = part * kColsPerWarp + c * 16;
                     uint32_t r[16];
                     tmem_ld_32x16(taddr_base + col_local, r);
@@ -653,14 +760,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         // piece, outside the element loops: left inside, every element pays for the
                         // predicated-off SiLU and residual code (22 instructions per element measured).
                         float v[16];
-                        uint4 res_raw[2];
-                        const bool has_residual = p.residual != nullptr;
-                        if (has_residual) {
-                            const uint4* rp = reinterpret_cast<const uint4*>(
-                                p.residual + static_cast<size_t>(row) * p.ld_res + col);
-                            res_raw[0] = rp[0];
-                            res_raw[1] = rp[1];
-                        }
+                        const uint4 res_raw[2] = {res_pre[ci][0], res_pre[ci][1]};
+                        if (c + kAhead < kPieces) fetch_residual(res_pre[ci], c + kAhead);
                         const float rs_live = live ? rs : 0.0f;
                         if (!live) {              // accumulator never written: any bit pattern
 #pragma unroll
@@ -706,6 +807,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             store_piece(out_row, p.out_type, p.out_scale, v);
                         }
                     }
+                }
                 }
             } else if constexpr (Epi == EPI_GLU) {
                 // accumulator columns [0, BlockN/2) hold values, [BlockN/2, BlockN) their gates

@@ -8,6 +8,7 @@
 #include <stdint.h>
 
 #include "pk100_internal.h"
+#include "ptx_sm100.cuh"
 
 namespace pk100 {
 
@@ -165,6 +166,8 @@ layer_norm_kernel(const __half* __restrict__ in, const __half* __restrict__ gamm
                   const __half* __restrict__ beta2, void* __restrict__ out2, float* scales2,
                   int mode2, float inv_scale2, int total_rows, int seg_stride, int valid_rows,
                   const int* __restrict__ seg_valid, float eps) {
+    grid_dependents_launch();
+    grid_dependency_wait();
     const int lane = threadIdx.x % 32;
     const int row = blockIdx.x * 8 + threadIdx.x / 32;
     if (row >= total_rows) return;
@@ -335,6 +338,8 @@ depthwise_bn_silu_kernel(const __half* __restrict__ in, const __half* __restrict
                          int seg_stride, int valid_rows, const int* __restrict__ seg_valid,
                          float eps) {
     __shared__ float s_max[8][8];
+    grid_dependents_launch();
+    grid_dependency_wait();
     const int tid = threadIdx.x;
     const int lane = tid % 32, warp = tid / 32;
     const int c0 = tid * 4;
@@ -463,7 +468,7 @@ extern "C" int pk100_layer_norm(void* stream, const void* input, const void* gam
     if (total_rows <= 0) return total_rows == 0 ? PK100_OK : PK100_ERR_SHAPE;
     if (seg_stride <= 0 || mode < 0 || mode > PK100_LN_S8_ROW) return PK100_ERR_SHAPE;
     if ((mode == PK100_LN_E4M3_ROW || mode == PK100_LN_S8_ROW) && !scales) return PK100_ERR_NULL;
-    layer_norm_kernel<<<(total_rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    pk100_launch_chained(layer_norm_kernel, dim3((total_rows + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream),
         static_cast<const __half*>(input), static_cast<const __half*>(gamma),
         static_cast<const __half*>(beta), output, scales, mode, inv_scale, nullptr, nullptr,
         nullptr, nullptr, 0, 0.0f, total_rows, seg_stride, valid_rows, seg_valid, eps);
@@ -482,7 +487,7 @@ extern "C" int pk100_layer_norm_pair(void* stream, const void* input, const void
     if (seg_stride <= 0 || next_mode < 0 || next_mode > PK100_LN_S8_ROW) return PK100_ERR_SHAPE;
     if ((next_mode == PK100_LN_E4M3_ROW || next_mode == PK100_LN_S8_ROW) && !next_scales)
         return PK100_ERR_NULL;
-    layer_norm_kernel<<<(total_rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    pk100_launch_chained(layer_norm_kernel, dim3((total_rows + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream),
         static_cast<const __half*>(input), static_cast<const __half*>(gamma),
         static_cast<const __half*>(beta), output, nullptr, PK100_LN_F16, 0.0f,
         static_cast<const __half*>(next_gamma), static_cast<const __half*>(next_beta), next_output,
@@ -570,7 +575,7 @@ extern "C" int pk100_depthwise_bn_silu(void* stream, const void* input, const vo
         misaligned(bn_mean, 15) || misaligned(bn_var, 15) || misaligned(input, 7))
         return PK100_ERR_ALIGN;      // the kernel reads taps 8 bytes and BatchNorm vectors 16 bytes at a time
     const int strips = (seg_stride + kDwStrip - 1) / kDwStrip;
-    depthwise_bn_silu_kernel<<<segments * strips, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    pk100_launch_chained(depthwise_bn_silu_kernel, dim3(segments * strips), dim3(256), 0, static_cast<cudaStream_t>(stream),
         static_cast<const __half*>(input), static_cast<const __half*>(dw_weight), bn_gamma,
         bn_beta, bn_mean, bn_var, output, row_scales, quantize, seg_stride, valid_rows, seg_valid,
         eps);

@@ -69,7 +69,16 @@ def relative_position_encoding() -> np.ndarray:
 class EncoderLayers:
     """Packed weights of n layers on one GPU + the launch of `pk100_run_layers`."""
 
-    def __init__(self, device):
+    def __init__(self, device, out_proj_resident="f16"):
+        """`out_proj_resident`: how the INT4 group-128 attention output projection lives on the GPU.
+        "f16" (default): the codes are expanded once at load to the fp16 values the fused kernel
+        would produce (2 MB per layer) and the projection runs as a plain fp16 tcgen05 GEMM;
+        "int4": the codes stay packed (0.5 MB per layer) and the GEMM dequantises them in shared
+        memory.  Both give the same bits; on a 180 GB part the expanded form is the faster one
+        (21.7 vs 34.5 us at 6144 rows)."""
+        if out_proj_resident not in ("f16", "int4"):
+            raise ValueError("out_proj_resident must be 'f16' or 'int4'")
+        self.out_proj_resident = out_proj_resident
         self.device = torch.device(device)
         self.tensors = []          # keeps device memory alive
         self.layers = []           # list[LayerWeights]
@@ -107,7 +116,10 @@ class EncoderLayers:
         codes, gs = self._keep(*ops.pack_weight_rows(self._dev16(w["wo"]), L.PACK_S4_G128))
         (wo16,) = self._keep(ops.dequant_w4g128(codes, gs))
         lw.wo_f16 = wo16.data_ptr()
-        lw.wo_codes, lw.wo_group_scales = codes.data_ptr(), gs.data_ptr()
+        if self.out_proj_resident == "int4":
+            lw.wo_codes, lw.wo_group_scales = codes.data_ptr(), gs.data_ptr()
+        else:
+            lw.wo_codes, lw.wo_group_scales = None, None
         # position table: sinusoid . Wpos^T (fp16 linear), head-major
         proj = torch.empty((POSITION_ROWS_PADDED, 1024), dtype=torch.float16, device=self.device)
         ops.gemm(self._sinus, self._dev16(w["wpos"]), kind=L.KIND_F16, out=proj)

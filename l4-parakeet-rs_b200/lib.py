@@ -102,6 +102,8 @@ lib.pk100_set_gemm_cta_pairs.restype = None
 lib.pk100_set_gemm_cta_pairs.argtypes = [i32]
 lib.pk100_set_gemm_cta_cap.restype = None
 lib.pk100_set_gemm_cta_cap.argtypes = [i32]
+lib.pk100_set_dependent_launch.restype = None
+lib.pk100_set_dependent_launch.argtypes = [i32]
 lib.pk100_tensor_map_cache_stats.restype = None
 lib.pk100_tensor_map_cache_stats.argtypes = [C.POINTER(i64), C.POINTER(i64)]
 

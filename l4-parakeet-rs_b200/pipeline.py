@@ -39,7 +39,7 @@ def seg_stride_for(frames_out: int) -> int:
 
 class PipelineEngine:
     def __init__(self, device, layers=24, decoder_layers=2, seed=4, max_utterances=8, mel_frames=6000,
-                 randomize_norms=False, decode_groups=2):
+                 randomize_norms=False, decode_groups=2, out_proj_resident="f16"):
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
         self.max_utterances = max_utterances
@@ -50,7 +50,7 @@ class PipelineEngine:
         self.seg_stride = seg_stride_for(self.frames_out)
         self.rows = max_utterances * self.seg_stride
         self.sub = sub_mod.Subsampling(synth.subsampling_weights(seed), self.device)
-        self.enc = enc_mod.EncoderLayers(self.device)
+        self.enc = enc_mod.EncoderLayers(self.device, out_proj_resident=out_proj_resident)
         for l in range(layers):
             self.enc.add_layer(synth.layer_weights(seed, l, randomize_norms=randomize_norms))
         self.dec = dec_mod.TdtDecoder(synth.decoder_weights(seed, decoder_layers), self.device)

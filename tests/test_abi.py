@@ -23,7 +23,7 @@ def test_library_exports_every_declared_symbol(pk):
 
 
 def test_binding_table_matches_header(pk):
-    void_setters = ["pk100_set_gemm_cta_pairs", "pk100_set_gemm_cta_cap", "pk100_tensor_map_cache_stats"]
+    void_setters = ["pk100_set_gemm_cta_pairs", "pk100_set_gemm_cta_cap", "pk100_set_dependent_launch", "pk100_tensor_map_cache_stats"]
     assert sorted(list(pk.lib.SIGNATURES) + void_setters) == declared_symbols()
 
 

@@ -76,6 +76,27 @@ def test_single_layer_single_utterance(pk, cuda, rows, valid):
     assert np.max(np.abs(got - want)) <= 0.1
 
 
+def test_out_proj_resident_forms_give_the_same_bits(pk, cuda):
+    """INT4-g128 out-proj weights expanded to fp16 at load (plain fp16 GEMM) or kept packed
+    (dequantised inside the GEMM): two layers, two utterances, every output bit equal."""
+    rows, valid = 2 * 384, [384, 201]
+    x = _input(7, rows, rows)
+    outs = []
+    for form in ("f16", "int4"):
+        enc = pk.encoder.EncoderLayers(cuda, out_proj_resident=form)
+        for layer in range(2):
+            enc.add_layer(pk.synth.layer_weights(3, layer, randomize_norms=True), 0.05, 0.05)
+        arena, ws = enc.make_workspace(rows)
+        a, b = dev16(x), torch.zeros((rows, 1024), dtype=torch.float16, device=cuda)
+        sv = torch.tensor(valid, dtype=torch.int32, device=cuda)
+        out = enc.run(a, b, ws, 2, 384, 384, seg_valid=sv)
+        torch.cuda.synchronize()
+        assert enc.status(arena, ws) == 0
+        outs.append(host(out).copy())
+    assert np.array_equal(outs[0].view(np.uint16), outs[1].view(np.uint16))
+    assert np.any(outs[0] != 0)
+
+
 def test_packed_weights_match_oracle(pk, cuda):
     """Load-time packing on the GPU is bit-identical to the CPU twin, including the
     position table (fp16 GEMM of the sinusoid) up to fp16 rounding."""
