@@ -64,8 +64,14 @@ def parse_args():
     ap.add_argument("--utterances", type=int, default=UTTERANCES_PER_GPU,
                     help="utterances per GPU and step (8 = benchmark configuration 4; 1 = configuration 3, "
                          "the batch-1 encoder + decode)")
-    ap.add_argument("--decode-groups", type=int, default=2,
-                    help="groups the batch is cut into so that a group's decode overlaps the next group's encode")
+    ap.add_argument("--encode-groups", type=int, default=1,
+                    help="groups that pass through subsampling and the encoder one after the other (1 = the whole "
+                         "batch in one pass; more = a group's decode runs under the next group's encode)")
+    ap.add_argument("--stream-decode-groups", type=int, default=4,
+                    help="decoder clusters per batch in the streamed (throughput) measurement")
+    ap.add_argument("--decode-groups", type=int, default=None,
+                    help="groups decoded side by side, one 16-CTA cluster each (default: as many clusters as the "
+                         "device holds at once)")
     ap.add_argument("--no-reference-kernels", action="store_true",
                     help="skip the timing of the reference's own kernels (oracle/_ref) beside this build's")
     return ap.parse_args()
@@ -231,7 +237,7 @@ def workload_config(args):
                   "-> 8x conv subsampling -> 24-block FastConformer encoder (T=750 per utterance, 768-row "
                   "segments) -> TDT greedy decode"),
         utterances_per_gpu=min(args.utterances, UTTERANCES_PER_GPU), audio_seconds_per_utterance=AUDIO_SECONDS,
-        decode_groups=args.decode_groups,
+        encode_groups=args.encode_groups, decode_groups=args.decode_groups or "one per decoder cluster the device holds",
         encoder_layers=args.layers, decoder_lstm_layers=args.decoder_layers,
         precision_map=("FF: E4M3 x E4M3 expand + SiLU + 70% zero 128x64 tiles -> INT8 x INT8 contract with "
                        "tile skip; QKV INT8; out-proj INT4-g128 values, fp16 MMA (" +
@@ -639,7 +645,8 @@ def main():
         pk.lib.lib.pk100_set_dependent_launch(0)
     eng = pk.pipeline.PipelineEngine(device, layers=args.layers, decoder_layers=args.decoder_layers,
                                      seed=SEED, max_utterances=per_gpu, mel_frames=MEL_FRAMES,
-                                     decode_groups=args.decode_groups, out_proj_resident=args.out_proj)
+                                     decode_groups=args.decode_groups, encode_groups=args.encode_groups,
+                                     out_proj_resident=args.out_proj)
     mel_host = torch.from_numpy(np.stack([pk.synth.mel_input(100 + u, MEL_FRAMES) for u in my_utts])).pin_memory()
     eng.mel_dev.copy_(mel_host)
     cache = Path(args.tau_cache) if args.tau_cache else None
@@ -704,10 +711,20 @@ def main():
         gathered = pk.parallel.gather_token_lists({u: t for u, t in zip(my_utts, tokens)}, total_utts, group=gloo)
     e3.record()
     sync_all()
-    clocks = sampler.stop()
     ms_e2e = max_over_ranks(e2.elapsed_time(e3)) / args.steps
     if eng.status() != 0:
         raise SystemExit("a bounded wait expired inside a kernel")
+
+    # ---- throughput mode: a stream of batches through the public API, batch i + 1 copied in and
+    # encoded while batch i is decoded; host wall clock between the first and the last batch's results
+    stream_n = max(args.steps, 4) + 1
+    marks = []
+    for toks in eng.transcribe_stream((mel_host for _ in range(stream_n)), decode_groups=args.stream_decode_groups):
+        marks.append(time.perf_counter())
+        if any(len(a) != len(b) or (a != b).any() for a, b in zip(toks, tokens)):
+            raise SystemExit("the streamed batches returned other tokens than transcribe_batch")
+    ms_stream = max_over_ranks((marks[-1] - marks[0]) * 1e3 / (len(marks) - 1))
+    clocks = sampler.stop()
 
     audio_per_step = AUDIO_SECONDS * total_utts
     value = audio_per_step / (ms_resident / 1e3)
@@ -721,7 +738,7 @@ def main():
     mine = dict(rank=rank, ms_per_step=own_ms_resident, longest_chain_rounds=longest, groups=stages,
                 decode_us_per_round=dec_ms * 1e3 / max(dec_rounds, 1),
                 decode_end_ms=max(s["decode_end_ms"] for s in stages),
-                encode_ms=sum(s["encode_ms"] for s in stages))
+                encode_ms=sum({s["encode_group"]: s["encode_ms"] for s in stages}.values()))
     per_rank = [mine]
     if world > 1:
         per_rank = [None] * world
@@ -763,6 +780,11 @@ def main():
                 e2e=dict(value=e2e_value, unit="x real time", ms_per_step=ms_e2e,
                          h2d_bytes_per_step=int(mel_host.numel() * 4),
                          d2h_bytes_per_step=int(eng.tokens_host.numel() * 4 + eng.counts_host.numel() * 4)),
+                throughput=dict(value=AUDIO_SECONDS * total_utts / (ms_stream / 1e3), unit="x real time",
+                                ms_per_batch=ms_stream, batches=stream_n, decode_groups=args.stream_decode_groups,
+                                note=("PipelineEngine.transcribe_stream: the same batch from pinned host memory over and "
+                                      "over, batch i+1 encoded beside the decoder clusters of batch i; host wall clock "
+                                      "from the first batch's tokens to the last's, max over ranks; same tokens as e2e")),
                 gpu_launches=int(launches), roofline=roofline, decoder=decoder, per_rank=per_rank,
                 tensor_map_cache=dict(zip(("hits", "misses"), pk.lib.tensor_map_cache_stats())),
                 tokens_per_utterance=[int(len(t)) for t in tokens])

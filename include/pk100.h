@@ -337,6 +337,12 @@ long long pk100_tdt_workspace_bytes(int utterances);
  * leaves the word at zero. */
 long long pk100_tdt_rounds_offset(int utterances);
 
+/* How many 16-CTA clusters of the cluster decoder (1 or 2 LSTM layers) the current device can hold
+ * at once (a cluster has to fit one GPC; 7 on a B200), 0 when that kernel cannot run here.  A host
+ * that decodes several groups of utterances side by side on separate streams, each with its own
+ * workspace, should not start more calls than this: a call beyond it waits for a whole earlier one. */
+int pk100_tdt_cluster_capacity(int lstm_layers);
+
 /* Decodes `utterances` sequences in lockstep.  Chooses the cluster kernel when the device can
  * host a 16-CTA cluster, else the exchange kernel (both
  * below; same results up to the summation order of the fp32 partial sums).

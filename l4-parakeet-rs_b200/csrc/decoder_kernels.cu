@@ -2325,11 +2325,15 @@ namespace {
 // Can this device run a 16-CTA cluster of the cluster decoder?  Asked once per device and
 // kernel variant (one or two LSTM layers).
 template <int Layers, bool Cache>
-bool cluster_decoder_available() {
+bool cluster_decoder_available(int* capacity = nullptr) {
     static int cached[64] = {0};      // 0 = unknown, 1 = yes, 2 = no
+    static int resident[64] = {0};    // clusters of this kernel the device holds at once
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-    if (cached[dev] != 0) return cached[dev] == 1;
+    if (cached[dev] != 0) {
+        if (capacity != nullptr) *capacity = resident[dev];
+        return cached[dev] == 1;
+    }
     bool ok = false;
     do {
         int max_smem = 0;
@@ -2353,9 +2357,11 @@ bool cluster_decoder_available() {
         int clusters = 0;
         if (cudaOccupancyMaxActiveClusters(&clusters, tdt_cluster_kernel<Layers, Cache>, &cfg) != cudaSuccess) break;
         ok = clusters >= 1;
+        resident[dev] = clusters;
     } while (false);
     cudaGetLastError();
     cached[dev] = ok ? 1 : 2;
+    if (capacity != nullptr) *capacity = resident[dev];
     return ok;
 }
 
@@ -2364,6 +2370,18 @@ bool cluster_decoder_available_for(int layers, bool cache) {
     if (layers == 2) return cache ? cluster_decoder_available<2, true>() : cluster_decoder_available<2, false>();
     return false;
 }
+
+}  // namespace
+
+extern "C" int pk100_tdt_cluster_capacity(int lstm_layers) {
+    int clusters = 0;
+    bool ok = false;
+    if (lstm_layers == 1) ok = cluster_decoder_available<1, false>(&clusters);
+    else if (lstm_layers == 2) ok = cluster_decoder_available<2, false>(&clusters);
+    return ok ? clusters : 0;
+}
+
+namespace {
 
 template <int Layers, bool Cache>
 cudaError_t launch_cluster_kernel(cudaStream_t stream, const DecParams& p, const uint4* lstm, const uint4* pred,

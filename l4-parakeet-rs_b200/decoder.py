@@ -27,6 +27,8 @@ L.lib.pk100_tdt_workspace_bytes.argtypes = [C.c_int]
 L.lib.pk100_tdt_workspace_bytes.restype = C.c_longlong
 L.lib.pk100_tdt_rounds_offset.argtypes = [C.c_int]
 L.lib.pk100_tdt_rounds_offset.restype = C.c_longlong
+L.lib.pk100_tdt_cluster_capacity.argtypes = [C.c_int]
+L.lib.pk100_tdt_cluster_capacity.restype = C.c_int
 L.lib.pk100_tdt_decode.argtypes = [vp, C.POINTER(DecoderWeightsC), vp, C.c_int, C.c_int, vp, vp, vp, vp,
                                    vp, C.c_int, vp]
 L.lib.pk100_tdt_decode.restype = C.c_int

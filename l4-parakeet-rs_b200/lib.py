@@ -59,6 +59,7 @@ SIGNATURES = {
     "pk100_run_layers": None,
     "pk100_tdt_workspace_bytes": None,
     "pk100_tdt_rounds_offset": None,
+    "pk100_tdt_cluster_capacity": None,
     "pk100_tdt_decode": None,
     "pk100_tdt_decode_barrier": None,
     "pk100_tdt_decode_cluster": None,

@@ -9,12 +9,17 @@ frames (`transcribe_batch`) or from PCM through the log-mel frontend (`transcrib
 Everything between the two copies is stream-ordered launches of libpk100 kernels
 without host synchronisation.
 
-Decode is a latency-bound chain on 16 SMs (one thread-block cluster); the encoder wants the
-other 132.  With `decode_groups` > 1 the batch is cut into that many groups of utterances:
-group g is encoded on the caller's stream, then decoded on a high-priority side stream
-while group g + 1 is being encoded, the encoder's persistent GEMMs capped at the SMs the
-decoders in flight leave free.  Results are identical to the ungrouped run (every kernel
-is batch-invariant); only the schedule changes."""
+Decode is a latency-bound chain on 16 SMs (one thread-block cluster) whose length is the
+longest utterance's rounds and whose cost per round grows with the utterances that step in
+it; the encoder is throughput-bound and most efficient on the whole batch.  So the batch is
+cut twice: into `encode_groups` groups that go through subsampling and the encoder blocks
+one after the other on the caller's stream (default 1: the whole batch in one pass), and
+into `decode_groups` groups (default: as many 16-CTA clusters as the device holds at once,
+7 on a B200) that are decoded side by side, each on its own high-priority stream with its
+own workspace, as soon as the encode group they belong to is done.  With more than one encode
+group the decoders of the earlier groups run under the encoder of the next, whose persistent
+GEMMs are capped at the SMs those decoders leave free.  Results are identical whatever the
+grouping (every kernel is batch-invariant); only the schedule changes."""
 from __future__ import annotations
 
 import ctypes as C
@@ -37,13 +42,37 @@ def seg_stride_for(frames_out: int) -> int:
     return (frames_out + 127) // 128 * 128
 
 
+class _Slot:
+    """Per-request device and host buffers of one batch in flight (the engine itself is slot 0;
+    `transcribe_stream` adds a second one so that a batch can be encoded while the one before
+    it is still being decoded)."""
+
+    def __init__(self, eng):
+        dev, n = eng.device, eng.max_utterances
+        self.mel_dev = torch.zeros_like(eng.mel_dev)
+        self.mel_frames_dev = torch.full((n,), eng.mel_frames, dtype=torch.int32, device=dev)
+        self.out_frames_dev = torch.full((n,), eng.frames_out, dtype=torch.int32, device=dev)
+        self.out_frames_host = torch.full((n,), eng.frames_out, dtype=torch.int32)
+        self.longest_out_frames = eng.frames_out
+        self._lengths = tuple([eng.mel_frames] * n)
+        self.enc_proj = torch.zeros_like(eng.enc_proj)
+        self.tokens, self.durations, self.counts = (torch.zeros_like(t) for t in (eng.tokens, eng.durations, eng.counts))
+        self.tokens_host = torch.zeros_like(eng.tokens_host).pin_memory()
+        self.counts_host = torch.zeros_like(eng.counts_host).pin_memory()
+        self.dec_streams = [torch.cuda.Stream(device=dev, priority=-1) for _ in range(eng.decode_groups)]
+        self.dec_scratch = [eng.dec.make_scratch() for _ in range(eng.decode_groups)]
+
+
 class PipelineEngine:
     def __init__(self, device, layers=24, decoder_layers=2, seed=4, max_utterances=8, mel_frames=6000,
-                 randomize_norms=False, decode_groups=2, out_proj_resident="f16"):
+                 randomize_norms=False, decode_groups=None, out_proj_resident="f16", encode_groups=1):
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
         self.max_utterances = max_utterances
-        self.decode_groups = max(1, min(int(decode_groups), max_utterances))
+        self.encode_groups = max(1, min(int(encode_groups), max_utterances))
+        if decode_groups is None:
+            decode_groups = max(1, int(L.lib.pk100_tdt_cluster_capacity(decoder_layers)))
+        self.decode_groups = max(self.encode_groups, min(int(decode_groups), max_utterances))
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.mel_frames = mel_frames
         self.frames_out = sub_mod.output_frames(mel_frames)
@@ -82,10 +111,10 @@ class PipelineEngine:
 
     # ---- profiling hook: CUDA events around the FF-expand GEMMs
     def enable_gemm_timing(self):
-        """CUDA events around every FF-expand GEMM (two per block), one set per decode group."""
+        """CUDA events around every FF-expand GEMM (two per block), one set per encode group."""
         n = 2 * 2 * len(self.enc.layers)
         self._events, self._event_arrays = [], []
-        for _ in range(self.decode_groups):
+        for _ in range(self.encode_groups):
             events = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
             for e in events:
                 e.record()                   # creates the underlying cudaEvent_t
@@ -97,8 +126,8 @@ class PipelineEngine:
     def gemm_times_ms(self):
         """[(milliseconds, rows of that launch)] for every FF-expand launch of the last request."""
         out = []
-        for g, (u0, u1) in enumerate(self.last_groups):
-            ev = self._events[g]
+        for e, (u0, u1) in enumerate(self.last_encode_groups):
+            ev = self._events[e]
             out += [(ev[2 * i].elapsed_time(ev[2 * i + 1]), (u1 - u0) * self.seg_stride) for i in range(len(ev) // 2)]
         return out
 
@@ -106,30 +135,34 @@ class PipelineEngine:
     def enable_stage_timing(self):
         """CUDA events around the encode and the decode of every group (recording does not synchronise)."""
         mk = lambda: torch.cuda.Event(enable_timing=True)
-        self._stage_events = [dict(enc0=mk(), enc1=mk(), dec0=mk(), dec1=mk()) for _ in range(self.decode_groups)]
+        self._stage_events = dict(enc=[(mk(), mk()) for _ in range(self.encode_groups)],
+                                  dec=[(mk(), mk()) for _ in range(self.decode_groups)])
 
     def stage_times(self):
         """After a synchronise: per decode group of the last request, its utterance range, encode
         and decode milliseconds, the decode's lockstep rounds, and when the decode started and
         ended relative to the start of the request."""
         out = []
-        first = self._stage_events[0]["enc0"]
+        first = self._stage_events["enc"][0][0]
         for g, (u0, u1) in enumerate(self.last_groups):
-            ev = self._stage_events[g]
-            out.append(dict(utterances=[u0, u1], encode_ms=ev["enc0"].elapsed_time(ev["enc1"]),
-                            decode_ms=ev["dec0"].elapsed_time(ev["dec1"]),
-                            decode_start_ms=first.elapsed_time(ev["dec0"]), decode_end_ms=first.elapsed_time(ev["dec1"]),
+            enc0, enc1 = self._stage_events["enc"][self.last_encode_of[g]]
+            dec0, dec1 = self._stage_events["dec"][g]
+            out.append(dict(utterances=[u0, u1], encode_group=self.last_encode_of[g],
+                            encode_ms=enc0.elapsed_time(enc1), encode_end_ms=first.elapsed_time(enc1),
+                            decode_ms=dec0.elapsed_time(dec1),
+                            decode_start_ms=first.elapsed_time(dec0), decode_end_ms=first.elapsed_time(dec1),
                             rounds=self.dec.last_rounds(u1 - u0, self.dec_scratch[g])))
         return out
 
-    def set_lengths(self, mel_frames_per_utt):
-        self._lengths = tuple(int(f) for f in mel_frames_per_utt) + self._lengths[len(mel_frames_per_utt):]
+    def set_lengths(self, mel_frames_per_utt, slot=None):
+        b = self if slot is None else slot
+        b._lengths = tuple(int(f) for f in mel_frames_per_utt) + b._lengths[len(mel_frames_per_utt):]
         mf = torch.tensor(mel_frames_per_utt, dtype=torch.int32)
         of = torch.tensor([sub_mod.output_frames(int(f)) for f in mel_frames_per_utt], dtype=torch.int32)
-        self.mel_frames_dev[:len(mf)].copy_(mf)
-        self.out_frames_dev[:len(of)].copy_(of)
-        self.out_frames_host[:len(of)].copy_(of)
-        self.longest_out_frames = int(self.out_frames_host.max())
+        b.mel_frames_dev[:len(mf)].copy_(mf)
+        b.out_frames_dev[:len(of)].copy_(of)
+        b.out_frames_host[:len(of)].copy_(of)
+        b.longest_out_frames = int(b.out_frames_host.max())
 
     def encode(self, utterances):
         self.sub.run(self.mel_dev[:utterances], self.seg_stride, mel_frames=self.mel_frames_dev,
@@ -147,58 +180,83 @@ class PipelineEngine:
                                           seg_valid=self.out_frames_dev)
         self.calibrated = True
 
-    def _group_bounds(self, utterances):
-        groups = min(self.decode_groups, utterances)
-        base, extra = divmod(utterances, groups)
-        bounds, u = [], 0
-        for g in range(groups):
+    @staticmethod
+    def _split(first, last, parts):
+        """[first, last) cut into `parts` contiguous ranges whose sizes differ by at most one."""
+        base, extra = divmod(last - first, parts)
+        bounds, u = [], first
+        for g in range(parts):
             n = base + (1 if g < extra else 0)
             bounds.append((u, u + n))
             u += n
         return bounds
 
-    def run_resident(self, utterances):
+    def _plan(self, utterances, decode_groups=None):
+        """[((first, last) of an encode group, [(first, last) of each of its decode groups])]:
+        the utterances cut into decode groups, consecutive decode groups joined into encode groups."""
+        dg = min(self.decode_groups if decode_groups is None else max(1, min(decode_groups, self.decode_groups)),
+                 utterances)
+        eg = min(self.encode_groups, dg)
+        decs = self._split(0, utterances, dg)
+        plan = []
+        for (g0, g1) in self._split(0, dg, eg):
+            plan.append(((decs[g0][0], decs[g1 - 1][1]), decs[g0:g1]))
+        return plan
+
+    def run_resident(self, utterances, slot=None, join=True, clusters_in_flight=0, decode_groups=None):
         """Hot path with the inputs already in HBM: subsampling -> encoder -> projection -> decode,
         group by group (see the module text); returns with everything queued on the caller's
-        stream, which waits for the side streams."""
+        stream, which waits for the side streams (join=False: it does not, and the decode groups'
+        streams are returned).  slot: the buffers of the batch (default: the engine's own);
+        clusters_in_flight: decoder clusters of an earlier batch still running beside this one."""
+        b = self if slot is None else slot
         # the reference switches decoder kernels (and numerics) at 1024 frames per request
         # (src/cuda/decoder.rs:88); a batch of short utterances needs one launch only
-        cache = "auto" if self.longest_out_frames >= dec_mod.LONG_REQUEST_FRAMES else "fp16"
+        cache = "auto" if b.longest_out_frames >= dec_mod.LONG_REQUEST_FRAMES else "fp16"
         main = torch.cuda.current_stream()
-        bounds = self._group_bounds(utterances)
-        self.last_groups = bounds
+        plan = self._plan(utterances, decode_groups)
+        self.last_encode_groups = [enc for enc, _ in plan]
+        self.last_groups = [d for _, decs in plan for d in decs]
+        self.last_encode_of = [e for e, (_, decs) in enumerate(plan) for _ in decs]
+        single = len(self.last_groups) == 1 and join
         seg = self.seg_stride
-        for g, (u0, u1) in enumerate(bounds):
-            ev = self._stage_events[g] if self._stage_events is not None else None
-            r0, r1 = u0 * seg, u1 * seg
-            if g > 0:
-                # decoders of the earlier groups hold 16 SMs each while this group is encoded
-                L.lib.pk100_set_gemm_cta_cap(max(self.sm_count - 16 * g, 16))
+        g = 0
+        for e, ((a0, a1), decs) in enumerate(plan):
+            ev = self._stage_events if slot is None else None
+            r0, r1 = a0 * seg, a1 * seg
+            if g + clusters_in_flight > 0:
+                # decoders already running hold 16 SMs each while this group is encoded
+                L.lib.pk100_set_gemm_cta_cap(max(self.sm_count - 16 * (g + clusters_in_flight), 16))
             if ev:
-                ev["enc0"].record(main)
-            if self._events is not None:
-                self.ws.profile_events = C.cast(self._event_arrays[g], C.POINTER(C.c_void_p))
-            self.sub.run(self.mel_dev[u0:u1], seg, mel_frames=self.mel_frames_dev[u0:u1], out=self.state_a[r0:r1])
-            encoded = self.enc.run(self.state_a[r0:r1], self.state_b[r0:r1], self.ws, u1 - u0, seg,
-                                   self.frames_out, seg_valid=self.out_frames_dev[u0:u1])
-            self.dec.project(encoded, out=self.enc_proj[r0:r1])
+                ev["enc"][e][0].record(main)
+            if self._events is not None and slot is None:
+                self.ws.profile_events = C.cast(self._event_arrays[e], C.POINTER(C.c_void_p))
+            self.sub.run(b.mel_dev[a0:a1], seg, mel_frames=b.mel_frames_dev[a0:a1], out=self.state_a[r0:r1])
+            encoded = self.enc.run(self.state_a[r0:r1], self.state_b[r0:r1], self.ws, a1 - a0, seg,
+                                   self.frames_out, seg_valid=b.out_frames_dev[a0:a1])
+            self.dec.project(encoded, out=b.enc_proj[r0:r1])
             if ev:
-                ev["enc1"].record(main)
-            side = self.dec_streams[g] if len(bounds) > 1 else main
-            if side is not main:
-                side.wait_stream(main)
-            with torch.cuda.stream(side):
-                if ev:
-                    ev["dec0"].record(side)
-                self.dec.decode(self.enc_proj[r0:r1], u1 - u0, seg, self.out_frames_dev[u0:u1], self.max_tokens,
-                                self.tokens[u0:u1], self.durations[u0:u1], self.counts[u0:u1], lstm_cache=cache,
-                                scratch=self.dec_scratch[g])
-                if ev:
-                    ev["dec1"].record(side)
-        if len(bounds) > 1:
-            L.lib.pk100_set_gemm_cta_cap(0)
-            for g in range(len(bounds)):
-                main.wait_stream(self.dec_streams[g])
+                ev["enc"][e][1].record(main)
+            for (u0, u1) in decs:
+                side = main if single else b.dec_streams[g]
+                if side is not main:
+                    side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    if ev:
+                        ev["dec"][g][0].record(side)
+                    self.dec.decode(b.enc_proj[u0 * seg:u1 * seg], u1 - u0, seg, b.out_frames_dev[u0:u1],
+                                    self.max_tokens, b.tokens[u0:u1], b.durations[u0:u1], b.counts[u0:u1],
+                                    lstm_cache=cache, scratch=b.dec_scratch[g])
+                    if ev:
+                        ev["dec"][g][1].record(side)
+                g += 1
+        L.lib.pk100_set_gemm_cta_cap(0)
+        if single:
+            return []
+        if join:
+            for k in range(g):
+                main.wait_stream(b.dec_streams[k])
+        return b.dec_streams[:g]
 
     def transcribe_batch(self, mel_host, mel_frames_per_utt=None):
         """mel_host: pinned fp32 CPU tensor [U, frames, 128]; mel_frames_per_utt: true frame
@@ -222,6 +280,59 @@ class PipelineEngine:
             raise RuntimeError(f"libpk100 reported an expired bounded wait (status {status})")
         counts = self.counts_host.numpy()
         return [self.tokens_host[u, :int(counts[u])].numpy().copy() for u in range(utterances)]
+
+    def transcribe_stream(self, batches, decode_groups=4):
+        """Throughput mode: a generator over `batches` (each a pinned fp32 CPU tensor [U, frames, 128]
+        or a pair (tensor, true frame counts)) that yields, in order, what `transcribe_batch` returns
+        for each.  Batch i + 1 is copied in and encoded while batch i is still being decoded: two sets
+        of request buffers alternate, the encoder's persistent GEMMs are capped at the SMs the
+        `decode_groups` decoder clusters of the batch before leave free (fewer clusters than in
+        `transcribe_batch`, where nothing runs beside them), and the host only waits for a batch's
+        tokens after the next batch has been queued.  Steady state per batch: the longer of the
+        (slowed) encode and the longest decode chain, instead of their sum."""
+        if not hasattr(self, "_second_slot"):
+            self._second_slot = _Slot(self)
+            self._collect_streams = [torch.cuda.Stream(device=self.device) for _ in range(2)]
+        slots = [self, self._second_slot]
+        main = torch.cuda.current_stream()
+
+        def finish(pending):
+            b, utterances, done = pending
+            done.synchronize()
+            status = self.status()
+            if status != 0:
+                raise RuntimeError(f"libpk100 reported an expired bounded wait (status {status})")
+            counts = b.counts_host.numpy()
+            return [b.tokens_host[u, :int(counts[u])].numpy().copy() for u in range(utterances)]
+
+        pending, in_flight = None, 0
+        for i, item in enumerate(batches):
+            mel_host, lengths = item if isinstance(item, (tuple, list)) else (item, None)
+            b = slots[i % 2]              # its batch before (i - 2) was collected before batch i - 1 was queued
+            utterances = mel_host.shape[0]
+            lengths = tuple([int(mel_host.shape[1])] * utterances if lengths is None else [int(f) for f in lengths])
+            if max(lengths) > mel_host.shape[1] or mel_host.shape[1] > self.mel_frames or utterances > self.max_utterances:
+                raise ValueError("batch larger than the engine was sized for")
+            if lengths != b._lengths[:utterances]:
+                self.set_lengths(lengths, slot=b)
+            b.mel_dev[:utterances, :mel_host.shape[1]].copy_(mel_host, non_blocking=True)
+            streams = self.run_resident(utterances, slot=b, join=False, clusters_in_flight=in_flight,
+                                        decode_groups=decode_groups)
+            collect = self._collect_streams[i % 2]
+            for st in streams:
+                collect.wait_stream(st)
+            with torch.cuda.stream(collect):
+                b.counts_host.copy_(b.counts, non_blocking=True)
+                b.tokens_host.copy_(b.tokens, non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(collect)
+            in_flight = len(streams)
+            if pending is not None:
+                yield finish(pending)
+            pending = (b, utterances, done)
+        if pending is not None:
+            yield finish(pending)
+        main.synchronize()
 
     # ---- one long utterance cut into chunks over several GPUs (see parallel.py)
     def encode_chunk(self, mel_chunk_host, lead_rows, rows):
@@ -292,8 +403,9 @@ class PipelineEngine:
     def status(self):
         """Non-zero when a bounded wait expired inside a kernel (saturation is reported separately)."""
         dec = int(self.dec.status.item()) & ~4          # bit 4: a decode round had only NaN scores
-        for scratch in self.dec_scratch[1:]:
-            dec |= int(scratch[1].item())
+        extra = self.dec_scratch[1:] + (self._second_slot.dec_scratch if hasattr(self, "_second_slot") else [])
+        for scratch in extra:
+            dec |= int(scratch[1].item()) & ~4
         return (self.enc.status(self.arena, self.ws) & ~self.HIDDEN_SATURATED) | dec | int(self.sub.status.item())
 
 

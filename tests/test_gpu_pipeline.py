@@ -74,10 +74,37 @@ def test_resident_path_is_deterministic_and_ragged_lengths(pk, cuda, engine):
     assert tuple(eng.out_frames_host.tolist()) == (eng.frames_out,) * 3
     again = eng.transcribe_batch(mel_host, [1000, 1000, 1000])
     assert all(np.array_equal(x, y) for x, y in zip(full, again))
-    # and the grouped schedule (a group's decode beside the next group's encode) changes no token
-    one = pk.pipeline.PipelineEngine(cuda, layers=2, decoder_layers=2, seed=9, max_utterances=3,
-                                     mel_frames=1000, randomize_norms=True, decode_groups=1)
-    for l, lw in enumerate(eng.enc.layers):
-        one.enc.set_tau(l, lw.ff1.tau, lw.ff2.tau)
-    ungrouped = one.transcribe_batch(mel_host, frames)
-    assert one.status() == 0 and all(np.array_equal(x, y) for x, y in zip(ungrouped, a))
+    # and the schedule changes no token: one group for everything, or two encode groups whose
+    # decodes run under the next group's encode (the engine above: one encode pass, a decoder
+    # cluster per utterance)
+    assert eng.encode_groups == 1 and eng.decode_groups == 3
+    for enc_groups, dec_groups in ((1, 1), (2, 2), (2, 3)):
+        other = pk.pipeline.PipelineEngine(cuda, layers=2, decoder_layers=2, seed=9, max_utterances=3, mel_frames=1000,
+                                           randomize_norms=True, encode_groups=enc_groups, decode_groups=dec_groups)
+        for l, lw in enumerate(eng.enc.layers):
+            other.enc.set_tau(l, lw.ff1.tau, lw.ff2.tau)
+        got = other.transcribe_batch(mel_host, frames)
+        assert other.status() == 0 and all(np.array_equal(x, y) for x, y in zip(got, a))
+        assert len(other.last_groups) == dec_groups and len(other.last_encode_groups) == enc_groups
+
+
+def test_streamed_batches_return_what_single_requests_return(pk, cuda, engine):
+    """transcribe_stream (batch i + 1 encoded beside the decode of batch i, two alternating sets
+    of request buffers) yields, in order, exactly the tokens of one transcribe_batch per batch."""
+    eng = engine
+    rng = np.random.default_rng(5)
+    batches, want = [], []
+    for i in range(5):
+        n = 1 + i % 3
+        frames = [int(f) for f in rng.integers(40, 1001, size=n)]
+        mels = np.zeros((n, 1000, 128), np.float32)
+        for u, f in enumerate(frames):
+            mels[u, :f] = pk.synth.mel_input(300 + 10 * i + u, f)
+        batches.append((torch.from_numpy(mels).pin_memory(), frames))
+    for mel, frames in batches:
+        want.append(eng.transcribe_batch(mel, frames))
+    got = list(eng.transcribe_stream(iter(batches), decode_groups=2))
+    assert len(got) == len(want) and eng.status() == 0
+    for g, w in zip(got, want):
+        assert len(g) == len(w) and all(np.array_equal(x, y) for x, y in zip(g, w))
+    assert any(len(t) > 0 for batch in got for t in batch)
