@@ -1,13 +1,20 @@
-// TDT greedy decode for a batch of utterances, one persistent cooperative kernel.
-//
-// Every decoder weight (LSTM input/recurrent gates, prediction projection,
-// joint head; ~15 MB fp16) is sliced across the CTAs once and stays resident in
-// shared memory for the whole decode; the utterances of the batch advance in
-// lockstep rounds so each round reads the weights once for all of them.
-// Per round: [LSTM layer 0 | barrier | LSTM layer 1 | barrier | prediction
-// projection | barrier] for the utterances that just emitted a token, then
-// joint + argmax | barrier.  Grid barriers are bounded: when one expires the
-// kernel records it in the status word and every CTA leaves.
+// TDT greedy decode for a batch of up to 8 utterances that advance in lockstep rounds
+// (a round = LSTM -> prediction projection for the utterances that just emitted a token, then
+// joint + argmax for all live ones).  Three kernels share one contract and one set of decision
+// rules:
+//   tdt_cluster_kernel   one 16-CTA thread-block cluster; vectors are exchanged through
+//                        distributed shared memory (st.async + mbarrier complete_tx), layer 0's
+//                        recurrent weights live in tensor memory, the joint rows in shared
+//                        memory, the rest streams from L2.  The kernel of the hot path.
+//   tdt_exchange_kernel  one CTA per SM, all weights resident in shared memory, exchanges
+//                        through tagged 64-bit global-memory slots (no cluster needed).
+//   tdt_greedy_kernel    one persistent cooperative kernel with the reference's structure: per
+//                        round [LSTM layer 0 | barrier | LSTM layer 1 | barrier | prediction
+//                        projection | barrier], then joint + argmax | barrier.  A cross-check.
+// The cluster and the barrier kernel also have the numerics of the reference's long-request
+// kernel (INT8 codes of the recurrent weights and of the hidden state, kernels/sm89/
+// decoder.cu:452-784).  Every wait (grid barrier, mbarrier, slot poll) is bounded: when one
+// expires the kernel records it in the status word and every CTA leaves.
 //
 // Decision rules follow kernels/sm89/decoder.cu:35-46 (order-preserving key,
 // ties to the lower token id), :416-422 (first strict maximum duration) and
