@@ -336,9 +336,8 @@ def run_micro(args):
             call = lambda: pk.ops.local_attention(qkv[:, :1024], qkv[:, 1024:2048], qkv[:, 2048:], pos, u, v,
                                                   seg_stride=seg, valid_rows=750, out=out)
         else:
-            scratch = torch.empty(m * 1024 * 2, dtype=torch.uint8, device=dev)
             call = lambda: pk.ops.local_attention_tcgen05(qkv[:, :1024], qkv[:, 1024:2048], qkv[:, 2048:], pos, u, v,
-                                                          seg_stride=seg, valid_rows=750, out=out, scratch=scratch)
+                                                          seg_stride=seg, valid_rows=750, out=out)
         nbytes = m * 1024 * 2 * 4
         work, peak, unit, bound = nbytes / 1e9, peaks["hbm_gbs"], "GB/s", "hbm"
     elif args.micro == "depthwise":

@@ -218,17 +218,15 @@ int pk100_local_relpos_attention(void* stream, const void* query, int ldq, const
 
 /* The same operator on tcgen05 tensor cores (the kernel of the hot path on B200): one CTA per 128
  * queries of a head, Q.P^T, Q.K^T and Pr.V as tcgen05.mma kind::f16 with the accumulators in tensor
- * memory, operands staged by TMA, fp32 softmax.  Arguments as above plus
- *   scratch: device buffer of pk100_attention_scratch_bytes(segments, seg_stride) bytes (16-byte
- *            aligned) that receives the transposed copy of `value` the last contraction reads;
+ * memory, operands staged by TMA (the value rows as they lie in memory: an MN-major B operand, no
+ * transposed copy), fp32 softmax.  Arguments as above plus
  *   status:  device int, set to 1 when a bounded wait expired (may be NULL).
  * Needs seg_stride % 128 == 0 (PK100_ERR_SHAPE otherwise: use pk100_local_relpos_attention). */
-long long pk100_attention_scratch_bytes(int segments, int seg_stride);
 int pk100_local_relpos_attention_tcgen05(void* stream, const void* query, int ldq, const void* key, int ldk,
                                          const void* value, int ldv, const void* position,
                                          const void* bias_u, const void* bias_v, void* output, int ldo,
                                          int segments, int seg_stride, int valid_rows, const int* seg_valid,
-                                         void* scratch, int* status);
+                                         int* status);
 
 /* pk_sm89_pack_position_heads (kernels/sm89/encoder.cu:1321-1336):
  * [272, 1024] -> head-major [8, 272, 128]. */
@@ -278,7 +276,7 @@ typedef struct pk100_layer_weights {
 /* Caller-owned scratch for `rows` = segments * seg_stride rows.  Sizes in bytes:
  * q8 rows*1024, row_scales rows*4, hidden8 rows*4096, keep ceil(rows/128)*64,
  * qkv rows*3072*2, att rows*1024*2, glu rows*1024*2, dw8 rows*1024,
- * dw_scales rows*4, status 4, value_t rows*1024*2.  All 256-byte aligned. */
+ * dw_scales rows*4, status 4.  All 256-byte aligned. */
 typedef struct pk100_encoder_workspace {
     void* q8; float* row_scales; void* hidden8; uint8_t* keep; void* qkv; void* att;
     void* glu; void* dw8; float* dw_scales; int* status;
@@ -286,9 +284,6 @@ typedef struct pk100_encoder_workspace {
      * layer l, module m (0/1) is bracketed by events[2*(2*l+m)] and [2*(2*l+m)+1] when
      * 2*(2*l+m)+1 < profile_events_len.  Recording an event does not synchronise. */
     void** profile_events; int profile_events_len;
-    /* rows*1024*2 bytes: transposed value plane for pk100_local_relpos_attention_tcgen05; when NULL
-     * (or seg_stride is not a multiple of 128) the sequencer uses pk100_local_relpos_attention */
-    void* value_t;
 } pk100_encoder_workspace;
 
 /* Bytes needed for one arena holding every field above. */
@@ -301,8 +296,8 @@ int pk100_encoder_workspace_carve(void* base, int rows, pk100_encoder_workspace*
  * (i even) or state_a (i odd) and the next layer continues from there;
  * *output receives the buffer that holds the final result.  tile_stats, when not
  * NULL, receives max|SiLU| per 128x64 tile: [n_layers][2][ceil(rows/128)*64].
- * attention_impl: 0 = tensor-core kernel (tcgen05 when ws->value_t is set and seg_stride is a multiple
- * of 128, else the mma.sync kernel), 1 = fp32 CUDA-core kernel, 2 = the mma.sync kernel. */
+ * attention_impl: 0 = tensor-core kernel (tcgen05 when seg_stride is a multiple of 128, else the
+ * mma.sync kernel), 1 = fp32 CUDA-core kernel, 2 = the mma.sync kernel. */
 int pk100_run_layers(void* stream, const pk100_layer_weights* layers, int n_layers, void* state_a,
                      void* state_b, const pk100_encoder_workspace* ws, int segments,
                      int seg_stride, int valid_rows, const int* seg_valid, float* tile_stats,

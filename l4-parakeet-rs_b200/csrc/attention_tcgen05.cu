@@ -12,9 +12,12 @@
 //     S  = Q . K^T     (three key blocks of N = 128)                 [384, 512), [0, 128), [128, 256)
 //     O  = Pr . V      (Pr = softmax probabilities, fp16, K = keys)  [256, 384)
 // Operands arrive by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into three 32 KB slots
-// that hold blocks of P_h, then K, then V^T in turn, each load issued as soon as its slot is free (V is
-// read through a transposed copy, so that every operand is K-major).  The u / v biases are added in fp32 outside the MMAs (u . K_k and v . P_j are
-// per-column constants).  QP is drained to shared memory as fp16 so that the relative shift is a plain
+// that hold blocks of P_h, then K, then V in turn, each load issued as soon as its slot is free.  Q, P
+// and K are K-major operands; V is used as it lies in memory (rows = keys = the K dimension of
+// Pr . V, features contiguous), i.e. as an MN-major B operand: instruction-descriptor bit 16, and a
+// shared-memory descriptor whose leading-dimension offset is the distance between the two 64-feature
+// atoms and whose stride is the 1024 bytes between 8-key groups.  The u / v biases are added in fp32
+// outside the MMAs (u . K_k and v . P_j are per-column constants).  QP is drained to shared memory as fp16 so that the relative shift is a plain
 // gather (key kk of query ql reads column kk - ql).  The softmax is two passes over the S accumulators
 // (row maximum, then exponentials) by sixteen warps, four per TMEM lane quadrant; the probabilities go
 // back through swizzled shared memory as the A operand of the last contraction.
@@ -68,7 +71,7 @@ enum : int {
 
 // Operand staging: three 32 KB slots take, in turn, the position rows (slots 0, 1 and the 4 KB tail),
 // the key blocks (K0 -> slot 2 at once, K1 / K2 -> slots 0 / 1 when the position rows are done with)
-// and the transposed value blocks (V_b -> the slot K_b had, when S_b and its bias term are done).
+// and the value blocks (V_b -> the slot K_b had, when S_b and its bias term are done).
 struct Smem {
     alignas(1024) uint8_t q[kSlotBytes];              // Q tile, later the probability block
     alignas(1024) uint8_t slot[3][kSlotBytes];
@@ -128,7 +131,7 @@ __device__ __noinline__ bool att_wait(uint64_t* bar, volatile int* abort_flag) {
 __global__ void __launch_bounds__(kThreads, 1)
 local_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_p16,
-                               const __grid_constant__ CUtensorMap map_vt, const Params p) {
+                               const __grid_constant__ CUtensorMap map_v, const Params p) {
     extern __shared__ uint8_t att5_raw[];
     Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(att5_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -165,7 +168,7 @@ local_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const 
         prefetch_tensormap(&map_k);
         prefetch_tensormap(&map_p);
         prefetch_tensormap(&map_p16);
-        prefetch_tensormap(&map_vt);
+        prefetch_tensormap(&map_v);
     }
     if (tid < kDim) {
         sm.bias_u[tid] = __half2float(p.bias_u[head * kDim + tid]);
@@ -179,7 +182,7 @@ local_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const 
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sm.tmem_base;
-    grid_dependency_wait();                  // Q, K and the transposed V come from the kernels before
+    grid_dependency_wait();                  // Q, K and V come from the kernel before
     const int key_first = q0 - kReach;       // window index kk <-> key key_first + kk
     // slot of key block b, and of value block b after it
     auto slot_of = [](int b) { return b == 0 ? 2 : b - 1; };
@@ -210,16 +213,17 @@ local_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const 
                 ATT_WAIT(B_BIAS_DONE);
                 load_keys(1);
                 load_keys(2);
-                // values (transposed: rows = features, columns = keys) follow their key block into its slot
+                // values follow their key block into its slot
                 bool ok = true;
                 for (int b = 0; b < 3 && ok; ++b) {
                     ok = att_wait(&sm.bar[B_S_DONE + b], abort_flag) &&
                          att_wait(&sm.bar[B_UK_DONE + b], abort_flag);
                     if (!ok) break;
                     mbar_arrive_expect_tx(&sm.bar[B_V_IN + b], kSlotBytes);
+                    // rows = keys, 64 features per atom: the MN-major form of the B operand of Pr.V
                     for (int a = 0; a < 2; ++a)
-                        tma_load_2d(sm.slot[slot_of(b)] + a * kAtomBytes, &map_vt, &sm.bar[B_V_IN + b],
-                                    base + key_first + (2 * b + a) * 64, head * kDim);
+                        tma_load_2d(sm.slot[slot_of(b)] + a * kAtomBytes, &map_v, &sm.bar[B_V_IN + b],
+                                    head * kDim + a * 64, base + key_first + b * 128);
                 }
             } while (false);
         }
@@ -265,9 +269,14 @@ local_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const 
                     const uint32_t v_addr = smem_u32(sm.slot[slot_of(b)]);
                     for (int ks = 0; ks < 8; ++ks) {       // 16 keys per MMA
                         const int a = ks / 4, j = ks % 4;
+                        // B = V[keys, features] as it lies in memory: MN-major (features contiguous),
+                        // 8-key groups 1024 bytes apart, the second 64 features 16 KB on; 16 keys = 2048 bytes
+                        constexpr uint32_t idesc_v = idesc128 | (1u << 16);
+                        const uint64_t dv = static_cast<uint64_t>(((v_addr + ks * 2048u) & 0x3FFFFu) >> 4) |
+                                            (static_cast<uint64_t>(kAtomBytes >> 4) << 16) | (64ull << 32) |
+                                            (1ull << 46) | (2ull << 61);
                         tc_mma<KIND_F16>(tmem + kCtxCol, make_smem_desc<128>(q_addr + a * kAtomBytes) + 2u * j,
-                                         make_smem_desc<128>(v_addr + a * kAtomBytes) + 2u * j, idesc128,
-                                         (b > 0 || ks > 0) ? 1u : 0u);
+                                         dv, idesc_v, (b > 0 || ks > 0) ? 1u : 0u);
                     }
                     tc_commit(&sm.bar[B_PV_DONE + b]);
                 }
@@ -509,68 +518,34 @@ local_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const 
     }
 }
 
-// V [rows, ldv] (one 1024-column plane) -> Vt [1024, rows]: 64 x 64 tiles through shared memory.
-__global__ void __launch_bounds__(256) transpose_value_kernel(const __half* __restrict__ v, int ldv, __half* __restrict__ vt,
-                                                              int rows) {
-    __shared__ __half tile[64][66];
-    grid_dependents_launch();
-    grid_dependency_wait();
-    const int r0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
-    const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;       // 8 row groups
-    for (int i = ty; i < 64; i += 8) {
-        const int row = r0 + i;
-        const __half2 x = row < rows ? *reinterpret_cast<const __half2*>(v + static_cast<size_t>(row) * ldv + c0 + 2 * tx)
-                                     : __floats2half2_rn(0.0f, 0.0f);
-        tile[i][2 * tx] = __low2half(x);
-        tile[i][2 * tx + 1] = __high2half(x);
-    }
-    __syncthreads();
-    for (int i = ty; i < 64; i += 8) {
-        const int col = c0 + i;
-        if (r0 + 2 * tx < rows)
-            *reinterpret_cast<__half2*>(vt + static_cast<size_t>(col) * rows + r0 + 2 * tx) =
-                __halves2half2(tile[2 * tx][i], tile[2 * tx + 1][i]);
-    }
-}
-
 }  // namespace att5
 }  // namespace pk100
 
 using namespace pk100;
 
-extern "C" long long pk100_attention_scratch_bytes(int segments, int seg_stride) {
-    if (segments <= 0 || seg_stride <= 0) return 0;
-    return static_cast<long long>(segments) * seg_stride * 1024 * 2;
-}
-
 extern "C" int pk100_local_relpos_attention_tcgen05(
     void* stream_v, const void* query, int ldq, const void* key, int ldk, const void* value, int ldv,
     const void* position, const void* bias_u, const void* bias_v, void* output, int ldo, int segments,
-    int seg_stride, int valid_rows, const int* seg_valid, void* scratch, int* status) {
+    int seg_stride, int valid_rows, const int* seg_valid, int* status) {
     using namespace att5;
-    if (!query || !key || !value || !position || !bias_u || !bias_v || !output || !scratch) return PK100_ERR_NULL;
+    if (!query || !key || !value || !position || !bias_u || !bias_v || !output) return PK100_ERR_NULL;
     if (segments < 0 || seg_stride <= 0) return PK100_ERR_SHAPE;
-    if (seg_stride % kTile != 0) return PK100_ERR_SHAPE;          // tiles and the transposed copy start on 256-byte boundaries
+    if (seg_stride % kTile != 0) return PK100_ERR_SHAPE;          // whole 128-query tiles
     if (ldq < 1024 || ldk < 1024 || ldv < 1024 || ldo < 1024 || (ldq | ldk | ldv | ldo) % 8 != 0) return PK100_ERR_SHAPE;
     const uintptr_t bits = reinterpret_cast<uintptr_t>(query) | reinterpret_cast<uintptr_t>(key) |
                            reinterpret_cast<uintptr_t>(value) | reinterpret_cast<uintptr_t>(position) |
-                           reinterpret_cast<uintptr_t>(output) | reinterpret_cast<uintptr_t>(scratch);
+                           reinterpret_cast<uintptr_t>(output);
     if (bits & 15u) return PK100_ERR_ALIGN;
     if (segments == 0) return PK100_OK;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const unsigned long long rows = static_cast<unsigned long long>(segments) * seg_stride;
 
-    CUtensorMap map_q, map_k, map_p, map_p16, map_vt;
+    CUtensorMap map_q, map_k, map_p, map_p16, map_v;
     int rc = pk100_tensor_map_2d(&map_q, query, 2, rows, 1024, ldq, kTile, 128);
     if (rc == PK100_OK) rc = pk100_tensor_map_2d(&map_k, key, 2, rows, 1024, ldk, 128, 128);
     if (rc == PK100_OK) rc = pk100_tensor_map_2d(&map_p, position, 2, kHeads * kPosRows, kDim, kDim, 128, 128);
     if (rc == PK100_OK) rc = pk100_tensor_map_2d(&map_p16, position, 2, kHeads * kPosRows, kDim, kDim, 16, 128);
-    if (rc == PK100_OK) rc = pk100_tensor_map_2d(&map_vt, scratch, 2, 1024, rows, rows, kDim, 128);
-    if (rc != PK100_OK) return rc;
-
-    pk100_launch_chained(transpose_value_kernel, dim3(static_cast<unsigned>((rows + 63) / 64), 1024 / 64), dim3(256), 0, stream,
-        static_cast<const __half*>(value), ldv, static_cast<__half*>(scratch), static_cast<int>(rows));
-    rc = pk100_launch_status();
+    if (rc == PK100_OK) rc = pk100_tensor_map_2d(&map_v, value, 2, rows, 1024, ldv, 128, 128);
     if (rc != PK100_OK) return rc;
 
     constexpr int smem_bytes = static_cast<int>(sizeof(Smem)) + 1024;
@@ -584,6 +559,6 @@ extern "C" int pk100_local_relpos_attention_tcgen05(
     Params p{static_cast<const __half*>(bias_u), static_cast<const __half*>(bias_v), static_cast<__half*>(output), ldo,
              segments, seg_stride, valid_rows, seg_valid, status};
     dim3 grid(seg_stride / kTile, kHeads, segments);
-    pk100_launch_chained(local_attention_tcgen05_kernel, grid, dim3(kThreads), smem_bytes, stream, map_q, map_k, map_p, map_p16, map_vt, p);
+    pk100_launch_chained(local_attention_tcgen05_kernel, grid, dim3(kThreads), smem_bytes, stream, map_q, map_k, map_p, map_p16, map_v, p);
     return pk100_launch_status();
 }

@@ -76,7 +76,7 @@ extern "C" long long pk100_encoder_workspace_bytes(int rows) {
     const long long tiles = (r + 127) / 128;
     return align256(r * 1024) + align256(r * 4) + align256(r * 4096) + align256(tiles * 64) +
            align256(r * 3072 * 2) + align256(r * 1024 * 2) + align256(r * 1024 * 2) +
-           align256(r * 1024) + align256(r * 4) + 256 + align256(r * 1024 * 2);
+           align256(r * 1024) + align256(r * 4) + 256;
 }
 
 extern "C" int pk100_encoder_workspace_carve(void* base, int rows, pk100_encoder_workspace* out) {
@@ -99,7 +99,6 @@ extern "C" int pk100_encoder_workspace_carve(void* base, int rows, pk100_encoder
     out->status = reinterpret_cast<int*>(take(4));
     out->profile_events = nullptr;
     out->profile_events_len = 0;
-    out->value_t = take(r * 1024 * 2);
     return PK100_OK;
 }
 
@@ -150,11 +149,11 @@ extern "C" int pk100_run_layers(void* stream, const pk100_layer_weights* layers,
                     stream, qkv, 3 * kWidth, qkv + kWidth, 3 * kWidth, qkv + 2 * kWidth, 3 * kWidth,
                     w.position, w.bias_u, w.bias_v, ws.att, kWidth, segments, seg_stride, valid_rows,
                     seg_valid));
-            } else if (attention_impl == 0 && ws.value_t != nullptr && seg_stride % 128 == 0) {
+            } else if (attention_impl == 0 && seg_stride % 128 == 0) {
                 PK_TRY(pk100_local_relpos_attention_tcgen05(
                     stream, qkv, 3 * kWidth, qkv + kWidth, 3 * kWidth, qkv + 2 * kWidth, 3 * kWidth,
                     w.position, w.bias_u, w.bias_v, ws.att, kWidth, segments, seg_stride, valid_rows,
-                    seg_valid, ws.value_t, ws.status));
+                    seg_valid, ws.status));
             } else {
                 PK_TRY(pk100_local_relpos_attention(
                     stream, qkv, 3 * kWidth, qkv + kWidth, 3 * kWidth, qkv + 2 * kWidth, 3 * kWidth,

@@ -40,7 +40,7 @@ class LayerWeights(C.Structure):
 class Workspace(C.Structure):
     _fields_ = [("q8", vp), ("row_scales", vp), ("hidden8", vp), ("keep", vp), ("qkv", vp),
                 ("att", vp), ("glu", vp), ("dw8", vp), ("dw_scales", vp), ("status", vp),
-                ("profile_events", C.POINTER(vp)), ("profile_events_len", C.c_int), ("value_t", vp)]
+                ("profile_events", C.POINTER(vp)), ("profile_events_len", C.c_int)]
 
 
 L.lib.pk100_encoder_workspace_bytes.argtypes = [C.c_int]

@@ -50,8 +50,7 @@ SIGNATURES = {
     "pk100_local_relpos_attention": [vp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, i32,
                                      i32, i32, i32, vp],
     "pk100_local_relpos_attention_tcgen05": [vp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, i32,
-                                             i32, i32, i32, vp, vp, vp],
-    "pk100_attention_scratch_bytes": [i32, i32],
+                                             i32, i32, i32, vp, vp],
     "pk100_pack_position_heads": [vp, vp, vp],
     # struct-taking entry points: argtypes are completed in encoder.py / decoder.py
     "pk100_encoder_workspace_bytes": None,
@@ -96,7 +95,6 @@ for _name, _argtypes in SIGNATURES.items():
     if _argtypes is not None:
         _fn.argtypes = _argtypes
     _fn.restype = i32
-lib.pk100_attention_scratch_bytes.restype = i64
 lib.pk100_launch_count.restype = i64
 lib.pk100_launch_count.argtypes = []
 lib.pk100_set_gemm_cta_pairs.restype = None

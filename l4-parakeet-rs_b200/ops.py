@@ -179,20 +179,17 @@ def local_attention(q, k, v, pos, bias_u, bias_v, seg_stride=None, valid_rows=No
 
 
 def local_attention_tcgen05(q, k, v, pos, bias_u, bias_v, seg_stride=None, valid_rows=None,
-                            seg_valid=None, out=None, scratch=None, status=None):
+                            seg_valid=None, out=None, status=None):
     """The tcgen05 kernel (128 queries per CTA, accumulators in tensor memory); seg_stride % 128 == 0."""
     rows = q.shape[0]
     seg_stride = rows if seg_stride is None else seg_stride
     valid_rows = seg_stride if valid_rows is None else valid_rows
     if out is None:
         out = torch.empty((rows, 1024), device=q.device, dtype=torch.float16)
-    if scratch is None:
-        scratch = torch.empty(L.lib.pk100_attention_scratch_bytes(rows // seg_stride, seg_stride),
-                              device=q.device, dtype=torch.uint8)
     L.check(L.lib.pk100_local_relpos_attention_tcgen05(
         _stream(), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(pos),
         _ptr(bias_u), _ptr(bias_v), _ptr(out), out.stride(0), rows // seg_stride, seg_stride,
-        valid_rows, _ptr(seg_valid), _ptr(scratch), _ptr(status)), "pk100_local_relpos_attention_tcgen05")
+        valid_rows, _ptr(seg_valid), _ptr(status)), "pk100_local_relpos_attention_tcgen05")
     return out
 
 
