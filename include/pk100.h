@@ -184,6 +184,20 @@ int pk100_pack_weight_rows(void* stream, const void* weight, int n, int k, int l
 int pk100_dequant_w4g128(void* stream, const void* codes, const void* group_scales, int n, int k,
                          void* weight_f16);
 
+/* 2:4 structured sparsity of E4M3 activations: the input format of the reference's sparse FF2
+ * (pk_sm89_ffn_expand_int4_sparse epilogue 7, kernels/sm89/encoder.cu:685-704, :1037-1054, consumed by
+ * pk_sm89_ffn_contract_fp8_sparse :1087-1095 with mma.sp).  Per four consecutive bytes the two largest
+ * 7-bit magnitudes are kept, ties to the lower index.  cols % 16 == 0, 16-byte aligned pointers.
+ *   prune:      dense [rows, cols] -> dense [rows, cols] with the dropped bytes zero (may be in place);
+ *   compress:   dense -> the reference's arena: data [rows, cols/2] then metadata [rows, cols/8]
+ *               (rows * cols * 5 / 8 bytes);
+ *   decompress: that arena -> dense [rows, cols].
+ * The reference-parity FF2 on B200 is decompress (or prune) + pk100_gemm kind E4M3 with row_scale 1/16,
+ * the weight's column scales, alpha 0.5 and the residual in place: dense math on the same values. */
+int pk100_prune_2of4_e4m3(void* stream, const void* dense, void* pruned, int rows, int cols);
+int pk100_compress_2of4_e4m3(void* stream, const void* dense, void* compressed, int rows, int cols);
+int pk100_decompress_2of4_e4m3(void* stream, const void* compressed, void* dense, int rows, int cols);
+
 /* pk_sm89_glu_masked (kernels/sm89/encoder.cu:308-330). input [rows, 2048]. */
 int pk100_glu_masked(void* stream, const void* input, void* output, int total_rows,
                      int seg_stride, int valid_rows, const int* seg_valid);

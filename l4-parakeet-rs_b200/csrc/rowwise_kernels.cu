@@ -191,6 +191,78 @@ layer_norm_kernel(const __half* __restrict__ in, const __half* __restrict__ gamm
     }
 }
 
+// ------------------------------------------------- 2:4 structured sparsity of E4M3 activations
+// The reference's FF2 input format (kernels/sm89/encoder.cu:685-704, :1037-1054): per four
+// consecutive bytes the two largest 7-bit magnitudes are kept, ties to the lower index.
+// Returns the two kept bytes (low 16 bits, index order) and their 2-bit indices (bits 16-19).
+__device__ __forceinline__ uint32_t compress_quartet(uint32_t packed) {
+    uint32_t data = 0, meta = 0;
+    int count = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t mag = (packed >> (8 * i)) & 127u;
+        int rank = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t other = (packed >> (8 * j)) & 127u;
+            rank += (other > mag || (other == mag && j < i)) ? 1 : 0;
+        }
+        if (rank < 2) {
+            data |= ((packed >> (8 * i)) & 255u) << (8 * count);
+            meta |= static_cast<uint32_t>(i) << (2 * count);
+            ++count;
+        }
+    }
+    return data | (meta << 16);
+}
+
+__device__ __forceinline__ uint32_t expand_quartet(uint32_t two_bytes, uint32_t meta4) {
+    return ((two_bytes & 255u) << (8 * (meta4 & 3u))) | (((two_bytes >> 8) & 255u) << (8 * ((meta4 >> 2) & 3u)));
+}
+
+// mode 0: dense -> dense with the dropped bytes zeroed; 1: dense -> data [rows, cols/2] + metadata
+// [rows, cols/8] behind it; 2: that layout -> dense.  One thread per 16 dense bytes (4 quartets).
+__global__ void sparse24_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int rows, int cols,
+                                int mode) {
+    const size_t chunk = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const size_t chunks_per_row = static_cast<size_t>(cols) / 16;
+    if (chunk >= chunks_per_row * rows) return;
+    const size_t row = chunk / chunks_per_row, c16 = chunk % chunks_per_row;
+    const size_t data_bytes = static_cast<size_t>(rows) * (cols / 2);
+    if (mode == 2) {
+        const uint2 data = *reinterpret_cast<const uint2*>(in + row * (cols / 2) + c16 * 8);
+        const uint32_t meta = *reinterpret_cast<const uint16_t*>(in + data_bytes + row * (cols / 8) + c16 * 2);
+        uint4 dense;
+        dense.x = expand_quartet(data.x & 0xFFFFu, meta & 15u);
+        dense.y = expand_quartet(data.x >> 16, (meta >> 4) & 15u);
+        dense.z = expand_quartet(data.y & 0xFFFFu, (meta >> 8) & 15u);
+        dense.w = expand_quartet(data.y >> 16, (meta >> 12) & 15u);
+        *reinterpret_cast<uint4*>(out + row * cols + c16 * 16) = dense;
+        return;
+    }
+    const uint4 v = *reinterpret_cast<const uint4*>(in + row * cols + c16 * 16);
+    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+    uint32_t packed[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) packed[i] = compress_quartet(words[i]);
+    if (mode == 0) {
+        uint4 dense;
+        dense.x = expand_quartet(packed[0] & 0xFFFFu, packed[0] >> 16);
+        dense.y = expand_quartet(packed[1] & 0xFFFFu, packed[1] >> 16);
+        dense.z = expand_quartet(packed[2] & 0xFFFFu, packed[2] >> 16);
+        dense.w = expand_quartet(packed[3] & 0xFFFFu, packed[3] >> 16);
+        *reinterpret_cast<uint4*>(out + row * cols + c16 * 16) = dense;
+    } else {
+        uint2 data;
+        data.x = (packed[0] & 0xFFFFu) | (packed[1] << 16);
+        data.y = (packed[2] & 0xFFFFu) | (packed[3] << 16);
+        *reinterpret_cast<uint2*>(out + row * (cols / 2) + c16 * 8) = data;
+        const uint32_t meta = (packed[0] >> 16) | ((packed[1] >> 16) << 4) | ((packed[2] >> 16) << 8) |
+                              ((packed[3] >> 16) << 12);
+        *reinterpret_cast<uint16_t*>(out + data_bytes + row * (cols / 8) + c16 * 2) = static_cast<uint16_t>(meta);
+    }
+}
+
 // ------------------------------------------------------------ quantisers
 __global__ void quantize_fixed_kernel(const __half* __restrict__ in, uint8_t* __restrict__ out,
                                       size_t elements, float inv_scale, int to_s8) {
@@ -544,6 +616,27 @@ extern "C" int pk100_dequant_w4g128(void* stream, const void* codes, const void*
         static_cast<const uint8_t*>(codes), static_cast<const __half*>(group_scales), n, k,
         static_cast<__half*>(weight_f16));
     return pk100_launch_status();
+}
+
+static int sparse24_launch(void* stream, const void* input, void* output, int rows, int cols, int mode) {
+    if (!input || !output) return PK100_ERR_NULL;
+    if (rows < 0 || cols <= 0 || cols % 16 != 0) return PK100_ERR_SHAPE;
+    if (rows == 0) return PK100_OK;
+    if ((reinterpret_cast<uintptr_t>(input) | reinterpret_cast<uintptr_t>(output)) & 15u) return PK100_ERR_ALIGN;
+    const size_t chunks = static_cast<size_t>(rows) * (cols / 16);
+    sparse24_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(input), static_cast<uint8_t*>(output), rows, cols, mode);
+    return pk100_launch_status();
+}
+
+extern "C" int pk100_prune_2of4_e4m3(void* stream, const void* dense, void* pruned, int rows, int cols) {
+    return sparse24_launch(stream, dense, pruned, rows, cols, 0);
+}
+extern "C" int pk100_compress_2of4_e4m3(void* stream, const void* dense, void* compressed, int rows, int cols) {
+    return sparse24_launch(stream, dense, compressed, rows, cols, 1);
+}
+extern "C" int pk100_decompress_2of4_e4m3(void* stream, const void* compressed, void* dense, int rows, int cols) {
+    return sparse24_launch(stream, compressed, dense, rows, cols, 2);
 }
 
 extern "C" int pk100_glu_masked(void* stream, const void* input, void* output, int total_rows,

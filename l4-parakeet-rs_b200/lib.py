@@ -52,6 +52,9 @@ SIGNATURES = {
     "pk100_local_relpos_attention_tcgen05": [vp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, i32,
                                              i32, i32, i32, vp, vp],
     "pk100_pack_position_heads": [vp, vp, vp],
+    "pk100_prune_2of4_e4m3": [vp, vp, vp, i32, i32],
+    "pk100_compress_2of4_e4m3": [vp, vp, vp, i32, i32],
+    "pk100_decompress_2of4_e4m3": [vp, vp, vp, i32, i32],
     # struct-taking entry points: argtypes are completed in encoder.py / decoder.py
     "pk100_encoder_workspace_bytes": None,
     "pk100_encoder_workspace_carve": None,

@@ -147,6 +147,30 @@ def glu_masked(e, seg_stride=None, valid_rows=None, seg_valid=None):
     return out
 
 
+def prune_2of4_e4m3(dense):
+    """E4M3 bytes [rows, cols] with the two smaller magnitudes of every quartet zeroed
+    (the values the reference's 2:4-sparse FF2 multiplies, kernels/sm89/encoder.cu:685-713)."""
+    rows, cols = dense.shape
+    out = torch.empty_like(dense)
+    L.check(L.lib.pk100_prune_2of4_e4m3(_stream(), _ptr(dense), _ptr(out), rows, cols), "pk100_prune_2of4_e4m3")
+    return out
+
+
+def compress_2of4_e4m3(dense):
+    """The reference's compressed FF2 activation arena: data [rows, cols/2] + metadata [rows, cols/8], flat."""
+    rows, cols = dense.shape
+    out = torch.empty(rows * cols * 5 // 8, dtype=torch.uint8, device=dense.device)
+    L.check(L.lib.pk100_compress_2of4_e4m3(_stream(), _ptr(dense), _ptr(out), rows, cols), "pk100_compress_2of4_e4m3")
+    return out
+
+
+def decompress_2of4_e4m3(flat, rows, cols):
+    out = torch.empty((rows, cols), dtype=torch.uint8, device=flat.device)
+    L.check(L.lib.pk100_decompress_2of4_e4m3(_stream(), _ptr(flat), _ptr(out), rows, cols),
+            "pk100_decompress_2of4_e4m3")
+    return out
+
+
 def depthwise_bn_silu(g, wdw, bn_gamma, bn_beta, bn_mean, bn_var, quantize=False, seg_stride=None,
                       valid_rows=None, seg_valid=None):
     _need(g, torch.float16)

@@ -225,6 +225,58 @@ def compress_fp8_quartet(b4) -> tuple[np.ndarray, int]:
     return np.array(kept, dtype=np.uint8), meta
 
 
+def keep_2of4(dense) -> np.ndarray:
+    """Boolean mask [rows, cols] of the bytes the 2:4 rule keeps: per 4 consecutive columns the
+    two largest 7-bit magnitudes, ties -> lower index (kernels/sm89/encoder.cu:685-704)."""
+    dense = np.asarray(dense, dtype=np.uint8)
+    rows, cols = dense.shape
+    mag = (dense & 127).astype(np.int32).reshape(rows, cols // 4, 4)
+    idx = np.arange(4)
+    # rank[i] = #{j : mag[j] > mag[i] or (mag[j] == mag[i] and j < i)}
+    greater = mag[:, :, None, :] > mag[:, :, :, None]
+    tie_lower = (mag[:, :, None, :] == mag[:, :, :, None]) & (idx[None, None, None, :] < idx[None, None, :, None])
+    rank = (greater | tie_lower).sum(axis=3)
+    return (rank < 2).reshape(rows, cols)
+
+
+def prune_2of4_e4m3(dense) -> np.ndarray:
+    """E4M3 bytes [rows, cols] with the two smaller magnitudes of every quartet set to +0: the
+    values the reference's 2:4-sparse contraction multiplies (`mma.sp`, encoder.cu:706-713)."""
+    dense = np.asarray(dense, dtype=np.uint8)
+    return np.where(keep_2of4(dense), dense, np.uint8(0)).astype(np.uint8)
+
+
+def compress_2of4_e4m3(dense) -> np.ndarray:
+    """The reference's compressed activation arena (encoder.cu:1037-1054; consumer :740-764) as one
+    flat byte array: data `bytes[row * cols/2 + col/2]` (the two kept bytes of a quartet, in index
+    order) followed by metadata `bytes[rows * cols/2 + row * cols/8 + col/8]` (4 bits per quartet:
+    two 2-bit indices, low first; two quartets per byte, low nibble first)."""
+    dense = np.asarray(dense, dtype=np.uint8)
+    rows, cols = dense.shape
+    keep = keep_2of4(dense).reshape(rows, cols // 4, 4)
+    quart = dense.reshape(rows, cols // 4, 4)
+    order = np.argsort(~keep, axis=2, kind="stable")[:, :, :2]          # indices of the kept two, ascending
+    data = np.take_along_axis(quart, order, axis=2).reshape(rows, cols // 2)
+    meta4 = (order[:, :, 0] | (order[:, :, 1] << 2)).astype(np.uint8)   # [rows, cols/4]
+    meta = (meta4[:, 0::2] | (meta4[:, 1::2] << 4)).astype(np.uint8)    # [rows, cols/8]
+    return np.concatenate([data.reshape(-1), meta.reshape(-1)]).astype(np.uint8)
+
+
+def decompress_2of4_e4m3(flat, rows, cols) -> np.ndarray:
+    """Inverse of `compress_2of4_e4m3`: dense E4M3 bytes [rows, cols] with zeros where nothing was kept."""
+    flat = np.asarray(flat, dtype=np.uint8)
+    data = flat[:rows * cols // 2].reshape(rows, cols // 4, 2)
+    meta = flat[rows * cols // 2:rows * cols // 2 + rows * cols // 8].reshape(rows, cols // 8)
+    meta4 = np.empty((rows, cols // 4), dtype=np.uint8)
+    meta4[:, 0::2] = meta & 15
+    meta4[:, 1::2] = meta >> 4
+    out = np.zeros((rows, cols // 4, 4), dtype=np.uint8)
+    r, q = np.meshgrid(np.arange(rows), np.arange(cols // 4), indexing="ij")
+    out[r, q, meta4 & 3] = data[:, :, 0]
+    out[r, q, (meta4 >> 2) & 3] = data[:, :, 1]
+    return out.reshape(rows, cols)
+
+
 # ----------------------------------------------------------------------------
 # Deterministic generator of the reference's micro-benchmarks
 # ----------------------------------------------------------------------------

@@ -108,6 +108,21 @@ def ffn_expand_fp8(xq, wq, w_scales, rows):
     return out
 
 
+def ffn_contract_fp8(hq, wq, w_scales, x16, rows, sparse=False):
+    """launch_ffn_contract_fp8 (src/cuda/encoder.rs:1128-1202) without its weight re-quantisation:
+    pk_sm89_ffn_contract_fp8 on dense E4M3 activations [rows, 4096], or (sparse) pk_sm89_ffn_contract_fp8_sparse
+    on the 2:4-compressed arena (data [rows, 2048] + metadata [rows, 512], `mma.sp`); both add
+    0.5 * acc / 16 * w_scale to the fp16 state [rows, 1024] in place.  Grid (8, ceil(rows/128)) x 256."""
+    out = x16.clone()
+    if sparse:
+        module("encoder").launch("pk_sm89_ffn_contract_fp8_sparse", (8, _cdiv(rows, 128)), (256,),
+                                 2 * (128 * 32 + 128 * 64 + 128 * 8), [hq, wq, w_scales, out, rows, 4096])
+    else:
+        module("encoder").launch("pk_sm89_ffn_contract_fp8", (8, _cdiv(rows, 128)), (256,),
+                                 2 * (128 * 64 + 128 * 64), [hq, wq, w_scales, out, rows])
+    return out
+
+
 def layer_norm_pair(x, gamma, beta, next_gamma, next_beta, rows, padded_rows, inverse_scale=0.0, eps=1e-5):
     """launch_norm_pair (src/cuda/encoder.rs:1394-1433): grid padded_rows x 256.  Returns the fp16
     first output and the second output: fp16 when inverse_scale == 0, else E4M3 bytes."""

@@ -88,6 +88,11 @@ def cases():
     sw["proj_w"] = codec.f16_round(rng.standard_normal((1024, 4096)) * 0.02)
     sw["proj_b"] = (rng.standard_normal(1024) * 0.05).astype(np.float32)
     c["sub"] = dict(w=sw, mel=rng.standard_normal((40, 128)).astype(np.float32), frames=40)
+    rng = np.random.default_rng(124)
+    h = codec.quantize_fp8_fixed(codec.f16_round(np.maximum(rng.standard_normal((40, 4096)), -0.2)), 16.0)
+    h[3, 8:12] = 0x30                                  # equal magnitudes: ties go to the lower index
+    c["sparse24"] = dict(h=h, w=codec.f16_round(rng.standard_normal((1024, 4096)) * 0.02),
+                         x=codec.f16_round(rng.standard_normal((40, 1024))), rows=40)
     return c
 
 
@@ -165,5 +170,23 @@ def main(out_path):
     print("wrote", out_path, {k: v.shape for k, v in g.items()})
 
 
+def main_sparse24(out_path):
+    """Second fixture file (reference_sparse24.npz): pk_sm89_ffn_contract_fp8_sparse (`mma.sp` on the 2:4
+    arena written by the oracle's compressor) and pk_sm89_ffn_contract_fp8 on the pruned dense bytes."""
+    from oracle import refkernels as R
+    from tests.util import dev, dev16, host
+    c = cases()["sparse24"]
+    wq, ws = codec.quantize_rows_fp8(c["w"])
+    flat, pruned = codec.compress_2of4_e4m3(c["h"]), codec.prune_2of4_e4m3(c["h"])
+    g = {"sparse": host(R.ffn_contract_fp8(dev(flat), dev(wq), dev(ws), dev16(c["x"]), c["rows"], sparse=True)).astype(np.float16),
+         "dense_pruned": host(R.ffn_contract_fp8(dev(pruned), dev(wq), dev(ws), dev16(c["x"]), c["rows"])).astype(np.float16),
+         "dense_full": host(R.ffn_contract_fp8(dev(c["h"]), dev(wq), dev(ws), dev16(c["x"]), c["rows"])).astype(np.float16)}
+    np.savez_compressed(out_path, **g)
+    print("wrote", out_path, {k: v.shape for k, v in g.items()})
+
+
 if __name__ == "__main__":
-    main(sys.argv[1])
+    if sys.argv[1] == "sparse24":
+        main_sparse24(sys.argv[2])
+    else:
+        main(sys.argv[1])

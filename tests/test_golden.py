@@ -159,3 +159,21 @@ def test_subsampling_stack():
     assert got.shape == want.shape == (5, 1024)
     assert np.max(np.abs(got - want)) <= 2e-2
     assert float(np.sqrt(np.mean((got - want) ** 2)) / np.sqrt(np.mean(want ** 2))) <= 2e-3
+
+
+def test_sparse_2of4_contract():
+    """pk_sm89_ffn_contract_fp8_sparse (`mma.sp` on the compressed 2:4 arena, kernels/sm89/encoder.cu:685-713,
+    :1087-1095) run on a B200 on the arena the oracle's compressor wrote: equals the oracle's dense sums over
+    the pruned values (so the arena layout and the selection rule are the reference's), equals the reference's
+    dense kernel on the pruned bytes, and differs from the dense kernel on the unpruned bytes."""
+    gold = np.load(HERE / "golden" / "reference_sparse24.npz")
+    c = CASES["sparse24"]
+    wq, ws = codec.quantize_rows_fp8(c["w"])
+    pruned = codec.prune_2of4_e4m3(c["h"])
+    want = O.linear_fp8(pruned, wq, ws, np.float32(1.0 / 16.0), residual16=c["x"], alpha=0.5)
+    sparse = gold["sparse"].astype(np.float32)
+    assert np.max(np.abs(sparse - want)) <= 4e-3
+    assert np.max(np.abs(sparse - gold["dense_pruned"].astype(np.float32))) <= 2e-3
+    full = O.linear_fp8(c["h"], wq, ws, np.float32(1.0 / 16.0), residual16=c["x"], alpha=0.5)
+    assert np.max(np.abs(gold["dense_full"].astype(np.float32) - full)) <= 4e-3
+    assert np.max(np.abs(sparse - full)) > 5e-2          # pruning half the activations is visible

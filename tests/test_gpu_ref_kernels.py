@@ -179,3 +179,37 @@ def test_subsampling_stack(cuda):
     # the reference's own gate for this stage is max abs <= 2.0, nRMSE <= 0.002 (src/cuda/subsampling.rs:375)
     assert np.max(np.abs(got - want)) <= 2e-2
     assert float(np.sqrt(np.mean((got - want) ** 2)) / np.sqrt(np.mean(want ** 2))) <= 2e-3
+
+
+def test_sparse_2of4_contract_matches_reference_mma_sp(pk, cuda):
+    """The reference's 2:4-sparse FF2 (pk_sm89_ffn_contract_fp8_sparse, `mma.sp` on the compressed arena,
+    kernels/sm89/encoder.cu:685-713, :1087-1095) against (a) the oracle: dense float64 sums over the
+    pruned values, (b) this library: compress / decompress / prune bit-exact with the oracle, and
+    decompress + pk100_gemm (dense tcgen05 math on the same values) within one fp16 ulp of the reference."""
+    rng = np.random.default_rng(24)
+    rows = 200
+    h = codec.quantize_fp8_fixed(codec.f16_round(np.maximum(rng.standard_normal((rows, 4096)), -0.2)), 16.0)
+    h[3, 8:12] = 0x30                                   # a quartet of equal magnitudes: ties -> lower index
+    w = codec.f16_round(rng.standard_normal((1024, 4096)) * 0.02)
+    wq, ws = codec.quantize_rows_fp8(w)
+    x = codec.f16_round(rng.standard_normal((rows, 1024)))
+    pruned = codec.prune_2of4_e4m3(h)
+    flat = codec.compress_2of4_e4m3(h)
+    # this library's three format kernels
+    assert np.array_equal(host(pk.ops.prune_2of4_e4m3(dev(h))), pruned)
+    assert np.array_equal(host(pk.ops.compress_2of4_e4m3(dev(h))), flat)
+    assert np.array_equal(host(pk.ops.decompress_2of4_e4m3(dev(flat), rows, 4096)), pruned)
+    # the reference kernels: sparse on the compressed arena == dense on the pruned bytes (same products)
+    ref_sparse = host(R.ffn_contract_fp8(dev(flat), dev(wq), dev(ws), dev16(x), rows, sparse=True))
+    ref_dense = host(R.ffn_contract_fp8(dev(pruned), dev(wq), dev(ws), dev16(x), rows, sparse=False))
+    want = O.linear_fp8(pruned, wq, ws, np.float32(1.0 / 16.0), residual16=x, alpha=0.5)
+    assert np.max(np.abs(ref_sparse - want)) <= 4e-3
+    assert np.max(np.abs(ref_sparse - ref_dense)) <= 2e-3
+    # this library: dense tcgen05 GEMM on the decompressed values
+    dense = pk.ops.decompress_2of4_e4m3(dev(flat), rows, 4096)
+    out = dev16(x)
+    pk.ops.gemm(dense, dev(wq), kind=pk.lib.KIND_E4M3, out=out, row_scale=1.0 / 16.0, col_scales=dev(ws),
+                residual=out, alpha=0.5)
+    got = host(out)
+    assert np.max(np.abs(got - want)) <= 4e-3
+    assert np.max(np.abs(got - ref_sparse)) <= 2e-3

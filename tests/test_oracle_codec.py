@@ -122,3 +122,28 @@ def test_two_four_selection():
     assert list(kept) == [0x38, 0x40] and meta == (0 | (3 << 2))
     kept, meta = codec.compress_fp8_quartet([0x10, 0x10, 0x10, 0x10])
     assert list(kept) == [0x10, 0x10] and meta == (0 | (1 << 2))
+
+
+def test_2of4_format_known_answers_and_round_trip():
+    """kernels/sm89/encoder.cu:685-704 (selection), :1037-1054 (arena layout): the vectorised format
+    functions agree with the scalar quartet rule, the arena has data then metadata, and
+    decompress(compress(x)) == prune(x)."""
+    rng = np.random.default_rng(3)
+    d = rng.integers(0, 256, (7, 64), dtype=np.uint8)
+    d[0, :4] = [0x10, 0x90, 0x10, 0x10]          # equal magnitudes (sign ignored): indices 0 and 1 stay
+    d[1, :4] = [0x01, 0x7E, 0x00, 0xFE]          # 0x7E and 0xFE (magnitude 126) stay
+    keep = codec.keep_2of4(d)
+    assert keep[0, :4].tolist() == [True, True, False, False]
+    assert keep[1, :4].tolist() == [False, True, False, True]
+    assert np.all(keep.reshape(7, 16, 4).sum(axis=2) == 2)
+    flat = codec.compress_2of4_e4m3(d)
+    assert flat.size == 7 * 32 + 7 * 8
+    for r in range(7):
+        for q in range(16):
+            kept, meta = codec.compress_fp8_quartet(d[r, 4 * q:4 * q + 4])
+            assert flat[r * 32 + 2 * q:r * 32 + 2 * q + 2].tolist() == kept.tolist()
+            byte = flat[7 * 32 + r * 8 + q // 2]
+            assert ((byte >> (4 * (q % 2))) & 15) == meta
+    pruned = codec.prune_2of4_e4m3(d)
+    assert np.array_equal(codec.decompress_2of4_e4m3(flat, 7, 64), pruned)
+    assert np.array_equal(pruned[keep], d[keep]) and not pruned[~keep].any()
