@@ -62,7 +62,11 @@ enum {
     PK100_LN_F16 = 0,        /* fp16 */
     PK100_LN_E4M3_FIXED = 1, /* E4M3(y * inv_scale)                          */
     PK100_LN_E4M3_ROW = 2,   /* E4M3(y / s), s = absmax/448 per row (0 -> 1) */
-    PK100_LN_S8_ROW = 3      /* clamp(rne(y / s)), s = absmax/127 per row    */
+    PK100_LN_S8_ROW = 3,     /* clamp(rne(y / s)), s = absmax/127 per row    */
+    PK100_LN_S4_ROW = 4      /* INT4 codes clamp(rne(y / s), -8, 7), s = max(y/7, -y/8) per row (0 -> 1), one
+                              * code per INT8 byte: pk_sm89_layer_norm_quantize_int4_dynamic
+                              * (kernels/sm89/encoder.cu:211-306) without the nibble packing, so that the
+                              * INT4 x INT4 products of its consumer run exactly on kind::i8 */
 };
 /* Weight packing formats of pk100_pack_weight_rows. */
 enum { PK100_PACK_E4M3 = 0, PK100_PACK_S8 = 1, PK100_PACK_S4_ROW = 2, PK100_PACK_S4_G128 = 3 };
@@ -183,6 +187,14 @@ int pk100_pack_weight_rows(void* stream, const void* weight, int n, int k, int l
  * idea of pk_sm89_q4_k_dequantize, kernels/sm89/linear.cu:458-472). */
 int pk100_dequant_w4g128(void* stream, const void* codes, const void* group_scales, int n, int k,
                          void* weight_f16);
+
+/* Packed INT4 codes (two per byte, low nibble = even index, two's complement: the storage of
+ * PK100_PACK_S4_ROW weights and of the reference's INT4 activations, kernels/sm89/encoder.cu:279-290) ->
+ * one INT8 byte per code, the operand form of kind::i8.  The reference's INT4 x INT4 FF1
+ * (pk_sm89_ffn_expand_int4_sparse, mma m16n8k64 s4, :1079-1085) is then pk100_layer_norm mode
+ * PK100_LN_S4_ROW + pk100_gemm kind S8 on the unpacked weight codes (row_scales, col_scales, SiLU,
+ * PK100_OUT_E4M3 x 16) + pk100_compress_2of4_e4m3: the same integer sums, exactly. */
+int pk100_unpack_s4(void* stream, const void* packed, void* codes, long long packed_bytes);
 
 /* 2:4 structured sparsity of E4M3 activations: the input format of the reference's sparse FF2
  * (pk_sm89_ffn_expand_int4_sparse epilogue 7, kernels/sm89/encoder.cu:685-704, :1037-1054, consumed by

@@ -118,6 +118,28 @@ __device__ __forceinline__ void emit_row(const float (&x)[4][8], int mode, float
     float mult = inv_scale;
     bool divide = false;
     float scale = 1.0f;
+    if (mode == PK100_LN_S4_ROW) {
+        // every signed 4-bit code is used: the scale is the larger of max/7 and -min/8
+        float mx = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fmaxf(__fdiv_rn(x[i][j], 7.0f), __fdiv_rn(-x[i][j], 8.0f)));
+        mx = warp_max_all(mx);
+        scale = mx > 0.0f ? mx : 1.0f;
+        if (lane == 0) scales[row] = scale;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t w[2] = {0u, 0u};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int q = max(-8, min(7, __float2int_rn(__fdiv_rn(x[i][j], scale))));
+                w[j / 4] |= static_cast<uint32_t>(q & 255) << (8 * (j % 4));
+            }
+            *reinterpret_cast<uint2*>(o + i * 256 + lane * 8) = make_uint2(w[0], w[1]);
+        }
+        return;
+    }
     if (mode == PK100_LN_E4M3_ROW || mode == PK100_LN_S8_ROW) {
         float mx = 0.0f;
 #pragma unroll
@@ -260,6 +282,30 @@ __global__ void sparse24_kernel(const uint8_t* __restrict__ in, uint8_t* __restr
         const uint32_t meta = (packed[0] >> 16) | ((packed[1] >> 16) << 4) | ((packed[2] >> 16) << 8) |
                               ((packed[3] >> 16) << 12);
         *reinterpret_cast<uint16_t*>(out + data_bytes + row * (cols / 8) + c16 * 2) = static_cast<uint16_t>(meta);
+    }
+}
+
+// Packed INT4 codes (low nibble = even index, two's complement) -> one INT8 byte per code.
+__global__ void unpack_s4_kernel(const uint8_t* __restrict__ packed, int8_t* __restrict__ out, size_t bytes) {
+    const size_t i = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+    if (i + 4 <= bytes) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(packed + i);
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int byte = (w >> (8 * b)) & 255;
+            const int even = (byte & 15) >= 8 ? (byte & 15) - 16 : (byte & 15);
+            const int odd = (byte >> 4) >= 8 ? (byte >> 4) - 16 : (byte >> 4);
+            const uint32_t pair = static_cast<uint32_t>(even & 255) | (static_cast<uint32_t>(odd & 255) << 8);
+            if (b < 2) lo |= pair << (16 * b); else hi |= pair << (16 * (b - 2));
+        }
+        *reinterpret_cast<uint2*>(out + 2 * i) = make_uint2(lo, hi);
+    } else {
+        for (size_t j = i; j < bytes; ++j) {
+            const int byte = packed[j];
+            out[2 * j] = static_cast<int8_t>((byte & 15) >= 8 ? (byte & 15) - 16 : (byte & 15));
+            out[2 * j + 1] = static_cast<int8_t>((byte >> 4) >= 8 ? (byte >> 4) - 16 : (byte >> 4));
+        }
     }
 }
 
@@ -538,8 +584,8 @@ extern "C" int pk100_layer_norm(void* stream, const void* input, const void* gam
                                 const int* seg_valid, float eps) {
     if (!input || !gamma || !beta || !output) return PK100_ERR_NULL;
     if (total_rows <= 0) return total_rows == 0 ? PK100_OK : PK100_ERR_SHAPE;
-    if (seg_stride <= 0 || mode < 0 || mode > PK100_LN_S8_ROW) return PK100_ERR_SHAPE;
-    if ((mode == PK100_LN_E4M3_ROW || mode == PK100_LN_S8_ROW) && !scales) return PK100_ERR_NULL;
+    if (seg_stride <= 0 || mode < 0 || mode > PK100_LN_S4_ROW) return PK100_ERR_SHAPE;
+    if (mode >= PK100_LN_E4M3_ROW && !scales) return PK100_ERR_NULL;
     pk100_launch_chained(layer_norm_kernel, dim3((total_rows + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream),
         static_cast<const __half*>(input), static_cast<const __half*>(gamma),
         static_cast<const __half*>(beta), output, scales, mode, inv_scale, nullptr, nullptr,
@@ -556,8 +602,8 @@ extern "C" int pk100_layer_norm_pair(void* stream, const void* input, const void
     if (!input || !gamma || !beta || !output || !next_gamma || !next_beta || !next_output)
         return PK100_ERR_NULL;
     if (total_rows <= 0) return total_rows == 0 ? PK100_OK : PK100_ERR_SHAPE;
-    if (seg_stride <= 0 || next_mode < 0 || next_mode > PK100_LN_S8_ROW) return PK100_ERR_SHAPE;
-    if ((next_mode == PK100_LN_E4M3_ROW || next_mode == PK100_LN_S8_ROW) && !next_scales)
+    if (seg_stride <= 0 || next_mode < 0 || next_mode > PK100_LN_S4_ROW) return PK100_ERR_SHAPE;
+    if (next_mode >= PK100_LN_E4M3_ROW && !next_scales)
         return PK100_ERR_NULL;
     pk100_launch_chained(layer_norm_kernel, dim3((total_rows + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream),
         static_cast<const __half*>(input), static_cast<const __half*>(gamma),
@@ -615,6 +661,17 @@ extern "C" int pk100_dequant_w4g128(void* stream, const void* codes, const void*
                             static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint8_t*>(codes), static_cast<const __half*>(group_scales), n, k,
         static_cast<__half*>(weight_f16));
+    return pk100_launch_status();
+}
+
+extern "C" int pk100_unpack_s4(void* stream, const void* packed, void* codes, long long packed_bytes) {
+    if (!packed || !codes) return PK100_ERR_NULL;
+    if (packed_bytes < 0) return PK100_ERR_SHAPE;
+    if (packed_bytes == 0) return PK100_OK;
+    if ((reinterpret_cast<uintptr_t>(packed) & 3u) || (reinterpret_cast<uintptr_t>(codes) & 7u)) return PK100_ERR_ALIGN;
+    const size_t threads = (static_cast<size_t>(packed_bytes) + 3) / 4;
+    unpack_s4_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(packed), static_cast<int8_t*>(codes), static_cast<size_t>(packed_bytes));
     return pk100_launch_status();
 }
 

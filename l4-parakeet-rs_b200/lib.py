@@ -52,6 +52,7 @@ SIGNATURES = {
     "pk100_local_relpos_attention_tcgen05": [vp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, i32,
                                              i32, i32, i32, vp, vp],
     "pk100_pack_position_heads": [vp, vp, vp],
+    "pk100_unpack_s4": [vp, vp, vp, i64],
     "pk100_prune_2of4_e4m3": [vp, vp, vp, i32, i32],
     "pk100_compress_2of4_e4m3": [vp, vp, vp, i32, i32],
     "pk100_decompress_2of4_e4m3": [vp, vp, vp, i32, i32],
@@ -121,7 +122,7 @@ KIND_F16, KIND_E4M3, KIND_S8, KIND_F16_W4G128 = 0, 1, 2, 3
 OUT_F16, OUT_F32, OUT_E4M3, OUT_S8 = 0, 1, 2, 3
 ACT_NONE, ACT_SILU, ACT_RELU = 0, 1, 2
 EPI_LINEAR, EPI_GLU, EPI_SPARSE_OUT = 0, 1, 2
-LN_F16, LN_E4M3_FIXED, LN_E4M3_ROW, LN_S8_ROW = 0, 1, 2, 3
+LN_F16, LN_E4M3_FIXED, LN_E4M3_ROW, LN_S8_ROW, LN_S4_ROW = 0, 1, 2, 3, 4
 PACK_E4M3, PACK_S8, PACK_S4_ROW, PACK_S4_G128 = 0, 1, 2, 3
 
 

@@ -65,8 +65,8 @@ def layer_norm(x, gamma, beta, mode=L.LN_F16, inv_scale=0.0, seg_stride=None, va
     if out is None:
         out = torch.empty((rows, 1024), device=x.device,
                           dtype=torch.float16 if mode == L.LN_F16 else
-                          (torch.int8 if mode == L.LN_S8_ROW else torch.uint8))
-    if scales is None and mode in (L.LN_E4M3_ROW, L.LN_S8_ROW):
+                          (torch.int8 if mode in (L.LN_S8_ROW, L.LN_S4_ROW) else torch.uint8))
+    if scales is None and mode in (L.LN_E4M3_ROW, L.LN_S8_ROW, L.LN_S4_ROW):
         scales = torch.empty(rows, device=x.device, dtype=torch.float32)
     L.check(L.lib.pk100_layer_norm(_stream(), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(out),
                                    _ptr(scales), mode, inv_scale, rows, seg_stride, valid_rows,
@@ -86,8 +86,8 @@ def layer_norm_pair(x, gamma, beta, next_gamma, next_beta, next_mode, next_inv_s
     if next_out is None:
         next_out = torch.empty((rows, 1024), device=x.device,
                                dtype=torch.float16 if next_mode == L.LN_F16 else
-                               (torch.int8 if next_mode == L.LN_S8_ROW else torch.uint8))
-    if next_scales is None and next_mode in (L.LN_E4M3_ROW, L.LN_S8_ROW):
+                               (torch.int8 if next_mode in (L.LN_S8_ROW, L.LN_S4_ROW) else torch.uint8))
+    if next_scales is None and next_mode in (L.LN_E4M3_ROW, L.LN_S8_ROW, L.LN_S4_ROW):
         next_scales = torch.empty(rows, device=x.device, dtype=torch.float32)
     L.check(L.lib.pk100_layer_norm_pair(
         _stream(), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(out), _ptr(next_gamma), _ptr(next_beta),
@@ -144,6 +144,13 @@ def glu_masked(e, seg_stride=None, valid_rows=None, seg_valid=None):
     out = torch.empty((rows, 1024), device=e.device, dtype=torch.float16)
     L.check(L.lib.pk100_glu_masked(_stream(), _ptr(e), _ptr(out), rows, seg_stride, valid_rows,
                                    _ptr(seg_valid)), "pk100_glu_masked")
+    return out
+
+
+def unpack_s4(packed):
+    """Packed INT4 codes [..., n/2] (low nibble = even index) -> INT8 codes [..., n]."""
+    out = torch.empty(packed.shape[:-1] + (packed.shape[-1] * 2,), dtype=torch.int8, device=packed.device)
+    L.check(L.lib.pk100_unpack_s4(_stream(), _ptr(packed), _ptr(out), packed.numel()), "pk100_unpack_s4")
     return out
 
 

@@ -101,6 +101,32 @@ def quant_rows_int8_dynamic(y16, rows=None):
     return q, scale
 
 
+def quant_rows_int4_dynamic(y16, rows=None):
+    """Per-row dynamic INT4 of `layer_norm_quantize_dynamic<true>` (kernels/sm89/encoder.cu:266-290):
+    scale = max(v/7, -v/8) over the row (0 -> 1), q = clamp(rne(v/scale), -8, 7).  Returns the codes
+    one per INT8 element (the reference stores them two per byte, low nibble = even feature:
+    `codec.pack_nibbles`) and the scales; rows >= `rows` are zero with scale 1."""
+    y = np.asarray(y16, dtype=F32)
+    rows = y.shape[0] if rows is None else rows
+    top = np.max(np.maximum(y / F32(7.0), -y / F32(8.0)), axis=1)
+    scale = np.where(top > 0, top, F32(1.0)).astype(F32)
+    q = np.clip(codec.rne((y / scale[:, None]).astype(F32)), -8, 7).astype(np.int8)
+    q[rows:] = 0
+    scale[rows:] = 1
+    return q, scale
+
+
+def ff_expand_int4(xq, x_scales, wq, w_scales):
+    """`pk_sm89_ffn_expand_int4_sparse` before its 2:4 compression (kernels/sm89/encoder.cu:1079-1085,
+    epilogue 7 :1001-1022): exact INT32 sums of INT4 x INT4 codes, x row scale x weight scale, SiLU,
+    fp16 rounding, x 16, E4M3.  xq [rows, 1024] and wq [4096, 1024] hold one code per element.
+    Returns the dense E4M3 bytes [rows, 4096] (`codec.compress_2of4_e4m3` gives the kernel's arena)."""
+    acc = accumulate(np.asarray(xq, dtype=np.float64), np.asarray(wq, dtype=np.float64))
+    v = (acc.astype(F32) * np.asarray(x_scales, dtype=F32)[:, None]) * np.asarray(w_scales, dtype=F32)[None, :]
+    h16 = codec.f16_round(silu(v))
+    return codec.e4m3_encode((h16 * F32(16.0)).astype(F32))
+
+
 # ----------------------------------------------------------------------------
 # GEMM with the reference's epilogue algebra
 # ----------------------------------------------------------------------------

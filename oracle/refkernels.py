@@ -108,6 +108,26 @@ def ffn_expand_fp8(xq, wq, w_scales, rows):
     return out
 
 
+def layer_norm_quantize_int4_dynamic(x, gamma, beta, rows, padded_rows, eps=1e-5):
+    """launch_norm_quantize_fp8 with pk_sm89_layer_norm_quantize_int4_dynamic (src/cuda/encoder.rs:1029-1039):
+    packed INT4 codes [padded_rows, 512] and fp32 row scales."""
+    out = torch.zeros((padded_rows, 512), dtype=torch.uint8, device=x.device)
+    scales = torch.zeros(padded_rows, dtype=torch.float32, device=x.device)
+    module("encoder").launch("pk_sm89_layer_norm_quantize_int4_dynamic", (padded_rows,), (256,), 0,
+                             [x, gamma, beta, out, scales, rows, padded_rows, float(eps)])
+    return out, scales
+
+
+def ffn_expand_int4_sparse(xq_packed, x_scales, wq_packed, w_scales, rows):
+    """launch_ffn_expand_fp8 with pk_sm89_ffn_expand_int4_sparse and dynamic row scales
+    (src/cuda/encoder.rs:1040-1050, :1322-1358): INT4 x INT4 `mma m16n8k64 s4`, SiLU -> fp16 -> x 16 -> E4M3,
+    2:4 compression.  Returns the arena as flat bytes: data [rows, 2048] then metadata [rows, 512]."""
+    out = torch.zeros(rows * 2560, dtype=torch.uint8, device=xq_packed.device)
+    module("encoder").launch("pk_sm89_ffn_expand_int4_sparse", (32, _cdiv(rows, 128)), (256,), 32768,
+                             [xq_packed, wq_packed, w_scales, x_scales, out, rows, 8.0 / 448.0, 1])
+    return out
+
+
 def ffn_contract_fp8(hq, wq, w_scales, x16, rows, sparse=False):
     """launch_ffn_contract_fp8 (src/cuda/encoder.rs:1128-1202) without its weight re-quantisation:
     pk_sm89_ffn_contract_fp8 on dense E4M3 activations [rows, 4096], or (sparse) pk_sm89_ffn_contract_fp8_sparse

@@ -213,3 +213,47 @@ def test_sparse_2of4_contract_matches_reference_mma_sp(pk, cuda):
     got = host(out)
     assert np.max(np.abs(got - want)) <= 4e-3
     assert np.max(np.abs(got - ref_sparse)) <= 2e-3
+
+
+def test_int4_ff1_chain_matches_reference_mma_s4(pk, cuda):
+    """The reference's INT4 x INT4 FF1 of its long-audio chain (pk_sm89_layer_norm_quantize_int4_dynamic
+    kernels/sm89/encoder.cu:211-306, pk_sm89_ffn_expand_int4_sparse :1079-1085 with `mma m16n8k64 s4`,
+    SiLU -> fp16 -> x 16 -> E4M3 -> 2:4 arena) run on this GPU, against the oracle and against this
+    library's form of it: LayerNorm mode S4_ROW (one code per byte) -> kind::i8 tcgen05 GEMM on the
+    unpacked weight codes with the E4M3 x 16 output -> 2:4 compression.  Integer sums are exact in
+    both, so the bytes differ only where the fast-math SiLU lands on the other side of a rounding."""
+    rng = np.random.default_rng(31)
+    rows, padded = 130, 256
+    x = codec.f16_round(rng.standard_normal((padded, 1024)) * 1.5)
+    x[rows:] = 0
+    g = codec.f16_round(1 + 0.1 * rng.standard_normal(1024))
+    b = codec.f16_round(0.1 * rng.standard_normal(1024))
+    w = codec.f16_round(rng.standard_normal((4096, 1024)) * 0.02)
+    wq_packed, ws = codec.quantize_rows_int4(w)
+    wq = codec.unpack_nibbles(wq_packed)
+    # activation quantiser: reference kernel == oracle == this library (codes exact up to the
+    # fast-math division of the reference; scales to fp32 rounding)
+    ref_q, ref_s = R.layer_norm_quantize_int4_dynamic(dev16(x), dev16(g), dev16(b), rows, padded)
+    y = O.layer_norm(x, g, b, rows)
+    want_q, want_s = O.quant_rows_int4_dynamic(y, rows)
+    ref_codes = codec.unpack_nibbles(host(ref_q))
+    assert np.allclose(host(ref_s)[:rows], want_s[:rows], rtol=1e-6, atol=0)
+    assert np.mean(ref_codes[:rows] != want_q[:rows]) < 2e-3 and np.max(np.abs(ref_codes[:rows].astype(int) - want_q[:rows])) <= 1
+    got_q, got_s = pk.ops.layer_norm(dev16(x), dev16(g), dev16(b), pk.lib.LN_S4_ROW, valid_rows=rows)
+    assert np.allclose(host(got_s)[:rows], want_s[:rows], rtol=1e-6, atol=0)
+    assert np.mean(host(got_q)[:rows] != want_q[:rows]) < 2e-3 and not host(got_q)[rows:].any()
+    assert np.array_equal(host(pk.ops.unpack_s4(dev(wq_packed))), wq)
+    # expand on IDENTICAL codes (the reference's): reference arena vs oracle vs this library
+    arena = host(R.ffn_expand_int4_sparse(ref_q, ref_s, dev(wq_packed), dev(ws), rows))
+    want_dense = O.ff_expand_int4(ref_codes[:rows], host(ref_s)[:rows], wq, ws)
+    ref_dense = codec.decompress_2of4_e4m3(arena, rows, 4096)
+    want_pruned = codec.prune_2of4_e4m3(want_dense)
+    assert np.mean(ref_dense != want_pruned) < 5e-3
+    codes8 = dev(ref_codes[:rows].astype(np.int8))
+    out = torch.empty((rows, 4096), dtype=torch.uint8, device=cuda)
+    pk.ops.gemm(codes8, pk.ops.unpack_s4(dev(wq_packed)), kind=pk.lib.KIND_S8, out=out, out_type=pk.lib.OUT_E4M3,
+                out_scale=16.0, row_scales=ref_s[:rows].contiguous(), col_scales=dev(ws), act=pk.lib.ACT_SILU)
+    got_dense = host(out)
+    assert np.mean(got_dense != want_dense) < 5e-3
+    got_arena = host(pk.ops.compress_2of4_e4m3(out))
+    assert np.mean(got_arena[:rows * 2048] != arena[:rows * 2048]) < 1e-2

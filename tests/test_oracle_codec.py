@@ -147,3 +147,17 @@ def test_2of4_format_known_answers_and_round_trip():
     pruned = codec.prune_2of4_e4m3(d)
     assert np.array_equal(codec.decompress_2of4_e4m3(flat, 7, 64), pruned)
     assert np.array_equal(pruned[keep], d[keep]) and not pruned[~keep].any()
+
+
+def test_int4_row_quantiser_uses_every_code():
+    """kernels/sm89/encoder.cu:266-290: scale = max(v/7, -v/8), so +7 and -8 are both reachable."""
+    from oracle import ops as O
+    y = np.zeros((3, 1024), np.float32)
+    y[0, :4] = [7.0, -8.0, 3.5, -0.4]
+    y[1, :3] = [-4.0, 1.0, 0.26]                   # scale 0.5: -8, 2, rne(0.52) = 1
+    q, s = O.quant_rows_int4_dynamic(y, rows=2)
+    assert s.tolist() == [1.0, 0.5, 1.0]
+    assert q[0, :4].tolist() == [7, -8, 4, 0] and q[1, :3].tolist() == [-8, 2, 1]
+    assert not q[2].any()
+    packed = codec.pack_nibbles(q)
+    assert packed[0, 0] == (7 | (8 << 4)) and np.array_equal(codec.unpack_nibbles(packed), q)
