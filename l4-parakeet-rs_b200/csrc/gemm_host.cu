@@ -336,9 +336,18 @@ extern "C" int pk100_gemm(void* stream_v, const pk100_gemm_args* a) {
     p.status = a->status;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
-    // Tile width: 256 columns unless that leaves too few tiles to fill the SMs.
+    // Tile width: the one with the shorter schedule, counting whole waves over the CTAs available and a
+    // 128-column tile as 0.7 of a 256-column one (measured: at 3072 x 1024 one wave of 96 wide tiles
+    // takes 17.6 us against 20.3 us for two waves of 192 narrow ones; at 6144 x 1024 two wide waves
+    // take 24.3 us against 28.7 us for three narrow ones; a single partial wave prefers the narrow tile).
     const int m_tiles = (a->m + kBlockM - 1) / kBlockM;
-    bool narrow = (a->n % 256 != 0) || (m_tiles * (a->n / 256) < sm_count());
+    bool narrow = a->n % 256 != 0;
+    if (!narrow) {
+        const long long ctas = cta_budget(*a);
+        const long long wide = (static_cast<long long>(m_tiles) * (a->n / 256) + ctas - 1) / ctas;
+        const long long thin = (static_cast<long long>(m_tiles) * (a->n / 128) + ctas - 1) / ctas;
+        narrow = thin * 7 < wide * 10;
+    }
 
     if (w4) return launch_w4(*a, p, stream);
     switch (a->epilogue) {
