@@ -97,6 +97,34 @@ def test_out_proj_resident_forms_give_the_same_bits(pk, cuda):
     assert np.any(outs[0] != 0)
 
 
+def test_dependent_launch_switch_changes_no_bit(pk, cuda):
+    """Programmatic dependent launch (each kernel of the block chain resident while its predecessor
+    drains, waiting for the whole predecessor grid before its first global access) against plain
+    stream order: three layers, two utterances, several runs each, every output bit equal."""
+    rows, valid = 2 * 256, [256, 77]
+    x = _input(11, rows, rows)
+    enc = pk.encoder.EncoderLayers(cuda)
+    for layer in range(3):
+        enc.add_layer(pk.synth.layer_weights(5, layer, randomize_norms=True), 0.05, 0.05)
+    arena, ws = enc.make_workspace(rows)
+    sv = torch.tensor(valid, dtype=torch.int32, device=cuda)
+    outs = []
+    try:
+        for enable in (1, 0, 1):
+            pk.lib.lib.pk100_set_dependent_launch(enable)
+            for _ in range(3):
+                a, b = dev16(x), torch.zeros((rows, 1024), dtype=torch.float16, device=cuda)
+                out = enc.run(a, b, ws, 2, 256, 256, seg_valid=sv)
+                torch.cuda.synchronize()
+                assert enc.status(arena, ws) == 0
+                outs.append(host(out).copy())
+    finally:
+        pk.lib.lib.pk100_set_dependent_launch(1)
+    for o in outs[1:]:
+        assert np.array_equal(o.view(np.uint16), outs[0].view(np.uint16))
+    assert np.any(outs[0] != 0)
+
+
 def test_packed_weights_match_oracle(pk, cuda):
     """Load-time packing on the GPU is bit-identical to the CPU twin, including the
     position table (fp16 GEMM of the sinusoid) up to fp16 rounding."""

@@ -110,3 +110,27 @@ def test_gloo_row_gather_and_stitch_world_size_2():
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
+
+
+def test_pipeline_plan_of_encode_and_decode_groups(pk):
+    """PipelineEngine._plan: the utterances cut into decode groups, consecutive decode groups joined
+    into encode groups; every utterance exactly once, group sizes differ by at most one."""
+    from types import SimpleNamespace
+    plan_of = pk.pipeline.PipelineEngine._plan
+    split = pk.pipeline.PipelineEngine._split
+    for utterances in range(1, 9):
+        for enc_groups in (1, 2, 3):
+            for dec_groups in (1, 2, 4, 7, 8):
+                eng = SimpleNamespace(encode_groups=enc_groups, decode_groups=max(enc_groups, dec_groups), _split=split)
+                plan = plan_of(eng, utterances)
+                decs = [d for _, ds in plan for d in ds]
+                assert decs[0][0] == 0 and decs[-1][1] == utterances
+                assert all(a[1] == b[0] for a, b in zip(decs, decs[1:]))
+                assert len(decs) == min(eng.decode_groups, utterances) and len(plan) == min(enc_groups, len(decs))
+                sizes = [b - a for a, b in decs]
+                assert max(sizes) - min(sizes) <= 1 and min(sizes) >= 1
+                for (e0, e1), ds in plan:
+                    assert ds[0][0] == e0 and ds[-1][1] == e1
+    eng = SimpleNamespace(encode_groups=1, decode_groups=7, _split=split)
+    assert plan_of(eng, 8) == [((0, 8), [(0, 2), (2, 3), (3, 4), (4, 5), (5, 6), (6, 7), (7, 8)])]
+    assert plan_of(eng, 8, 4)[0][1] == [(0, 2), (2, 4), (4, 6), (6, 8)]
