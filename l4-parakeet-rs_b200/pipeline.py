@@ -274,8 +274,9 @@ class PipelineEngine:
         self.run_resident(utterances)
         self.counts_host.copy_(self.counts, non_blocking=True)
         self.tokens_host.copy_(self.tokens, non_blocking=True)
+        self._queue_status()
         torch.cuda.current_stream().synchronize()
-        status = self.status()
+        status = self._queued_status()
         if status != 0:
             raise RuntimeError(f"libpk100 reported an expired bounded wait (status {status})")
         counts = self.counts_host.numpy()
@@ -386,8 +387,9 @@ class PipelineEngine:
         self.run_resident(utterances)
         self.counts_host.copy_(self.counts, non_blocking=True)
         self.tokens_host.copy_(self.tokens, non_blocking=True)
+        self._queue_status()
         torch.cuda.current_stream().synchronize()
-        status = self.status()
+        status = self._queued_status()
         if status != 0:
             raise RuntimeError(f"libpk100 reported an expired bounded wait (status {status})")
         counts = self.counts_host.numpy()
@@ -399,6 +401,29 @@ class PipelineEngine:
         """True when an FF hidden activation exceeded the INT8 range (x 1/32) since the engine was
         built: harmless for N(0, 0.02) weights, a sign of a wrong hidden scale on a real checkpoint."""
         return bool(self.enc.status(self.arena, self.ws) & self.HIDDEN_SATURATED)
+
+    def _status_words(self):
+        """Device int32 views of every status word: encoder, subsampling, then the decoders'."""
+        off = self.ws.status - self.arena.data_ptr()
+        extra = self.dec_scratch[1:] + (self._second_slot.dec_scratch if hasattr(self, "_second_slot") else [])
+        return [self.arena[off:off + 4].view(torch.int32), self.sub.status, self.dec.status] + [s[1] for s in extra]
+
+    def _queue_status(self):
+        """Copies the status words to pinned host memory on the current stream, behind the request
+        (one synchronise then serves the tokens and the status: no further device round trips)."""
+        words = self._status_words()
+        if getattr(self, "_status_host", None) is None or self._status_host.numel() != len(words):
+            self._status_host = torch.zeros(len(words), dtype=torch.int32).pin_memory()
+        for i, w in enumerate(words):
+            self._status_host[i:i + 1].copy_(w, non_blocking=True)
+
+    def _queued_status(self):
+        """After a synchronise: what `status()` would return, from the words `_queue_status` copied."""
+        h = self._status_host.tolist()
+        dec = 0
+        for v in h[2:]:
+            dec |= v & ~4                               # bit 4: a decode round had only NaN scores
+        return (h[0] & ~self.HIDDEN_SATURATED) | h[1] | dec
 
     def status(self):
         """Non-zero when a bounded wait expired inside a kernel (saturation is reported separately)."""
