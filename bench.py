@@ -57,6 +57,9 @@ def parse_args():
     ap.add_argument("--out-proj", default="f16", choices=["f16", "int4"],
                     help="resident form of the INT4-g128 out-proj weights: expanded fp16 (default) or packed codes "
                          "dequantised inside the GEMM; same bits")
+    ap.add_argument("--subsampling", default="fp16", choices=["fp16", "fp8"],
+                    help="pointwise / projection GEMMs of the subsampling stage: fp16 (default) or the reference's "
+                         "long-request variant with E4M3 activations and weights")
     ap.add_argument("--plain-launch", action="store_true",
                     help="launch the kernels of the block chain in plain stream order (no programmatic dependent launch)")
     ap.add_argument("--cta-pairs", action="store_true",
@@ -645,7 +648,7 @@ def main():
     eng = pk.pipeline.PipelineEngine(device, layers=args.layers, decoder_layers=args.decoder_layers,
                                      seed=SEED, max_utterances=per_gpu, mel_frames=MEL_FRAMES,
                                      decode_groups=args.decode_groups, encode_groups=args.encode_groups,
-                                     out_proj_resident=args.out_proj)
+                                     out_proj_resident=args.out_proj, subsampling_precision=args.subsampling)
     mel_host = torch.from_numpy(np.stack([pk.synth.mel_input(100 + u, MEL_FRAMES) for u in my_utts])).pin_memory()
     eng.mel_dev.copy_(mel_host)
     cache = Path(args.tau_cache) if args.tau_cache else None

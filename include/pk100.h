@@ -490,6 +490,25 @@ int pk100_run_subsampling(void* stream, const pk100_subsampling_weights* weights
                           int utterances, int frames, const int* mel_frames, void* workspace,
                           void* output, int seg_stride, int* status);
 
+/* The reference's variant for requests of 1024 output frames or more (FP8_MIN_FRAMES, src/cuda/subsampling.rs:22,
+ * :551-630, :718-775): the fp16 output of the first depthwise convolution is quantised per row to E4M3
+ * (absmax / 448; pk_sm89_subsample_depthwise_fp8 kernels/sm89/subsampling.cu:126-165) and its pointwise layer
+ * runs E4M3 x E4M3 against per-row E4M3 weights (pk_sm89_subsample_pointwise_fp8 kernels/sm89/encoder.cu:1113-1119);
+ * the second stage stays fp16; the flattened rows are quantised per row (pk_sm89_quantize_ffn_contract :1161-1180)
+ * and projected E4M3 x E4M3 (pk_sm89_subsample_projection_fp8 :1105-1111).  The packed weights come from
+ * pk100_pack_weight_rows(PK100_PACK_E4M3) of pw1_w and proj_w once at load (the reference re-quantises them in
+ * every request).  Workspace: pk100_subsampling_fp8_workspace_bytes. */
+typedef struct pk100_subsampling_fp8 {
+    const void* pw1_q;  const float* pw1_scales;    /* E4M3 [256,256], fp32 [256] */
+    const void* proj_q; const float* proj_scales;   /* E4M3 [1024,4096], fp32 [1024] */
+} pk100_subsampling_fp8;
+
+long long pk100_subsampling_fp8_workspace_bytes(int utterances, int frames, int seg_stride);
+
+int pk100_run_subsampling_fp8(void* stream, const pk100_subsampling_weights* weights,
+                              const pk100_subsampling_fp8* fp8, const float* mel, int utterances, int frames,
+                              const int* mel_frames, void* workspace, void* output, int seg_stride, int* status);
+
 /* ------------------------------------------------------------------------
  * ".pkl4" weight artifact: reader and layout packers (host code, no GPU).
  * Replaces AotArtifactIndex::open / read_f32 and validate_header

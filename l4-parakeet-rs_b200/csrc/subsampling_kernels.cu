@@ -199,10 +199,37 @@ extern "C" long long pk100_subsampling_workspace_bytes(int utterances, int frame
            2 * up256(u * c.f3 * 16 * 256 * 2) + up256(u * seg_stride * 4096LL * 2) + 256;
 }
 
+extern "C" long long pk100_subsampling_fp8_workspace_bytes(int utterances, int frames, int seg_stride) {
+    if (utterances <= 0 || frames <= 0 || seg_stride <= 0) return 0;
+    const Caps c = caps(frames);
+    const long long u = utterances;
+    return pk100_subsampling_workspace_bytes(utterances, frames, seg_stride) +
+           up256(u * c.f2 * 32 * 256) + up256(u * c.f2 * 32 * 4) + up256(u * seg_stride * 4096LL) + up256(u * seg_stride * 4);
+}
+
+static int run_subsampling(void* stream_v, const pk100_subsampling_weights* w, const pk100_subsampling_fp8* q,
+                           const float* mel, int utterances, int frames, const int* mel_frames, void* workspace,
+                           void* output, int seg_stride, int* status);
+
 extern "C" int pk100_run_subsampling(void* stream_v, const pk100_subsampling_weights* w,
                                      const float* mel, int utterances, int frames,
                                      const int* mel_frames, void* workspace, void* output,
                                      int seg_stride, int* status) {
+    return run_subsampling(stream_v, w, nullptr, mel, utterances, frames, mel_frames, workspace, output, seg_stride,
+                           status);
+}
+
+extern "C" int pk100_run_subsampling_fp8(void* stream_v, const pk100_subsampling_weights* w,
+                                         const pk100_subsampling_fp8* q, const float* mel, int utterances,
+                                         int frames, const int* mel_frames, void* workspace, void* output,
+                                         int seg_stride, int* status) {
+    if (!q || !q->pw1_q || !q->pw1_scales || !q->proj_q || !q->proj_scales) return PK100_ERR_NULL;
+    return run_subsampling(stream_v, w, q, mel, utterances, frames, mel_frames, workspace, output, seg_stride, status);
+}
+
+static int run_subsampling(void* stream_v, const pk100_subsampling_weights* w, const pk100_subsampling_fp8* q,
+                           const float* mel, int utterances, int frames, const int* mel_frames, void* workspace,
+                           void* output, int seg_stride, int* status) {
     if (!w || !mel || !workspace || !output) return PK100_ERR_NULL;
     if (!w->conv0_w || !w->conv0_b || !w->dw1_w || !w->dw1_b || !w->pw1_w || !w->pw1_b || !w->dw2_w ||
         !w->dw2_b || !w->pw2_w || !w->pw2_b || !w->proj_w || !w->proj_b)
@@ -221,6 +248,12 @@ extern "C" int pk100_run_subsampling(void* stream_v, const pk100_subsampling_wei
     __half* s4 = reinterpret_cast<__half*>(take(u * c.f3 * 16 * 256 * 2));
     __half* s5 = reinterpret_cast<__half*>(take(u * c.f3 * 16 * 256 * 2));
     __half* flat = reinterpret_cast<__half*>(take(u * seg_stride * 4096LL * 2));
+    take(256);                                              // (slack counted by the fp16 size function)
+    // E4M3 variant: quantised rows of the first depthwise output and of the flattened features
+    uint8_t* q2 = q ? reinterpret_cast<uint8_t*>(take(u * c.f2 * 32 * 256)) : nullptr;
+    float* q2_scales = q ? reinterpret_cast<float*>(take(u * c.f2 * 32 * 4)) : nullptr;
+    uint8_t* qflat = q ? reinterpret_cast<uint8_t*>(take(u * seg_stride * 4096LL)) : nullptr;
+    float* qflat_scales = q ? reinterpret_cast<float*>(take(u * seg_stride * 4)) : nullptr;
 
     subsample_first_fused_kernel<<<dim3(c.f2, utterances), 256, 0, stream>>>(
         mel, static_cast<const __half*>(w->conv0_w), static_cast<const __half*>(w->conv0_b),
@@ -235,7 +268,16 @@ extern "C" int pk100_run_subsampling(void* stream_v, const pk100_subsampling_wei
     a.a = s2; a.lda = 256; a.b = w->pw1_w; a.ldb = 256;
     a.row_scale = 1.0f; a.alpha = 1.0f; a.bias = w->pw1_b; a.act = PK100_ACT_RELU;
     a.out = s3; a.ld_out = 256; a.out_type = PK100_OUT_F16; a.out_scale = 1.0f; a.status = status;
-    if ((rc = pk100_gemm(stream, &a)) != PK100_OK) return rc;
+    if (q != nullptr) {
+        // per-row E4M3 of the fp16 depthwise output (absmax / 448), E4M3 x E4M3 pointwise layer
+        if ((rc = pk100_pack_weight_rows(stream, s2, a.m, 256, 256, PK100_PACK_E4M3, q2, q2_scales, nullptr)) != PK100_OK)
+            return rc;
+        pk100_gemm_args f = a;
+        f.kind = PK100_KIND_E4M3; f.a = q2; f.b = q->pw1_q; f.row_scales = q2_scales; f.col_scales = q->pw1_scales;
+        if ((rc = pk100_gemm(stream, &f)) != PK100_OK) return rc;
+    } else if ((rc = pk100_gemm(stream, &a)) != PK100_OK) {
+        return rc;
+    }
 
     subsample_depthwise_kernel<<<dim3(16 / kGroup, c.f3, utterances), 256, 0, stream>>>(
         s3, static_cast<const __half*>(w->dw2_w), static_cast<const __half*>(w->dw2_b), s4, c.f2, 32,
@@ -253,5 +295,12 @@ extern "C" int pk100_run_subsampling(void* stream_v, const pk100_subsampling_wei
     a.m = static_cast<int>(u * seg_stride); a.n = 1024; a.k = 4096;
     a.a = flat; a.lda = 4096; a.b = w->proj_w; a.ldb = 4096; a.bias = w->proj_b; a.act = PK100_ACT_NONE;
     a.out = output; a.ld_out = 1024;
+    if (q != nullptr) {
+        if ((rc = pk100_pack_weight_rows(stream, flat, a.m, 4096, 4096, PK100_PACK_E4M3, qflat, qflat_scales,
+                                         nullptr)) != PK100_OK)
+            return rc;
+        a.kind = PK100_KIND_E4M3; a.a = qflat; a.b = q->proj_q; a.row_scales = qflat_scales;
+        a.col_scales = q->proj_scales;
+    }
     return pk100_gemm(stream, &a);
 }

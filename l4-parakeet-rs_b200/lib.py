@@ -91,6 +91,8 @@ SIGNATURES = {
     "pk100_mel_frontend": None,
     "pk100_subsampling_workspace_bytes": None,
     "pk100_run_subsampling": None,
+    "pk100_subsampling_fp8_workspace_bytes": None,
+    "pk100_run_subsampling_fp8": None,
     "pk100_launch_count": None,
 }
 

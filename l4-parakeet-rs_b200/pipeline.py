@@ -65,7 +65,8 @@ class _Slot:
 
 class PipelineEngine:
     def __init__(self, device, layers=24, decoder_layers=2, seed=4, max_utterances=8, mel_frames=6000,
-                 randomize_norms=False, decode_groups=None, out_proj_resident="f16", encode_groups=1):
+                 randomize_norms=False, decode_groups=None, out_proj_resident="f16", encode_groups=1,
+                 subsampling_precision="fp16"):
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
         self.max_utterances = max_utterances
@@ -78,7 +79,7 @@ class PipelineEngine:
         self.frames_out = sub_mod.output_frames(mel_frames)
         self.seg_stride = seg_stride_for(self.frames_out)
         self.rows = max_utterances * self.seg_stride
-        self.sub = sub_mod.Subsampling(synth.subsampling_weights(seed), self.device)
+        self.sub = sub_mod.Subsampling(synth.subsampling_weights(seed), self.device, precision=subsampling_precision)
         self.enc = enc_mod.EncoderLayers(self.device, out_proj_resident=out_proj_resident)
         for l in range(layers):
             self.enc.add_layer(synth.layer_weights(seed, l, randomize_norms=randomize_norms))

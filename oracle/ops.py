@@ -478,16 +478,40 @@ def _conv_s2(x, w, b):
     return acc
 
 
-def subsampling(mel, w):
+def subsampling(mel, w, fp8=False, collect=None):
     """mel fp32 [frames, 128] -> fp16 [ceil(frames/8), 1024]
     (src/cuda/subsampling.rs:436-804 without the 256-frame tiling, which only bounds
-    memory; kernels/sm89/subsampling.cu)."""
+    memory; kernels/sm89/subsampling.cu).
+    fp8: the reference's variant for requests of 1024 output frames or more (subsampling.rs:22,
+    :551-630, :718-775): the first depthwise output (rounded to fp16 first, subsampling.cu:133-134) is
+    quantised per row to E4M3 (absmax / 448) and its pointwise layer runs as an E4M3 GEMM against
+    per-row E4M3 weights (pk_sm89_quantize_rows256, pk_sm89_subsample_pointwise_fp8: + bias, ReLU);
+    the second stage stays fp16; the flattened rows are quantised per row (pk_sm89_quantize_ffn_contract)
+    and the projection is an E4M3 GEMM (pk_sm89_subsample_projection_fp8: + bias)."""
     x = f16_round(np.maximum(_conv_s2(np.asarray(mel, dtype=F32)[:, :, None], w["conv0_w"].reshape(256, 3, 3),
                                       w["conv0_b"]), 0))
     for stage in (1, 2):
         x = f16_round(_conv_s2(x, w[f"dw{stage}_w"].reshape(256, 3, 3), w[f"dw{stage}_b"]))
         f, t, c = x.shape
-        x = linear_f16(x.reshape(f * t, c), w[f"pw{stage}_w"], bias=w[f"pw{stage}_b"], act=2).reshape(f, t, c)
+        rows = x.reshape(f * t, c)
+        if fp8 and stage == 1:
+            xq, xs = codec.quantize_rows_fp8(rows)
+            wq, ws = codec.quantize_rows_fp8(w["pw1_w"])
+            if collect is not None:
+                collect.update(dw1_q=xq, dw1_s=xs)
+            y = f16_round(epilogue(accumulate(codec.e4m3_decode(xq), codec.e4m3_decode(wq)), xs[:, None], ws,
+                                   w["pw1_b"], act=2))
+        else:
+            y = linear_f16(rows, w[f"pw{stage}_w"], bias=w[f"pw{stage}_b"], act=2)
+        x = y.reshape(f, t, c)
+        if collect is not None:
+            collect[f"pw{stage}"] = y
     f, t, c = x.shape                                   # [F3, 16, 256]
     flat = np.ascontiguousarray(x.transpose(0, 2, 1)).reshape(f, c * t)   # channel*16 + feature
-    return linear_f16(flat, w["proj_w"], bias=w["proj_b"])
+    if not fp8:
+        return linear_f16(flat, w["proj_w"], bias=w["proj_b"])
+    fq, fs = codec.quantize_rows_fp8(flat)
+    pq, ps = codec.quantize_rows_fp8(w["proj_w"])
+    if collect is not None:
+        collect.update(flat_q=fq, flat_s=fs)
+    return f16_round(epilogue(accumulate(codec.e4m3_decode(fq), codec.e4m3_decode(pq)), fs[:, None], ps, w["proj_b"]))

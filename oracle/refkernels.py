@@ -264,6 +264,42 @@ def subsample_depthwise(x, weight, bias, in_frames, in_features, pad_rows_to=16)
     return out
 
 
+def subsample_depthwise_fp8(x, weight, bias, in_frames, in_features, pad_rows_to=16):
+    """launch of pk_sm89_subsample_depthwise_fp8 (src/cuda/subsampling.rs:583-608): the depthwise conv with
+    its output rounded to fp16, then quantised per row (256 channels) to E4M3 with scale absmax / 448.
+    Returns (bytes [rows, 256], fp32 scales [rows]); rows padded with zero bytes / zero scales."""
+    f_out, feat = _cdiv(in_frames, 2), _cdiv(in_features, 2)
+    rows = _cdiv(f_out * feat, pad_rows_to) * pad_rows_to
+    out = torch.zeros((rows, 256), dtype=torch.uint8, device=x.device)
+    scales = torch.zeros(rows, dtype=torch.float32, device=x.device)
+    module("subsampling").launch("pk_sm89_subsample_depthwise_fp8", (_cdiv(feat, 8), f_out), (256,), 0,
+                                 [x, weight, bias, out, 0, in_frames, in_features, 0, f_out, feat, scales])
+    return out, scales
+
+
+def quantize_rows_fp8(x16, width):
+    """pk_sm89_quantize_rows256 / pk_sm89_quantize_ffn_contract (kernels/sm89/encoder.cu:1150-1180): one CTA per
+    row of 256 or 4096 fp16 values -> E4M3 bytes and the fp32 scale absmax / 448 (0 -> 1)."""
+    rows = x16.shape[0]
+    out = torch.empty((rows, width), dtype=torch.uint8, device=x16.device)
+    scales = torch.empty(rows, dtype=torch.float32, device=x16.device)
+    name = {256: "pk_sm89_quantize_rows256", 4096: "pk_sm89_quantize_ffn_contract"}[width]
+    module("encoder").launch(name, (rows,), (256,), 0, [x16, out, scales])
+    return out, scales
+
+
+def subsample_linear_fp8(xq, x_scales, wq, w_scales, bias, rows, projection=False):
+    """pk_sm89_subsample_pointwise_fp8 (K = N = 256, + bias, ReLU) or pk_sm89_subsample_projection_fp8
+    (K = 4096, N = 1024, + bias): E4M3 x E4M3 with per-row activation scales (kernels/sm89/encoder.cu:1105-1119;
+    launches src/cuda/subsampling.rs:613-630, :757-775: grid (N/128, ceil(rows/128)) x 256, 32768 B)."""
+    n = 1024 if projection else 256
+    out = torch.zeros((rows, n), dtype=torch.float16, device=xq.device)
+    name = "pk_sm89_subsample_projection_fp8" if projection else "pk_sm89_subsample_pointwise_fp8"
+    module("encoder").launch(name, (n // 128, _cdiv(rows, 128)), (256,), 32768,
+                             [xq, wq, w_scales, x_scales, bias, out, rows])
+    return out
+
+
 def subsample_flatten(x, frames, padded_frames, features, valid_frames):
     """launch_flatten: [frames * features, 256] -> [padded_frames, 256 * features], column =
     channel * features + feature; rows >= valid_frames are zero."""
@@ -294,6 +330,31 @@ def subsampling(mel, w, frames):
     flat = subsample_flatten(x, f3, padded, 16, f3)
     stages["flat"] = flat
     out = fp16_linear(flat, w["proj_w"], w["proj_b"], None, padded, 1024, 4096)
+    return stages, out[:f3]
+
+
+def subsampling_fp8(mel, w, frames):
+    """run_subsampling for a request of 1024 output frames or more, restated on one tile (the FP8 branches
+    of src/cuda/subsampling.rs:551-630 and :718-775): the first depthwise stage quantised per row with an
+    E4M3 pointwise layer, the second stage in fp16, the flattened rows quantised per row and projected in
+    E4M3.  Weights are quantised per row by the reference's own kernels, as it does in every request."""
+    stages = {}
+    f1, f2, f3 = _cdiv(frames, 2), _cdiv(_cdiv(frames, 2), 2), _cdiv(_cdiv(_cdiv(frames, 2), 2), 2)
+    x = subsample_first(mel, w["conv0_w"], w["conv0_b"], frames)
+    xq, xs = subsample_depthwise_fp8(x, w["dw1_w"], w["dw1_b"], f1, 64, pad_rows_to=128)
+    stages["dw1_q"], stages["dw1_s"] = xq, xs
+    wq, ws = quantize_rows_fp8(w["pw1_w"], 256)
+    x = subsample_linear_fp8(xq, xs, wq, ws, w["pw1_b"], xq.shape[0])
+    stages["pw1"] = x
+    x = subsample_depthwise(x, w["dw2_w"], w["dw2_b"], f2, 32)
+    x = fp16_linear(x, w["pw2_w"], w["pw2_b"], None, x.shape[0], 256, 256, 1.0, 0.0, 2)
+    stages["pw2"] = x
+    padded = _cdiv(f3, 128) * 128
+    flat = subsample_flatten(x, f3, padded, 16, f3)
+    fq, fs = quantize_rows_fp8(flat, 4096)
+    stages["flat_q"], stages["flat_s"] = fq, fs
+    pq, ps = quantize_rows_fp8(w["proj_w"], 4096)
+    out = subsample_linear_fp8(fq, fs, pq, ps, w["proj_b"], padded, projection=True)
     return stages, out[:f3]
 
 

@@ -257,3 +257,41 @@ def test_int4_ff1_chain_matches_reference_mma_s4(pk, cuda):
     assert np.mean(got_dense != want_dense) < 5e-3
     got_arena = host(pk.ops.compress_2of4_e4m3(out))
     assert np.mean(got_arena[:rows * 2048] != arena[:rows * 2048]) < 1e-2
+
+
+def test_subsampling_fp8_variant(pk, cuda):
+    """The reference's subsampling for requests of 1024 output frames or more (its FP8 kernels:
+    pk_sm89_subsample_depthwise_fp8, _quantize_rows256, _subsample_pointwise_fp8, _quantize_ffn_contract,
+    _subsample_projection_fp8; src/cuda/subsampling.rs:551-630, :718-775) run on this GPU, against the oracle
+    (`subsampling(..., fp8=True)`) and against pk100_run_subsampling_fp8."""
+    if not R.subsampling_available():
+        pytest.skip("subsampling.cubin was not built")
+    frames = 203
+    w = pk.synth.subsampling_weights(2)
+    mel = pk.synth.mel_input(31, frames)
+    dw = {k: (dev(np.ascontiguousarray(v, dtype=np.float32)) if k in ("pw1_b", "pw2_b", "proj_b") else dev16(v))
+          for k, v in w.items()}
+    stages, ref_out = R.subsampling_fp8(dev(mel), dw, frames)
+    info = {}
+    want = O.subsampling(mel, w, fp8=True, collect=info)
+    rows1 = info["dw1_q"].shape[0]
+    # the quantised rows of the first depthwise stage: scales to fp32 rounding, bytes up to roundings of the
+    # reference's fast-math division
+    assert np.allclose(host(stages["dw1_s"])[:rows1], info["dw1_s"], rtol=1e-6, atol=0)
+    assert np.mean(host(stages["dw1_q"])[:rows1] != info["dw1_q"]) < 5e-3
+    ref = host(ref_out)
+    assert ref.shape == want.shape
+    # tolerance: an E4M3 byte that rounds the other way (the reference divides with fast math) is a 6 % step
+    # of that activation, so the outputs agree to nRMSE 1e-2, not to the 2e-3 of the fp16 stack; the two
+    # variants themselves are 5e-2 apart, so the comparison is not vacuous
+    nr = lambda a, b: float(np.sqrt(np.mean((a - b) ** 2)) / np.sqrt(np.mean(b ** 2)))
+    assert np.max(np.abs(ref - want)) <= 4e-2 and nr(ref, want) <= 1e-2
+    plain = O.subsampling(mel, w)
+    assert nr(plain, want) > 3e-2
+    # this library
+    sub = pk.subsampling.Subsampling(w, cuda, precision="fp8")
+    seg = 128
+    got = host(sub.run(dev(mel[None]), seg))[:want.shape[0]]
+    assert int(sub.status.item()) == 0
+    assert np.max(np.abs(got - want)) <= 4e-2 and nr(got, want) <= 1e-2
+    assert np.max(np.abs(got - ref)) <= 4e-2 and nr(got, ref) <= 1e-2

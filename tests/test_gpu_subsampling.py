@@ -9,10 +9,14 @@ from tests.util import dev, host, nrmse
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("precision", ["fp16", "fp8"])
 @pytest.mark.parametrize("frames_list", [[400, 400], [203, 77, 8, 1]])
-def test_subsampling_matches_oracle(pk, cuda, frames_list):
+def test_subsampling_matches_oracle(pk, cuda, frames_list, precision):
     w = pk.synth.subsampling_weights(2)
-    sub = pk.subsampling.Subsampling(w, cuda)
+    sub = pk.subsampling.Subsampling(w, cuda, precision=precision)
+    # the E4M3 variant (the reference's path from 1024 output frames on) agrees with its oracle to the
+    # tolerance of a quantised stage: a byte that rounds the other way is a 6 % step of that activation
+    max_abs, max_nrmse = (2e-2, 2e-3) if precision == "fp16" else (4e-2, 1e-2)
     cap = max(frames_list)
     mels = [pk.synth.mel_input(30 + i, f) for i, f in enumerate(frames_list)]
     batch = np.zeros((len(mels), cap, 128), np.float32)
@@ -24,10 +28,10 @@ def test_subsampling_matches_oracle(pk, cuda, frames_list):
     torch.cuda.synchronize()
     assert int(sub.status.item()) == 0
     for i, m in enumerate(mels):
-        want = O.subsampling(m, w)
+        want = O.subsampling(m, w, fp8=precision == "fp8")
         got = out[i * seg_stride:i * seg_stride + want.shape[0]]
         assert want.shape[0] == pk.subsampling.output_frames(frames_list[i])
         # reference gate for this stage: max abs <= 2.0 and nRMSE <= 0.002
         # (src/cuda/subsampling.rs:375); ours is far inside it
-        assert np.max(np.abs(got - want)) <= 2e-2
-        assert nrmse(got, want) <= 2e-3
+        assert np.max(np.abs(got - want)) <= max_abs
+        assert nrmse(got, want) <= max_nrmse
