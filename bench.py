@@ -70,7 +70,9 @@ def parse_args():
     ap.add_argument("--encode-groups", type=int, default=1,
                     help="groups that pass through subsampling and the encoder one after the other (1 = the whole "
                          "batch in one pass; more = a group's decode runs under the next group's encode)")
-    ap.add_argument("--stream-decode-groups", type=int, default=4,
+    ap.add_argument("--stream-depth", type=int, default=4,
+                    help="sets of request buffers in the streamed measurement (batches in flight)")
+    ap.add_argument("--stream-decode-groups", type=int, default=1,
                     help="decoder clusters per batch in the streamed (throughput) measurement")
     ap.add_argument("--decode-groups", type=int, default=None,
                     help="groups decoded side by side, one 16-CTA cluster each (default: as many clusters as the "
@@ -719,13 +721,16 @@ def main():
 
     # ---- throughput mode: a stream of batches through the public API, batch i + 1 copied in and
     # encoded while batch i is decoded; host wall clock between the first and the last batch's results
-    stream_n = max(args.steps, 4) + 1
+    stream_n = max(args.steps, 4) + args.stream_depth
     marks = []
-    for toks in eng.transcribe_stream((mel_host for _ in range(stream_n)), decode_groups=args.stream_decode_groups):
+    for toks in eng.transcribe_stream((mel_host for _ in range(stream_n)), decode_groups=args.stream_decode_groups,
+                                      depth=args.stream_depth):
         marks.append(time.perf_counter())
         if any(len(a) != len(b) or (a != b).any() for a, b in zip(toks, tokens)):
             raise SystemExit("the streamed batches returned other tokens than transcribe_batch")
-    ms_stream = max_over_ranks((marks[-1] - marks[0]) * 1e3 / (len(marks) - 1))
+    # steady state: from the results of batch `depth - 1` (the pipeline is full) to the last batch's
+    first = args.stream_depth - 1
+    ms_stream = max_over_ranks((marks[-1] - marks[first]) * 1e3 / (len(marks) - 1 - first))
     clocks = sampler.stop()
 
     audio_per_step = AUDIO_SECONDS * total_utts
@@ -784,9 +789,11 @@ def main():
                          d2h_bytes_per_step=int(eng.tokens_host.numel() * 4 + eng.counts_host.numel() * 4)),
                 throughput=dict(value=AUDIO_SECONDS * total_utts / (ms_stream / 1e3), unit="x real time",
                                 ms_per_batch=ms_stream, batches=stream_n, decode_groups=args.stream_decode_groups,
+                                depth=args.stream_depth,
                                 note=("PipelineEngine.transcribe_stream: the same batch from pinned host memory over and "
-                                      "over, batch i+1 encoded beside the decoder clusters of batch i; host wall clock "
-                                      "from the first batch's tokens to the last's, max over ranks; same tokens as e2e")),
+                                      "over, `depth` batches in flight: one is encoded beside the decoder clusters of the "
+                                      "earlier ones; host wall clock per batch in steady state, max over ranks; same "
+                                      "tokens as e2e")),
                 gpu_launches=int(launches), roofline=roofline, decoder=decoder, per_rank=per_rank,
                 tensor_map_cache=dict(zip(("hits", "misses"), pk.lib.tensor_map_cache_stats())),
                 tokens_per_utterance=[int(len(t)) for t in tokens])

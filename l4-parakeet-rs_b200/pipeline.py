@@ -283,34 +283,48 @@ class PipelineEngine:
         counts = self.counts_host.numpy()
         return [self.tokens_host[u, :int(counts[u])].numpy().copy() for u in range(utterances)]
 
-    def transcribe_stream(self, batches, decode_groups=4):
+    def transcribe_stream(self, batches, decode_groups=1, depth=4):
         """Throughput mode: a generator over `batches` (each a pinned fp32 CPU tensor [U, frames, 128]
         or a pair (tensor, true frame counts)) that yields, in order, what `transcribe_batch` returns
-        for each.  Batch i + 1 is copied in and encoded while batch i is still being decoded: two sets
-        of request buffers alternate, the encoder's persistent GEMMs are capped at the SMs the
-        `decode_groups` decoder clusters of the batch before leave free (fewer clusters than in
-        `transcribe_batch`, where nothing runs beside them), and the host only waits for a batch's
-        tokens after the next batch has been queued.  Steady state per batch: the longer of the
-        (slowed) encode and the longest decode chain, instead of their sum."""
-        if not hasattr(self, "_second_slot"):
-            self._second_slot = _Slot(self)
-            self._collect_streams = [torch.cuda.Stream(device=self.device) for _ in range(2)]
-        slots = [self, self._second_slot]
+        for each.  `depth` sets of request buffers rotate: a batch is copied in and encoded while the
+        decoder clusters of up to depth - 1 earlier batches are still running, the encoder's persistent
+        GEMMs capped at the SMs those clusters leave free (`decode_groups` clusters per batch: fewer
+        than in `transcribe_batch`, where nothing runs beside them), and the host waits for a batch's
+        tokens only when its buffers are needed again or the newest batch has been queued.  Steady
+        state per batch: the larger of the (slowed) encode and the decoder-cluster time of a batch
+        divided by the clusters in flight, instead of encode + longest chain.  Measured for batches of
+        8 x 60 s: one lockstep cluster per batch and four batches in flight (the defaults) give 11.5 ms
+        per batch; four clusters per batch and two batches in flight 19.9 ms; a batch on its own 34.4 ms."""
+        depth = max(2, int(depth))
+        if not hasattr(self, "_extra_slots"):
+            self._extra_slots, self._collect_streams, self._slot_status = [], [], []
+        while len(self._extra_slots) < depth - 1:
+            self._extra_slots.append(_Slot(self))
+        while len(self._collect_streams) < depth:
+            self._collect_streams.append(torch.cuda.Stream(device=self.device))
+        slots = [self] + self._extra_slots[:depth - 1]
+        words = self._status_words()
+        while len(self._slot_status) < depth or any(t.numel() != len(words) for t in self._slot_status):
+            self._slot_status = [torch.zeros(len(words), dtype=torch.int32).pin_memory() for _ in range(depth)]
         main = torch.cuda.current_stream()
 
-        def finish(pending):
-            b, utterances, done = pending
+        def finish(entry):
+            k, utterances, done, _ = entry
+            b = slots[k]
             done.synchronize()
-            status = self.status()
+            status = self._combine_status(self._slot_status[k].tolist())
             if status != 0:
                 raise RuntimeError(f"libpk100 reported an expired bounded wait (status {status})")
             counts = b.counts_host.numpy()
             return [b.tokens_host[u, :int(counts[u])].numpy().copy() for u in range(utterances)]
 
-        pending, in_flight = None, 0
+        pending = []                              # oldest first: (slot index, utterances, event, clusters)
         for i, item in enumerate(batches):
             mel_host, lengths = item if isinstance(item, (tuple, list)) else (item, None)
-            b = slots[i % 2]              # its batch before (i - 2) was collected before batch i - 1 was queued
+            k = i % depth
+            if len(pending) == depth:             # the slot's previous batch has to be out first
+                yield finish(pending.pop(0))
+            b = slots[k]
             utterances = mel_host.shape[0]
             lengths = tuple([int(mel_host.shape[1])] * utterances if lengths is None else [int(f) for f in lengths])
             if max(lengths) > mel_host.shape[1] or mel_host.shape[1] > self.mel_frames or utterances > self.max_utterances:
@@ -318,22 +332,23 @@ class PipelineEngine:
             if lengths != b._lengths[:utterances]:
                 self.set_lengths(lengths, slot=b)
             b.mel_dev[:utterances, :mel_host.shape[1]].copy_(mel_host, non_blocking=True)
-            streams = self.run_resident(utterances, slot=b, join=False, clusters_in_flight=in_flight,
-                                        decode_groups=decode_groups)
-            collect = self._collect_streams[i % 2]
+            streams = self.run_resident(utterances, slot=b, join=False,
+                                        clusters_in_flight=sum(e[3] for e in pending), decode_groups=decode_groups)
+            collect = self._collect_streams[k]
             for st in streams:
                 collect.wait_stream(st)
             with torch.cuda.stream(collect):
                 b.counts_host.copy_(b.counts, non_blocking=True)
                 b.tokens_host.copy_(b.tokens, non_blocking=True)
+                for n, w in enumerate(words):
+                    self._slot_status[k][n:n + 1].copy_(w, non_blocking=True)
                 done = torch.cuda.Event()
                 done.record(collect)
-            in_flight = len(streams)
-            if pending is not None:
-                yield finish(pending)
-            pending = (b, utterances, done)
-        if pending is not None:
-            yield finish(pending)
+            pending.append((k, utterances, done, len(streams)))
+            if len(pending) == depth:
+                yield finish(pending.pop(0))
+        while pending:
+            yield finish(pending.pop(0))
         main.synchronize()
 
     # ---- one long utterance cut into chunks over several GPUs (see parallel.py)
@@ -406,7 +421,9 @@ class PipelineEngine:
     def _status_words(self):
         """Device int32 views of every status word: encoder, subsampling, then the decoders'."""
         off = self.ws.status - self.arena.data_ptr()
-        extra = self.dec_scratch[1:] + (self._second_slot.dec_scratch if hasattr(self, "_second_slot") else [])
+        extra = list(self.dec_scratch[1:])
+        for slot in getattr(self, "_extra_slots", []):
+            extra += slot.dec_scratch
         return [self.arena[off:off + 4].view(torch.int32), self.sub.status, self.dec.status] + [s[1] for s in extra]
 
     def _queue_status(self):
@@ -420,7 +437,9 @@ class PipelineEngine:
 
     def _queued_status(self):
         """After a synchronise: what `status()` would return, from the words `_queue_status` copied."""
-        h = self._status_host.tolist()
+        return self._combine_status(self._status_host.tolist())
+
+    def _combine_status(self, h):
         dec = 0
         for v in h[2:]:
             dec |= v & ~4                               # bit 4: a decode round had only NaN scores
@@ -428,11 +447,7 @@ class PipelineEngine:
 
     def status(self):
         """Non-zero when a bounded wait expired inside a kernel (saturation is reported separately)."""
-        dec = int(self.dec.status.item()) & ~4          # bit 4: a decode round had only NaN scores
-        extra = self.dec_scratch[1:] + (self._second_slot.dec_scratch if hasattr(self, "_second_slot") else [])
-        for scratch in extra:
-            dec |= int(scratch[1].item()) & ~4
-        return (self.enc.status(self.arena, self.ws) & ~self.HIDDEN_SATURATED) | dec | int(self.sub.status.item())
+        return self._combine_status([int(w.item()) for w in self._status_words()])
 
 
 def transcribe_long(eng, mel_host, rank=0, world_size=1, group=None, halo=None, decoder=None):

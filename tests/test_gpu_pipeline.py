@@ -103,8 +103,9 @@ def test_streamed_batches_return_what_single_requests_return(pk, cuda, engine):
         batches.append((torch.from_numpy(mels).pin_memory(), frames))
     for mel, frames in batches:
         want.append(eng.transcribe_batch(mel, frames))
-    got = list(eng.transcribe_stream(iter(batches), decode_groups=2))
-    assert len(got) == len(want) and eng.status() == 0
-    for g, w in zip(got, want):
-        assert len(g) == len(w) and all(np.array_equal(x, y) for x, y in zip(g, w))
+    for depth, groups in ((2, 2), (3, 1)):
+        got = list(eng.transcribe_stream(iter(batches), decode_groups=groups, depth=depth))
+        assert len(got) == len(want) and eng.status() == 0
+        for g, w in zip(got, want):
+            assert len(g) == len(w) and all(np.array_equal(x, y) for x, y in zip(g, w))
     assert any(len(t) > 0 for batch in got for t in batch)
